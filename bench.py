@@ -1,0 +1,569 @@
+#!/usr/bin/env python
+"""Benchmark of the tensor hot path: `python bench.py --gpus N --steps K --warmup W`.
+
+Workloads (seeded synthetic inputs with the shapes and distributions of the reference
+configurations; no dataset is used):
+  mlp    3-layer MLP forward, batch 4096, 784->1024->1024->10, relu/relu/softmax+argmax
+         (metric: samples/s) - the default
+  gemm   one fp32 GEMM M=N=K (default 16384, --size), 3xTF32 (or --precision bf16)
+  conv   conv2d 256x64x56x56 * 128x64x3x3, pad 1, + bias + relu
+  add    elementwise add of 2^28 float32 (HBM-bound)
+
+Under torchrun every rank runs the same per-GPU workload on its own shard (weak scaling, no
+data-path collective: samples / row blocks are independent); rank 0 prints ONE JSON line.
+`--impl reference` times the reference's own CPU operators (oracle/_ref) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+                for n, v in zip(names, r[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except (ValueError, IndexError):
+                continue
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------
+# seeded inputs (numpy PCG64; identical on every rank and on the CPU baseline)
+# ---------------------------------------------------------------------------------------
+
+def mlp_inputs(batch):
+    rng = np.random.default_rng(1)
+
+    def kaiming(fi, fo):
+        lim = np.sqrt(6.0 / fi)
+        return rng.uniform(-lim, lim, (fi, fo)).astype(np.float32)
+
+    w = [kaiming(784, 1024), kaiming(1024, 1024), kaiming(1024, 10)]
+    b = [np.zeros(1024, np.float32), np.zeros(1024, np.float32), np.zeros(10, np.float32)]
+    x = np.random.default_rng(2).uniform(0, 1, (batch, 784)).astype(np.float32)
+    return x, w, b
+
+
+MLP_FLOP_PER_SAMPLE = 2 * (784 * 1024 + 1024 * 1024 + 1024 * 10)
+
+
+def gemm_inputs(m, k, n, seed=5):
+    rng = np.random.default_rng(seed)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    return a, b
+
+
+def conv_inputs(batch):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((batch, 64, 56, 56), dtype=np.float32)
+    w = (rng.standard_normal((128, 64, 3, 3)) * np.sqrt(2.0 / (64 * 9))).astype(np.float32)
+    b = np.zeros(128, np.float32)
+    return x, w, b
+
+
+# ---------------------------------------------------------------------------------------
+# reference arm: the reference's own CPU operators on a bounded sample
+# ---------------------------------------------------------------------------------------
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    import oracle
+
+    cores = os.cpu_count() or 1
+    if not oracle.Reference.available():
+        kind, be = "port", None
+    else:
+        kind, be = "reference", oracle.ref()
+    p = oracle.port()
+    times = []
+    if args.workload == "mlp":
+        sample = 16  # samples per step; the reference loop is single-threaded (~0.2 GFLOP/s)
+        x, w, b = mlp_inputs(sample)
+        from oracle import IntArray
+
+        def step():
+            t0 = time.perf_counter()
+            h = x
+            for i in range(3):
+                if be is not None:
+                    xb = be.call("concat", h, be.call("ones", IntArray([h.shape[0], 1])), 1)
+                    wb = be.call("concat", w[i], b[i].reshape(1, -1), 0)
+                    h = be.call("matmul", xb, wb)
+                    if i < 2:
+                        h = be.call("multiply", h, be.call("gt", h, 0))
+                else:
+                    h = p.dense(h, w[i], b[i], 1 if i < 2 else 0)
+            probs = p.softmax_rows(h)
+            p.argmax_axis(h, 1)
+            return time.perf_counter() - t0, probs
+
+        units, unit, metric = sample, "samples/s", "mlp_forward_samples_per_s"
+        sample_desc = f"{sample} of 4096 samples per step, full layer widths, 1 thread (reference kernels are single-threaded)"
+    elif args.workload == "gemm":
+        n = args.size
+        rows = max(1, min(n, int(2.0e9 / (2.0 * n * n)) or 1))  # ~2 GFLOP per step
+        a, bm = gemm_inputs(rows, n, n)
+
+        def step():
+            t0 = time.perf_counter()
+            out = be.call("matmul", a, bm) if be is not None else p.matmul(a, bm)
+            return time.perf_counter() - t0, out
+
+        units, unit, metric = 2.0 * rows * n * n / 1e12, "TFLOP/s", "gemm_fp32_tflops"
+        sample_desc = f"{rows} rows of A against the full {n}x{n} B per step (scale x{n / rows:.0f} for the whole GEMM), 1 thread"
+    else:
+        print(json.dumps({"impl": "reference", "unavailable": f"workload {args.workload} has no reference arm"}))
+        return
+    for _ in range(max(0, min(args.warmup, 1))):
+        step()
+    for _ in range(max(1, min(args.steps, 3))):
+        times.append(step()[0])
+    t = float(np.mean(times))
+    value = units / t
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": 0, "steps": len(times),
+            "warmup": min(args.warmup, 1), "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f64-accumulate/f32", "data": "synthetic",
+            "config": {"workload": args.workload, "note": "reference CPU operators, bounded sample"},
+            "cpu_baseline": {"value": value, "unit": unit, "cores": 1, "kind": kind, "sample": sample_desc,
+                             "host_cores_available": cores},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------
+
+class Workload:
+    """One step = one pass of the hot path over one batch.  `step()` runs with inputs resident
+    in HBM; `e2e_step()` goes through host buffers (pinned) with the copies inside."""
+
+    name = ""
+    metric = ""
+    unit = ""
+    dominant = "gemm_tc"
+    bound = "tensor"
+
+    def units_per_step(self):  # in the metric's unit numerator
+        raise NotImplementedError
+
+    def algorithmic_per_step(self):  # flops (tensor) or bytes (hbm) of the dominant kernel
+        raise NotImplementedError
+
+
+def _pin(torch, a):
+    t = torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+    return t
+
+
+class MlpWorkload(Workload):
+    name, metric, unit = "mlp", "mlp_forward_samples_per_s", "samples/s"
+
+    def __init__(self, torch, T, batch):
+        self.T, self.torch, self.batch = T, torch, batch
+        x, w, b = mlp_inputs(batch)
+        self.w = [T.from_numpy(v) for v in w]
+        self.b = [T.from_numpy(v) for v in b]
+        self.x = T.from_numpy(x)
+        self.x_host = _pin(torch, x)
+        self.x_stage = T.Tensor(0, x.shape)
+        self.probs_host = torch.empty((batch, 10), dtype=torch.float32).pin_memory()
+        self.arg_host = torch.empty((batch,), dtype=torch.int64).pin_memory()
+        self.h2d = x.nbytes
+        self.d2h = batch * 10 * 4 + batch * 8
+
+    def forward(self, x):
+        T = self.T
+        h = T.dense(x, self.w[0], self.b[0], "relu")
+        h = T.dense(h, self.w[1], self.b[1], "relu")
+        return T.dense(h, self.w[2], self.b[2], "softmax", with_argmax=True)
+
+    def step(self):
+        self.out = self.forward(self.x)
+
+    def e2e_step(self):
+        from camel_b200._lib import check, lib
+        check(lib.ct_h2d(self.x_stage.ptr, self.x_host.data_ptr(), self.h2d))
+        probs, arg = self.forward(self.x_stage)
+        check(lib.ct_d2h(self.probs_host.data_ptr(), probs.ptr, self.batch * 40))
+        check(lib.ct_d2h(self.arg_host.data_ptr(), arg.ptr, self.batch * 8))
+
+    def units_per_step(self):
+        return self.batch
+
+    def algorithmic_per_step(self):
+        return 2.0 * self.batch * (784 * 1024 + 1024 * 1024)  # the two tensor-core layers
+
+    def resident_bytes(self):
+        return self.x.nbytes + sum(t.nbytes for t in self.w) + 2 * self.batch * 1024 * 4
+
+    def config(self):
+        return {"workload": "mlp_forward 784-1024-1024-10 relu,relu,softmax+argmax (BASELINE configs[1])",
+                "batch_per_gpu": self.batch, "precision": "3xtf32"}
+
+
+class GemmWorkload(Workload):
+    name, metric, unit = "gemm", "gemm_fp32_tflops", "TFLOP/s"
+
+    def __init__(self, torch, T, n, precision):
+        self.T, self.n, self.precision = T, n, precision
+        dev = torch.device("cuda")
+        g = torch.Generator(device=dev)
+        g.manual_seed(5)
+        # U(-1,1) generated on the device: 2 GiB of host RNG per rank would dominate start-up
+        self.a_t = torch.rand((n, n), generator=g, device=dev, dtype=torch.float32) * 2 - 1
+        self.b_t = torch.rand((n, n), generator=g, device=dev, dtype=torch.float32) * 2 - 1
+        self.c_t = torch.empty((n, n), device=dev, dtype=torch.float32)
+        torch.cuda.synchronize()
+        self.a = T.wrap_device(self.a_t.data_ptr(), 0, (n, n), keep=self.a_t)
+        self.b = T.wrap_device(self.b_t.data_ptr(), 0, (n, n), keep=self.b_t)
+        self.e2e_rows = min(n, 2048)
+        self.a_host = _pin(torch, self.a_t[: self.e2e_rows].cpu().numpy())
+        self.c_host = torch.empty((self.e2e_rows, n), dtype=torch.float32).pin_memory()
+        self.h2d = self.e2e_rows * n * 4
+        self.d2h = self.e2e_rows * n * 4
+
+    def step(self):
+        from camel_b200._lib import check, lib
+        n = self.n
+        check(lib.ct_matmul(0, self.a.ptr, 0, self.b.ptr, n, n, n, self.c_t.data_ptr()))
+
+    def e2e_step(self):
+        # B is the replicated operand (resident); a row block of A comes from the host and the
+        # matching block of C goes back: what a row-sharded caller does per block.
+        from camel_b200._lib import check, lib
+        n, r = self.n, self.e2e_rows
+        check(lib.ct_h2d(self.a_t.data_ptr(), self.a_host.data_ptr(), self.h2d))
+        check(lib.ct_matmul(0, self.a.ptr, 0, self.b.ptr, r, n, n, self.c_t.data_ptr()))
+        check(lib.ct_d2h(self.c_host.data_ptr(), self.c_t.data_ptr(), self.d2h))
+
+    def units_per_step(self):
+        return 2.0 * self.n ** 3 / 1e12
+
+    def e2e_units_per_step(self):
+        return 2.0 * self.e2e_rows * self.n * self.n / 1e12
+
+    def algorithmic_per_step(self):
+        return 2.0 * self.n ** 3
+
+    def resident_bytes(self):
+        return 3 * self.n * self.n * 4
+
+    def config(self):
+        return {"workload": f"gemm fp32 M=N=K={self.n} U(-1,1) (BASELINE configs[4] per-GPU problem)",
+                "precision": self.precision}
+
+
+class ConvWorkload(Workload):
+    name, metric, unit = "conv", "conv2d_fp32_tflops", "TFLOP/s"
+
+    def __init__(self, torch, T, batch):
+        self.T, self.batch = T, batch
+        x, w, b = conv_inputs(batch)
+        self.x, self.w, self.b = T.from_numpy(x), T.from_numpy(w), T.from_numpy(b)
+        self.x_host = _pin(torch, x)
+        self.out_host = torch.empty((batch, 128, 56, 56), dtype=torch.float32).pin_memory()
+        self.h2d, self.d2h = x.nbytes, batch * 128 * 56 * 56 * 4
+        self.flops = 2.0 * batch * 128 * 56 * 56 * 64 * 9
+
+    def step(self):
+        self.out = self.T.conv2d(self.x, self.w, self.b, 1, 1, "relu")
+
+    def e2e_step(self):
+        from camel_b200._lib import check, lib
+        check(lib.ct_h2d(self.x.ptr, self.x_host.data_ptr(), self.h2d))
+        out = self.T.conv2d(self.x, self.w, self.b, 1, 1, "relu")
+        check(lib.ct_d2h(self.out_host.data_ptr(), out.ptr, self.d2h))
+
+    def units_per_step(self):
+        return self.flops / 1e12
+
+    def algorithmic_per_step(self):
+        return self.flops
+
+    def resident_bytes(self):
+        return self.h2d + self.d2h
+
+    def config(self):
+        return {"workload": "conv2d 64->128 56x56 3x3 pad1 +bias +relu (BASELINE configs[2])",
+                "batch_per_gpu": self.batch, "precision": "3xtf32"}
+
+
+class AddWorkload(Workload):
+    name, metric, unit = "add", "elementwise_add_gbs", "GB/s"
+    dominant, bound = "elementwise", "hbm"
+
+    def __init__(self, torch, T, n):
+        self.T, self.n = T, n
+        rng = np.random.default_rng(6)
+        x = rng.uniform(-1, 1, n).astype(np.float32)
+        y = rng.uniform(-1, 1, n).astype(np.float32)
+        self.x, self.y = T.from_numpy(x), T.from_numpy(y)
+        self.out = T.Tensor(0, (n,))
+        self.e2e_n = min(n, 1 << 24)
+        self.x_host, self.y_host = _pin(torch, x[: self.e2e_n]), _pin(torch, y[: self.e2e_n])
+        self.o_host = torch.empty((self.e2e_n,), dtype=torch.float32).pin_memory()
+        self.h2d, self.d2h = 8 * self.e2e_n, 4 * self.e2e_n
+
+    def step(self):
+        from camel_b200._lib import check, lib
+        check(lib.ct_binary(0, 0, self.x.ptr, 0, self.y.ptr, self.n, self.out.ptr))
+
+    def e2e_step(self):
+        from camel_b200._lib import check, lib
+        check(lib.ct_binary_host(0, self.x_host.data_ptr(), self.y_host.data_ptr(), self.e2e_n, self.o_host.data_ptr()))
+
+    def units_per_step(self):
+        return 12.0 * self.n / 1e9
+
+    def e2e_units_per_step(self):
+        return 12.0 * self.e2e_n / 1e9
+
+    def algorithmic_per_step(self):
+        return 12.0 * self.n
+
+    def resident_bytes(self):
+        return 12 * self.n
+
+    def config(self):
+        return {"workload": f"elementwise add of {self.n} float32 (12 B/element)"}
+
+
+def run_gpu(args, rank, world):
+    import torch
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import camel_b200
+    from camel_b200 import _lib, tensor as T
+    from camel_b200._lib import check, lib
+
+    check(lib.ct_set_device(local))
+    check(lib.ct_set_stream(None))  # legacy default stream: ordered with torch's default stream
+    if args.precision == "bf16":
+        check(lib.ct_set_precision(_lib.PREC_BF16))
+
+    if args.workload == "mlp":
+        wl = MlpWorkload(torch, T, args.batch or 4096)
+    elif args.workload == "gemm":
+        wl = GemmWorkload(torch, T, args.size, args.precision)
+    elif args.workload == "conv":
+        wl = ConvWorkload(torch, T, args.batch or 256)
+    else:
+        wl = AddWorkload(torch, T, args.size if args.size != 16384 else 1 << 28)
+
+    flush = torch.empty(L2_BYTES * 2, dtype=torch.uint8, device="cuda") if wl.resident_bytes() < 2 * L2_BYTES else None
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        """K steps, CUDA events around each step on the launching stream, L2 flushed between
+        steps when the working set is smaller than L2; returns total device ms."""
+        evs = []
+        barrier()
+        for _ in range(steps):
+            if flush is not None:
+                flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            evs.append((e0, e1))
+        barrier()
+        return sum(a.elapsed_time(b) for a, b in evs)
+
+    for _ in range(max(args.warmup, 3)):
+        wl.step()
+    T.check_async()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    check(lib.ct_profile_enable(1))
+    launches0 = lib.ct_launch_count()
+    ms = timed(wl.step, args.steps)
+    launches = lib.ct_launch_count() - launches0
+    tot, cnt = ctypes_double(), ctypes_u64()
+    check(lib.ct_profile_read(wl.dominant.encode(), tot, cnt))
+    check(lib.ct_profile_read(None, None, None))
+    check(lib.ct_profile_enable(0))
+    clocks = sampler.stop() if rank == 0 else None
+    T.check_async()
+
+    # end to end through host buffers
+    for _ in range(2):
+        wl.e2e_step()
+    e2e_steps = max(1, min(args.steps, 10))
+    barrier()
+    t0 = time.perf_counter()
+    e2e_ms_dev = timed(wl.e2e_step, e2e_steps)
+    e2e_wall = time.perf_counter() - t0
+    T.check_async()
+
+    def reduce_max(v):
+        if dist is None:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms = reduce_max(ms)
+    e2e_ms = reduce_max(max(e2e_ms_dev, 0.0))
+    value = wl.units_per_step() * args.steps * world / (ms / 1e3)
+    e2e_units = getattr(wl, "e2e_units_per_step", wl.units_per_step)()
+    e2e_value = e2e_units * e2e_steps * world / (e2e_ms / 1e3)
+
+    if rank == 0:
+        pk = peaks()
+        dom_ms = tot.value / max(1, cnt.value)
+        launches_per_step = cnt.value / args.steps
+        alg = wl.algorithmic_per_step() / max(1.0, launches_per_step)
+        if wl.bound == "tensor":
+            if args.precision == "bf16":
+                peak, peak_note = pk["bf16_tflops"], f"{pk['source']} bf16 dense burst"
+            else:
+                peak = pk["bf16_tflops"] / 6.0
+                peak_note = (f"{pk['source']} bf16 dense burst / 2 (tf32 rate) / 3 (three MMAs per product); "
+                             f"sustained variant {pk['bf16_tflops_sustained'] / 6.0:.1f}")
+            achieved = alg / (dom_ms / 1e3) / 1e12 if dom_ms > 0 else 0.0
+            runit = "TFLOP/s"
+        else:
+            peak, peak_note = pk["hbm_gbs"], f"{pk['source']} STREAM-style copy"
+            achieved = alg / (dom_ms / 1e3) / 1e9 if dom_ms > 0 else 0.0
+            runit = "GB/s"
+        roofline = {"bound": wl.bound, "kernel": wl.dominant, "achieved": achieved, "peak": peak, "unit": runit,
+                    "frac": achieved / peak if peak else None, "traffic": None, "peak_note": peak_note,
+                    "launches_per_step": launches_per_step, "avg_launch_ms": dom_ms}
+        cpu = cpu_baseline(args) if world == 1 and not args.no_cpu_baseline else None
+        line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, f32 accumulate)"
+                if args.precision != "bf16" else "bf16 in / f32 accumulate", "data": "synthetic",
+                "config": {**wl.config(), "l2": "flushed between steps" if flush is not None else "inputs larger than L2",
+                           "parallelism": f"{world} ranks, independent shards, no data-path collective"},
+                "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
+                        "steps": e2e_steps, "wall_s": e2e_wall},
+                "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks}
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def ctypes_double():
+    import ctypes
+    return ctypes.c_double()
+
+
+def ctypes_u64():
+    import ctypes
+    return ctypes.c_uint64()
+
+
+def cpu_baseline(args):
+    """Rank 0, N=1: the reference CPU operators on a bounded sample of the same workload."""
+    import contextlib
+    import io
+
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        run_reference(args, 0)
+    try:
+        ref = json.loads(buf.getvalue().strip().splitlines()[-1])
+    except (ValueError, IndexError):
+        return None
+    return ref.get("cpu_baseline")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mlp", choices=["mlp", "gemm", "conv", "add"])
+    ap.add_argument("--size", type=int, default=16384)
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "bf16"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_gpu(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

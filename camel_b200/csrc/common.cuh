@@ -1,0 +1,112 @@
+// Shared host/device plumbing of libcamel_tensor_b200.so: per-thread error text, the current
+// device/stream, the launch counter, the device-side error words and cached workspaces.
+#pragma once
+
+#include "camel_tensor_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+namespace ct {
+
+// Device-side error words, read back by the entry points that must report them.
+enum FlagWord : int {
+    FLAG_DIV_ZERO   = 0, // a divisor was 0 (reference: "Division by zero")
+    FLAG_LOG_DOMAIN = 1, // an input of log was <= 0
+    FLAG_TIMEOUT    = 2, // a bounded in-kernel wait ran out (value = where)
+    FLAG_COUNT      = 8
+};
+
+struct DeviceState {
+    bool ready           = false;
+    int device           = -1;
+    int sm_count         = 0;
+    uint32_t *flags_dev  = nullptr; // FLAG_COUNT words
+    uint32_t *flags_host = nullptr; // pinned mirror
+    void *reduce_ws      = nullptr; // partials of the two-pass reductions
+    size_t reduce_ws_bytes = 0;
+    void *gemm_ws        = nullptr; // split operand planes of the tensor-core GEMM
+    size_t gemm_ws_bytes = 0;
+    void *stage_ws[3]    = {nullptr, nullptr, nullptr}; // device staging of the *_host forms
+    size_t stage_ws_bytes[3] = {0, 0, 0};
+};
+
+void set_error(const char *fmt, ...);
+ct_status fail(ct_status code, const char *fmt, ...);
+ct_status cuda_fail(cudaError_t e, const char *what);
+
+// Current device state (initialised on first use) and stream of the calling process.
+ct_status current(DeviceState **out);
+cudaStream_t stream();
+void count_launch(unsigned n = 1);
+
+// Grows a cached workspace (never shrinks); contents are undefined after the call.
+ct_status ensure_ws(void **ptr, size_t *cap, size_t bytes);
+
+// Clears the device error words on the stream.
+ct_status clear_flags(DeviceState *st);
+// Synchronises the stream and copies the error words to st->flags_host.
+ct_status fetch_flags(DeviceState *st);
+
+#define CT_CUDA(call)                                                                              \
+    do {                                                                                           \
+        cudaError_t e__ = (call);                                                                  \
+        if (e__ != cudaSuccess)                                                                    \
+            return ::ct::cuda_fail(e__, #call);                                                    \
+    } while (0)
+
+#define CT_TRY(call)                                                                               \
+    do {                                                                                           \
+        ct_status s__ = (call);                                                                    \
+        if (s__ != CT_OK)                                                                          \
+            return s__;                                                                            \
+    } while (0)
+
+#define CT_LAUNCH_CHECK(name)                                                                      \
+    do {                                                                                           \
+        ::ct::count_launch();                                                                      \
+        cudaError_t e__ = cudaGetLastError();                                                      \
+        if (e__ != cudaSuccess)                                                                    \
+            return ::ct::cuda_fail(e__, name);                                                     \
+    } while (0)
+
+// When profiling is on (ct_profile_enable), brackets the launches made in its scope with CUDA
+// events on the launching stream, filed under `name` (a string literal).
+class ProfScope {
+  public:
+    explicit ProfScope(const char *name);
+    ~ProfScope();
+    ProfScope(const ProfScope &)            = delete;
+    ProfScope &operator=(const ProfScope &) = delete;
+
+  private:
+    const char *name_;
+    cudaEvent_t e0_, e1_;
+};
+
+inline size_t dtype_size(int dt) { return dt == CT_F32 ? 4 : (dt == CT_I64 ? 8 : 1); }
+inline bool valid_dtype(int dt) { return dt == CT_F32 || dt == CT_I64 || dt == CT_BOOL; }
+
+// Entry points of the other translation units used across files.
+ct_status gemm_f32_tc(
+    DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
+    int64_t n, int act, float *out);
+// mode: 0 = 3xTF32 (float32 hi/lo planes), 1 = bf16 (one plane).
+ct_status gemm_planes(
+    DeviceState *st, int mode, const void *a_hi, const void *a_lo, const void *b_hi,
+    const void *b_lo, int64_t m, int64_t n, int64_t kp, const float *bias, int act, float *out,
+    int batch, int64_t out_batch_stride, int bias_per_row);
+ct_status split_rows_planes(
+    DeviceState *st, int mode, const float *in, int64_t rows, int64_t k, int64_t kp, void *hi,
+    void *lo);
+ct_status gemm_f32_skinny(
+    DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
+    int64_t n, int act, float *out, int64_t *argmax);
+ct_status matmul_generic(
+    int adt, const void *a, int bdt, const void *b, int64_t m, int64_t k, int64_t n, void *out);
+
+} // namespace ct

@@ -1,0 +1,295 @@
+// Entry points of the contractions (matmul, dense, conv2d) and maxpool2d: argument checks,
+// dispatch between the tensor-core kernel and the CUDA-core kernels, and the conv2d lowering.
+#include "common.cuh"
+#include "split.cuh"
+
+#include <cuda_bf16.h>
+
+namespace ct {
+namespace {
+
+// Problems below this many multiply-adds stay on the CUDA-core kernel: the tensor-core path
+// costs three launches and a tile of 128 rows.
+constexpr int64_t kTinyMacs = 64ll * 64 * 64;
+
+// ---- conv2d lowering ----------------------------------------------------------------------
+//
+// out[img][ko][pix] = sum_{c,r,s} w[ko][c][r][s] * x[img][c][y*stride-pad+r][x*stride-pad+s]
+// is the GEMM  W[ko][kdim] . P[img][pix][kdim]^T  with kdim = c*kh*kw in (c,r,s) order, which is
+// exactly the OIHW weight layout.  The patch matrix P is written once, already split into the
+// operand planes the tensor-core kernel reads (zero for padded taps and for kdim..kp), and the
+// kernel's output rows are output channels, so the result lands in NCHW without a transpose.
+template <int MODE>
+__global__ void __launch_bounds__(256) im2col_planes_kernel(
+    const float *__restrict__ x, int64_t c, int64_t h, int64_t w, int64_t kh, int64_t kw,
+    int64_t stride, int64_t pad, int64_t ho, int64_t wo, int64_t kdim, int64_t kp, int64_t total,
+    void *__restrict__ p_hi, void *__restrict__ p_lo) {
+    int64_t step = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+        int64_t kk  = i % kp;
+        int64_t row = i / kp; // img * ho*wo + pix
+        float v     = 0.0f;
+        if (kk < kdim) {
+            int64_t pix = row % (ho * wo), img = row / (ho * wo);
+            int64_t oy = pix / wo, ox = pix - oy * wo;
+            int64_t s = kk % kw, r = (kk / kw) % kh, ic = kk / (kw * kh);
+            int64_t iy = oy * stride - pad + r, ix = ox * stride - pad + s;
+            if (iy >= 0 && iy < h && ix >= 0 && ix < w)
+                v = __ldg(x + ((img * c + ic) * h + iy) * w + ix);
+        }
+        if (MODE == 0) {
+            float hi, lo;
+            split_tf32(v, hi, lo);
+            static_cast<float *>(p_hi)[i] = hi;
+            static_cast<float *>(p_lo)[i] = lo;
+        } else {
+            static_cast<__nv_bfloat16 *>(p_hi)[i] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+// Small problems: one thread per output, float64 accumulation in (c,r,s) order.
+__global__ void __launch_bounds__(256) conv2d_direct_kernel(
+    const float *__restrict__ x, const float *__restrict__ wt, const float *__restrict__ bias,
+    int64_t n, int64_t c, int64_t h, int64_t w, int64_t ko, int64_t kh, int64_t kw, int64_t stride,
+    int64_t pad, int64_t ho, int64_t wo, int act, float *__restrict__ out) {
+    int64_t total = n * ko * ho * wo;
+    int64_t step  = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+        int64_t ox = i % wo, oy = (i / wo) % ho, o = (i / (wo * ho)) % ko, img = i / (wo * ho * ko);
+        double acc = 0.0;
+        for (int64_t ic = 0; ic < c; ++ic)
+            for (int64_t r = 0; r < kh; ++r) {
+                int64_t iy = oy * stride - pad + r;
+                if (iy < 0 || iy >= h)
+                    continue;
+                for (int64_t s = 0; s < kw; ++s) {
+                    int64_t ix = ox * stride - pad + s;
+                    if (ix < 0 || ix >= w)
+                        continue;
+                    acc += (double)x[((img * c + ic) * h + iy) * w + ix] *
+                           (double)wt[((o * c + ic) * kh + r) * kw + s];
+                }
+            }
+        if (bias)
+            acc += (double)bias[o];
+        float v = (float)acc;
+        if (act == CT_ACT_RELU)
+            v = __fmul_rn(v, v > 0.0f ? 1.0f : 0.0f);
+        out[i] = v;
+    }
+}
+
+// maxpool, window == stride: one thread per output, strict '>' from the window's first element.
+__global__ void __launch_bounds__(256) maxpool2d_kernel(
+    const float *__restrict__ x, int64_t planes, int64_t h, int64_t w, int64_t win, int64_t ho,
+    int64_t wo, float *__restrict__ out) {
+    int64_t total = planes * ho * wo;
+    int64_t step  = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+        int64_t ox = i % wo, oy = (i / wo) % ho, p = i / (wo * ho);
+        const float *src = x + (p * h + oy * win) * w + ox * win;
+        float best       = src[0];
+        for (int64_t r = 0; r < win; ++r)
+            for (int64_t s = 0; s < win; ++s) {
+                float v = src[r * w + s];
+                if (v > best)
+                    best = v;
+            }
+        out[i] = best;
+    }
+}
+
+// 2x2 windows on even widths: each thread reads two float2 and writes one value, so a warp
+// reads 2 x 256 contiguous bytes.
+__global__ void __launch_bounds__(256) maxpool2x2_kernel(
+    const float *__restrict__ x, int64_t planes, int64_t h, int64_t w, int64_t ho, int64_t wo,
+    float *__restrict__ out) {
+    int64_t total = planes * ho * wo;
+    int64_t step  = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+        int64_t ox = i % wo, oy = (i / wo) % ho, p = i / (wo * ho);
+        const float *src = x + (p * h + oy * 2) * w + ox * 2;
+        float2 a         = __ldcs(reinterpret_cast<const float2 *>(src));
+        float2 b         = __ldcs(reinterpret_cast<const float2 *>(src + w));
+        float best       = a.x;
+        if (a.y > best)
+            best = a.y;
+        if (b.x > best)
+            best = b.x;
+        if (b.y > best)
+            best = b.y;
+        out[i] = best;
+    }
+}
+
+unsigned capped_blocks(DeviceState *st, int64_t total, int per_sm) {
+    int64_t blocks = (total + 255) / 256;
+    int64_t cap    = (int64_t)st->sm_count * per_sm;
+    if (blocks > cap)
+        blocks = cap;
+    return (unsigned)(blocks < 1 ? 1 : blocks);
+}
+
+} // namespace
+} // namespace ct
+
+using namespace ct;
+
+extern "C" {
+
+ct_status ct_matmul(
+    ct_dtype adt, const void *a, ct_dtype bdt, const void *b, int64_t m, int64_t k, int64_t n,
+    void *out) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (!valid_dtype(adt) || !valid_dtype(bdt))
+        return fail(CT_ERR_INVALID, "matmul: bad dtype");
+    if (m < 0 || k < 0 || n < 0)
+        return fail(CT_ERR_INVALID, "matmul: negative dimension");
+    if (m == 0 || n == 0)
+        return CT_OK;
+    if (!out || (k > 0 && (!a || !b)))
+        return fail(CT_ERR_INVALID, "matmul: null pointer");
+    if (adt == CT_F32 && bdt == CT_F32) {
+        const float *af = static_cast<const float *>(a), *bf = static_cast<const float *>(b);
+        float *of = static_cast<float *>(out);
+        if (n <= 32)
+            return gemm_f32_skinny(st, af, bf, nullptr, m, k, n, CT_ACT_NONE, of, nullptr);
+        if (m * n * (k > 0 ? k : 1) < kTinyMacs)
+            return matmul_generic(adt, a, bdt, b, m, k, n, out);
+        CT_TRY(clear_flags(st));
+        return gemm_f32_tc(st, af, bf, nullptr, m, k, n, CT_ACT_NONE, of);
+    }
+    return matmul_generic(adt, a, bdt, b, m, k, n, out);
+}
+
+ct_status ct_dense(
+    const float *x, const float *w, const float *bias, int64_t m, int64_t k, int64_t n,
+    ct_activation act, float *out, int64_t *argmax) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (m < 0 || k < 0 || n < 0)
+        return fail(CT_ERR_INVALID, "dense: negative dimension");
+    if (act != CT_ACT_NONE && act != CT_ACT_RELU && act != CT_ACT_SOFTMAX)
+        return fail(CT_ERR_INVALID, "dense: unknown activation");
+    if (m == 0 || n == 0)
+        return CT_OK;
+    if (!out || (k > 0 && (!x || !w)))
+        return fail(CT_ERR_INVALID, "dense: null pointer");
+    if (n <= 32)
+        return gemm_f32_skinny(st, x, w, bias, m, k, n, act, out, argmax);
+    int gemm_act = act == CT_ACT_RELU ? CT_ACT_RELU : CT_ACT_NONE;
+    CT_TRY(clear_flags(st));
+    CT_TRY(gemm_f32_tc(st, x, w, bias, m, k, n, gemm_act, out));
+    if (act == CT_ACT_SOFTMAX) {
+        // wide classifier: logits are complete rows in `out`; finish in place
+        if (argmax)
+            CT_TRY(ct_argmax_axis(CT_F32, out, m, n, 1, argmax));
+        CT_TRY(ct_softmax_rows(out, m, n, out));
+    }
+    return CT_OK;
+}
+
+ct_status ct_matmul_host(
+    const float *a, const float *b, int64_t m, int64_t k, int64_t n, float *out) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (m < 0 || k < 0 || n < 0)
+        return fail(CT_ERR_INVALID, "matmul: negative dimension");
+    if (m == 0 || n == 0)
+        return CT_OK;
+    size_t ab = (size_t)m * k * 4, bb = (size_t)k * n * 4, ob = (size_t)m * n * 4;
+    CT_TRY(ensure_ws(&st->stage_ws[0], &st->stage_ws_bytes[0], ab ? ab : 4));
+    CT_TRY(ensure_ws(&st->stage_ws[1], &st->stage_ws_bytes[1], bb ? bb : 4));
+    CT_TRY(ensure_ws(&st->stage_ws[2], &st->stage_ws_bytes[2], ob));
+    if (ab)
+        CT_CUDA(cudaMemcpyAsync(st->stage_ws[0], a, ab, cudaMemcpyHostToDevice, stream()));
+    if (bb)
+        CT_CUDA(cudaMemcpyAsync(st->stage_ws[1], b, bb, cudaMemcpyHostToDevice, stream()));
+    CT_TRY(ct_matmul(CT_F32, st->stage_ws[0], CT_F32, st->stage_ws[1], m, k, n, st->stage_ws[2]));
+    CT_CUDA(cudaMemcpyAsync(out, st->stage_ws[2], ob, cudaMemcpyDeviceToHost, stream()));
+    CT_TRY(fetch_flags(st));
+    if (st->flags_host[FLAG_TIMEOUT])
+        return fail(CT_ERR_TIMEOUT, "matmul: a bounded wait inside the GEMM kernel ran out (block %u)",
+                    st->flags_host[FLAG_TIMEOUT] - 1);
+    return CT_OK;
+}
+
+ct_status ct_conv2d(
+    const float *x, const float *w, const float *bias, int64_t n, int64_t c, int64_t h,
+    int64_t wd, int64_t ko, int64_t kh, int64_t kw, int64_t stride, int64_t pad,
+    ct_activation act, float *out) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (n < 0 || c < 0 || h < 0 || wd < 0 || ko < 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0)
+        return fail(CT_ERR_INVALID, "conv2d: bad dimension");
+    if (act != CT_ACT_NONE && act != CT_ACT_RELU)
+        return fail(CT_ERR_INVALID, "conv2d: activation must be none or relu");
+    if (h + 2 * pad < kh || wd + 2 * pad < kw)
+        return fail(CT_ERR_INVALID, "conv2d: kernel larger than padded input");
+    int64_t ho = (h + 2 * pad - kh) / stride + 1, wo = (wd + 2 * pad - kw) / stride + 1;
+    int64_t total_out = n * ko * ho * wo;
+    if (total_out == 0)
+        return CT_OK;
+    if (!x || !w || !out)
+        return fail(CT_ERR_INVALID, "conv2d: null pointer");
+    int64_t kdim = c * kh * kw;
+    int64_t pix  = ho * wo;
+    if (kdim * ko * pix * n < kTinyMacs * 8 || ko < 16 || pix < 64 || n > 0x7fffffff) {
+        conv2d_direct_kernel<<<capped_blocks(st, total_out, 16), 256, 0, stream()>>>(
+            x, w, bias, n, c, h, wd, ko, kh, kw, stride, pad, ho, wo, act, out);
+        CT_LAUNCH_CHECK("conv2d_direct");
+        return CT_OK;
+    }
+    const int mode   = ct_get_precision() == CT_PREC_BF16 ? 1 : 0;
+    const int elem   = mode == 0 ? 4 : 2;
+    const int planes = mode == 0 ? 2 : 1;
+    const int kblock = 128 / elem;
+    int64_t kp       = (kdim + kblock - 1) / kblock * kblock;
+    auto align_up    = [](size_t v) { return (v + 1023) & ~(size_t)1023; };
+    size_t w_plane   = align_up((size_t)ko * kp * elem);
+    size_t p_plane   = align_up((size_t)n * pix * kp * elem);
+    CT_TRY(ensure_ws(&st->gemm_ws, &st->gemm_ws_bytes, planes * (w_plane + p_plane)));
+    uint8_t *ws = static_cast<uint8_t *>(st->gemm_ws);
+    void *w_hi = ws, *w_lo = ws + w_plane;
+    void *p_hi = ws + planes * w_plane, *p_lo = ws + planes * w_plane + p_plane;
+    CT_TRY(clear_flags(st));
+    CT_TRY(split_rows_planes(st, mode, w, ko, kdim, kp, w_hi, w_lo));
+    int64_t total = n * pix * kp;
+    {
+        ProfScope prof("im2col");
+        if (mode == 0)
+        im2col_planes_kernel<0><<<capped_blocks(st, total, 32), 256, 0, stream()>>>(
+            x, c, h, wd, kh, kw, stride, pad, ho, wo, kdim, kp, total, p_hi, p_lo);
+    else
+        im2col_planes_kernel<1><<<capped_blocks(st, total, 32), 256, 0, stream()>>>(
+            x, c, h, wd, kh, kw, stride, pad, ho, wo, kdim, kp, total, p_hi, p_lo);
+    }
+    CT_LAUNCH_CHECK("im2col_planes");
+    return gemm_planes(
+        st, mode, w_hi, w_lo, p_hi, p_lo, ko, pix, kp, bias, act, out, (int)n, ko * pix,
+        bias ? 1 : 0);
+}
+
+ct_status ct_maxpool2d(
+    const float *x, int64_t n, int64_t c, int64_t h, int64_t w, int64_t window, float *out) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (n < 0 || c < 0 || h < 0 || w < 0 || window <= 0)
+        return fail(CT_ERR_INVALID, "maxpool2d: bad dimension");
+    int64_t ho = h / window, wo = w / window;
+    int64_t total = n * c * ho * wo;
+    if (total == 0)
+        return CT_OK;
+    if (!x || !out)
+        return fail(CT_ERR_INVALID, "maxpool2d: null pointer");
+    if (window == 2 && (w & 1) == 0 && (reinterpret_cast<uintptr_t>(x) & 7u) == 0)
+        maxpool2x2_kernel<<<capped_blocks(st, total, 32), 256, 0, stream()>>>(x, n * c, h, w, ho, wo, out);
+    else
+        maxpool2d_kernel<<<capped_blocks(st, total, 32), 256, 0, stream()>>>(x, n * c, h, w, window, ho, wo, out);
+    CT_LAUNCH_CHECK("maxpool2d");
+    return CT_OK;
+}
+
+} // extern "C"

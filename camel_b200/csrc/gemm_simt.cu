@@ -1,0 +1,170 @@
+// CUDA-core contractions for the shapes and dtypes the tensor-core kernel does not take:
+//  - matmul_generic: any dtype pair, float64 accumulation per output element, exactly the
+//    reference loop (modules/tensor/operators.cpp:757-766); used for int64/bool operands and
+//    for tiny problems.
+//  - gemm_f32_skinny: float32 x float32 with n <= 32 output columns (the classifier layer of
+//    an MLP): one warp per output row, float64 accumulation, with bias / relu / row-softmax /
+//    argmax fused, so the logits never round-trip through HBM.
+#include "common.cuh"
+
+#include <cmath>
+
+namespace ct {
+namespace {
+
+__device__ __forceinline__ double ld_as_double(int dt, const void *p, int64_t i) {
+    switch (dt) {
+    case CT_F32:
+        return (double)static_cast<const float *>(p)[i];
+    case CT_I64:
+        return (double)static_cast<const int64_t *>(p)[i];
+    default:
+        return static_cast<const uint8_t *>(p)[i] != 0 ? 1.0 : 0.0;
+    }
+}
+
+__device__ __forceinline__ void st_from_double(int dt, void *p, int64_t i, double v) {
+    switch (dt) {
+    case CT_F32:
+        static_cast<float *>(p)[i] = (float)v;
+        break;
+    case CT_I64:
+        static_cast<int64_t *>(p)[i] = (int64_t)v;
+        break;
+    default:
+        static_cast<uint8_t *>(p)[i] = v != 0.0 ? 1 : 0;
+        break;
+    }
+}
+
+// 16x16 outputs per block, operands staged through shared memory as float64.
+__global__ void __launch_bounds__(256) matmul_generic_kernel(
+    int adt, const void *a, int bdt, const void *b, int64_t m, int64_t k, int64_t n, int odt,
+    void *out) {
+    __shared__ double sa[16][17];
+    __shared__ double sb[16][17];
+    int tx      = threadIdx.x & 15;
+    int ty      = threadIdx.x >> 4;
+    int64_t row = (int64_t)blockIdx.y * 16 + ty;
+    int64_t col = (int64_t)blockIdx.x * 16 + tx;
+    double acc  = 0.0;
+    for (int64_t k0 = 0; k0 < k; k0 += 16) {
+        int64_t ka = k0 + tx, kb = k0 + ty;
+        sa[ty][tx] = (row < m && ka < k) ? ld_as_double(adt, a, row * k + ka) : 0.0;
+        sb[ty][tx] = (kb < k && col < n) ? ld_as_double(bdt, b, kb * n + col) : 0.0;
+        __syncthreads();
+        int lim = (int)((k - k0) < 16 ? (k - k0) : 16);
+        for (int kk = 0; kk < lim; ++kk)
+            acc += sa[ty][kk] * sb[kk][tx]; // k ascending, like the reference
+        __syncthreads();
+    }
+    if (row < m && col < n)
+        st_from_double(odt, out, row * n + col, acc);
+}
+
+// One warp per output row; lanes split k.  N_MAX bounds the register accumulators.
+template <int N_MAX>
+__global__ void __launch_bounds__(256) gemm_skinny_kernel(
+    const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+    int64_t m, int64_t k, int n, int act, float *__restrict__ out, int64_t *__restrict__ argmax) {
+    int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= m)
+        return;
+    int lane        = threadIdx.x & 31;
+    const float *xr = x + row * k;
+    double acc[N_MAX];
+#pragma unroll
+    for (int j = 0; j < N_MAX; ++j)
+        acc[j] = 0.0;
+    for (int64_t kk = lane; kk < k; kk += 32) {
+        double xv       = (double)xr[kk];
+        const float *wr = w + kk * n;
+#pragma unroll
+        for (int j = 0; j < N_MAX; ++j)
+            if (j < n)
+                acc[j] += xv * (double)__ldg(wr + j);
+    }
+#pragma unroll
+    for (int j = 0; j < N_MAX; ++j) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    }
+    // Every lane now holds all n sums; lane j finishes column j.
+    float logit = 0.0f;
+#pragma unroll
+    for (int j = 0; j < N_MAX; ++j) {
+        if (j == lane && j < n) {
+            double v = acc[j];
+            if (bias)
+                v += (double)bias[j]; // the bias is the last term of the float64 sum
+            logit = (float)v;
+        }
+    }
+    bool live = lane < n;
+    if (act == CT_ACT_RELU) {
+        logit = __fmul_rn(logit, logit > 0.0f ? 1.0f : 0.0f);
+    }
+    if (act != CT_ACT_SOFTMAX) {
+        if (live)
+            out[row * n + lane] = logit;
+        return;
+    }
+    // Row softmax and argmax across the first n lanes, with the reference's scan semantics:
+    // element 0 seeds, a later element wins only on strict '>'.
+    float best   = __shfl_sync(0xffffffffu, logit, 0);
+    int best_idx = 0;
+    for (int j = 1; j < n; ++j) {
+        float v = __shfl_sync(0xffffffffu, logit, j);
+        if (v > best) {
+            best     = v;
+            best_idx = j;
+        }
+    }
+    float e  = live ? (float)exp((double)__fsub_rn(logit, best)) : 0.0f;
+    double s = 0.0;
+    for (int j = 0; j < n; ++j)
+        s += (double)__shfl_sync(0xffffffffu, e, j);
+    float d = (float)s;
+    if (live)
+        out[row * n + lane] = __fdiv_rn(e, d);
+    if (argmax && lane == 0)
+        argmax[row] = best_idx;
+}
+
+} // namespace
+
+ct_status matmul_generic(
+    int adt, const void *a, int bdt, const void *b, int64_t m, int64_t k, int64_t n, void *out) {
+    if (m == 0 || n == 0)
+        return CT_OK;
+    int odt = ct_result_dtype(CT_ADD, (ct_dtype)adt, (ct_dtype)bdt);
+    if ((m + 15) / 16 > 65535)
+        return fail(CT_ERR_TOO_LARGE, "matmul: too many rows for the generic kernel");
+    dim3 grid((unsigned)((n + 15) / 16), (unsigned)((m + 15) / 16));
+    matmul_generic_kernel<<<grid, 256, 0, stream()>>>(adt, a, bdt, b, m, k, n, odt, out);
+    CT_LAUNCH_CHECK("matmul_generic");
+    return CT_OK;
+}
+
+ct_status gemm_f32_skinny(
+    DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
+    int64_t n, int act, float *out, int64_t *argmax) {
+    (void)st;
+    if (m == 0 || n == 0)
+        return CT_OK;
+    if (n > 32)
+        return fail(CT_ERR_INVALID, "skinny GEMM takes at most 32 output columns");
+    unsigned blocks = (unsigned)((m + 7) / 8);
+    ProfScope prof("gemm_skinny");
+    if (n <= 8)
+        gemm_skinny_kernel<8><<<blocks, 256, 0, stream()>>>(a, b, bias, m, k, (int)n, act, out, argmax);
+    else if (n <= 16)
+        gemm_skinny_kernel<16><<<blocks, 256, 0, stream()>>>(a, b, bias, m, k, (int)n, act, out, argmax);
+    else
+        gemm_skinny_kernel<32><<<blocks, 256, 0, stream()>>>(a, b, bias, m, k, (int)n, act, out, argmax);
+    CT_LAUNCH_CHECK("gemm_skinny");
+    return CT_OK;
+}
+
+} // namespace ct

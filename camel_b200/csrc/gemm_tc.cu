@@ -1,0 +1,577 @@
+// Tensor-core GEMM for sm_100a: C[m,n] = act(A[m,k] . B[k,n] + bias), float32 in and out.
+//
+// Precision modes
+//   3xTF32 (default): every operand value v is split as v = hi + lo with hi = tf32(v) and
+//   lo = tf32(v - hi); the kernel issues hi*hi + hi*lo + lo*hi on the tf32 tensor pipe
+//   (the dropped lo*lo term is ~2^-22 relative).  The tensor core adds into float32
+//   accumulators in tensor memory; to keep the rounding error of a long k loop at float32
+//   level the accumulator is drained every `chunk` k-blocks into registers and summed there
+//   with round-to-nearest adds, while the next chunk accumulates into the second TMEM buffer.
+//   BF16: operands rounded to bf16 once, one MMA per k-step, same pipeline.
+//
+// Data layout in HBM
+//   A pre-pass writes operand "planes": A -> [m][kp] (hi and lo), B -> transposed [n][kp]
+//   (hi and lo), kp = k rounded up to the k-block, zero padded.  Both operands are then
+//   K-major, so one TMA box of 128-byte rows with the 128-byte swizzle is exactly the
+//   canonical shared-memory layout tcgen05.mma reads.  The pre-pass moves 12 bytes per operand
+//   element once; the GEMM then reads planes only.
+//
+// Kernel structure (one CTA per 128 x BN output tile, one CTA per SM)
+//   warp 0   : TMA producer - fills a ring of STAGES stages (A hi/lo + B hi/lo per k-block)
+//   warp 1   : allocates TMEM, one elected lane issues tcgen05.mma and commits barriers
+//   warps 2+ : epilogue - drain TMEM chunks into registers, then bias/activation and store
+// Every barrier wait is bounded; on a timeout the kernel raises an error word, unwinds and
+// frees its TMEM, and the host reports CT_ERR_TIMEOUT.
+#include "common.cuh"
+#include "tc_ptx.cuh"
+#include "split.cuh"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstdlib>
+#include <mutex>
+
+namespace ct {
+namespace {
+
+using namespace ptx;
+
+constexpr int BM       = 128;
+constexpr int ROW_B    = 128; // bytes of one operand row per k-block (= swizzle span)
+constexpr int MODE_3X  = 0;
+constexpr int MODE_BF  = 1;
+
+template <int BN, int MODE> struct Cfg {
+    static constexpr int kElem       = MODE == MODE_3X ? 4 : 2;
+    static constexpr int kBlockK     = ROW_B / kElem; // elements of k per k-block
+    static constexpr int kPlanes     = MODE == MODE_3X ? 2 : 1;
+    static constexpr int kABytes     = BM * ROW_B;
+    static constexpr int kBBytes     = BN * ROW_B;
+    static constexpr int kStageBytes = kPlanes * (kABytes + kBBytes);
+    static constexpr int kStages     = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+    static constexpr int kEpiWarps   = BN / 32; // 128 accumulator columns per thread
+    static constexpr int kThreads    = 64 + 32 * kEpiWarps;
+    static constexpr int kTmemCols   = 2 * BN;
+    static constexpr int kSmemBytes  = kStages * kStageBytes + 1024;
+    static constexpr uint32_t kIdesc = make_idesc(MODE == MODE_3X ? 2u : 1u, BM, BN);
+};
+
+struct GemmParams {
+    int64_t m, n;
+    int num_k_blocks;
+    int chunk_blocks;
+    int tiles_m, tiles_n;
+    const float *bias;
+    int act;
+    float *out;
+    int64_t ldc;
+    int batch;                // B planes and the output carry a leading batch dimension
+    int64_t out_batch_stride; // elements between consecutive outputs of the batch
+    int bias_per_row;         // bias indexed by output row (conv: one per output channel)
+    uint32_t *flags;
+};
+
+// ---- operand pre-pass ---------------------------------------------------------------------
+
+// in [rows][k] row-major  ->  hi/lo (or bf16) planes [rows][kp]
+template <int MODE>
+__global__ void __launch_bounds__(256) split_rows_kernel(
+    const float *__restrict__ in, int64_t rows, int64_t k, int64_t kp, void *__restrict__ p_hi,
+    void *__restrict__ p_lo) {
+    int64_t total  = rows * kp;
+    int64_t stride = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += stride) {
+        int64_t r = i / kp, c = i - r * kp;
+        float v   = c < k ? in[r * k + c] : 0.0f;
+        if (MODE == MODE_3X) {
+            float hi, lo;
+            split_tf32(v, hi, lo);
+            static_cast<float *>(p_hi)[i] = hi;
+            static_cast<float *>(p_lo)[i] = lo;
+        } else {
+            static_cast<__nv_bfloat16 *>(p_hi)[i] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+// in [k][n] row-major  ->  transposed planes [n][kp]
+template <int MODE>
+__global__ void __launch_bounds__(256) split_transpose_kernel(
+    const float *__restrict__ in, int64_t k, int64_t n, int64_t kp, void *__restrict__ p_hi,
+    void *__restrict__ p_lo) {
+    __shared__ float tile[32][33];
+    int tx     = threadIdx.x & 31;
+    int ty     = threadIdx.x >> 5;
+    int64_t n0 = (int64_t)blockIdx.x * 32;
+    int64_t k0 = (int64_t)blockIdx.y * 32;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        int64_t kk = k0 + ty + j * 8, nn = n0 + tx;
+        tile[ty + j * 8][tx] = (kk < k && nn < n) ? in[kk * n + nn] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        int64_t nn = n0 + ty + j * 8, kk = k0 + tx;
+        if (nn < n && kk < kp) {
+            float v     = tile[tx][ty + j * 8];
+            int64_t at  = nn * kp + kk;
+            if (MODE == MODE_3X) {
+                float hi, lo;
+                split_tf32(v, hi, lo);
+                static_cast<float *>(p_hi)[at] = hi;
+                static_cast<float *>(p_lo)[at] = lo;
+            } else {
+                static_cast<__nv_bfloat16 *>(p_hi)[at] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+// ---- main kernel ------------------------------------------------------------------------
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
+    const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+    const GemmParams p) {
+    using C = Cfg<BN, MODE>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full[C::kStages];
+    __shared__ uint64_t bar_empty[C::kStages];
+    __shared__ uint64_t bar_tmem_full[2];
+    __shared__ uint64_t bar_tmem_empty[2];
+    __shared__ uint64_t bar_done;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag_s;
+    volatile int *abort_flag = &abort_flag_s;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // If an earlier CTA of this launch already timed out, do not start: the launch has failed
+    // and the remaining CTAs should drain at once instead of each waiting out its own budget.
+    if (threadIdx.x == 0)
+        abort_flag_s = *reinterpret_cast<volatile uint32_t *>(p.flags + FLAG_TIMEOUT) != 0 ? 1 : 0;
+    __syncthreads();
+    if (abort_flag_s)
+        return;
+
+    // tile coordinates: groups of 16 row-tiles sweep the column tiles, so that the CTAs
+    // running at the same time share operand tiles in L2
+    int tm, tn, tz;
+    {
+        int per_batch  = p.tiles_m * p.tiles_n;
+        tz             = blockIdx.x / per_batch;
+        int bid        = blockIdx.x - tz * per_batch;
+        int group_size = 16 * p.tiles_n;
+        int g          = bid / group_size;
+        int first_m    = g * 16;
+        int gm         = p.tiles_m - first_m < 16 ? p.tiles_m - first_m : 16;
+        int in_group   = bid - g * group_size;
+        tm             = first_m + in_group % gm;
+        tn             = in_group / gm;
+    }
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    auto stage_addr          = [&](int s) { return smem_base + (uint32_t)s * C::kStageBytes; };
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bar_tmem_full[b]), 1);
+            mbar_init(smem_u32(&bar_tmem_empty[b]), C::kEpiWarps);
+        }
+        mbar_init(smem_u32(&bar_done), 1);
+        mbar_fence_init();
+        prefetch_tensormap(&map_a_hi);
+        prefetch_tensormap(&map_b_hi);
+        if (MODE == MODE_3X) {
+            prefetch_tensormap(&map_a_lo);
+            prefetch_tensormap(&map_b_lo);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int nkb        = p.num_k_blocks;
+    const int chunk      = p.chunk_blocks;
+    const int num_chunks = (nkb + chunk - 1) / chunk;
+
+    if (warp == 0) {
+        // ===== TMA producer =====
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < nkb; ++kb) {
+                int s       = kb % C::kStages;
+                uint32_t ph = (uint32_t)(kb / C::kStages) & 1u;
+                if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_flag))
+                    break;
+                uint32_t full = smem_u32(&bar_full[s]);
+                uint32_t dst  = stage_addr(s);
+                mbar_expect_tx(full, C::kStageBytes);
+                int32_t kc = kb * C::kBlockK;
+                tma_load_2d(dst, &map_a_hi, full, kc, tm * BM);
+                dst += C::kABytes;
+                if (MODE == MODE_3X) {
+                    tma_load_2d(dst, &map_a_lo, full, kc, tm * BM);
+                    dst += C::kABytes;
+                }
+                tma_load_3d(dst, &map_b_hi, full, kc, tn * BN, tz);
+                dst += C::kBBytes;
+                if (MODE == MODE_3X)
+                    tma_load_3d(dst, &map_b_lo, full, kc, tn * BN, tz);
+                issued = kb + 1;
+            }
+            if (*abort_flag) {
+                // unwind: let the copies still in flight land before the CTA goes away
+                int first = issued - C::kStages < 0 ? 0 : issued - C::kStages;
+                for (int kb = first; kb < issued; ++kb) {
+                    uint32_t bar = smem_u32(&bar_full[kb % C::kStages]);
+                    uint32_t ph  = (uint32_t)(kb / C::kStages) & 1u;
+                    uint64_t t0  = globaltimer_ns();
+                    while (!mbar_try_wait(bar, ph) && globaltimer_ns() - t0 < kWaitBudgetNs) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        if (lane == 0) {
+            int kb = 0;
+            bool ok = true;
+            for (int c = 0; c < num_chunks && ok; ++c) {
+                int buf = c & 1;
+                if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), (((uint32_t)c >> 1) & 1u) ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
+                int kb_end      = kb + chunk < nkb ? kb + chunk : nkb;
+                bool first      = true;
+                for (; kb < kb_end; ++kb) {
+                    int s       = kb % C::kStages;
+                    uint32_t ph = (uint32_t)(kb / C::kStages) & 1u;
+                    if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    uint32_t a_hi = stage_addr(s);
+                    uint32_t a_lo = a_hi + C::kABytes;
+                    uint32_t b_hi = a_hi + C::kPlanes * C::kABytes;
+                    uint32_t b_lo = b_hi + C::kBBytes;
+                    uint64_t da_hi = smem_desc_k_sw128(a_hi), db_hi = smem_desc_k_sw128(b_hi);
+                    uint64_t da_lo = smem_desc_k_sw128(a_lo), db_lo = smem_desc_k_sw128(b_lo);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        uint64_t adv = (uint64_t)(kk * 32 >> 4);
+                        if (MODE == MODE_3X) {
+                            // small terms first, then the leading term
+                            mma_tf32(d_tmem, da_lo + adv, db_hi + adv, C::kIdesc, first ? 0u : 1u);
+                            mma_tf32(d_tmem, da_hi + adv, db_lo + adv, C::kIdesc, 1u);
+                            mma_tf32(d_tmem, da_hi + adv, db_hi + adv, C::kIdesc, 1u);
+                        } else {
+                            mma_f16(d_tmem, da_hi + adv, db_hi + adv, C::kIdesc, first ? 0u : 1u);
+                        }
+                        first = false;
+                    }
+                    tc_commit(smem_u32(&bar_empty[s])); // stage reusable once these MMAs retire
+                }
+                if (ok)
+                    tc_commit(smem_u32(&bar_tmem_full[buf]));
+            }
+            if (!ok || *abort_flag) {
+                // unwind: wait until every MMA issued so far has retired
+                tc_commit(smem_u32(&bar_done));
+                uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(smem_u32(&bar_done), 0) && globaltimer_ns() - t0 < kWaitBudgetNs) {
+                }
+            }
+        }
+    } else {
+        // ===== epilogue =====
+        const int ew      = warp - 2;
+        const int quarter = warp & 3;      // TMEM lanes this warp may read: 32*quarter ..
+        const int half    = ew >> 2;       // which 128-column half of the tile (BN = 256)
+        float acc[128];
+#pragma unroll
+        for (int j = 0; j < 128; ++j)
+            acc[j] = 0.0f;
+        bool ok = true;
+        for (int c = 0; c < num_chunks; ++c) {
+            int buf  = c & 1;
+            bool got = mbar_wait(smem_u32(&bar_tmem_full[buf]), ((uint32_t)c >> 1) & 1u, abort_flag);
+            ok       = __all_sync(0xffffffffu, got);
+            if (!ok)
+                break;
+            tc_fence_after_sync();
+            uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + g * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    acc[g * 32 + j] = __fadd_rn(acc[g * 32 + j], __uint_as_float(r[j]));
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+        }
+        if (ok) {
+            int64_t row  = (int64_t)tm * BM + quarter * 32 + lane;
+            int64_t col0 = (int64_t)tn * BN + half * 128;
+            if (row < p.m) {
+                float *dst      = p.out + (int64_t)tz * p.out_batch_stride + row * p.ldc;
+                const float rb  = (p.bias && p.bias_per_row) ? p.bias[row] : 0.0f;
+                const bool vec4 = (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
+#pragma unroll
+                for (int j = 0; j < 128; j += 4) {
+                    int64_t col = col0 + j;
+                    float v[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float x = acc[j + q];
+                        if (p.bias_per_row)
+                            x = __fadd_rn(x, rb);
+                        else if (p.bias && col + q < p.n)
+                            x = __fadd_rn(x, p.bias[col + q]);
+                        if (p.act == CT_ACT_RELU)
+                            x = __fmul_rn(x, x > 0.0f ? 1.0f : 0.0f);
+                        v[q] = x;
+                    }
+                    if (vec4 && col + 3 < p.n) {
+                        *reinterpret_cast<float4 *>(dst + col) = make_float4(v[0], v[1], v[2], v[3]);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (col + q < p.n)
+                                dst[col + q] = v[q];
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag)
+        atomicExch(p.flags + FLAG_TIMEOUT, 1u + (uint32_t)blockIdx.x);
+}
+
+} // namespace
+
+// ---- host side --------------------------------------------------------------------------
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(
+    CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is fetched through the runtime, so the library carries no link-time
+// dependency on libcuda.
+ct_status encode_fn(EncodeTiledFn *out) {
+    static EncodeTiledFn fn = nullptr;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CT_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres));
+        if (qres != cudaDriverEntryPointSuccess || !sym)
+            return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    *out = fn;
+    return CT_OK;
+}
+
+// Tensor map over a plane [rows][kp] (kp contiguous); box = one k-block x box_rows rows,
+// 128-byte swizzle, out-of-range rows read as zero.
+ct_status make_plane_map(
+    CUtensorMap *map, const void *base, int elem_bytes, int64_t rows, int64_t kp, int box_rows,
+    int batch /* 0: rank-2 map; >= 1: rank-3 map [batch][rows][kp] */) {
+    EncodeTiledFn fn;
+    CT_TRY(encode_fn(&fn));
+    cuuint64_t dims[3]    = {(cuuint64_t)kp, (cuuint64_t)rows, (cuuint64_t)(batch > 0 ? batch : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)kp * (cuuint64_t)elem_bytes,
+                             (cuuint64_t)kp * (cuuint64_t)elem_bytes * (cuuint64_t)rows};
+    cuuint32_t box[3]     = {(cuuint32_t)(ROW_B / elem_bytes), (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3]    = {1, 1, 1};
+    CUtensorMapDataType dt =
+        elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    CUresult r = fn(
+        map, dt, batch > 0 ? 3 : 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return CT_OK;
+}
+
+int chunk_blocks_setting() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("CAMEL_TENSOR_KCHUNK");
+        int x         = e ? atoi(e) : 0;
+        v             = x > 0 ? x : 8; // 8 k-blocks = 256 float32 values of k per drain
+    }
+    return v;
+}
+
+template <int BN, int MODE>
+ct_status launch_gemm(
+    DeviceState *st, const void *a_hi, const void *a_lo, const void *b_hi, const void *b_lo,
+    int64_t m, int64_t n, int64_t kp, const float *bias, int act, float *out, int batch,
+    int64_t out_batch_stride, int bias_per_row) {
+    using C = Cfg<BN, MODE>;
+    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    CT_TRY(make_plane_map(&ma_hi, a_hi, C::kElem, m, kp, BM, 0));
+    CT_TRY(make_plane_map(&mb_hi, b_hi, C::kElem, n, kp, BN, batch));
+    if (MODE == MODE_3X) {
+        CT_TRY(make_plane_map(&ma_lo, a_lo, C::kElem, m, kp, BM, 0));
+        CT_TRY(make_plane_map(&mb_lo, b_lo, C::kElem, n, kp, BN, batch));
+    } else {
+        ma_lo = ma_hi;
+        mb_lo = mb_hi;
+    }
+    GemmParams p;
+    p.m            = m;
+    p.n            = n;
+    p.num_k_blocks = (int)(kp / C::kBlockK);
+    p.chunk_blocks = chunk_blocks_setting();
+    p.tiles_m      = (int)((m + BM - 1) / BM);
+    p.tiles_n      = (int)((n + BN - 1) / BN);
+    p.bias         = bias;
+    p.act          = act;
+    p.out          = out;
+    p.ldc          = n;
+    p.batch        = batch;
+    p.out_batch_stride = out_batch_stride;
+    p.bias_per_row = bias_per_row;
+    p.flags        = st->flags_dev;
+    int64_t tiles  = (int64_t)p.tiles_m * p.tiles_n * batch;
+    if (tiles > 0x7fffffffll)
+        return fail(CT_ERR_TOO_LARGE, "gemm: too many tiles");
+    static bool attr_set = false;
+    if (!attr_set) {
+        CT_CUDA(cudaFuncSetAttribute(
+            gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        attr_set = true;
+    }
+    ProfScope prof("gemm_tc");
+    gemm_tc_kernel<BN, MODE><<<(unsigned)tiles, C::kThreads, C::kSmemBytes, stream()>>>(
+        ma_hi, ma_lo, mb_hi, mb_lo, p);
+    CT_LAUNCH_CHECK("gemm_tc");
+    return CT_OK;
+}
+
+} // namespace
+
+// Contraction over prepared operand planes: out[z][m][n] = act(A[m][kp] . B[z][n][kp]^T + bias).
+ct_status gemm_planes(
+    DeviceState *st, int mode, const void *a_hi, const void *a_lo, const void *b_hi,
+    const void *b_lo, int64_t m, int64_t n, int64_t kp, const float *bias, int act, float *out,
+    int batch, int64_t out_batch_stride, int bias_per_row) {
+    // 128 x 256 tiles when they fill the machine, 128 x 128 otherwise
+    int64_t tiles256 = ((m + BM - 1) / BM) * ((n + 255) / 256) * batch;
+    bool wide        = n > 128 && tiles256 >= st->sm_count / 2;
+    if (getenv("CAMEL_TENSOR_BN"))
+        wide = atoi(getenv("CAMEL_TENSOR_BN")) == 256;
+    if (mode == MODE_3X) {
+        if (wide)
+            return launch_gemm<256, MODE_3X>(
+                st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row);
+        return launch_gemm<128, MODE_3X>(
+            st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row);
+    }
+    if (wide)
+        return launch_gemm<256, MODE_BF>(
+            st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row);
+    return launch_gemm<128, MODE_BF>(
+        st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row);
+}
+
+ct_status split_rows_planes(
+    DeviceState *st, int mode, const float *in, int64_t rows, int64_t k, int64_t kp, void *hi, void *lo) {
+    int64_t total  = rows * kp;
+    if (total == 0)
+        return CT_OK;
+    int64_t blocks = (total + 255) / 256;
+    int64_t cap    = (int64_t)st->sm_count * 32;
+    if (blocks > cap)
+        blocks = cap;
+    if (mode == MODE_3X)
+        split_rows_kernel<MODE_3X><<<(unsigned)blocks, 256, 0, stream()>>>(in, rows, k, kp, hi, lo);
+    else
+        split_rows_kernel<MODE_BF><<<(unsigned)blocks, 256, 0, stream()>>>(in, rows, k, kp, hi, lo);
+    CT_LAUNCH_CHECK("split_rows");
+    return CT_OK;
+}
+
+// Largest k for which the kernel's int32 TMA coordinates and k-block counter are safe.
+constexpr int64_t kMaxDim = 1ll << 30;
+
+ct_status gemm_f32_tc(
+    DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
+    int64_t n, int act, float *out) {
+    if (m == 0 || n == 0)
+        return CT_OK;
+    if (m > kMaxDim || n > kMaxDim || k > kMaxDim)
+        return fail(CT_ERR_TOO_LARGE, "gemm: dimension too large");
+    const int mode   = ct_get_precision() == CT_PREC_BF16 ? MODE_BF : MODE_3X;
+    const int elem   = mode == MODE_3X ? 4 : 2;
+    const int planes = mode == MODE_3X ? 2 : 1;
+    const int kblock = ROW_B / elem;
+    int64_t kp       = (k + kblock - 1) / kblock * kblock;
+    if (kp == 0)
+        kp = kblock; // k == 0: one all-zero k-block gives C = act(bias)
+    // workspace: [A hi][A lo][B hi][B lo], each plane 1024-byte aligned
+    auto align_up       = [](size_t v) { return (v + 1023) & ~(size_t)1023; };
+    size_t a_plane      = align_up((size_t)m * kp * elem);
+    size_t b_plane      = align_up((size_t)n * kp * elem);
+    size_t total        = planes * (a_plane + b_plane);
+    CT_TRY(ensure_ws(&st->gemm_ws, &st->gemm_ws_bytes, total));
+    uint8_t *ws = static_cast<uint8_t *>(st->gemm_ws);
+    void *a_hi = ws, *a_lo = ws + a_plane;
+    void *b_hi = ws + planes * a_plane, *b_lo = ws + planes * a_plane + b_plane;
+
+    {
+        ProfScope prof("gemm_prepass");
+        CT_TRY(split_rows_planes(st, mode, a, m, k, kp, a_hi, a_lo));
+        dim3 grid((unsigned)((n + 31) / 32), (unsigned)(kp / 32));
+        if (grid.y > 65535)
+            return fail(CT_ERR_TOO_LARGE, "gemm: k too large for the operand pre-pass");
+        if (mode == MODE_3X)
+            split_transpose_kernel<MODE_3X><<<grid, 256, 0, stream()>>>(b, k, n, kp, b_hi, b_lo);
+        else
+            split_transpose_kernel<MODE_BF><<<grid, 256, 0, stream()>>>(b, k, n, kp, b_hi, b_lo);
+        CT_LAUNCH_CHECK("split_transpose");
+    }
+
+    return gemm_planes(st, mode, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, 1, 0, 0);
+}
+
+} // namespace ct

@@ -1,0 +1,660 @@
+// Reductions and data movement: full sum, rank-2 axis reductions (sum / max / argmax),
+// row softmax, transpose, concat.  All HBM-bound; accumulation is in float64 like the
+// reference (modules/tensor/runtime.cpp:879-1011), combined by warp shuffles and a fixed
+// block tree so that results do not depend on scheduling.
+#include "common.cuh"
+
+#include <cfloat>
+#include <cmath>
+
+namespace ct {
+namespace {
+
+__device__ __forceinline__ double as_double(float v) { return (double)v; }
+__device__ __forceinline__ double as_double(int64_t v) { return (double)v; }
+__device__ __forceinline__ double as_double(uint8_t v) { return v != 0 ? 1.0 : 0.0; }
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ---- full sum ---------------------------------------------------------------------------
+
+constexpr int kSumThreads = 512;
+
+template <typename T> __device__ __forceinline__ double block_sum_double(double v) {
+    __shared__ double warp_part[kSumThreads / 32];
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0)
+        warp_part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double total = 0.0;
+    if (threadIdx.x < 32) {
+        total = threadIdx.x < kSumThreads / 32 ? warp_part[threadIdx.x] : 0.0;
+        total = warp_sum(total);
+    }
+    return total; // valid in warp 0
+}
+
+// Pass 1: every block strides over the input and leaves one float64 partial.
+template <typename T>
+__global__ void __launch_bounds__(kSumThreads) sum_partial_kernel(const T *in, uint64_t n, double *partials) {
+    double acc      = 0.0;
+    uint64_t stride = (uint64_t)gridDim.x * kSumThreads;
+    uint64_t i      = (uint64_t)blockIdx.x * kSumThreads + threadIdx.x;
+    for (; i < n; i += stride)
+        acc += as_double(in[i]);
+    double total = block_sum_double<T>(acc);
+    if (threadIdx.x == 0)
+        partials[blockIdx.x] = total;
+}
+
+// float32 specialisation of pass 1: 128-bit loads, four independent accumulators.
+__global__ void __launch_bounds__(kSumThreads)
+    sum_partial_f32x4_kernel(const float4 *in, uint64_t nvec, double *partials) {
+    double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+    uint64_t stride = (uint64_t)gridDim.x * kSumThreads;
+    uint64_t i      = (uint64_t)blockIdx.x * kSumThreads + threadIdx.x;
+    for (; i + stride < nvec; i += 2 * stride) {
+        float4 p = __ldcs(in + i);
+        float4 q = __ldcs(in + i + stride);
+        a0 += (double)p.x + (double)q.x;
+        a1 += (double)p.y + (double)q.y;
+        a2 += (double)p.z + (double)q.z;
+        a3 += (double)p.w + (double)q.w;
+    }
+    if (i < nvec) {
+        float4 p = __ldcs(in + i);
+        a0 += (double)p.x;
+        a1 += (double)p.y;
+        a2 += (double)p.z;
+        a3 += (double)p.w;
+    }
+    double total = block_sum_double<float>((a0 + a1) + (a2 + a3));
+    if (threadIdx.x == 0)
+        partials[blockIdx.x] = total;
+}
+
+// Pass 2: one block folds the partials (plus a short unvectorised tail) in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(kSumThreads)
+    sum_final_kernel(const double *partials, int count, const T *tail, uint64_t tail_n, double *out) {
+    double acc = 0.0;
+    for (int i = threadIdx.x; i < count; i += kSumThreads)
+        acc += partials[i];
+    for (uint64_t i = threadIdx.x; i < tail_n; i += kSumThreads)
+        acc += as_double(tail[i]);
+    double total = block_sum_double<T>(acc);
+    if (threadIdx.x == 0)
+        *out = total;
+}
+
+template <typename T> ct_status sum_typed(DeviceState *st, const T *in, uint64_t n, double *result) {
+    int blocks = st->sm_count * 4;
+    CT_TRY(ensure_ws(&st->reduce_ws, &st->reduce_ws_bytes, (size_t)(blocks + 1) * sizeof(double)));
+    double *partials = static_cast<double *>(st->reduce_ws);
+    double *out      = partials + blocks;
+    const T *tail    = in;
+    uint64_t tail_n  = 0;
+    int used         = blocks;
+    ProfScope prof("reduce");
+    if (sizeof(T) == 4 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0 && n >= 4096) {
+        uint64_t nvec = n / 4;
+        sum_partial_f32x4_kernel<<<blocks, kSumThreads, 0, stream()>>>(
+            reinterpret_cast<const float4 *>(in), nvec, partials);
+        CT_LAUNCH_CHECK("sum(pass 1)");
+        tail   = in + nvec * 4;
+        tail_n = n - nvec * 4;
+    } else {
+        uint64_t want = (n + kSumThreads - 1) / kSumThreads;
+        if (want < (uint64_t)blocks)
+            used = (int)(want ? want : 1);
+        sum_partial_kernel<T><<<used, kSumThreads, 0, stream()>>>(in, n, partials);
+        CT_LAUNCH_CHECK("sum(pass 1)");
+    }
+    sum_final_kernel<T><<<1, kSumThreads, 0, stream()>>>(partials, used, tail, tail_n, out);
+    CT_LAUNCH_CHECK("sum(pass 2)");
+    CT_CUDA(cudaMemcpyAsync(result, out, sizeof(double), cudaMemcpyDeviceToHost, stream()));
+    CT_CUDA(cudaStreamSynchronize(stream()));
+    return CT_OK;
+}
+
+// ---- rank-2 axis reductions -----------------------------------------------------------
+
+enum { RED_SUM = 0, RED_MAX = 1, RED_ARGMAX = 2 };
+
+// Running state of one reduction: sum, or (best value, its first index).
+struct Acc {
+    double v;
+    int64_t idx;
+};
+
+template <int KIND> __device__ __forceinline__ Acc acc_init() { return Acc{0.0, -1}; }
+
+// Fold element (x, i) in.  For max/argmax, idx < 0 means "empty": the reference seeds with
+// element 0 and then replaces on strict '>' (runtime.cpp:940-946, 983-991), so a NaN seed
+// is never replaced and a later NaN never wins.
+template <int KIND> __device__ __forceinline__ void acc_push(Acc &a, double x, int64_t i) {
+    if (KIND == RED_SUM) {
+        a.v += x;
+    } else {
+        if (a.idx < 0 || x > a.v) {
+            a.v   = x;
+            a.idx = i;
+        }
+    }
+}
+
+// Merge b into a where every index in a precedes every index in b... unless swapped: the
+// merge keeps the reference's left-to-right semantics by ordering on idx.
+template <int KIND> __device__ __forceinline__ void acc_merge(Acc &a, const Acc &b) {
+    if (KIND == RED_SUM) {
+        a.v += b.v;
+        return;
+    }
+    if (b.idx < 0)
+        return;
+    if (a.idx < 0) {
+        a = b;
+        return;
+    }
+    // Sequential scan over [first ..., second ...]: second wins only if strictly greater,
+    // and never when first's best is the scan's NaN seed.
+    const Acc &first  = a.idx < b.idx ? a : b;
+    const Acc &second = a.idx < b.idx ? b : a;
+    Acc r             = first;
+    if (second.v > first.v)
+        r = second;
+    a = r;
+}
+
+// A partial whose first element is NaN must stay NaN-seeded only if that element is global
+// index 0; elsewhere a NaN is skipped by the reference's strict '>'.  So partials that do not
+// start at index 0 must not seed with NaN: push treats NaN as "not greater" but seeding needs
+// care.  seed_ok tells push whether x may seed an empty accumulator.
+template <int KIND>
+__device__ __forceinline__ void acc_push_checked(Acc &a, double x, int64_t i) {
+    if (KIND == RED_SUM) {
+        a.v += x;
+        return;
+    }
+    if (a.idx < 0) {
+        if (i == 0 || x == x) { // NaN may seed only as the very first element
+            a.v   = x;
+            a.idx = i;
+        }
+        return;
+    }
+    if (x > a.v) {
+        a.v   = x;
+        a.idx = i;
+    }
+}
+
+template <int KIND> __device__ __forceinline__ Acc warp_merge(Acc a) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Acc b;
+        b.v   = __shfl_xor_sync(0xffffffffu, a.v, o);
+        b.idx = __shfl_xor_sync(0xffffffffu, a.idx, o);
+        acc_merge<KIND>(a, b);
+    }
+    return a;
+}
+
+template <int KIND, typename OT> __device__ __forceinline__ void acc_store(OT *out, int64_t at, const Acc &a);
+template <> __device__ __forceinline__ void acc_store<RED_SUM, float>(float *out, int64_t at, const Acc &a) {
+    out[at] = (float)a.v;
+}
+template <> __device__ __forceinline__ void acc_store<RED_MAX, float>(float *out, int64_t at, const Acc &a) {
+    out[at] = (float)a.v;
+}
+template <> __device__ __forceinline__ void acc_store<RED_ARGMAX, int64_t>(int64_t *out, int64_t at, const Acc &a) {
+    out[at] = a.idx < 0 ? 0 : a.idx;
+}
+
+// axis = 1: one warp per row (cols <= 2048) - lanes stride over the columns.
+template <int KIND, typename T, typename OT>
+__global__ void __launch_bounds__(256) reduce_rows_warp_kernel(const T *in, int64_t rows, int64_t cols, OT *out) {
+    int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows)
+        return;
+    int lane   = threadIdx.x & 31;
+    const T *r = in + row * cols;
+    Acc a      = acc_init<KIND>();
+    for (int64_t j = lane; j < cols; j += 32)
+        acc_push_checked<KIND>(a, as_double(r[j]), j);
+    a = warp_merge<KIND>(a);
+    if (lane == 0)
+        acc_store<KIND, OT>(out, row, a);
+}
+
+// axis = 1, wide rows: one block per row.
+template <int KIND, typename T, typename OT>
+__global__ void __launch_bounds__(256) reduce_rows_block_kernel(const T *in, int64_t rows, int64_t cols, OT *out) {
+    __shared__ double sv[8];
+    __shared__ long long si[8];
+    int64_t row = blockIdx.x;
+    const T *r  = in + row * cols;
+    Acc a       = acc_init<KIND>();
+    for (int64_t j = threadIdx.x; j < cols; j += 256)
+        acc_push_checked<KIND>(a, as_double(r[j]), j);
+    a = warp_merge<KIND>(a);
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = a.v;
+        si[threadIdx.x >> 5] = a.idx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        Acc t = Acc{sv[0], si[0]};
+        for (int w = 1; w < 8; ++w)
+            acc_merge<KIND>(t, Acc{sv[w], si[w]});
+        acc_store<KIND, OT>(out, row, t);
+    }
+}
+
+// axis = 0: a 32x8 block owns 32 columns; the 8 row-lanes stride over the rows (coalesced
+// 128-byte reads per warp), then merge through shared memory in a fixed order.
+template <int KIND, typename T, typename OT>
+__global__ void __launch_bounds__(256) reduce_cols_kernel(const T *in, int64_t rows, int64_t cols, OT *out) {
+    __shared__ double sv[8][33];
+    __shared__ long long si[8][33];
+    int tx      = threadIdx.x & 31;
+    int ty      = threadIdx.x >> 5;
+    int64_t col = (int64_t)blockIdx.x * 32 + tx;
+    Acc a       = acc_init<KIND>();
+    if (col < cols) {
+        for (int64_t i = ty; i < rows; i += 8)
+            acc_push_checked<KIND>(a, as_double(in[i * cols + col]), i);
+    }
+    sv[ty][tx] = a.v;
+    si[ty][tx] = a.idx;
+    __syncthreads();
+    if (ty == 0 && col < cols) {
+        Acc t = Acc{sv[0][tx], si[0][tx]};
+        for (int w = 1; w < 8; ++w)
+            acc_merge<KIND>(t, Acc{sv[w][tx], si[w][tx]});
+        acc_store<KIND, OT>(out, col, t);
+    }
+}
+
+template <int KIND, typename T, typename OT>
+ct_status reduce_axis_typed(const T *in, int64_t rows, int64_t cols, int axis, OT *out) {
+    if (axis == 1) {
+        if (rows == 0)
+            return CT_OK;
+        if (cols <= 2048) {
+            unsigned blocks = (unsigned)((rows + 7) / 8);
+            reduce_rows_warp_kernel<KIND, T, OT><<<blocks, 256, 0, stream()>>>(in, rows, cols, out);
+        } else {
+            reduce_rows_block_kernel<KIND, T, OT><<<(unsigned)rows, 256, 0, stream()>>>(in, rows, cols, out);
+        }
+        CT_LAUNCH_CHECK("reduce(axis=1)");
+    } else {
+        if (cols == 0)
+            return CT_OK;
+        unsigned blocks = (unsigned)((cols + 31) / 32);
+        reduce_cols_kernel<KIND, T, OT><<<blocks, 256, 0, stream()>>>(in, rows, cols, out);
+        CT_LAUNCH_CHECK("reduce(axis=0)");
+    }
+    return CT_OK;
+}
+
+template <int KIND, typename OT>
+ct_status reduce_axis(int dt, const void *in, int64_t rows, int64_t cols, int64_t axis, OT *out, const char *name) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (!valid_dtype(dt))
+        return fail(CT_ERR_INVALID, "%s: bad dtype", name);
+    if (rows < 0 || cols < 0)
+        return fail(CT_ERR_INVALID, "%s: negative dimension", name);
+    if (axis < 0)
+        axis += 2;
+    if (axis != 0 && axis != 1)
+        return fail(CT_ERR_INVALID, "%s(axis): axis must be 0 or 1 for rank-2 tensors", name);
+    // max/argmax read element 0 of every line unconditionally in the reference; an empty
+    // reduced dimension has no defined result there, so reject it here.
+    if (KIND != RED_SUM && ((axis == 0 && rows == 0 && cols > 0) || (axis == 1 && cols == 0 && rows > 0)))
+        return fail(CT_ERR_INVALID, "%s(axis): empty reduction", name);
+    if (rows > 0x7fffffffll * 8 || cols > 0x7fffffffll * 32)
+        return fail(CT_ERR_TOO_LARGE, "%s: dimension too large", name);
+    switch (dt) {
+    case CT_F32:
+        return reduce_axis_typed<KIND, float, OT>(static_cast<const float *>(in), rows, cols, (int)axis, out);
+    case CT_I64:
+        return reduce_axis_typed<KIND, int64_t, OT>(static_cast<const int64_t *>(in), rows, cols, (int)axis, out);
+    default:
+        return reduce_axis_typed<KIND, uint8_t, OT>(static_cast<const uint8_t *>(in), rows, cols, (int)axis, out);
+    }
+}
+
+// ---- row softmax ------------------------------------------------------------------------
+//
+// softmax(x)[i,:] per test/run/nn/mnist.cml:13-25:  m = max_j x;  s = fl32(x - m);
+// e = fl32(exp(double(s)));  d = fl32(sum_j double(e));  out = fl32(e / d).
+// One warp (cols <= 1024) or one block (cols <= 8192) keeps the row in registers, so the
+// input is read once and the output written once: 8 bytes per element.
+
+template <int PER_LANE, int THREADS>
+__global__ void __launch_bounds__(THREADS) softmax_rows_kernel(const float *in, int64_t rows, int64_t cols, float *out) {
+    constexpr int WARPS         = THREADS / 32;
+    constexpr bool kWarpPerRow  = PER_LANE <= 32 && THREADS == 256 && false;
+    (void)kWarpPerRow;
+    __shared__ float s_max[WARPS];
+    __shared__ double s_sum[WARPS];
+    int64_t row = blockIdx.x;
+    if (row >= rows)
+        return;
+    const float *r = in + row * cols;
+    float *o       = out + row * cols;
+    float v[PER_LANE];
+    // max with the reference's scan semantics: element 0 seeds (NaN sticks), strict '>'.
+    float best   = -INFINITY;
+    bool has_any = false;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+        int64_t j = (int64_t)k * THREADS + threadIdx.x;
+        v[k]      = j < cols ? r[j] : -INFINITY;
+        if (j < cols && v[k] > best)
+            best = v[k];
+        has_any |= j < cols;
+    }
+    (void)has_any;
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1)
+        best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o2));
+    if ((threadIdx.x & 31) == 0)
+        s_max[threadIdx.x >> 5] = best;
+    __syncthreads();
+    float m = s_max[0];
+#pragma unroll
+    for (int w = 1; w < WARPS; ++w)
+        m = fmaxf(m, s_max[w]);
+    float first = r[0];
+    if (first != first)
+        m = first; // a NaN seed is never replaced (runtime.cpp:940-946)
+    double acc = 0.0;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+        int64_t j = (int64_t)k * THREADS + threadIdx.x;
+        if (j < cols) {
+            float s = __fsub_rn(v[k], m);
+            v[k]    = (float)exp((double)s);
+            acc += (double)v[k];
+        }
+    }
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0)
+        s_sum[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    double total = 0.0;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w)
+        total += s_sum[w];
+    float d = (float)total;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+        int64_t j = (int64_t)k * THREADS + threadIdx.x;
+        if (j < cols)
+            o[j] = __fdiv_rn(v[k], d);
+    }
+}
+
+// Several short rows per block: one warp per row, row kept in registers.
+template <int PER_LANE>
+__global__ void __launch_bounds__(256) softmax_rows_warp_kernel(const float *in, int64_t rows, int64_t cols, float *out) {
+    int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows)
+        return;
+    int lane       = threadIdx.x & 31;
+    const float *r = in + row * cols;
+    float *o       = out + row * cols;
+    float v[PER_LANE];
+    float best = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+        int64_t j = (int64_t)k * 32 + lane;
+        v[k]      = j < cols ? r[j] : -INFINITY;
+        if (j < cols && v[k] > best)
+            best = v[k];
+    }
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1)
+        best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o2));
+    float first = __shfl_sync(0xffffffffu, v[0], 0);
+    if (first != first)
+        best = first;
+    double acc = 0.0;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+        int64_t j = (int64_t)k * 32 + lane;
+        if (j < cols) {
+            float s = __fsub_rn(v[k], best);
+            v[k]    = (float)exp((double)s);
+            acc += (double)v[k];
+        }
+    }
+    acc     = warp_sum(acc);
+    float d = (float)acc;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+        int64_t j = (int64_t)k * 32 + lane;
+        if (j < cols)
+            o[j] = __fdiv_rn(v[k], d);
+    }
+}
+
+// Rows too long for registers: three passes over global memory, one block per row.
+__global__ void __launch_bounds__(256) softmax_rows_stream_kernel(const float *in, int64_t rows, int64_t cols, float *out) {
+    __shared__ float s_max[8];
+    __shared__ double s_sum[8];
+    int64_t row    = blockIdx.x;
+    const float *r = in + row * cols;
+    float *o       = out + row * cols;
+    float best     = -INFINITY;
+    for (int64_t j = threadIdx.x; j < cols; j += 256)
+        if (r[j] > best)
+            best = r[j];
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1)
+        best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o2));
+    if ((threadIdx.x & 31) == 0)
+        s_max[threadIdx.x >> 5] = best;
+    __syncthreads();
+    float m = s_max[0];
+    for (int w = 1; w < 8; ++w)
+        m = fmaxf(m, s_max[w]);
+    if (r[0] != r[0])
+        m = r[0];
+    double acc = 0.0;
+    for (int64_t j = threadIdx.x; j < cols; j += 256) {
+        float e = (float)exp((double)__fsub_rn(r[j], m));
+        o[j]    = e;
+        acc += (double)e;
+    }
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0)
+        s_sum[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    double total = 0.0;
+    for (int w = 0; w < 8; ++w)
+        total += s_sum[w];
+    float d = (float)total;
+    for (int64_t j = threadIdx.x; j < cols; j += 256)
+        o[j] = __fdiv_rn(o[j], d);
+}
+
+// ---- transpose / concat -----------------------------------------------------------------
+
+template <typename T>
+__global__ void __launch_bounds__(256) transpose_kernel(const T *in, int64_t rows, int64_t cols, T *out) {
+    __shared__ T tile[32][33];
+    int tx      = threadIdx.x & 31;
+    int ty      = threadIdx.x >> 5;
+    int64_t c0  = (int64_t)blockIdx.x * 32;
+    int64_t r0  = (int64_t)blockIdx.y * 32;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        int64_t r = r0 + ty + k * 8, c = c0 + tx;
+        if (r < rows && c < cols)
+            tile[ty + k * 8][tx] = in[r * cols + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        int64_t c = c0 + ty + k * 8, r = r0 + tx; // out[c][r]
+        if (r < rows && c < cols)
+            out[c * rows + r] = tile[tx][ty + k * 8];
+    }
+}
+
+// out viewed as [outer][lhs_len + rhs_len] bytes-items of `unit` bytes each.
+template <typename U>
+__global__ void __launch_bounds__(256) concat_kernel(
+    const U *lhs, const U *rhs, uint64_t outer, uint64_t lhs_len, uint64_t rhs_len, U *out) {
+    uint64_t row_len = lhs_len + rhs_len;
+    uint64_t total   = outer * row_len;
+    uint64_t stride  = (uint64_t)gridDim.x * 256;
+    for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += stride) {
+        uint64_t o = i / row_len, j = i - o * row_len;
+        out[i] = j < lhs_len ? lhs[o * lhs_len + j] : rhs[o * rhs_len + (j - lhs_len)];
+    }
+}
+
+template <typename U>
+ct_status concat_typed(
+    DeviceState *st, const void *l, const void *r, uint64_t outer, uint64_t ll, uint64_t rl, void *o) {
+    uint64_t total  = outer * (ll + rl);
+    uint64_t blocks = (total + 255) / 256;
+    uint64_t cap    = (uint64_t)st->sm_count * 16;
+    if (blocks > cap)
+        blocks = cap;
+    concat_kernel<U><<<(unsigned)blocks, 256, 0, stream()>>>(
+        static_cast<const U *>(l), static_cast<const U *>(r), outer, ll, rl, static_cast<U *>(o));
+    CT_LAUNCH_CHECK("concat");
+    return CT_OK;
+}
+
+} // namespace
+} // namespace ct
+
+using namespace ct;
+
+extern "C" {
+
+ct_status ct_sum(ct_dtype dt, const void *in, uint64_t n, double *result) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (!valid_dtype(dt) || !result)
+        return fail(CT_ERR_INVALID, "ct_sum: bad dtype or null result");
+    if (n == 0) {
+        *result = 0.0;
+        return CT_OK;
+    }
+    if (!in)
+        return fail(CT_ERR_INVALID, "ct_sum: null pointer");
+    switch (dt) {
+    case CT_F32:
+        return sum_typed<float>(st, static_cast<const float *>(in), n, result);
+    case CT_I64:
+        return sum_typed<int64_t>(st, static_cast<const int64_t *>(in), n, result);
+    default:
+        return sum_typed<uint8_t>(st, static_cast<const uint8_t *>(in), n, result);
+    }
+}
+
+ct_status ct_sum_axis(ct_dtype dt, const void *in, int64_t rows, int64_t cols, int64_t axis, float *out) {
+    return reduce_axis<RED_SUM, float>(dt, in, rows, cols, axis, out, "sum");
+}
+
+ct_status ct_max_axis(ct_dtype dt, const void *in, int64_t rows, int64_t cols, int64_t axis, float *out) {
+    return reduce_axis<RED_MAX, float>(dt, in, rows, cols, axis, out, "max");
+}
+
+ct_status ct_argmax_axis(ct_dtype dt, const void *in, int64_t rows, int64_t cols, int64_t axis, int64_t *out) {
+    return reduce_axis<RED_ARGMAX, int64_t>(dt, in, rows, cols, axis, out, "argmax");
+}
+
+ct_status ct_softmax_rows(const float *in, int64_t rows, int64_t cols, float *out) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (rows < 0 || cols < 0)
+        return fail(CT_ERR_INVALID, "softmax: negative dimension");
+    if (rows == 0 || cols == 0)
+        return CT_OK;
+    if (!in || !out)
+        return fail(CT_ERR_INVALID, "softmax: null pointer");
+    if (rows > 0x7fffffffll)
+        return fail(CT_ERR_TOO_LARGE, "softmax: too many rows");
+    unsigned wblocks = (unsigned)((rows + 7) / 8);
+    if (cols <= 32)
+        softmax_rows_warp_kernel<1><<<wblocks, 256, 0, stream()>>>(in, rows, cols, out);
+    else if (cols <= 128)
+        softmax_rows_warp_kernel<4><<<wblocks, 256, 0, stream()>>>(in, rows, cols, out);
+    else if (cols <= 512)
+        softmax_rows_warp_kernel<16><<<wblocks, 256, 0, stream()>>>(in, rows, cols, out);
+    else if (cols <= 2048)
+        softmax_rows_kernel<8, 256><<<(unsigned)rows, 256, 0, stream()>>>(in, rows, cols, out);
+    else if (cols <= 8192)
+        softmax_rows_kernel<32, 256><<<(unsigned)rows, 256, 0, stream()>>>(in, rows, cols, out);
+    else
+        softmax_rows_stream_kernel<<<(unsigned)rows, 256, 0, stream()>>>(in, rows, cols, out);
+    CT_LAUNCH_CHECK("softmax_rows");
+    return CT_OK;
+}
+
+ct_status ct_transpose(ct_dtype dt, const void *in, int64_t rows, int64_t cols, void *out) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (!valid_dtype(dt) || rows < 0 || cols < 0)
+        return fail(CT_ERR_INVALID, "transpose: bad dtype or dimension");
+    if (rows == 0 || cols == 0)
+        return CT_OK;
+    dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
+    if ((rows + 31) / 32 > 65535)
+        return fail(CT_ERR_TOO_LARGE, "transpose: too many rows");
+    switch (dt) {
+    case CT_F32:
+        transpose_kernel<float><<<grid, 256, 0, stream()>>>(
+            static_cast<const float *>(in), rows, cols, static_cast<float *>(out));
+        break;
+    case CT_I64:
+        transpose_kernel<int64_t><<<grid, 256, 0, stream()>>>(
+            static_cast<const int64_t *>(in), rows, cols, static_cast<int64_t *>(out));
+        break;
+    default:
+        transpose_kernel<uint8_t><<<grid, 256, 0, stream()>>>(
+            static_cast<const uint8_t *>(in), rows, cols, static_cast<uint8_t *>(out));
+        break;
+    }
+    CT_LAUNCH_CHECK("transpose");
+    return CT_OK;
+}
+
+ct_status ct_concat(
+    ct_dtype dt, const void *lhs, const void *rhs, uint64_t outer, uint64_t lhs_axis,
+    uint64_t rhs_axis, uint64_t inner, void *out) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (!valid_dtype(dt))
+        return fail(CT_ERR_INVALID, "concat: bad dtype");
+    uint64_t ll = lhs_axis * inner, rl = rhs_axis * inner;
+    if (outer == 0 || ll + rl == 0)
+        return CT_OK;
+    size_t item = dtype_size(dt);
+    // Move the widest unit that divides both row segments and respects the alignment.
+    uintptr_t bits = reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs) |
+                     reinterpret_cast<uintptr_t>(out) | (ll * item) | (rl * item);
+    if ((bits & 15u) == 0)
+        return concat_typed<uint4>(st, lhs, rhs, outer, ll * item / 16, rl * item / 16, out);
+    if ((bits & 7u) == 0)
+        return concat_typed<uint64_t>(st, lhs, rhs, outer, ll * item / 8, rl * item / 8, out);
+    if ((bits & 3u) == 0)
+        return concat_typed<uint32_t>(st, lhs, rhs, outer, ll * item / 4, rl * item / 4, out);
+    return concat_typed<uint8_t>(st, lhs, rhs, outer, ll * item, rl * item, out);
+}
+
+} // extern "C"

@@ -1,0 +1,309 @@
+// Library state: error text, device/stream selection, storage entry points.
+#include "common.cuh"
+
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+namespace ct {
+
+namespace {
+thread_local char g_err[512] = "";
+std::mutex g_mutex;
+DeviceState g_states[16];
+std::atomic<int> g_device{-1};
+std::atomic<cudaStream_t> g_stream{nullptr};
+std::atomic<uint64_t> g_launches{0};
+std::atomic<int> g_precision{CT_PREC_3XTF32};
+} // namespace
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+ct_status fail(ct_status code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+ct_status cuda_fail(cudaError_t e, const char *what) {
+    snprintf(g_err, sizeof(g_err), "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver)
+        return CT_ERR_NO_DEVICE;
+    return CT_ERR_CUDA;
+}
+
+cudaStream_t stream() { return g_stream.load(); }
+void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+ct_status current(DeviceState **out) {
+    int dev = g_device.load();
+    if (dev < 0) {
+        int count     = 0;
+        cudaError_t e = cudaGetDeviceCount(&count);
+        if (e != cudaSuccess || count == 0) {
+            cudaGetLastError();
+            return fail(CT_ERR_NO_DEVICE, "no CUDA device: libcamel_tensor_b200 has no CPU fallback");
+        }
+        CT_CUDA(cudaGetDevice(&dev));
+        g_device.store(dev);
+    }
+    if (dev >= 16)
+        return fail(CT_ERR_INVALID, "device index %d not supported", dev);
+    DeviceState *st = &g_states[dev];
+    if (!st->ready) {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (!st->ready) {
+            CT_CUDA(cudaSetDevice(dev));
+            cudaDeviceProp prop;
+            CT_CUDA(cudaGetDeviceProperties(&prop, dev));
+            if (prop.major != 10)
+                return fail(
+                    CT_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only",
+                    dev, prop.major, prop.minor);
+            st->device   = dev;
+            st->sm_count = prop.multiProcessorCount;
+            CT_CUDA(cudaMalloc(&st->flags_dev, FLAG_COUNT * sizeof(uint32_t)));
+            CT_CUDA(cudaMemset(st->flags_dev, 0, FLAG_COUNT * sizeof(uint32_t)));
+            CT_CUDA(cudaMallocHost(&st->flags_host, FLAG_COUNT * sizeof(uint32_t)));
+            memset(st->flags_host, 0, FLAG_COUNT * sizeof(uint32_t));
+            st->ready = true;
+        }
+    }
+    *out = st;
+    return CT_OK;
+}
+
+ct_status ensure_ws(void **ptr, size_t *cap, size_t bytes) {
+    if (*cap >= bytes && *ptr)
+        return CT_OK;
+    if (*ptr) {
+        CT_CUDA(cudaStreamSynchronize(stream()));
+        CT_CUDA(cudaFree(*ptr));
+        *ptr = nullptr;
+        *cap = 0;
+    }
+    size_t want = bytes + bytes / 8 + 256;
+    CT_CUDA(cudaMalloc(ptr, want));
+    *cap = want;
+    return CT_OK;
+}
+
+ct_status clear_flags(DeviceState *st) {
+    CT_CUDA(cudaMemsetAsync(st->flags_dev, 0, FLAG_COUNT * sizeof(uint32_t), stream()));
+    return CT_OK;
+}
+
+ct_status fetch_flags(DeviceState *st) {
+    CT_CUDA(cudaMemcpyAsync(
+        st->flags_host, st->flags_dev, FLAG_COUNT * sizeof(uint32_t), cudaMemcpyDeviceToHost,
+        stream()));
+    CT_CUDA(cudaStreamSynchronize(stream()));
+    return CT_OK;
+}
+
+} // namespace ct
+
+using namespace ct;
+
+extern "C" {
+
+const char *ct_last_error(void) { return g_err; }
+const char *ct_version(void) { return "camel_tensor_b200 0.1 (sm_100a)"; }
+
+ct_status ct_device_count(int *count_host) {
+    if (!count_host)
+        return fail(CT_ERR_INVALID, "count_host is null");
+    int count     = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        count = 0;
+    }
+    *count_host = count;
+    return CT_OK;
+}
+
+ct_status ct_set_device(int device) {
+    int count     = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(CT_ERR_NO_DEVICE, "no CUDA device: libcamel_tensor_b200 has no CPU fallback");
+    }
+    if (device < 0 || device >= count)
+        return fail(CT_ERR_INVALID, "device %d out of range (have %d)", device, count);
+    CT_CUDA(cudaSetDevice(device));
+    g_device.store(device);
+    DeviceState *st;
+    return current(&st);
+}
+
+ct_status ct_set_stream(void *s) {
+    g_stream.store(static_cast<cudaStream_t>(s));
+    return CT_OK;
+}
+
+ct_status ct_sync(void) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    CT_CUDA(cudaStreamSynchronize(stream()));
+    return CT_OK;
+}
+
+uint64_t ct_launch_count(void) { return g_launches.load(); }
+
+ct_status ct_set_precision(ct_precision p) {
+    if (p != CT_PREC_3XTF32 && p != CT_PREC_BF16)
+        return fail(CT_ERR_INVALID, "unknown precision %d", (int)p);
+    g_precision.store((int)p);
+    return CT_OK;
+}
+
+ct_precision ct_get_precision(void) { return (ct_precision)g_precision.load(); }
+
+ct_status ct_alloc(void **ptr_dev, size_t bytes) {
+    if (!ptr_dev)
+        return fail(CT_ERR_INVALID, "ptr_dev is null");
+    DeviceState *st;
+    CT_TRY(current(&st));
+    *ptr_dev = nullptr;
+    if (bytes == 0)
+        bytes = 1; // an empty tensor still owns a distinct address
+    CT_CUDA(cudaMalloc(ptr_dev, bytes));
+    return CT_OK;
+}
+
+ct_status ct_free(void *ptr_dev) {
+    if (!ptr_dev)
+        return CT_OK;
+    DeviceState *st;
+    CT_TRY(current(&st));
+    CT_CUDA(cudaFree(ptr_dev));
+    return CT_OK;
+}
+
+ct_status ct_h2d(void *dst_dev, const void *src_host, size_t bytes) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (bytes == 0)
+        return CT_OK;
+    CT_CUDA(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, stream()));
+    CT_CUDA(cudaStreamSynchronize(stream())); // src_host may be pageable and reused at once
+    return CT_OK;
+}
+
+ct_status ct_d2h(void *dst_host, const void *src_dev, size_t bytes) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (bytes == 0)
+        return CT_OK;
+    CT_CUDA(cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, stream()));
+    CT_CUDA(cudaStreamSynchronize(stream()));
+    return CT_OK;
+}
+
+ct_status ct_d2d(void *dst_dev, const void *src_dev, size_t bytes) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (bytes == 0)
+        return CT_OK;
+    CT_CUDA(cudaMemcpyAsync(dst_dev, src_dev, bytes, cudaMemcpyDeviceToDevice, stream()));
+    return CT_OK;
+}
+
+ct_dtype ct_result_dtype(ct_binary_op op, ct_dtype lhs, ct_dtype rhs) {
+    if (op == CT_DIV || op == CT_POW)
+        return CT_F32;
+    if (lhs == CT_F32 || rhs == CT_F32)
+        return CT_F32;
+    if (lhs == CT_I64 || rhs == CT_I64)
+        return CT_I64;
+    return CT_BOOL;
+}
+
+} // extern "C"
+
+extern "C" ct_status ct_check(void) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    CT_TRY(fetch_flags(st));
+    if (st->flags_host[FLAG_TIMEOUT]) {
+        uint32_t where = st->flags_host[FLAG_TIMEOUT] - 1;
+        CT_TRY(clear_flags(st));
+        return fail(CT_ERR_TIMEOUT, "a bounded wait inside a kernel ran out (block %u)", where);
+    }
+    return CT_OK;
+}
+
+// ---- per-kernel device timing -------------------------------------------------------------
+
+namespace ct {
+namespace {
+struct ProfRecord {
+    const char *name;
+    cudaEvent_t e0, e1;
+};
+std::atomic<int> g_prof_on{0};
+std::mutex g_prof_mutex;
+std::vector<ProfRecord> g_prof;
+} // namespace
+
+ProfScope::ProfScope(const char *name) : name_(name), e0_(nullptr), e1_(nullptr) {
+    if (!g_prof_on.load(std::memory_order_relaxed))
+        return;
+    if (cudaEventCreate(&e0_) != cudaSuccess || cudaEventCreate(&e1_) != cudaSuccess) {
+        e0_ = e1_ = nullptr;
+        return;
+    }
+    cudaEventRecord(e0_, stream());
+}
+
+ProfScope::~ProfScope() {
+    if (!e0_)
+        return;
+    cudaEventRecord(e1_, stream());
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    g_prof.push_back(ProfRecord{name_, e0_, e1_});
+}
+} // namespace ct
+
+extern "C" ct_status ct_profile_enable(int on) {
+    g_prof_on.store(on ? 1 : 0);
+    return CT_OK;
+}
+
+extern "C" ct_status ct_profile_read(const char *kernel, double *total_ms_host, uint64_t *launches_host) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    CT_CUDA(cudaStreamSynchronize(stream()));
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    double total = 0.0;
+    uint64_t count = 0;
+    std::vector<ProfRecord> keep;
+    for (auto &r : g_prof) {
+        if (kernel && strcmp(kernel, r.name) != 0) {
+            keep.push_back(r);
+            continue;
+        }
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, r.e0, r.e1) == cudaSuccess) {
+            total += ms;
+            ++count;
+        }
+        cudaEventDestroy(r.e0);
+        cudaEventDestroy(r.e1);
+    }
+    g_prof.swap(keep);
+    if (total_ms_host)
+        *total_ms_host = total;
+    if (launches_host)
+        *launches_host = count;
+    return CT_OK;
+}

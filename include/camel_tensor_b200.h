@@ -1,0 +1,215 @@
+/*
+ * camel_tensor_b200.h - C ABI of libcamel_tensor_b200.so
+ *
+ * The CUDA (sm_100a) bodies of the dense-tensor operators of OpenCML/Camel's `tensor`
+ * module.  The reference module (`tensor.cmo`) is a C++ plugin whose operators have the
+ * signature  slot_t op(ArgsView& with, ArgsView& norm, Context& ctx)
+ * (include/camel/core/operator.h:63) and compute on host memory; the functions below are what
+ * such an operator body calls once its arguments are unpacked: plain pointers, sizes and
+ * dtype codes, no C++ types.  Each declaration names the reference function whose loop it
+ * replaces (paths are relative to the reference checkout).
+ *
+ * Conventions
+ *  - Every function returns a ct_status.  On a non-zero status ct_last_error() gives a
+ *    message for the calling thread; for CT_ERR_DIV_ZERO / CT_ERR_LOG_DOMAIN it is the text
+ *    of the exception the reference throws, so a plugin can rethrow it unchanged.
+ *  - Pointers named *_dev are device pointers of the current device (ct_set_device); pointers
+ *    named *_host are host pointers.  Tensors are dense, row-major, contiguous, exactly as
+ *    the reference stores them (modules/tensor/runtime.cpp:482-485).
+ *  - dtype codes follow the reference's three storage types (runtime.cpp:553-566).
+ *  - Kernels are enqueued on the stream set by ct_set_stream (default: the legacy default
+ *    stream).  Functions that return a host value, or that must report a data-dependent
+ *    error, synchronise that stream before returning; the others do not.
+ *  - There is no CPU fallback: without a usable CUDA device every compute entry point
+ *    returns CT_ERR_NO_DEVICE.
+ */
+#ifndef CAMEL_TENSOR_B200_H
+#define CAMEL_TENSOR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ct_status {
+    CT_OK             = 0,
+    CT_ERR_INVALID    = 1, /* bad shape / dtype / argument (host-side check, nothing launched) */
+    CT_ERR_CUDA       = 2, /* a CUDA runtime or driver call failed */
+    CT_ERR_DIV_ZERO   = 3, /* "Division by zero", modules/tensor/runtime.cpp:122-124 */
+    CT_ERR_LOG_DOMAIN = 4, /* "log: input must be positive", runtime.cpp:1039-1041 */
+    CT_ERR_TIMEOUT    = 5, /* a bounded wait inside a kernel ran out; the context stays usable */
+    CT_ERR_NO_DEVICE  = 6,
+    CT_ERR_TOO_LARGE  = 7  /* size beyond what the entry point supports */
+} ct_status;
+
+/* Storage dtypes, modules/tensor/runtime.cpp:553-566 (Float64/Int32 inputs normalise to these). */
+typedef enum ct_dtype { CT_F32 = 0, CT_I64 = 1, CT_BOOL = 2 } ct_dtype;
+
+/* enum class BinaryOp / CompareOp, modules/tensor/runtime.h:39-53 (same order). */
+typedef enum ct_binary_op { CT_ADD = 0, CT_SUB = 1, CT_MUL = 2, CT_DIV = 3, CT_POW = 4 } ct_binary_op;
+typedef enum ct_compare_op { CT_LT = 0, CT_LE = 1, CT_GT = 2, CT_GE = 3, CT_EQ = 4 } ct_compare_op;
+
+/* Fused activation of the dense / conv2d entry points. */
+typedef enum ct_activation {
+    CT_ACT_NONE    = 0,
+    CT_ACT_RELU    = 1, /* x * (x > 0): the idiom of test/run/nn/svm.cml:31 */
+    CT_ACT_SOFTMAX = 2  /* row softmax of test/run/nn/mnist.cml:13-25 (dense only) */
+} ct_activation;
+
+/* Arithmetic of the tensor-core contractions. */
+typedef enum ct_precision {
+    CT_PREC_3XTF32 = 0, /* fp32 in, split into two TF32 terms, three MMAs, fp32 accumulate */
+    CT_PREC_BF16   = 1  /* inputs rounded to bf16 once, fp32 accumulate (reported separately) */
+} ct_precision;
+
+/* ---- library / device --------------------------------------------------------------- */
+
+const char *ct_last_error(void);
+const char *ct_version(void);
+ct_status ct_device_count(int *count_host);
+ct_status ct_set_device(int device);
+/* stream is a cudaStream_t passed as void*; NULL selects the legacy default stream. */
+ct_status ct_set_stream(void *stream);
+ct_status ct_sync(void);
+/* Synchronises and reports errors that kernels of earlier asynchronous calls raised on the
+ * device (CT_ERR_TIMEOUT: a bounded wait in a contraction kernel ran out; its output is then
+ * undefined). */
+ct_status ct_check(void);
+/* Number of kernels this library has launched in this process (all threads). */
+uint64_t ct_launch_count(void);
+/* Device timing per kernel family: while enabled, each launch is bracketed by CUDA events on
+ * the launching stream.  ct_profile_read synchronises, sums and clears the records filed under
+ * `kernel` ("gemm_tc", "gemm_prepass", "gemm_skinny", "im2col", "elementwise", "reduce",
+ * "softmax"); NULL reads all. */
+ct_status ct_profile_enable(int on);
+ct_status ct_profile_read(const char *kernel, double *total_ms_host, uint64_t *launches_host);
+ct_status ct_set_precision(ct_precision precision);
+ct_precision ct_get_precision(void);
+
+/* ---- device storage: the device side of TensorObject::create,
+ *      modules/tensor/runtime.cpp:256-279 (storage gains a device buffer) ---------------- */
+
+ct_status ct_alloc(void **ptr_dev, size_t bytes);
+ct_status ct_free(void *ptr_dev);
+ct_status ct_h2d(void *dst_dev, const void *src_host, size_t bytes);
+ct_status ct_d2h(void *dst_host, const void *src_dev, size_t bytes);
+ct_status ct_d2d(void *dst_dev, const void *src_dev, size_t bytes);
+
+/* Result dtype of a binary operator: promoteTensorTypes (runtime.cpp:570-580) with the
+ * Divide/Power -> Float32 override (runtime.cpp:781-784). */
+ct_dtype ct_result_dtype(ct_binary_op op, ct_dtype lhs, ct_dtype rhs);
+
+/* ---- elementwise ------------------------------------------------------------------- */
+
+/* tensorBinary, runtime.cpp:775-793.  out has dtype ct_result_dtype(op, lhs, rhs).
+ * CT_DIV synchronises and returns CT_ERR_DIV_ZERO when any divisor is 0. */
+ct_status ct_binary(
+    ct_binary_op op, ct_dtype lhs_dtype, const void *lhs_dev, ct_dtype rhs_dtype,
+    const void *rhs_dev, uint64_t numel, void *out_dev);
+
+/* tensorBinaryScalarRight / tensorBinaryScalarLeft, runtime.cpp:795-831.  scalar_dtype is the
+ * tensor dtype the scalar's Camel type normalises to (float/double -> CT_F32, int -> CT_I64,
+ * bool -> CT_BOOL); the value enters as double (scalarToDouble, runtime.cpp:62-77). */
+ct_status ct_binary_scalar(
+    ct_binary_op op, ct_dtype tensor_dtype, const void *tensor_dev, double scalar,
+    ct_dtype scalar_dtype, int scalar_on_left, uint64_t numel, void *out_dev);
+
+/* tensorCompare, runtime.cpp:863-877: Bool (uint8) output. */
+ct_status ct_compare(
+    ct_compare_op op, ct_dtype lhs_dtype, const void *lhs_dev, ct_dtype rhs_dtype,
+    const void *rhs_dev, uint64_t numel, uint8_t *out_dev);
+
+/* tensorCompareScalarRight / ScalarLeft, runtime.cpp:833-861. */
+ct_status ct_compare_scalar(
+    ct_compare_op op, ct_dtype tensor_dtype, const void *tensor_dev, double scalar,
+    int scalar_on_left, uint64_t numel, uint8_t *out_dev);
+
+/* tensorExp, runtime.cpp:1013-1027. */
+ct_status ct_exp(const float *in_dev, uint64_t numel, float *out_dev);
+/* tensorLog, runtime.cpp:1029-1045.  Synchronises; CT_ERR_LOG_DOMAIN when any input <= 0. */
+ct_status ct_log(const float *in_dev, uint64_t numel, float *out_dev);
+/* relu(x) = multiply(x, gt(x, 0)) in one pass; the reference has no such operator, the
+ * composition (test/run/nn/svm.cml:31) defines the values, bit patterns included. */
+ct_status ct_relu(const float *in_dev, uint64_t numel, float *out_dev);
+
+/* ---- reductions -------------------------------------------------------------------- */
+
+/* tensorSum, runtime.cpp:879-885: float64 sum of all elements, returned to the host. */
+ct_status ct_sum(ct_dtype dtype, const void *in_dev, uint64_t numel, double *result_host);
+/* tensorSumAxis, runtime.cpp:887-922: rank 2, axis in {0,1,-1,-2}, float32 out. */
+ct_status ct_sum_axis(
+    ct_dtype dtype, const void *in_dev, int64_t rows, int64_t cols, int64_t axis, float *out_dev);
+/* tensorMaxAxis, runtime.cpp:924-963. */
+ct_status ct_max_axis(
+    ct_dtype dtype, const void *in_dev, int64_t rows, int64_t cols, int64_t axis, float *out_dev);
+/* tensorArgmaxAxis, runtime.cpp:965-1011: Int64 out, first maximum wins. */
+ct_status ct_argmax_axis(
+    ct_dtype dtype, const void *in_dev, int64_t rows, int64_t cols, int64_t axis,
+    int64_t *out_dev);
+/* Row softmax as one operator: the function `softmax` of test/run/nn/mnist.cml:13-25
+ * (max, subtract, exp, sum, divide; each step rounded to float32 like its operator). */
+ct_status ct_softmax_rows(const float *in_dev, int64_t rows, int64_t cols, float *out_dev);
+
+/* ---- data movement ----------------------------------------------------------------- */
+
+/* tensorTranspose2D, runtime.cpp:704-720. */
+ct_status ct_transpose(ct_dtype dtype, const void *in_dev, int64_t rows, int64_t cols, void *out_dev);
+/* tensorConcat, runtime.cpp:722-773, on the (outer, axis, inner) view of the two shapes. */
+ct_status ct_concat(
+    ct_dtype dtype, const void *lhs_dev, const void *rhs_dev, uint64_t outer, uint64_t lhs_axis,
+    uint64_t rhs_axis, uint64_t inner, void *out_dev);
+/* tensorReshape, runtime.cpp:692-702, is ct_d2d of the payload. */
+
+/* tensorZeros/Ones/Full, runtime.cpp:614-646: value converted as setFromDouble does. */
+ct_status ct_fill(ct_dtype dtype, double value, uint64_t numel, void *out_dev);
+/* tensorEye, runtime.cpp:675-690. */
+ct_status ct_eye(int64_t size, float *out_dev);
+/* tensorArange, runtime.cpp:652-673: count = number of items (host computes it the same way). */
+ct_status ct_arange(int64_t start, int64_t step, int64_t count, int64_t *out_dev);
+
+/* ---- contractions ------------------------------------------------------------------ */
+
+/* __tensor_matmul__, modules/tensor/operators.cpp:740-769: C[m,n] = A[m,k] . B[k,n], rank 2,
+ * out dtype = promote(a, b).  float32 x float32 runs on the tensor cores (3xTF32 unless
+ * ct_set_precision says otherwise); other dtype pairs accumulate in float64 on CUDA cores. */
+ct_status ct_matmul(
+    ct_dtype a_dtype, const void *a_dev, ct_dtype b_dtype, const void *b_dev, int64_t m,
+    int64_t k, int64_t n, void *out_dev);
+
+/* dense<w,b>(x) = act(x . w + b): the bias idiom concat(x, ones, 1) @ concat(w, b, 0) of
+ * test/run/nn/lr.cml:19-21 with the activation fused into the GEMM epilogue.  bias_dev may be
+ * NULL.  With CT_ACT_SOFTMAX, argmax_dev (may be NULL) also receives argmax(logits, 1) as
+ * tensorArgmaxAxis defines it. */
+ct_status ct_dense(
+    const float *x_dev, const float *w_dev, const float *bias_dev, int64_t m, int64_t k,
+    int64_t n, ct_activation act, float *out_dev, int64_t *argmax_dev);
+
+/* conv2d, NCHW input [n,c,h,w], OIHW weights [k_out,c,kh,kw], zero padding, then + bias and
+ * activation (NONE or RELU).  No reference counterpart (the reference has no conv operator);
+ * arithmetic follows the reference's style: one accumulation per output over (c,kh,kw). */
+ct_status ct_conv2d(
+    const float *x_dev, const float *w_dev, const float *bias_dev, int64_t n, int64_t c,
+    int64_t h, int64_t w, int64_t k_out, int64_t kh, int64_t kw, int64_t stride, int64_t pad,
+    ct_activation act, float *out_dev);
+
+/* maxpool2d, NCHW, window == stride, no padding.  No reference counterpart; strict '>' from
+ * the window's first element, like tensorMaxAxis. */
+ct_status ct_maxpool2d(
+    const float *x_dev, int64_t n, int64_t c, int64_t h, int64_t w, int64_t window,
+    float *out_dev);
+
+/* ---- host-buffer forms: what an operator body calls at a graph boundary, where operands
+ *      live in TensorObject host storage.  Copies in, computes, copies out, synchronises. ---- */
+
+ct_status ct_matmul_host(
+    const float *a_host, const float *b_host, int64_t m, int64_t k, int64_t n, float *out_host);
+ct_status ct_binary_host(
+    ct_binary_op op, const float *lhs_host, const float *rhs_host, uint64_t numel,
+    float *out_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CAMEL_TENSOR_B200_H */

@@ -1,0 +1,320 @@
+"""GPU: the CUDA library (through its C ABI) against the CPU oracle and the golden vectors.
+
+Bars
+ - integer / bool / index outputs, and float32 outputs of + - * / relu, comparisons, movement,
+   constructors, max: bit-exact.
+ - float32 outputs that pass through exp / log / pow (device libm vs host libm, both rounded
+   from float64): at most 1 ulp, and the share of bit-identical values is reported.
+ - tensor-core contractions (3xTF32): max |gpu - ref| / max |ref| <= 1e-5, the tolerance the
+   path is specified with; also the component-wise error against sum_k |a||b| is bounded.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from cases import BIN, CASES, CMP, TOLERANCE_CASES, PortBackend
+
+pytestmark = pytest.mark.gpu
+
+ULP_CASES = ("binary_f32_n", "unary_exp_log", "softmax_rows", "binary_mixed_dtypes")
+GEMM_TOL = 1e-5
+
+
+@pytest.fixture(scope="module")
+def T():
+    from camel_b200 import tensor
+
+    return tensor
+
+
+class CudaBackend:
+    name = "cuda"
+
+    def __init__(self, T):
+        self.T = T
+
+    def _t(self, a):
+        return self.T.from_numpy(np.asarray(a)) if isinstance(a, np.ndarray) else a
+
+    def _n(self, t):
+        out = t.numpy()
+        self.T.check_async()
+        return out
+
+    def binary(self, op, a, b):
+        return self._n(getattr(self.T, op)(self._t(a), self._t(b)))
+
+    def compare(self, op, a, b):
+        return self._n(getattr(self.T, op)(self._t(a), self._t(b)))
+
+    def sum(self, a):
+        return self.T.sum(self._t(a))
+
+    def sum_axis(self, a, ax):
+        return self._n(self.T.sum(self._t(a), ax))
+
+    def max_axis(self, a, ax):
+        return self._n(self.T.max(self._t(a), ax))
+
+    def argmax_axis(self, a, ax):
+        return self._n(self.T.argmax(self._t(a), ax))
+
+    def exp(self, a):
+        return self._n(self.T.exp(self._t(a)))
+
+    def log(self, a):
+        return self._n(self.T.log(self._t(a)))
+
+    def transpose(self, a):
+        return self._n(self.T.transpose(self._t(a)))
+
+    def concat(self, a, b, ax):
+        return self._n(self.T.concat(self._t(a), self._t(b), ax))
+
+    def reshape(self, a, shape):
+        return self._n(self.T.reshape(self._t(a), shape))
+
+    def matmul(self, a, b):
+        return self._n(self.T.matmul(self._t(a), self._t(b)))
+
+    def relu(self, a):
+        return self._n(self.T.relu(self._t(a)))
+
+    def softmax(self, a):
+        return self._n(self.T.softmax(self._t(a)))
+
+    def dense(self, x, w, b, act):
+        return self._n(self.T.dense(self._t(x), self._t(w), self._t(b) if b is not None else None, act))
+
+    def ones(self, shape):
+        return self._n(self.T.ones(shape))
+
+    def zeros(self, shape):
+        return self._n(self.T.zeros(shape))
+
+    def full(self, shape, v):
+        return self._n(self.T.full(shape, v))
+
+    def eye(self, n):
+        return self._n(self.T.eye(n))
+
+    def range(self, start, stop, step):
+        return self._n(self.T.range(start, stop, step))
+
+
+def ulp_distance(a, b):
+    """Distance in float32 ulps; NaN==NaN, equal infinities are 0."""
+    ai = a.view(np.int32).astype(np.int64)
+    bi = b.view(np.int32).astype(np.int64)
+    ai = np.where(ai < 0, np.int64(-(2**31)) - ai, ai)
+    bi = np.where(bi < 0, np.int64(-(2**31)) - bi, bi)
+    d = np.abs(ai - bi)
+    both_nan = np.isnan(a) & np.isnan(b)
+    return np.where(both_nan, 0, d)
+
+
+def assert_close_gemm(got, ref):
+    assert got.shape == ref.shape and got.dtype == ref.dtype
+    if ref.size == 0:
+        return
+    scale = float(np.max(np.abs(ref))) or 1.0
+    err = float(np.max(np.abs(got.astype(np.float64) - ref.astype(np.float64)))) / scale
+    assert err <= GEMM_TOL, f"max|d|/max|ref| = {err:.3e} > {GEMM_TOL}"
+
+
+def compare_outputs(name, got, ref, label):
+    got, ref = np.asarray(got), np.asarray(ref)
+    assert got.shape == ref.shape, f"{label}: shape {got.shape} vs {ref.shape}"
+    assert got.dtype == ref.dtype, f"{label}: dtype {got.dtype} vs {ref.dtype}"
+    if got.tobytes() == ref.tobytes():
+        return 1.0
+    if name in TOLERANCE_CASES:
+        assert_close_gemm(got, ref)
+        return float(np.mean(got == ref))
+    if ref.dtype == np.float64:  # full sums: float64 scalars, summation order differs
+        assert abs(float(got) - float(ref)) <= 1e-12 * max(1.0, abs(float(ref))) + 1e-9, label
+        return 0.0
+    if ref.dtype == np.float32 and name.startswith(ULP_CASES):
+        d = ulp_distance(got, ref)
+        assert d.max() <= 1, f"{label}: {int(d.max())} ulp apart at {np.unravel_index(d.argmax(), d.shape)}"
+        return float(np.mean(d == 0))
+    raise AssertionError(f"{label}: not bit-exact")
+
+
+@pytest.mark.parametrize("name,fn", CASES, ids=[c[0] for c in CASES])
+def test_cuda_matches_oracle_and_golden(name, fn, T, golden):
+    oracle.build(ref=False)
+    got = fn(CudaBackend(T))
+    ref = fn(PortBackend())
+    assert len(got) == len(ref)
+    for i, (g, r) in enumerate(zip(got, ref)):
+        compare_outputs(name, g, r, f"{name}[{i}] vs oracle")
+        compare_outputs(name, g, golden[f"{name}/{i}"], f"{name}[{i}] vs golden")
+
+
+def test_error_behaviour(T):
+    """Same exceptions, same text, as the reference (modules/tensor/runtime.cpp:122-124, 1039-1041)."""
+    import camel_b200
+
+    a = T.from_numpy(np.ones((3, 4), np.float32))
+    z = T.from_numpy(np.zeros((3, 4), np.float32))
+    zi = T.from_numpy(np.zeros((3, 4), np.int64))
+    for bad in (lambda: T.divide(a, z), lambda: T.divide(a, 0), lambda: T.divide(a, zi), lambda: T.divide(1.0, z)):
+        with pytest.raises(camel_b200.CamelTensorError, match="Division by zero") as e:
+            bad()
+        assert e.value.status == camel_b200._lib.ERR_DIV_ZERO
+    with pytest.raises(camel_b200.CamelTensorError, match="log: input must be positive"):
+        T.log(z)
+    with pytest.raises(camel_b200.CamelTensorError, match="matching shapes"):
+        T.add(a, T.from_numpy(np.ones((4, 3), np.float32)))
+    with pytest.raises(camel_b200.CamelTensorError, match="matmul dimension mismatch"):
+        T.matmul(a, a)
+    with pytest.raises(camel_b200.CamelTensorError, match="axis must be 0 or 1"):
+        T.sum(a, 2)
+    # the context is still healthy after the reported errors
+    assert T.sum(T.add(a, a)) == 24.0
+
+
+def _rel_err(got, ref):
+    return float(np.max(np.abs(got.astype(np.float64) - ref.astype(np.float64)))) / float(np.max(np.abs(ref)))
+
+
+def _ref_matmul_f64(a, b):
+    return (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+
+
+@pytest.mark.parametrize("m,k,n", [(512, 512, 512), (384, 1000, 640), (1024, 784, 1024), (2048, 4096, 512)])
+def test_gemm_3xtf32_large(T, m, k, n):
+    """Sizes past what the scalar oracle finishes quickly: numpy float64 matmul rounded once is
+    the same function (the oracle agrees with it to the last bit on the sizes of tests/cases.py
+    up to the summation order, which float64 makes immaterial at 1e-5)."""
+    rng = np.random.default_rng(m + k + n)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    got = T.matmul(T.from_numpy(a), T.from_numpy(b)).numpy()
+    T.check_async()
+    ref = _ref_matmul_f64(a, b)
+    err = _rel_err(got, ref)
+    comp = float(np.max(np.abs(got.astype(np.float64) - ref) / (np.abs(a).astype(np.float64) @ np.abs(b))))
+    print(f"gemm {m}x{k}x{n}: max|d|/max|ref|={err:.3e} componentwise={comp:.3e}")
+    assert err <= GEMM_TOL
+    assert comp <= 1e-5
+
+
+def test_gemm_cfg1_against_oracle(T):
+    """BASELINE config 1: 512^3, U(-1,1), seed 0 - against the scalar oracle itself."""
+    rng = np.random.default_rng(0)
+    a = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
+    b = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
+    ref = oracle.port().matmul(a, b)
+    got = T.matmul(T.from_numpy(a), T.from_numpy(b)).numpy()
+    T.check_async()
+    assert _rel_err(got, ref) <= GEMM_TOL
+
+
+def test_gemm_linearity_property(T):
+    """Size-independent property at a larger size: (A1 + A2) B == A1 B + A2 B within tolerance."""
+    rng = np.random.default_rng(5)
+    m = k = n = 2048
+    a1 = T.from_numpy(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    a2 = T.from_numpy(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    b = T.from_numpy(rng.uniform(-1, 1, (k, n)).astype(np.float32))
+    lhs = T.matmul(T.add(a1, a2), b).numpy()
+    rhs = T.add(T.matmul(a1, b), T.matmul(a2, b)).numpy()
+    T.check_async()
+    assert _rel_err(lhs, rhs) <= 3 * GEMM_TOL
+
+
+def test_gemm_bf16_mode(T):
+    import camel_b200
+    from camel_b200 import _lib
+
+    rng = np.random.default_rng(6)
+    a = rng.uniform(-1, 1, (512, 768)).astype(np.float32)
+    b = rng.uniform(-1, 1, (768, 384)).astype(np.float32)
+    _lib.check(camel_b200.lib.ct_set_precision(_lib.PREC_BF16))
+    try:
+        got = T.matmul(T.from_numpy(a), T.from_numpy(b)).numpy()
+        T.check_async()
+    finally:
+        _lib.check(camel_b200.lib.ct_set_precision(_lib.PREC_3XTF32))
+    assert _rel_err(got, _ref_matmul_f64(a, b)) <= 1e-2
+
+
+def test_mlp_forward_cfg2_slice(T):
+    """BASELINE config 2 on a 512-sample slice: probabilities within tolerance, argmax equal
+    wherever the oracle's top-2 logit gap exceeds the contraction tolerance."""
+    rng = np.random.default_rng(1)
+
+    def kaiming(fan_in, fan_out):
+        lim = np.sqrt(6.0 / fan_in)
+        return rng.uniform(-lim, lim, (fan_in, fan_out)).astype(np.float32)
+
+    w1, w2, w3 = kaiming(784, 1024), kaiming(1024, 1024), kaiming(1024, 10)
+    b1, b2, b3 = (np.zeros(n, np.float32) for n in (1024, 1024, 10))
+    x = np.random.default_rng(2).uniform(0, 1, (512, 784)).astype(np.float32)
+    p = oracle.port()
+    h1 = p.dense(x, w1, b1, 1)
+    h2 = p.dense(h1, w2, b2, 1)
+    logits = p.dense(h2, w3, b3, 0)
+    probs_ref = p.softmax_rows(logits)
+    arg_ref = p.argmax_axis(logits, 1)
+
+    tx = T.from_numpy(x)
+    g1 = T.dense(tx, T.from_numpy(w1), T.from_numpy(b1), "relu")
+    g2 = T.dense(g1, T.from_numpy(w2), T.from_numpy(b2), "relu")
+    probs, arg = T.dense(g2, T.from_numpy(w3), T.from_numpy(b3), "softmax", with_argmax=True)
+    probs, arg = probs.numpy(), arg.numpy()
+    T.check_async()
+    assert np.max(np.abs(probs - probs_ref)) <= 1e-5
+    srt = np.sort(logits, axis=1)
+    gap = srt[:, -1] - srt[:, -2]
+    decided = gap > 1e-4 * np.max(np.abs(logits))
+    assert decided.mean() > 0.95
+    assert np.array_equal(arg[decided], arg_ref[decided])
+    assert arg.dtype == np.int64
+
+
+@pytest.mark.parametrize("n,c,h,w,ko,kk,stride,pad,act", [
+    (2, 3, 9, 11, 5, 3, 1, 1, "relu"),      # direct kernel
+    (1, 1, 28, 28, 32, 3, 1, 1, "relu"),    # first CNN layer: c*kh*kw = 9
+    (3, 32, 28, 28, 64, 3, 1, 1, "relu"),   # second CNN layer
+    (2, 64, 56, 56, 128, 3, 1, 1, "relu"),  # BASELINE config 3 geometry, small batch
+    (2, 16, 20, 20, 48, 5, 2, 2, None),     # stride 2, 5x5
+])
+def test_conv2d(T, n, c, h, w, ko, kk, stride, pad, act):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((ko, c, kk, kk)) * np.sqrt(2.0 / (c * kk * kk))).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, ko).astype(np.float32)
+    ref = oracle.port().conv2d(x, wt, b, stride, pad, 1 if act == "relu" else 0)
+    got = T.conv2d(T.from_numpy(x), T.from_numpy(wt), T.from_numpy(b), stride, pad, act).numpy()
+    T.check_async()
+    assert got.shape == ref.shape
+    assert _rel_err(got, ref) <= GEMM_TOL
+
+
+def test_maxpool2d(T):
+    rng = np.random.default_rng(4)
+    for shape, win in (((3, 5, 28, 28), 2), ((2, 3, 9, 12), 3), ((1, 1, 7, 7), 2)):
+        x = rng.standard_normal(shape).astype(np.float32)
+        ref = oracle.port().maxpool2d(x, win)
+        got = T.maxpool2d(T.from_numpy(x), win).numpy()
+        assert got.tobytes() == ref.tobytes()
+
+
+def test_elementwise_large_roundtrip_properties(T):
+    """Properties that hold at any size, run at 2^26 elements: (a + b) - b == a wherever the sum is
+    exact enough, relu(x) + relu(-x) == |x|, sum of a 0/1 mask equals its popcount."""
+    n = 1 << 26
+    rng = np.random.default_rng(6)
+    x = rng.uniform(-1, 1, n).astype(np.float32)
+    tx = T.from_numpy(x)
+    pos = T.relu(tx)
+    neg = T.relu(T.multiply(tx, -1.0))
+    both = T.add(pos, neg).numpy()
+    assert np.array_equal(both, np.abs(x))
+    mask = T.gt(tx, 0.0)
+    assert T.sum(mask) == float(np.count_nonzero(x > 0))
+    s = T.sum(tx)
+    assert abs(s - float(np.sum(x.astype(np.float64)))) <= 1e-9 * n
