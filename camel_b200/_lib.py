@@ -66,7 +66,8 @@ PROTOTYPES = {
     "ct_dense": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),
     "ct_conv2d": (_int, [_vp, _vp, _vp] + [_i64] * 9 + [_int, _vp]),
     "ct_maxpool2d": (_int, [_vp, _i64, _i64, _i64, _i64, _i64, _vp]),
-    "ct_matmul_host": (_int, [_vp, _vp, _i64, _i64, _i64, _vp]),
+    "ct_matmul_f32_static": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "ct_matmul_host":(_int, [_vp, _vp, _i64, _i64, _i64, _vp]),
     "ct_binary_host": (_int, [_int, _vp, _vp, _u64, _vp]),
 }
 

@@ -574,4 +574,150 @@ ct_status gemm_f32_tc(
     return gemm_planes(st, mode, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, 1, 0, 0);
 }
 
+// ---- matmul without any allocation --------------------------------------------------------
+//
+// Some hosts of this library may not allocate device memory when they call it: a plugin that is
+// invoked while the embedding runtime holds a fixed memory budget, a call made from inside a
+// region where cudaMalloc would synchronise the whole device (another thread's work in flight),
+// or a real-time loop that has to stay free of allocator latency.  For them the operand planes
+// of the 3xTF32 GEMM live in the fixed array below instead of in a growing workspace.  The array
+// is part of the library image: every GPU on which the library is used holds these bytes from
+// the first use until the process exits.
+
+constexpr size_t kStaticScratchBytes = 16u << 20; // 16 MiB: e.g. m = n = k = 1024
+
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticScratchBytes];
+static __device__ __align__(256) uint32_t g_static_flags[FLAG_COUNT];
+
+namespace {
+
+struct StaticState {
+    bool ready       = false;
+    uint8_t *scratch = nullptr; // device address of g_static_scratch on this device
+    uint32_t *flags  = nullptr; // device address of g_static_flags on this device
+    int sm_count     = 0;
+};
+StaticState g_static_state[16];
+std::mutex g_static_mutex;
+
+// In host code the names g_static_scratch / g_static_flags are only handles of the symbols;
+// the addresses kernels can use come from cudaGetSymbolAddress, per device, with that device
+// current.
+ct_status static_state(StaticState **out) {
+    int dev = -1;
+    CT_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16)
+        return fail(CT_ERR_INVALID, "device index %d not supported", dev);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticState *s = &g_static_state[dev];
+    if (!s->ready) {
+        int major = 0;
+        CT_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        if (major != 10)
+            return fail(CT_ERR_NO_DEVICE, "device %d is not sm_100: this library is built for sm_100a only", dev);
+        CT_CUDA(cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, dev));
+        void *p = nullptr;
+        CT_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        s->scratch = static_cast<uint8_t *>(p);
+        CT_CUDA(cudaGetSymbolAddress(&p, g_static_flags));
+        s->flags = static_cast<uint32_t *>(p);
+        s->ready = true;
+    }
+    *out = s;
+    return CT_OK;
+}
+
+template <int BN>
+ct_status launch_static(
+    StaticState *s, const void *a_hi, const void *a_lo, const void *b_hi, const void *b_lo,
+    int64_t m, int64_t n, int64_t kp, float *out) {
+    using C = Cfg<BN, MODE_3X>;
+    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    CT_TRY(make_plane_map(&ma_hi, a_hi, C::kElem, m, kp, BM, 0));
+    CT_TRY(make_plane_map(&ma_lo, a_lo, C::kElem, m, kp, BM, 0));
+    CT_TRY(make_plane_map(&mb_hi, b_hi, C::kElem, n, kp, BN, 1));
+    CT_TRY(make_plane_map(&mb_lo, b_lo, C::kElem, n, kp, BN, 1));
+    GemmParams p;
+    p.m                = m;
+    p.n                = n;
+    p.num_k_blocks     = (int)(kp / C::kBlockK);
+    p.chunk_blocks     = 8;
+    p.tiles_m          = (int)((m + BM - 1) / BM);
+    p.tiles_n          = (int)((n + BN - 1) / BN);
+    p.bias             = nullptr;
+    p.act              = CT_ACT_NONE;
+    p.out              = out;
+    p.ldc              = n;
+    p.batch            = 1;
+    p.out_batch_stride = 0;
+    p.bias_per_row     = 0;
+    p.flags            = s->flags;
+    CT_CUDA(cudaFuncSetAttribute(
+        gemm_tc_kernel<BN, MODE_3X>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    gemm_tc_kernel<BN, MODE_3X><<<(unsigned)(p.tiles_m * p.tiles_n), C::kThreads, C::kSmemBytes, stream()>>>(
+        ma_hi, ma_lo, mb_hi, mb_lo, p);
+    CT_LAUNCH_CHECK("gemm_tc(static scratch)");
+    return CT_OK;
+}
+
+} // namespace
 } // namespace ct
+
+extern "C" ct_status ct_matmul_f32_static(
+    const float *a_dev, const float *b_dev, int64_t m, int64_t k, int64_t n, float *out_dev,
+    uint32_t *status_dev) {
+    using namespace ct;
+    if (m < 0 || k < 0 || n < 0)
+        return fail(CT_ERR_INVALID, "matmul: negative dimension");
+    if (m == 0 || n == 0) {
+        if (status_dev)
+            CT_CUDA(cudaMemsetAsync(status_dev, 0, sizeof(uint32_t), stream()));
+        return CT_OK;
+    }
+    if (!out_dev || (k > 0 && (!a_dev || !b_dev)))
+        return fail(CT_ERR_INVALID, "matmul: null pointer");
+    const int kblock = ROW_B / 4;
+    int64_t kp       = (k + kblock - 1) / kblock * kblock;
+    if (kp == 0)
+        kp = kblock;
+    auto align_up  = [](size_t v) { return (v + 1023) & ~(size_t)1023; };
+    if (m > (1 << 20) || n > (1 << 20) || kp > (1 << 20))
+        return fail(CT_ERR_TOO_LARGE, "ct_matmul_f32_static: dimension too large for the %zu-byte static scratch",
+                    kStaticScratchBytes);
+    size_t a_plane = align_up((size_t)m * kp * 4);
+    size_t b_plane = align_up((size_t)n * kp * 4);
+    if (2 * (a_plane + b_plane) > kStaticScratchBytes)
+        return fail(
+            CT_ERR_TOO_LARGE,
+            "ct_matmul_f32_static: operand planes need %zu bytes (8*(m+n)*roundup(k,32)), the static scratch "
+            "holds %zu; use ct_matmul for this size",
+            2 * (a_plane + b_plane), kStaticScratchBytes);
+    StaticState *s;
+    CT_TRY(static_state(&s));
+    // Every byte of the planes that the kernel reads is rewritten by the pre-pass below (padding
+    // included), so nothing of an earlier call is reused; only the error words start from zero.
+    CT_CUDA(cudaMemsetAsync(s->flags, 0, FLAG_COUNT * sizeof(uint32_t), stream()));
+    uint8_t *ws = s->scratch;
+    void *a_hi = ws, *a_lo = ws + a_plane, *b_hi = ws + 2 * a_plane, *b_lo = ws + 2 * a_plane + b_plane;
+    {
+        int64_t total  = m * kp;
+        int64_t blocks = (total + 255) / 256;
+        int64_t cap    = (int64_t)s->sm_count * 32;
+        if (blocks > cap)
+            blocks = cap;
+        split_rows_kernel<MODE_3X><<<(unsigned)blocks, 256, 0, stream()>>>(a_dev, m, k, kp, a_hi, a_lo);
+        CT_LAUNCH_CHECK("split_rows(static scratch)");
+        dim3 grid((unsigned)((n + 31) / 32), (unsigned)(kp / 32));
+        split_transpose_kernel<MODE_3X><<<grid, 256, 0, stream()>>>(b_dev, k, n, kp, b_hi, b_lo);
+        CT_LAUNCH_CHECK("split_transpose(static scratch)");
+    }
+    int64_t tiles256 = ((m + BM - 1) / BM) * ((n + 255) / 256);
+    if (n > 128 && tiles256 >= s->sm_count / 2)
+        CT_TRY(launch_static<256>(s, a_hi, a_lo, b_hi, b_lo, m, n, kp, out_dev));
+    else
+        CT_TRY(launch_static<128>(s, a_hi, a_lo, b_hi, b_lo, m, n, kp, out_dev));
+    if (status_dev) // stream-ordered copy of the kernel's error word into the caller's buffer
+        CT_CUDA(cudaMemcpyAsync(
+            status_dev, s->flags + FLAG_TIMEOUT, sizeof(uint32_t), cudaMemcpyDeviceToDevice, stream()));
+    return CT_OK;
+}

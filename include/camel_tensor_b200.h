@@ -200,6 +200,26 @@ ct_status ct_maxpool2d(
     const float *x_dev, int64_t n, int64_t c, int64_t h, int64_t w, int64_t window,
     float *out_dev);
 
+/* float32 matmul for callers that must not allocate.  No counterpart in the reference: it is
+ * ct_matmul (float32 x float32, 3xTF32) with the kernel's operand planes held in a fixed
+ * 16 MiB array inside the library instead of a workspace that grows on demand.  It is meant for
+ * a host that calls into the library where device allocation is off limits - under a fixed
+ * memory budget, while other threads have work in flight that a cudaMalloc would stall, or in
+ * a latency-bound loop - and it calls no cudaMalloc / cudaFree / allocating routine itself.
+ *  - Limit: 8 * (m + n) * roundup(k, 32) bytes (planes rounded up to 1 KiB each) must fit in
+ *    16 MiB, e.g. m = n = k = 1024; larger shapes return CT_ERR_TOO_LARGE and a message.
+ *  - The array is shared by all calls and keeps the previous call's bytes; each call rewrites
+ *    everything it later reads.  Calls that overlap on the GPU (different streams or threads)
+ *    race on it: serialise them.
+ *  - The first call on a device looks up the array's device address (once per device); make
+ *    that first call outside any stream capture.
+ *  - Asynchronous like ct_matmul.  status_dev (may be NULL) is a device word that receives 0,
+ *    or a non-zero value if a bounded wait inside the kernel ran out (output then undefined);
+ *    it is written in stream order, read it after synchronising. */
+ct_status ct_matmul_f32_static(
+    const float *a_dev, const float *b_dev, int64_t m, int64_t k, int64_t n, float *out_dev,
+    uint32_t *status_dev);
+
 /* ---- host-buffer forms: what an operator body calls at a graph boundary, where operands
  *      live in TensorObject host storage.  Copies in, computes, copies out, synchronises. ---- */
 
