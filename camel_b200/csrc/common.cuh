@@ -95,11 +95,25 @@ inline bool valid_dtype(int dt) { return dt == CT_F32 || dt == CT_I64 || dt == C
 ct_status gemm_f32_tc(
     DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
     int64_t n, int act, float *out);
-// mode: 0 = 3xTF32 (float32 hi/lo planes), 1 = bf16 (one plane).
+// Geometry of a stride-1 convolution run as an implicit GEMM over NHWC input planes.
+struct ConvGeom {
+    int c_pad;  // channels rounded up to the k-block
+    int h, w;   // input height / width
+    int ho, wo; // output height / width
+    int kh, kw, pad;
+    int th;     // output rows per tile (th * wo <= 256, multiple of 16)
+};
+
+// mode: 0 = 3xTF32 (float32 hi/lo planes), 1 = bf16 (one plane).  With conv != nullptr the B
+// planes are NHWC input planes [batch][h][w][c_pad] and n = ho*wo output pixels per image.
 ct_status gemm_planes(
     DeviceState *st, int mode, const void *a_hi, const void *a_lo, const void *b_hi,
     const void *b_lo, int64_t m, int64_t n, int64_t kp, const float *bias, int act, float *out,
-    int batch, int64_t out_batch_stride, int bias_per_row);
+    int batch, int64_t out_batch_stride, int bias_per_row, const ConvGeom *conv = nullptr);
+// x [batch][c][h*w] float32 -> NHWC planes [batch][h*w][c_pad] (transpose + split per image)
+ct_status nhwc_planes(
+    DeviceState *st, int mode, const float *x, int64_t batch, int64_t c, int64_t hw, int64_t c_pad,
+    void *hi, void *lo);
 ct_status split_rows_planes(
     DeviceState *st, int mode, const float *in, int64_t rows, int64_t k, int64_t kp, void *hi,
     void *lo);

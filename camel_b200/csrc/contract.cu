@@ -5,6 +5,8 @@
 
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 namespace ct {
 namespace {
 
@@ -46,6 +48,40 @@ __global__ void __launch_bounds__(256) im2col_planes_kernel(
             static_cast<__nv_bfloat16 *>(p_hi)[i] = __float2bfloat16_rn(v);
         }
     }
+}
+
+// Weights [ko][c][kh][kw] -> A-operand planes [ko][taps * c_pad] with k = (r*kw + s) * c_pad + ic:
+// tap-major, so that one k-block is 32 channels of one filter tap (what the implicit-GEMM
+// producer fetches from the NHWC input with one shifted TMA box).
+template <int MODE>
+__global__ void __launch_bounds__(256) conv_weight_planes_kernel(
+    const float *__restrict__ w, int64_t ko, int64_t c, int64_t taps, int64_t c_pad,
+    void *__restrict__ p_hi, void *__restrict__ p_lo) {
+    int64_t kp    = taps * c_pad;
+    int64_t total = ko * kp;
+    int64_t step  = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+        int64_t o = i / kp, kk = i - o * kp;
+        int64_t rs = kk / c_pad, ic = kk - rs * c_pad;
+        float v = ic < c ? w[(o * c + ic) * taps + rs] : 0.0f;
+        if (MODE == 0) {
+            float hi, lo;
+            split_tf32(v, hi, lo);
+            static_cast<float *>(p_hi)[i] = hi;
+            static_cast<float *>(p_lo)[i] = lo;
+        } else {
+            static_cast<__nv_bfloat16 *>(p_hi)[i] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+// Output rows per implicit-GEMM tile: the largest th <= ho with th*wo <= 256 and th*wo a
+// multiple of 16 (the MMA's N granularity); 0 when there is none.
+int conv_tile_rows(int64_t ho, int64_t wo) {
+    for (int64_t th = ho < 256 ? ho : 256; th >= 1; --th)
+        if (th * wo <= 256 && (th * wo) % 16 == 0)
+            return (int)th;
+    return 0;
 }
 
 // Small problems: one thread per output, float64 accumulation in (c,r,s) order.
@@ -246,8 +282,46 @@ ct_status ct_conv2d(
     const int elem   = mode == 0 ? 4 : 2;
     const int planes = mode == 0 ? 2 : 1;
     const int kblock = 128 / elem;
-    int64_t kp       = (kdim + kblock - 1) / kblock * kblock;
     auto align_up    = [](size_t v) { return (v + 1023) & ~(size_t)1023; };
+
+    // Implicit GEMM: stride 1, enough channels to fill k-blocks, and a row tile that the MMA
+    // accepts.  The input is rewritten once as NHWC hi/lo planes (12 B per input element); the
+    // patch matrix is never materialised - each k-block is one shifted 4-D TMA box.
+    const int th = (stride == 1 && c >= 16 && wo <= 256 && wd <= 0x7fffffff && h <= 0x7fffffff)
+                       ? conv_tile_rows(ho, wo) : 0;
+    if (th > 0 && !getenv("CAMEL_TENSOR_CONV_IM2COL")) {
+        int64_t c_pad  = (c + kblock - 1) / kblock * kblock;
+        int64_t taps   = kh * kw;
+        int64_t kp_i   = taps * c_pad;
+        size_t w_plane = align_up((size_t)ko * kp_i * elem);
+        size_t x_plane = align_up((size_t)n * h * wd * c_pad * elem);
+        CT_TRY(ensure_ws(&st->gemm_ws, &st->gemm_ws_bytes, planes * (w_plane + x_plane)));
+        uint8_t *ws = static_cast<uint8_t *>(st->gemm_ws);
+        void *w_hi = ws, *w_lo = ws + w_plane;
+        void *x_hi = ws + planes * w_plane, *x_lo = ws + planes * w_plane + x_plane;
+        CT_TRY(clear_flags(st));
+        {
+            ProfScope prof("conv_prepass");
+            int64_t wtotal = ko * kp_i;
+            if (mode == 0)
+                conv_weight_planes_kernel<0><<<capped_blocks(st, wtotal, 8), 256, 0, stream()>>>(
+                    w, ko, c, taps, c_pad, w_hi, w_lo);
+            else
+                conv_weight_planes_kernel<1><<<capped_blocks(st, wtotal, 8), 256, 0, stream()>>>(
+                    w, ko, c, taps, c_pad, w_hi, w_lo);
+            CT_LAUNCH_CHECK("conv_weight_planes");
+            CT_TRY(nhwc_planes(st, mode, x, n, c, h * wd, c_pad, x_hi, x_lo));
+        }
+        ConvGeom g;
+        g.c_pad = (int)c_pad;
+        g.h = (int)h, g.w = (int)wd, g.ho = (int)ho, g.wo = (int)wo;
+        g.kh = (int)kh, g.kw = (int)kw, g.pad = (int)pad, g.th = th;
+        return gemm_planes(
+            st, mode, w_hi, w_lo, x_hi, x_lo, ko, pix, kp_i, bias, act, out, (int)n, ko * pix,
+            bias ? 1 : 0, &g);
+    }
+
+    int64_t kp       = (kdim + kblock - 1) / kblock * kblock;
     size_t w_plane   = align_up((size_t)ko * kp * elem);
     size_t p_plane   = align_up((size_t)n * pix * kp * elem);
     CT_TRY(ensure_ws(&st->gemm_ws, &st->gemm_ws_bytes, planes * (w_plane + p_plane)));

@@ -132,6 +132,125 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(
         argmax[row] = best_idx;
 }
 
+// Finishes one output row held as per-lane partial sums: butterfly reduction, then bias,
+// activation, and (for softmax) the row softmax / argmax across the first n lanes.
+template <int N_MAX>
+__device__ __forceinline__ void skinny_finish_row(
+    double (&acc)[N_MAX], const float *__restrict__ bias, int64_t row, int n, int act, int lane,
+    float *__restrict__ out, int64_t *__restrict__ argmax) {
+#pragma unroll
+    for (int j = 0; j < N_MAX; ++j) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    }
+    float logit = 0.0f;
+#pragma unroll
+    for (int j = 0; j < N_MAX; ++j) {
+        if (j == lane && j < n) {
+            double v = acc[j];
+            if (bias)
+                v += (double)bias[j]; // the bias is the last term of the float64 sum
+            logit = (float)v;
+        }
+    }
+    bool live = lane < n;
+    if (act == CT_ACT_RELU)
+        logit = __fmul_rn(logit, logit > 0.0f ? 1.0f : 0.0f);
+    if (act != CT_ACT_SOFTMAX) {
+        if (live)
+            out[row * n + lane] = logit;
+        return;
+    }
+    float best   = __shfl_sync(0xffffffffu, logit, 0);
+    int best_idx = 0;
+    for (int j = 1; j < n; ++j) {
+        float v = __shfl_sync(0xffffffffu, logit, j);
+        if (v > best) {
+            best     = v;
+            best_idx = j;
+        }
+    }
+    float e  = live ? (float)exp((double)__fsub_rn(logit, best)) : 0.0f;
+    double s = 0.0;
+    for (int j = 0; j < n; ++j)
+        s += (double)__shfl_sync(0xffffffffu, e, j);
+    float d = (float)s;
+    if (live)
+        out[row * n + lane] = __fdiv_rn(e, d);
+    if (argmax && lane == 0)
+        argmax[row] = best_idx;
+}
+
+// Same contraction with the whole weight matrix [k][n] staged once per block in shared memory
+// (k*n*4 bytes <= 200 KB): the weight reads that made the kernel above latency-bound become
+// shared-memory reads, the activations stream in with 128-bit loads, and a persistent grid
+// of 2 blocks per SM walks the rows.
+template <int N_MAX>
+__global__ void __launch_bounds__(256) gemm_skinny_smem_kernel(
+    const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+    int64_t m, int64_t k, int n, int act, float *__restrict__ out, int64_t *__restrict__ argmax) {
+    extern __shared__ __align__(16) float w_s[];
+    // staged transposed, [n][k]: lanes then read consecutive k of one column, conflict-free
+    for (int64_t i = threadIdx.x; i < k * n; i += 256) {
+        int64_t kk = i / n, j = i - kk * n;
+        w_s[j * k + kk] = w[i];
+    }
+    __syncthreads();
+    const int lane     = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int64_t step = (int64_t)gridDim.x * 8;
+    const bool vec     = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    for (int64_t row = warp; row < m; row += step) {
+        const float *xr = x + row * k;
+        double acc[N_MAX];
+#pragma unroll
+        for (int j = 0; j < N_MAX; ++j)
+            acc[j] = 0.0;
+        if (vec) {
+            for (int64_t kk = (int64_t)lane * 4; kk < k; kk += 128) {
+                float4 q = __ldcs(reinterpret_cast<const float4 *>(xr + kk));
+                double x0 = (double)q.x, x1 = (double)q.y, x2 = (double)q.z, x3 = (double)q.w;
+#pragma unroll
+                for (int j = 0; j < N_MAX; ++j)
+                    if (j < n) {
+                        float4 wq = *reinterpret_cast<const float4 *>(w_s + (int64_t)j * k + kk);
+                        acc[j] += x0 * (double)wq.x;
+                        acc[j] += x1 * (double)wq.y;
+                        acc[j] += x2 * (double)wq.z;
+                        acc[j] += x3 * (double)wq.w;
+                    }
+            }
+        } else {
+            for (int64_t kk = lane; kk < k; kk += 32) {
+                double xd = (double)xr[kk];
+#pragma unroll
+                for (int j = 0; j < N_MAX; ++j)
+                    if (j < n)
+                        acc[j] += xd * (double)w_s[(int64_t)j * k + kk];
+            }
+        }
+        skinny_finish_row<N_MAX>(acc, bias, row, n, act, lane, out, argmax);
+    }
+}
+
+template <int N_MAX>
+ct_status launch_skinny_smem(
+    DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k, int n,
+    int act, float *out, int64_t *argmax) {
+    size_t smem = (size_t)k * n * sizeof(float);
+    if (smem > 48 * 1024)
+        CT_CUDA(cudaFuncSetAttribute(
+            gemm_skinny_smem_kernel<N_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    int64_t blocks = (m + 7) / 8;
+    int64_t cap    = (int64_t)st->sm_count * (smem > 100 * 1024 ? 1 : 2);
+    if (blocks > cap)
+        blocks = cap;
+    gemm_skinny_smem_kernel<N_MAX><<<(unsigned)blocks, 256, smem, stream()>>>(a, b, bias, m, k, n, act, out, argmax);
+    CT_LAUNCH_CHECK("gemm_skinny_smem");
+    return CT_OK;
+}
+
 } // namespace
 
 ct_status matmul_generic(
@@ -150,13 +269,19 @@ ct_status matmul_generic(
 ct_status gemm_f32_skinny(
     DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
     int64_t n, int act, float *out, int64_t *argmax) {
-    (void)st;
     if (m == 0 || n == 0)
         return CT_OK;
     if (n > 32)
         return fail(CT_ERR_INVALID, "skinny GEMM takes at most 32 output columns");
     unsigned blocks = (unsigned)((m + 7) / 8);
     ProfScope prof("gemm_skinny");
+    if ((size_t)k * n * sizeof(float) <= 200 * 1024 && k > 0) {
+        if (n <= 8)
+            return launch_skinny_smem<8>(st, a, b, bias, m, k, (int)n, act, out, argmax);
+        if (n <= 16)
+            return launch_skinny_smem<16>(st, a, b, bias, m, k, (int)n, act, out, argmax);
+        return launch_skinny_smem<32>(st, a, b, bias, m, k, (int)n, act, out, argmax);
+    }
     if (n <= 8)
         gemm_skinny_kernel<8><<<blocks, 256, 0, stream()>>>(a, b, bias, m, k, (int)n, act, out, argmax);
     else if (n <= 16)

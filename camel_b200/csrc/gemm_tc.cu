@@ -70,6 +70,14 @@ struct GemmParams {
     int64_t out_batch_stride; // elements between consecutive outputs of the batch
     int bias_per_row;         // bias indexed by output row (conv: one per output channel)
     uint32_t *flags;
+    int tile_n;               // output columns per tile: BN, or th*wo for the implicit-GEMM conv
+    // implicit-GEMM convolution (conv != 0): the B operand is the NHWC input itself, fetched by
+    // 4-D TMA boxes shifted by the filter tap, instead of a materialised patch matrix
+    int conv;
+    int conv_cblocks; // channel blocks of 32 per filter tap
+    int conv_kw;      // filter width (taps are numbered r * kw + s)
+    int conv_pad;
+    int conv_th;      // output rows per tile
 };
 
 // ---- operand pre-pass ---------------------------------------------------------------------
@@ -95,16 +103,58 @@ __global__ void __launch_bounds__(256) split_rows_kernel(
     }
 }
 
+// Same result, four consecutive k per thread: 128-bit loads and stores, rows on blockIdx.y, no
+// integer division.  kp is a multiple of 32 and the planes are 1 KiB aligned.
+template <int MODE>
+__global__ void __launch_bounds__(256) split_rows_vec_kernel(
+    const float *__restrict__ in, int64_t rows, int64_t k, int64_t kp, void *__restrict__ p_hi,
+    void *__restrict__ p_lo, int in_vec_ok) {
+    const int64_t c = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
+    if (c >= kp)
+        return;
+    for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+        const float *src = in + r * k + c;
+        float v[4];
+        if (in_vec_ok && c + 3 < k) {
+            float4 q = __ldcs(reinterpret_cast<const float4 *>(src));
+            v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+        } else {
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+                v[t] = c + t < k ? src[t] : 0.0f;
+        }
+        const int64_t at = r * kp + c;
+        if (MODE == MODE_3X) {
+            float hi[4], lo[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+                split_tf32(v[t], hi[t], lo[t]);
+            *reinterpret_cast<float4 *>(static_cast<float *>(p_hi) + at) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<float4 *>(static_cast<float *>(p_lo) + at) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+        } else {
+            __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
+            __nv_bfloat162 b = __floats2bfloat162_rn(v[2], v[3]);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t *>(&a);
+            packed.y = *reinterpret_cast<uint32_t *>(&b);
+            *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(p_hi) + at) = packed;
+        }
+    }
+}
+
 // in [k][n] row-major  ->  transposed planes [n][kp]
 template <int MODE>
 __global__ void __launch_bounds__(256) split_transpose_kernel(
     const float *__restrict__ in, int64_t k, int64_t n, int64_t kp, void *__restrict__ p_hi,
-    void *__restrict__ p_lo) {
+    void *__restrict__ p_lo, int64_t in_batch_stride = 0, int64_t out_batch_stride = 0) {
     __shared__ float tile[32][33];
     int tx     = threadIdx.x & 31;
     int ty     = threadIdx.x >> 5;
     int64_t n0 = (int64_t)blockIdx.x * 32;
     int64_t k0 = (int64_t)blockIdx.y * 32;
+    // blockIdx.z walks a batch of [k][n] matrices (conv: one [c][h*w] image each)
+    in += (int64_t)blockIdx.z * in_batch_stride;
+    const int64_t out_base = (int64_t)blockIdx.z * out_batch_stride;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         int64_t kk = k0 + ty + j * 8, nn = n0 + tx;
@@ -116,7 +166,7 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(
         int64_t nn = n0 + ty + j * 8, kk = k0 + tx;
         if (nn < n && kk < kp) {
             float v     = tile[tx][ty + j * 8];
-            int64_t at  = nn * kp + kk;
+            int64_t at  = out_base + nn * kp + kk;
             if (MODE == MODE_3X) {
                 float hi, lo;
                 split_tf32(v, hi, lo);
@@ -220,7 +270,7 @@ __global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
                     break;
                 uint32_t full = smem_u32(&bar_full[s]);
                 uint32_t dst  = stage_addr(s);
-                mbar_expect_tx(full, C::kStageBytes);
+                mbar_expect_tx(full, (uint32_t)(C::kPlanes * (C::kABytes + p.tile_n * ROW_B)));
                 int32_t kc = kb * C::kBlockK;
                 tma_load_2d(dst, &map_a_hi, full, kc, tm * BM);
                 dst += C::kABytes;
@@ -228,10 +278,22 @@ __global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
                     tma_load_2d(dst, &map_a_lo, full, kc, tm * BM);
                     dst += C::kABytes;
                 }
-                tma_load_3d(dst, &map_b_hi, full, kc, tn * BN, tz);
-                dst += C::kBBytes;
-                if (MODE == MODE_3X)
-                    tma_load_3d(dst, &map_b_lo, full, kc, tn * BN, tz);
+                if (p.conv) {
+                    // k-block = (filter tap rs, channel block cb); the box covers th output rows
+                    // by wo columns of 32 channels, shifted by the tap; the halo reads as zero
+                    int rs = kb / p.conv_cblocks, cb = kb - rs * p.conv_cblocks;
+                    int r = rs / p.conv_kw, sx = rs - r * p.conv_kw;
+                    int32_t c0 = cb * C::kBlockK, w0 = sx - p.conv_pad, h0 = tn * p.conv_th + r - p.conv_pad;
+                    tma_load_4d(dst, &map_b_hi, full, c0, w0, h0, tz);
+                    dst += C::kBBytes;
+                    if (MODE == MODE_3X)
+                        tma_load_4d(dst, &map_b_lo, full, c0, w0, h0, tz);
+                } else {
+                    tma_load_3d(dst, &map_b_hi, full, kc, tn * BN, tz);
+                    dst += C::kBBytes;
+                    if (MODE == MODE_3X)
+                        tma_load_3d(dst, &map_b_lo, full, kc, tn * BN, tz);
+                }
                 issued = kb + 1;
             }
             if (*abort_flag) {
@@ -249,6 +311,8 @@ __global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
     } else if (warp == 1) {
         // ===== MMA issuer =====
         if (lane == 0) {
+            // MMA shape 128 x tile_n x (32 bytes of k): tile_n == BN except for conv tiles
+            const uint32_t idesc = make_idesc(MODE == MODE_3X ? 2u : 1u, BM, (uint32_t)p.tile_n);
             int kb = 0;
             bool ok = true;
             for (int c = 0; c < num_chunks && ok; ++c) {
@@ -280,11 +344,11 @@ __global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
                         uint64_t adv = (uint64_t)(kk * 32 >> 4);
                         if (MODE == MODE_3X) {
                             // small terms first, then the leading term
-                            mma_tf32(d_tmem, da_lo + adv, db_hi + adv, C::kIdesc, first ? 0u : 1u);
-                            mma_tf32(d_tmem, da_hi + adv, db_lo + adv, C::kIdesc, 1u);
-                            mma_tf32(d_tmem, da_hi + adv, db_hi + adv, C::kIdesc, 1u);
+                            mma_tf32(d_tmem, da_lo + adv, db_hi + adv, idesc,first ? 0u : 1u);
+                            mma_tf32(d_tmem, da_hi + adv, db_lo + adv, idesc,1u);
+                            mma_tf32(d_tmem, da_hi + adv, db_hi + adv, idesc,1u);
                         } else {
-                            mma_f16(d_tmem, da_hi + adv, db_hi + adv, C::kIdesc, first ? 0u : 1u);
+                            mma_f16(d_tmem, da_hi + adv, db_hi + adv, idesc,first ? 0u : 1u);
                         }
                         first = false;
                     }
@@ -335,7 +399,8 @@ __global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
         }
         if (ok) {
             int64_t row  = (int64_t)tm * BM + quarter * 32 + lane;
-            int64_t col0 = (int64_t)tn * BN + half * 128;
+            int64_t col0 = (int64_t)tn * p.tile_n + half * 128;
+            int64_t lim  = (int64_t)(tn + 1) * p.tile_n < p.n ? (int64_t)(tn + 1) * p.tile_n : p.n;
             if (row < p.m) {
                 float *dst      = p.out + (int64_t)tz * p.out_batch_stride + row * p.ldc;
                 const float rb  = (p.bias && p.bias_per_row) ? p.bias[row] : 0.0f;
@@ -349,18 +414,18 @@ __global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
                         float x = acc[j + q];
                         if (p.bias_per_row)
                             x = __fadd_rn(x, rb);
-                        else if (p.bias && col + q < p.n)
+                        else if (p.bias && col + q < lim)
                             x = __fadd_rn(x, p.bias[col + q]);
                         if (p.act == CT_ACT_RELU)
                             x = __fmul_rn(x, x > 0.0f ? 1.0f : 0.0f);
                         v[q] = x;
                     }
-                    if (vec4 && col + 3 < p.n) {
+                    if (vec4 && col + 3 < lim) {
                         *reinterpret_cast<float4 *>(dst + col) = make_float4(v[0], v[1], v[2], v[3]);
                     } else {
 #pragma unroll
                         for (int q = 0; q < 4; ++q)
-                            if (col + q < p.n)
+                            if (col + q < lim)
                                 dst[col + q] = v[q];
                     }
                 }
@@ -431,6 +496,28 @@ ct_status make_plane_map(
     return CT_OK;
 }
 
+// Tensor map over NHWC input planes [batch][h][w][c_pad] (channels contiguous); box = 32 channels
+// (one k-block) x wo columns x th rows of one image, 128-byte swizzle.  Written to shared memory
+// the box is th*wo rows of 128 bytes: the K-major B tile of th*wo output pixels.
+ct_status make_conv_map(CUtensorMap *map, const void *base, int elem_bytes, const ConvGeom &g, int batch) {
+    EncodeTiledFn fn;
+    CT_TRY(encode_fn(&fn));
+    cuuint64_t row        = (cuuint64_t)g.c_pad * (cuuint64_t)elem_bytes;
+    cuuint64_t dims[4]    = {(cuuint64_t)g.c_pad, (cuuint64_t)g.w, (cuuint64_t)g.h, (cuuint64_t)batch};
+    cuuint64_t strides[3] = {row, row * (cuuint64_t)g.w, row * (cuuint64_t)g.w * (cuuint64_t)g.h};
+    cuuint32_t box[4]     = {(cuuint32_t)(ROW_B / elem_bytes), (cuuint32_t)g.wo, (cuuint32_t)g.th, 1};
+    cuuint32_t estr[4]    = {1, 1, 1, 1};
+    CUtensorMapDataType dt =
+        elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    CUresult r = fn(
+        map, dt, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled (conv) failed with code %d", (int)r);
+    return CT_OK;
+}
+
 int chunk_blocks_setting() {
     static int v = -1;
     if (v < 0) {
@@ -445,14 +532,20 @@ template <int BN, int MODE>
 ct_status launch_gemm(
     DeviceState *st, const void *a_hi, const void *a_lo, const void *b_hi, const void *b_lo,
     int64_t m, int64_t n, int64_t kp, const float *bias, int act, float *out, int batch,
-    int64_t out_batch_stride, int bias_per_row) {
+    int64_t out_batch_stride, int bias_per_row, const ConvGeom *cg) {
     using C = Cfg<BN, MODE>;
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     CT_TRY(make_plane_map(&ma_hi, a_hi, C::kElem, m, kp, BM, 0));
-    CT_TRY(make_plane_map(&mb_hi, b_hi, C::kElem, n, kp, BN, batch));
+    if (cg)
+        CT_TRY(make_conv_map(&mb_hi, b_hi, C::kElem, *cg, batch));
+    else
+        CT_TRY(make_plane_map(&mb_hi, b_hi, C::kElem, n, kp, BN, batch));
     if (MODE == MODE_3X) {
         CT_TRY(make_plane_map(&ma_lo, a_lo, C::kElem, m, kp, BM, 0));
-        CT_TRY(make_plane_map(&mb_lo, b_lo, C::kElem, n, kp, BN, batch));
+        if (cg)
+            CT_TRY(make_conv_map(&mb_lo, b_lo, C::kElem, *cg, batch));
+        else
+            CT_TRY(make_plane_map(&mb_lo, b_lo, C::kElem, n, kp, BN, batch));
     } else {
         ma_lo = ma_hi;
         mb_lo = mb_hi;
@@ -472,6 +565,20 @@ ct_status launch_gemm(
     p.out_batch_stride = out_batch_stride;
     p.bias_per_row = bias_per_row;
     p.flags        = st->flags_dev;
+    p.tile_n       = BN;
+    p.conv         = 0;
+    p.conv_cblocks = p.conv_kw = p.conv_pad = p.conv_th = 0;
+    if (cg) {
+        p.tile_n       = cg->th * cg->wo;
+        p.tiles_n      = (cg->ho + cg->th - 1) / cg->th;
+        p.conv         = 1;
+        p.conv_cblocks = cg->c_pad / C::kBlockK;
+        p.conv_kw      = cg->kw;
+        p.conv_pad     = cg->pad;
+        p.conv_th      = cg->th;
+        if (p.tile_n > BN || (p.tile_n & 15) != 0)
+            return fail(CT_ERR_INVALID, "conv2d: internal tile shape %d not usable", p.tile_n);
+    }
     int64_t tiles  = (int64_t)p.tiles_m * p.tiles_n * batch;
     if (tiles > 0x7fffffffll)
         return fail(CT_ERR_TOO_LARGE, "gemm: too many tiles");
@@ -494,24 +601,37 @@ ct_status launch_gemm(
 ct_status gemm_planes(
     DeviceState *st, int mode, const void *a_hi, const void *a_lo, const void *b_hi,
     const void *b_lo, int64_t m, int64_t n, int64_t kp, const float *bias, int act, float *out,
-    int batch, int64_t out_batch_stride, int bias_per_row) {
+    int batch, int64_t out_batch_stride, int bias_per_row, const ConvGeom *conv) {
     // 128 x 256 tiles when they fill the machine, 128 x 128 otherwise
     int64_t tiles256 = ((m + BM - 1) / BM) * ((n + 255) / 256) * batch;
     bool wide        = n > 128 && tiles256 >= st->sm_count / 2;
     if (getenv("CAMEL_TENSOR_BN"))
         wide = atoi(getenv("CAMEL_TENSOR_BN")) == 256;
-    if (mode == MODE_3X) {
-        if (wide)
-            return launch_gemm<256, MODE_3X>(
-                st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row);
-        return launch_gemm<128, MODE_3X>(
-            st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row);
-    }
-    if (wide)
-        return launch_gemm<256, MODE_BF>(
-            st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row);
-    return launch_gemm<128, MODE_BF>(
-        st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row);
+    if (conv)
+        wide = conv->th * conv->wo > 128;
+#define CT_GEMM_ARGS st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row, conv
+    if (mode == MODE_3X)
+        return wide ? launch_gemm<256, MODE_3X>(CT_GEMM_ARGS) : launch_gemm<128, MODE_3X>(CT_GEMM_ARGS);
+    return wide ? launch_gemm<256, MODE_BF>(CT_GEMM_ARGS) : launch_gemm<128, MODE_BF>(CT_GEMM_ARGS);
+#undef CT_GEMM_ARGS
+}
+
+ct_status nhwc_planes(
+    DeviceState *st, int mode, const float *x, int64_t batch, int64_t c, int64_t hw, int64_t c_pad,
+    void *hi, void *lo) {
+    (void)st;
+    if (batch == 0 || hw == 0)
+        return CT_OK;
+    if (batch > 65535 || c_pad / 32 > 65535)
+        return fail(CT_ERR_TOO_LARGE, "conv2d: batch or channel count too large for the layout pre-pass");
+    // per image: [c][hw] -> [hw][c_pad], i.e. the B-operand pre-pass of the GEMM with k = c, n = hw
+    dim3 grid((unsigned)((hw + 31) / 32), (unsigned)(c_pad / 32), (unsigned)batch);
+    if (mode == MODE_3X)
+        split_transpose_kernel<MODE_3X><<<grid, 256, 0, stream()>>>(x, c, hw, c_pad, hi, lo, c * hw, hw * c_pad);
+    else
+        split_transpose_kernel<MODE_BF><<<grid, 256, 0, stream()>>>(x, c, hw, c_pad, hi, lo, c * hw, hw * c_pad);
+    CT_LAUNCH_CHECK("nhwc_planes");
+    return CT_OK;
 }
 
 ct_status split_rows_planes(
@@ -519,14 +639,13 @@ ct_status split_rows_planes(
     int64_t total  = rows * kp;
     if (total == 0)
         return CT_OK;
-    int64_t blocks = (total + 255) / 256;
-    int64_t cap    = (int64_t)st->sm_count * 32;
-    if (blocks > cap)
-        blocks = cap;
+    (void)st;
+    dim3 grid((unsigned)((kp / 4 + 255) / 256), (unsigned)(rows < 65535 ? rows : 65535));
+    int vec_ok = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0;
     if (mode == MODE_3X)
-        split_rows_kernel<MODE_3X><<<(unsigned)blocks, 256, 0, stream()>>>(in, rows, k, kp, hi, lo);
+        split_rows_vec_kernel<MODE_3X><<<grid, 256, 0, stream()>>>(in, rows, k, kp, hi, lo, vec_ok);
     else
-        split_rows_kernel<MODE_BF><<<(unsigned)blocks, 256, 0, stream()>>>(in, rows, k, kp, hi, lo);
+        split_rows_vec_kernel<MODE_BF><<<grid, 256, 0, stream()>>>(in, rows, k, kp, hi, lo, vec_ok);
     CT_LAUNCH_CHECK("split_rows");
     return CT_OK;
 }
@@ -652,6 +771,9 @@ ct_status launch_static(
     p.out_batch_stride = 0;
     p.bias_per_row     = 0;
     p.flags            = s->flags;
+    p.tile_n           = BN;
+    p.conv             = 0;
+    p.conv_cblocks = p.conv_kw = p.conv_pad = p.conv_th = 0;
     CT_CUDA(cudaFuncSetAttribute(
         gemm_tc_kernel<BN, MODE_3X>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     gemm_tc_kernel<BN, MODE_3X><<<(unsigned)(p.tiles_m * p.tiles_n), C::kThreads, C::kSmemBytes, stream()>>>(

@@ -73,6 +73,12 @@ ct_status current(DeviceState **out) {
             CT_CUDA(cudaMemset(st->flags_dev, 0, FLAG_COUNT * sizeof(uint32_t)));
             CT_CUDA(cudaMallocHost(&st->flags_host, FLAG_COUNT * sizeof(uint32_t)));
             memset(st->flags_host, 0, FLAG_COUNT * sizeof(uint32_t));
+            // Tensor storage comes from the device's stream-ordered pool; keep freed blocks cached
+            // instead of returning them to the driver at every synchronisation.
+            cudaMemPool_t pool;
+            CT_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+            uint64_t keep = UINT64_MAX;
+            CT_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
             st->ready = true;
         }
     }
@@ -176,7 +182,8 @@ ct_status ct_alloc(void **ptr_dev, size_t bytes) {
     *ptr_dev = nullptr;
     if (bytes == 0)
         bytes = 1; // an empty tensor still owns a distinct address
-    CT_CUDA(cudaMalloc(ptr_dev, bytes));
+    // stream-ordered, pooled: an operator result costs microseconds, not a device-wide stall
+    CT_CUDA(cudaMallocAsync(ptr_dev, bytes, stream()));
     return CT_OK;
 }
 
@@ -185,7 +192,7 @@ ct_status ct_free(void *ptr_dev) {
         return CT_OK;
     DeviceState *st;
     CT_TRY(current(&st));
-    CT_CUDA(cudaFree(ptr_dev));
+    CT_CUDA(cudaFreeAsync(ptr_dev, stream()));
     return CT_OK;
 }
 

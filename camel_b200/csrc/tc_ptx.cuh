@@ -115,6 +115,19 @@ __device__ __forceinline__ void tma_load_3d(
         : "memory");
 }
 
+// Only c0 carries the 16-byte alignment rule; c1..c3 may be negative or past the end (the
+// out-of-range part of the box reads as zero), which is how a convolution's halo is fetched.
+__device__ __forceinline__ void tma_load_4d(
+    uint32_t dst_smem, const void *map, uint32_t bar, int32_t c0, int32_t c1, int32_t c2, int32_t c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        :
+        : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2),
+          "r"(c3)
+        : "memory");
+}
+
 // ---- tensor memory ----------------------------------------------------------------------
 
 // Whole-warp instructions (.sync.aligned): call from all 32 lanes of one warp.

@@ -292,7 +292,11 @@ def test_mlp_forward_cfg2_slice(T):
     (1, 1, 28, 28, 32, 3, 1, 1, "relu"),    # first CNN layer: c*kh*kw = 9
     (3, 32, 28, 28, 64, 3, 1, 1, "relu"),   # second CNN layer
     (2, 64, 56, 56, 128, 3, 1, 1, "relu"),  # BASELINE config 3 geometry, small batch
-    (2, 16, 20, 20, 48, 5, 2, 2, None),     # stride 2, 5x5
+    (2, 16, 20, 20, 48, 5, 2, 2, None),     # stride 2, 5x5: patch-matrix path
+    (3, 48, 30, 30, 200, 3, 1, 0, "relu"),  # no padding (wo < w), channels and filters off the tile sizes
+    (2, 32, 28, 28, 64, 1, 1, 0, None),     # 1x1 filter
+    (2, 20, 13, 16, 130, 3, 1, 1, "relu"),  # odd height, last row tile partial, c < 32
+    (1, 64, 7, 40, 16, 5, 1, 2, None),      # 5x5, pad 2
 ])
 def test_conv2d(T, n, c, h, w, ko, kk, stride, pad, act):
     rng = np.random.default_rng(3)
