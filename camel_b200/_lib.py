@@ -39,7 +39,11 @@ PROTOTYPES = {
     "ct_profile_read": (_int, [C.c_char_p, C.POINTER(_dbl), C.POINTER(_u64)]),
     "ct_set_precision": (_int, [_int]),
     "ct_get_precision": (_int, []),
-    "ct_alloc": (_int, [C.POINTER(_vp), _sz]),
+    "ct_graph_begin": (_int, []),
+    "ct_graph_end": (_int, [C.POINTER(_vp)]),
+    "ct_graph_launch": (_int, [_vp]),
+    "ct_graph_destroy": (_int, [_vp]),
+    "ct_alloc":(_int, [C.POINTER(_vp), _sz]),
     "ct_free": (_int, [_vp]),
     "ct_h2d": (_int, [_vp, _vp, _sz]),
     "ct_d2h": (_int, [_vp, _vp, _sz]),

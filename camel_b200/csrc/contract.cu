@@ -116,6 +116,62 @@ __global__ void __launch_bounds__(256) conv2d_direct_kernel(
     }
 }
 
+// Few input channels (c*kh*kw <= 64, e.g. the first layer of a CNN on grey images): the
+// contraction is too short for tensor-core tiles and the layer is bound by writing its output.
+// One thread per output pixel keeps the patch in registers and walks the filters from shared
+// memory; float64 accumulation in (c,r,s) order, bias last, as the reference style prescribes.
+// Stores are coalesced: consecutive threads own consecutive pixels of one output plane.
+constexpr int kSmallPatch = 64;
+__global__ void __launch_bounds__(256) conv2d_small_c_kernel(
+    const float *__restrict__ x, const float *__restrict__ wt, const float *__restrict__ bias,
+    int64_t n, int c, int64_t h, int64_t w, int ko, int kh, int kw, int64_t stride, int64_t pad,
+    int64_t ho, int64_t wo, int act, float *__restrict__ out) {
+    extern __shared__ float w_s[]; // [ko][kdim]
+    const int kdim = c * kh * kw;
+    for (int i = threadIdx.x; i < ko * kdim; i += 256)
+        w_s[i] = wt[i];
+    __syncthreads();
+    const int64_t pix   = ho * wo;
+    const int64_t total = n * pix;
+    const int64_t step  = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+        int64_t img = i / pix, p = i - img * pix;
+        int64_t oy = p / wo, ox = p - oy * wo;
+        float patch[kSmallPatch];
+#pragma unroll
+        for (int t = 0; t < kSmallPatch; ++t)
+            patch[t] = 0.0f;
+        int t = 0;
+        for (int ic = 0; ic < c; ++ic)
+            for (int r = 0; r < kh; ++r)
+                for (int s = 0; s < kw; ++s, ++t) {
+                    int64_t iy = oy * stride - pad + r, ix = ox * stride - pad + s;
+                    float v = 0.0f;
+                    if (iy >= 0 && iy < h && ix >= 0 && ix < w)
+                        v = __ldg(x + ((img * c + ic) * h + iy) * w + ix);
+#pragma unroll
+                    for (int u = 0; u < kSmallPatch; ++u)
+                        if (u == t)
+                            patch[u] = v;
+                }
+        float *dst = out + img * ko * pix + p;
+        for (int o = 0; o < ko; ++o) {
+            const float *wr = w_s + o * kdim;
+            double acc      = 0.0;
+#pragma unroll
+            for (int u = 0; u < kSmallPatch; ++u)
+                if (u < kdim)
+                    acc += (double)patch[u] * (double)wr[u];
+            if (bias)
+                acc += (double)bias[o];
+            float v = (float)acc;
+            if (act == CT_ACT_RELU)
+                v = __fmul_rn(v, v > 0.0f ? 1.0f : 0.0f);
+            dst[(int64_t)o * pix] = v;
+        }
+    }
+}
+
 // maxpool, window == stride: one thread per output, strict '>' from the window's first element.
 __global__ void __launch_bounds__(256) maxpool2d_kernel(
     const float *__restrict__ x, int64_t planes, int64_t h, int64_t w, int64_t win, int64_t ho,
@@ -272,6 +328,13 @@ ct_status ct_conv2d(
         return fail(CT_ERR_INVALID, "conv2d: null pointer");
     int64_t kdim = c * kh * kw;
     int64_t pix  = ho * wo;
+    if (kdim <= kSmallPatch && ko * kdim * 4 <= 48 * 1024 && ko <= 0x7fffffff) {
+        ProfScope prof("conv_small_c");
+        conv2d_small_c_kernel<<<capped_blocks(st, n * pix, 16), 256, (size_t)(ko * kdim * 4), stream()>>>(
+            x, w, bias, n, (int)c, h, wd, (int)ko, (int)kh, (int)kw, stride, pad, ho, wo, act, out);
+        CT_LAUNCH_CHECK("conv2d_small_c");
+        return CT_OK;
+    }
     if (kdim * ko * pix * n < kTinyMacs * 8 || ko < 16 || pix < 64 || n > 0x7fffffff) {
         conv2d_direct_kernel<<<capped_blocks(st, total_out, 16), 256, 0, stream()>>>(
             x, w, bias, n, c, h, wd, ko, kh, kw, stride, pad, ho, wo, act, out);

@@ -590,6 +590,7 @@ ct_status ct_softmax_rows(const float *in, int64_t rows, int64_t cols, float *ou
     if (rows > 0x7fffffffll)
         return fail(CT_ERR_TOO_LARGE, "softmax: too many rows");
     unsigned wblocks = (unsigned)((rows + 7) / 8);
+    ProfScope prof("softmax");
     if (cols <= 32)
         softmax_rows_warp_kernel<1><<<wblocks, 256, 0, stream()>>>(in, rows, cols, out);
     else if (cols <= 128)

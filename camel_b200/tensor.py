@@ -486,6 +486,38 @@ def flatten(x: Tensor) -> Tensor:
     return reshape(x, (x.shape[0], rest))
 
 
+class Graph:
+    """Records the operator calls made inside `with Graph() as g:` and replays them with
+    `g.launch()` (one CUDA-graph launch).  Tensors created inside the block and still referenced
+    afterwards (e.g. kept in `g.keep`) hold the results of the latest replay.  Run the same calls
+    once before recording, and do not let tensors created earlier die inside the block."""
+
+    def __init__(self):
+        self.handle = C.c_void_p()
+        self.keep = None
+
+    def __enter__(self):
+        check(lib.ct_graph_begin())
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        status = lib.ct_graph_end(C.byref(self.handle))
+        if exc_type is None:
+            check(status)
+        return False
+
+    def launch(self) -> None:
+        check(lib.ct_graph_launch(self.handle))
+
+    def __del__(self):
+        if getattr(self, "handle", None) is not None and self.handle.value:
+            try:
+                lib.ct_graph_destroy(self.handle)
+            except Exception:
+                pass
+            self.handle = C.c_void_p()
+
+
 def sync() -> None:
     check(lib.ct_sync())
 

@@ -88,6 +88,18 @@ ct_status ct_profile_read(const char *kernel, double *total_ms_host, uint64_t *l
 ct_status ct_set_precision(ct_precision precision);
 ct_precision ct_get_precision(void);
 
+/* Record-and-replay of a sequence of calls (CUDA graph).  Between ct_graph_begin and
+ * ct_graph_end the library's calls are recorded instead of executed; ct_graph_launch then runs
+ * the whole sequence with one launch on the current stream.  Recorded calls see the same device
+ * pointers at every replay; tensors allocated inside the recording (ct_alloc) are part of it and
+ * live from their point in the sequence until ct_free or the next replay.  Calls that return a
+ * host value or synchronise (ct_sum, ct_log, ct_binary with CT_DIV, ct_h2d/ct_d2h, ct_check)
+ * cannot be recorded, and the sequence must have run once before so that workspaces exist. */
+ct_status ct_graph_begin(void);
+ct_status ct_graph_end(void **graph_out);
+ct_status ct_graph_launch(void *graph);
+ct_status ct_graph_destroy(void *graph);
+
 /* ---- device storage: the device side of TensorObject::create,
  *      modules/tensor/runtime.cpp:256-279 (storage gains a device buffer) ---------------- */
 

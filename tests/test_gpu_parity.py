@@ -288,7 +288,8 @@ def test_mlp_forward_cfg2_slice(T):
 
 
 @pytest.mark.parametrize("n,c,h,w,ko,kk,stride,pad,act", [
-    (2, 3, 9, 11, 5, 3, 1, 1, "relu"),      # direct kernel
+    (2, 3, 9, 11, 5, 3, 1, 1, "relu"),      # few input channels: register-patch kernel
+    (1, 8, 6, 6, 4, 3, 1, 1, None),         # tiny: one thread per output
     (1, 1, 28, 28, 32, 3, 1, 1, "relu"),    # first CNN layer: c*kh*kw = 9
     (3, 32, 28, 28, 64, 3, 1, 1, "relu"),   # second CNN layer
     (2, 64, 56, 56, 128, 3, 1, 1, "relu"),  # BASELINE config 3 geometry, small batch
@@ -308,6 +309,42 @@ def test_conv2d(T, n, c, h, w, ko, kk, stride, pad, act):
     T.check_async()
     assert got.shape == ref.shape
     assert _rel_err(got, ref) <= GEMM_TOL
+
+
+def test_cnn_forward_cfg4_slice(T):
+    """BASELINE config 4 on 48 images: conv-relu, conv-relu, maxpool, flatten, dense-relu,
+    dense-softmax; probabilities within tolerance and argmax equal where the oracle's top-2 gap
+    is above the contraction tolerance."""
+    rng = np.random.default_rng(4)
+
+    def kaiming(shape, fan_in):
+        lim = np.sqrt(6.0 / fan_in)
+        return rng.uniform(-lim, lim, shape).astype(np.float32)
+
+    w1, w2 = kaiming((32, 1, 3, 3), 9), kaiming((64, 32, 3, 3), 288)
+    w3, w4 = kaiming((12544, 128), 12544), kaiming((128, 10), 128)
+    b1, b2, b3, b4 = (rng.uniform(-0.05, 0.05, n).astype(np.float32) for n in (32, 64, 128, 10))
+    x = rng.uniform(0, 1, (48, 1, 28, 28)).astype(np.float32)
+    p = oracle.port()
+    h = p.conv2d(x, w1, b1, 1, 1, 1)
+    h = p.conv2d(h, w2, b2, 1, 1, 1)
+    h = p.maxpool2d(h, 2).reshape(48, -1)
+    h = p.dense(h, w3, b3, 1)
+    logits = p.dense(h, w4, b4, 0)
+    probs_ref, arg_ref = p.softmax_rows(logits), p.argmax_axis(logits, 1)
+
+    g = T.conv2d(T.from_numpy(x), T.from_numpy(w1), T.from_numpy(b1), 1, 1, "relu")
+    g = T.conv2d(g, T.from_numpy(w2), T.from_numpy(b2), 1, 1, "relu")
+    g = T.flatten(T.maxpool2d(g, 2))
+    assert g.shape == (48, 12544)
+    g = T.dense(g, T.from_numpy(w3), T.from_numpy(b3), "relu")
+    probs, arg = T.dense(g, T.from_numpy(w4), T.from_numpy(b4), "softmax", with_argmax=True)
+    probs, arg = probs.numpy(), arg.numpy()
+    T.check_async()
+    assert np.max(np.abs(probs - probs_ref)) <= 1e-5
+    srt = np.sort(logits, axis=1)
+    decided = (srt[:, -1] - srt[:, -2]) > 1e-4 * np.max(np.abs(logits))
+    assert np.array_equal(arg[decided], arg_ref[decided])
 
 
 def test_maxpool2d(T):
@@ -334,3 +371,33 @@ def test_elementwise_large_roundtrip_properties(T):
     assert T.sum(mask) == float(np.count_nonzero(x > 0))
     s = T.sum(tx)
     assert abs(s - float(np.sum(x.astype(np.float64)))) <= 1e-9 * n
+
+
+def test_graph_replay_matches_eager(T):
+    """A recorded dense -> relu -> dense -> softmax chain replays with new input contents and
+    gives the same bytes as the call-by-call run."""
+    rng = np.random.default_rng(8)
+    w1 = T.from_numpy(rng.uniform(-0.2, 0.2, (96, 160)).astype(np.float32))
+    b1 = T.from_numpy(rng.uniform(-0.1, 0.1, 160).astype(np.float32))
+    w2 = T.from_numpy(rng.uniform(-0.2, 0.2, (160, 10)).astype(np.float32))
+    x_np = [rng.uniform(0, 1, (300, 96)).astype(np.float32) for _ in range(3)]
+    x = T.from_numpy(x_np[0])
+
+    def forward(inp):
+        h = T.dense(inp, w1, b1, "relu")
+        return T.dense(h, w2, None, "softmax", with_argmax=True)
+
+    warm = forward(x)
+    T.check_async()
+    with T.Graph() as g:
+        g.keep = forward(x)
+    for a in x_np:
+        from camel_b200._lib import check, lib
+        check(lib.ct_h2d(x.ptr, a.ctypes.data, a.nbytes))
+        g.launch()
+        probs_g, arg_g = g.keep[0].numpy(), g.keep[1].numpy()
+        probs_e, arg_e = forward(T.from_numpy(a))
+        assert probs_g.tobytes() == probs_e.numpy().tobytes()
+        assert arg_g.tobytes() == arg_e.numpy().tobytes()
+    T.check_async()
+    del warm
