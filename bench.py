@@ -122,25 +122,20 @@ def conv_inputs(batch):
 # reference arm: the reference's own CPU operators on a bounded sample
 # ---------------------------------------------------------------------------------------
 
-def run_reference(args, rank):
-    if rank != 0:
-        return
+def _reference_worker(workload, size, steps, warmup):
+    """One host process: builds its own inputs, runs `steps` bounded samples on the reference's
+    compiled operators (oracle/_ref), or on the C restatement when that library is absent.
+    Returns (kind, units per step, mean seconds per step, description of the sample)."""
     import oracle
+    from oracle import IntArray
 
-    cores = os.cpu_count() or 1
-    if not oracle.Reference.available():
-        kind, be = "port", None
-    else:
-        kind, be = "reference", oracle.ref()
+    be = oracle.ref() if oracle.Reference.available() else None
     p = oracle.port()
-    times = []
-    if args.workload == "mlp":
-        sample = 16  # samples per step; the reference loop is single-threaded (~0.2 GFLOP/s)
+    if workload == "mlp":
+        sample = 16  # the reference loop runs at ~0.2 GFLOP/s per thread
         x, w, b = mlp_inputs(sample)
-        from oracle import IntArray
 
         def step():
-            t0 = time.perf_counter()
             h = x
             for i in range(3):
                 if be is not None:
@@ -151,38 +146,65 @@ def run_reference(args, rank):
                         h = be.call("multiply", h, be.call("gt", h, 0))
                 else:
                     h = p.dense(h, w[i], b[i], 1 if i < 2 else 0)
-            probs = p.softmax_rows(h)
+            p.softmax_rows(h)
             p.argmax_axis(h, 1)
-            return time.perf_counter() - t0, probs
 
-        units, unit, metric = sample, "samples/s", "mlp_forward_samples_per_s"
-        sample_desc = f"{sample} of 4096 samples per step, full layer widths, 1 thread (reference kernels are single-threaded)"
-    elif args.workload == "gemm":
-        n = args.size
-        rows = max(1, min(n, int(2.0e9 / (2.0 * n * n)) or 1))  # ~2 GFLOP per step
-        a, bm = gemm_inputs(rows, n, n)
+        units = sample
+        desc = f"{sample} of 4096 samples per step and process, full layer widths"
+    elif workload == "gemm":
+        n, cols = size, min(size, 512)
+        rows = max(1, int(1.0e9 / (2.0 * n * cols)))
+        a, bm = gemm_inputs(rows, n, cols)
 
         def step():
-            t0 = time.perf_counter()
-            out = be.call("matmul", a, bm) if be is not None else p.matmul(a, bm)
-            return time.perf_counter() - t0, out
+            be.call("matmul", a, bm) if be is not None else p.matmul(a, bm)
 
-        units, unit, metric = 2.0 * rows * n * n / 1e12, "TFLOP/s", "gemm_fp32_tflops"
-        sample_desc = f"{rows} rows of A against the full {n}x{n} B per step (scale x{n / rows:.0f} for the whole GEMM), 1 thread"
+        units = 2.0 * rows * n * cols / 1e12
+        desc = f"{rows} rows of A x {cols} columns of B (k = {n}) per step and process"
     else:
+        return None
+    for _ in range(warmup):
+        step()
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    return ("reference" if be is not None else "port", units, float(np.mean(times)), desc)
+
+
+def run_reference(args, rank):
+    """The reference arm: the reference's own CPU operators.  Its kernels are single-threaded, so
+    the host's cores are used the only way the reference could use them: independent shards of
+    the batch (samples / row blocks) in parallel, one process per core."""
+    if rank != 0:
+        return
+    metric, unit = {"mlp": ("mlp_forward_samples_per_s", "samples/s"),
+                    "gemm": ("gemm_fp32_tflops", "TFLOP/s")}.get(args.workload, (None, None))
+    if metric is None:
         print(json.dumps({"impl": "reference", "unavailable": f"workload {args.workload} has no reference arm"}))
         return
-    for _ in range(max(0, min(args.warmup, 1))):
-        step()
-    for _ in range(max(1, min(args.steps, 3))):
-        times.append(step()[0])
-    t = float(np.mean(times))
-    value = units / t
-    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": 0, "steps": len(times),
-            "warmup": min(args.warmup, 1), "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+    import multiprocessing as mp
+    from concurrent.futures import ProcessPoolExecutor
+
+    cores = os.cpu_count() or 1
+    workers = 1 if args.ref_workers == 1 else max(1, min(cores, args.ref_workers or 32))
+    steps, warmup = max(1, min(args.steps, 3)), max(0, min(args.warmup, 1))
+    if workers == 1:
+        results = [_reference_worker(args.workload, args.size, steps, warmup)]
+    else:
+        with ProcessPoolExecutor(max_workers=workers, mp_context=mp.get_context("spawn")) as ex:
+            futs = [ex.submit(_reference_worker, args.workload, args.size, steps, warmup) for _ in range(workers)]
+            results = [f.result() for f in futs]
+    kind, units, _, desc = results[0]
+    t = max(r[2] for r in results)  # the slowest shard bounds the step
+    value = units * workers / t
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": 0, "steps": steps,
+            "warmup": warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f64-accumulate/f32", "data": "synthetic",
-            "config": {"workload": args.workload, "note": "reference CPU operators, bounded sample"},
-            "cpu_baseline": {"value": value, "unit": unit, "cores": 1, "kind": kind, "sample": sample_desc,
+            "config": {"workload": args.workload, "note": "reference CPU operators, bounded sample per process"},
+            "cpu_baseline": {"value": value, "unit": unit, "cores": workers, "kind": kind,
+                             "sample": desc + f"; {workers} processes (the kernels themselves are single-threaded)",
                              "host_cores_available": cores},
             "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -728,6 +750,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ref-workers", type=int, default=0, help="processes of the reference arm (0: one per core, max 32)")
     ap.add_argument("--eager", action="store_true", help="do not replay the forward pass as a CUDA graph")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

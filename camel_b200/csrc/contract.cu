@@ -6,6 +6,7 @@
 #include <cuda_bf16.h>
 
 #include <cstdlib>
+#include <type_traits>
 
 namespace ct {
 namespace {
@@ -122,14 +123,18 @@ __global__ void __launch_bounds__(256) conv2d_direct_kernel(
 // memory; float64 accumulation in (c,r,s) order, bias last, as the reference style prescribes.
 // Stores are coalesced: consecutive threads own consecutive pixels of one output plane.
 constexpr int kSmallPatch = 64;
+template <int KD> // register capacity of the patch: the smallest of 9 / 16 / 32 / 64 that holds kdim
 __global__ void __launch_bounds__(256) conv2d_small_c_kernel(
     const float *__restrict__ x, const float *__restrict__ wt, const float *__restrict__ bias,
     int64_t n, int c, int64_t h, int64_t w, int ko, int kh, int kw, int64_t stride, int64_t pad,
     int64_t ho, int64_t wo, int act, float *__restrict__ out) {
-    extern __shared__ float w_s[]; // [ko][kdim]
+    // [ko][kdim], widened to float64 once per block: float32 -> float64 conversions are the slow
+    // instruction here, so none is left in the multiply-add loop when the patch is short
+    extern __shared__ double w_s[];
+    using patch_t  = typename std::conditional<(KD <= 16), double, float>::type;
     const int kdim = c * kh * kw;
     for (int i = threadIdx.x; i < ko * kdim; i += 256)
-        w_s[i] = wt[i];
+        w_s[i] = (double)wt[i];
     __syncthreads();
     const int64_t pix   = ho * wo;
     const int64_t total = n * pix;
@@ -137,10 +142,10 @@ __global__ void __launch_bounds__(256) conv2d_small_c_kernel(
     for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
         int64_t img = i / pix, p = i - img * pix;
         int64_t oy = p / wo, ox = p - oy * wo;
-        float patch[kSmallPatch];
+        patch_t patch[KD];
 #pragma unroll
-        for (int t = 0; t < kSmallPatch; ++t)
-            patch[t] = 0.0f;
+        for (int t = 0; t < KD; ++t)
+            patch[t] = 0;
         int t = 0;
         for (int ic = 0; ic < c; ++ic)
             for (int r = 0; r < kh; ++r)
@@ -150,18 +155,18 @@ __global__ void __launch_bounds__(256) conv2d_small_c_kernel(
                     if (iy >= 0 && iy < h && ix >= 0 && ix < w)
                         v = __ldg(x + ((img * c + ic) * h + iy) * w + ix);
 #pragma unroll
-                    for (int u = 0; u < kSmallPatch; ++u)
+                    for (int u = 0; u < KD; ++u)
                         if (u == t)
-                            patch[u] = v;
+                            patch[u] = (patch_t)v;
                 }
         float *dst = out + img * ko * pix + p;
         for (int o = 0; o < ko; ++o) {
-            const float *wr = w_s + o * kdim;
-            double acc      = 0.0;
+            const double *wr = w_s + o * kdim;
+            double acc       = 0.0;
 #pragma unroll
-            for (int u = 0; u < kSmallPatch; ++u)
+            for (int u = 0; u < KD; ++u)
                 if (u < kdim)
-                    acc += (double)patch[u] * (double)wr[u];
+                    acc += (double)patch[u] * wr[u];
             if (bias)
                 acc += (double)bias[o];
             float v = (float)acc;
@@ -328,10 +333,20 @@ ct_status ct_conv2d(
         return fail(CT_ERR_INVALID, "conv2d: null pointer");
     int64_t kdim = c * kh * kw;
     int64_t pix  = ho * wo;
-    if (kdim <= kSmallPatch && ko * kdim * 4 <= 48 * 1024 && ko <= 0x7fffffff) {
+    if (kdim <= kSmallPatch && ko * kdim * 8 <= 48 * 1024 && ko <= 0x7fffffff) {
         ProfScope prof("conv_small_c");
-        conv2d_small_c_kernel<<<capped_blocks(st, n * pix, 16), 256, (size_t)(ko * kdim * 4), stream()>>>(
-            x, w, bias, n, (int)c, h, wd, (int)ko, (int)kh, (int)kw, stride, pad, ho, wo, act, out);
+        unsigned blocks = capped_blocks(st, n * pix, 16);
+        size_t smem     = (size_t)(ko * kdim * 8);
+#define CT_SMALL_C_ARGS x, w, bias, n, (int)c, h, wd, (int)ko, (int)kh, (int)kw, stride, pad, ho, wo, act, out
+        if (kdim <= 9)
+            conv2d_small_c_kernel<9><<<blocks, 256, smem, stream()>>>(CT_SMALL_C_ARGS);
+        else if (kdim <= 16)
+            conv2d_small_c_kernel<16><<<blocks, 256, smem, stream()>>>(CT_SMALL_C_ARGS);
+        else if (kdim <= 32)
+            conv2d_small_c_kernel<32><<<blocks, 256, smem, stream()>>>(CT_SMALL_C_ARGS);
+        else
+            conv2d_small_c_kernel<64><<<blocks, 256, smem, stream()>>>(CT_SMALL_C_ARGS);
+#undef CT_SMALL_C_ARGS
         CT_LAUNCH_CHECK("conv2d_small_c");
         return CT_OK;
     }

@@ -7,8 +7,10 @@
 // is provably the IEEE float32 result (53 >= 2*24+2), so the fast path uses the correctly
 // rounded single-precision instructions directly, with no fused multiply-add.
 #include "common.cuh"
+#include "fastmath.cuh"
 
 #include <cmath>
+#include <mutex>
 
 namespace ct {
 namespace {
@@ -436,7 +438,7 @@ enum { UN_EXP = 0, UN_LOG = 1, UN_RELU = 2 };
 
 template <int OP> __device__ __forceinline__ float apply_unary(float x, uint32_t *flags) {
     if (OP == UN_EXP)
-        return (float)exp((double)x); // tensorExp, runtime.cpp:1023
+        return exp_f32(x); // tensorExp, runtime.cpp:1023
     if (OP == UN_LOG) {
         if (x <= 0.0f) { // v <= 0 throws; NaN does not (runtime.cpp:1038-1042)
             flags[FLAG_LOG_DOMAIN] = 1;
@@ -475,6 +477,78 @@ template <int OP> ct_status unary(const float *t, uint64_t n, float *o, uint32_t
     }
     uint64_t done = nv * kVec;
     return launch_map(n - done, Unary<OP, false>{t, o, flags, done}, name);
+}
+
+// ---- log: table-driven, tables staged in shared memory --------------------------------
+
+__device__ double g_log_rc[kLogTableSize];
+__device__ double g_log_lc[kLogTableSize];
+
+// Fills the tables once per device from the host's libm (the values the reference's host
+// would use), so that log(c_j) and ln 2 are consistent doubles.
+ct_status ensure_log_tables(DeviceState *st) {
+    static std::mutex mu;
+    static bool done[16] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[st->device])
+        return CT_OK;
+    double rc[kLogTableSize], lc[kLogTableSize];
+    for (int j = 0; j < kLogTableSize; ++j) {
+        double c = 1.0 + j / 128.0;
+        rc[j]    = 1.0 / c;
+        lc[j]    = std::log(c);
+    }
+    lc[kLogTableSize - 1] = 0.693147180559945309417;
+    CT_CUDA(cudaMemcpyToSymbol(g_log_rc, rc, sizeof(rc)));
+    CT_CUDA(cudaMemcpyToSymbol(g_log_lc, lc, sizeof(lc)));
+    done[st->device] = true;
+    return CT_OK;
+}
+
+// tensorLog (runtime.cpp:1029-1045): any x <= 0 raises the flag (the reference throws there).
+__global__ void __launch_bounds__(kThreads) log_kernel(
+    const float *__restrict__ in, float *__restrict__ out, uint64_t n, int vec, uint32_t *flags) {
+    __shared__ double rc[kLogTableSize];
+    __shared__ double lc[kLogTableSize];
+    for (int j = threadIdx.x; j < kLogTableSize; j += kThreads) {
+        rc[j] = g_log_rc[j];
+        lc[j] = g_log_lc[j];
+    }
+    __syncthreads();
+    auto one = [&](float x) -> float {
+        if (x <= 0.0f) {
+            flags[FLAG_LOG_DOMAIN] = 1;
+            return 0.0f;
+        }
+        return (float)log_from_f32((double)x, rc, lc);
+    };
+    if (vec) {
+        uint64_t nv   = n / kVec;
+        uint64_t base = (uint64_t)blockIdx.x * (kThreads * kUnroll) + threadIdx.x;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            uint64_t i = base + (uint64_t)u * kThreads;
+            if (i < nv) {
+                VecT<float> a = load_vec<float>(in, i);
+                VecT<float> c;
+#pragma unroll
+                for (int k = 0; k < kVec; ++k)
+                    c.v[k] = one(a.v[k]);
+                store_vec(out, i, c);
+            }
+        }
+        // the last block also finishes the < 4 element tail
+        if (blockIdx.x == gridDim.x - 1)
+            for (uint64_t i = nv * kVec + threadIdx.x; i < n; i += kThreads)
+                out[i] = one(in[i]);
+    } else {
+        uint64_t base = (uint64_t)blockIdx.x * (kThreads * kUnroll * kVec) + threadIdx.x;
+        for (int u = 0; u < kUnroll * kVec; ++u) {
+            uint64_t i = base + (uint64_t)u * kThreads;
+            if (i < n)
+                out[i] = one(in[i]);
+        }
+    }
 }
 
 // ---- constructors ---------------------------------------------------------------------
@@ -714,8 +788,18 @@ ct_status ct_log(const float *in, uint64_t n, float *out) {
         return CT_OK;
     if (!in || !out)
         return fail(CT_ERR_INVALID, "ct_log: null pointer");
+    CT_TRY(ensure_log_tables(st));
     CT_TRY(clear_flags(st));
-    CT_TRY(unary<UN_LOG>(in, n, out, st->flags_dev, "log"));
+    {
+        uint64_t per_block = (uint64_t)kThreads * kUnroll * kVec;
+        uint64_t blocks    = (n + per_block - 1) / per_block;
+        if (blocks > 0x7fffffffull)
+            return fail(CT_ERR_TOO_LARGE, "log: too many elements");
+        int vec = aligned16(in) && aligned16(out);
+        ProfScope prof("elementwise");
+        log_kernel<<<(unsigned)blocks, kThreads, 0, stream()>>>(in, out, n, vec, st->flags_dev);
+        CT_LAUNCH_CHECK("log");
+    }
     CT_TRY(fetch_flags(st));
     if (st->flags_host[FLAG_LOG_DOMAIN])
         return fail(CT_ERR_LOG_DOMAIN, "log: input must be positive");

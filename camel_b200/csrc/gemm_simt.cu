@@ -6,6 +6,7 @@
 //    an MLP): one warp per output row, float64 accumulation, with bias / relu / row-softmax /
 //    argmax fused, so the logits never round-trip through HBM.
 #include "common.cuh"
+#include "fastmath.cuh"
 
 #include <cmath>
 
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(
             best_idx = j;
         }
     }
-    float e  = live ? (float)exp((double)__fsub_rn(logit, best)) : 0.0f;
+    float e  = live ? exp_f32(__fsub_rn(logit, best)) : 0.0f;
     double s = 0.0;
     for (int j = 0; j < n; ++j)
         s += (double)__shfl_sync(0xffffffffu, e, j);
@@ -171,7 +172,7 @@ __device__ __forceinline__ void skinny_finish_row(
             best_idx = j;
         }
     }
-    float e  = live ? (float)exp((double)__fsub_rn(logit, best)) : 0.0f;
+    float e  = live ? exp_f32(__fsub_rn(logit, best)) : 0.0f;
     double s = 0.0;
     for (int j = 0; j < n; ++j)
         s += (double)__shfl_sync(0xffffffffu, e, j);
@@ -190,11 +191,13 @@ template <int N_MAX>
 __global__ void __launch_bounds__(256) gemm_skinny_smem_kernel(
     const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
     int64_t m, int64_t k, int n, int act, float *__restrict__ out, int64_t *__restrict__ argmax) {
-    extern __shared__ __align__(16) float w_s[];
-    // staged transposed, [n][k]: lanes then read consecutive k of one column, conflict-free
+    extern __shared__ __align__(16) double w_s[];
+    // staged transposed [n][k] and already widened to float64: the float32 -> float64
+    // conversions run on the slow special-function pipe, so they are paid once per weight
+    // and block here instead of once per multiply-add
     for (int64_t i = threadIdx.x; i < k * n; i += 256) {
         int64_t kk = i / n, j = i - kk * n;
-        w_s[j * k + kk] = w[i];
+        w_s[j * k + kk] = (double)w[i];
     }
     __syncthreads();
     const int lane     = threadIdx.x & 31;
@@ -214,11 +217,12 @@ __global__ void __launch_bounds__(256) gemm_skinny_smem_kernel(
 #pragma unroll
                 for (int j = 0; j < N_MAX; ++j)
                     if (j < n) {
-                        float4 wq = *reinterpret_cast<const float4 *>(w_s + (int64_t)j * k + kk);
-                        acc[j] += x0 * (double)wq.x;
-                        acc[j] += x1 * (double)wq.y;
-                        acc[j] += x2 * (double)wq.z;
-                        acc[j] += x3 * (double)wq.w;
+                        const double2 *wp = reinterpret_cast<const double2 *>(w_s + (int64_t)j * k + kk);
+                        double2 wa = wp[0], wb = wp[1];
+                        acc[j] += x0 * wa.x;
+                        acc[j] += x1 * wa.y;
+                        acc[j] += x2 * wb.x;
+                        acc[j] += x3 * wb.y;
                     }
             }
         } else {
@@ -227,7 +231,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_smem_kernel(
 #pragma unroll
                 for (int j = 0; j < N_MAX; ++j)
                     if (j < n)
-                        acc[j] += xd * (double)w_s[(int64_t)j * k + kk];
+                        acc[j] += xd * w_s[(int64_t)j * k + kk];
             }
         }
         skinny_finish_row<N_MAX>(acc, bias, row, n, act, lane, out, argmax);
@@ -238,7 +242,7 @@ template <int N_MAX>
 ct_status launch_skinny_smem(
     DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k, int n,
     int act, float *out, int64_t *argmax) {
-    size_t smem = (size_t)k * n * sizeof(float);
+    size_t smem = (size_t)k * n * sizeof(double);
     if (smem > 48 * 1024)
         CT_CUDA(cudaFuncSetAttribute(
             gemm_skinny_smem_kernel<N_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -275,7 +279,7 @@ ct_status gemm_f32_skinny(
         return fail(CT_ERR_INVALID, "skinny GEMM takes at most 32 output columns");
     unsigned blocks = (unsigned)((m + 7) / 8);
     ProfScope prof("gemm_skinny");
-    if ((size_t)k * n * sizeof(float) <= 200 * 1024 && k > 0) {
+    if ((size_t)k * n * sizeof(double) <= 200 * 1024 && k > 0) {
         if (n <= 8)
             return launch_skinny_smem<8>(st, a, b, bias, m, k, (int)n, act, out, argmax);
         if (n <= 16)

@@ -3,6 +3,7 @@
 // reference (modules/tensor/runtime.cpp:879-1011), combined by warp shuffles and a fixed
 // block tree so that results do not depend on scheduling.
 #include "common.cuh"
+#include "fastmath.cuh"
 
 #include <cfloat>
 #include <cmath>
@@ -382,7 +383,7 @@ __global__ void __launch_bounds__(THREADS) softmax_rows_kernel(const float *in, 
         int64_t j = (int64_t)k * THREADS + threadIdx.x;
         if (j < cols) {
             float s = __fsub_rn(v[k], m);
-            v[k]    = (float)exp((double)s);
+            v[k]    = exp_f32(s);
             acc += (double)v[k];
         }
     }
@@ -433,7 +434,7 @@ __global__ void __launch_bounds__(256) softmax_rows_warp_kernel(const float *in,
         int64_t j = (int64_t)k * 32 + lane;
         if (j < cols) {
             float s = __fsub_rn(v[k], best);
-            v[k]    = (float)exp((double)s);
+            v[k]    = exp_f32(s);
             acc += (double)v[k];
         }
     }
@@ -471,7 +472,7 @@ __global__ void __launch_bounds__(256) softmax_rows_stream_kernel(const float *i
         m = r[0];
     double acc = 0.0;
     for (int64_t j = threadIdx.x; j < cols; j += 256) {
-        float e = (float)exp((double)__fsub_rn(r[j], m));
+        float e = exp_f32(__fsub_rn(r[j], m));
         o[j]    = e;
         acc += (double)e;
     }
@@ -600,7 +601,7 @@ ct_status ct_softmax_rows(const float *in, int64_t rows, int64_t cols, float *ou
     else if (cols <= 2048)
         softmax_rows_kernel<8, 256><<<(unsigned)rows, 256, 0, stream()>>>(in, rows, cols, out);
     else if (cols <= 8192)
-        softmax_rows_kernel<32, 256><<<(unsigned)rows, 256, 0, stream()>>>(in, rows, cols, out);
+        softmax_rows_kernel<8, 1024><<<(unsigned)rows, 1024, 0, stream()>>>(in, rows, cols, out);
     else
         softmax_rows_stream_kernel<<<(unsigned)rows, 256, 0, stream()>>>(in, rows, cols, out);
     CT_LAUNCH_CHECK("softmax_rows");
