@@ -1,0 +1,236 @@
+// Plain-C test harness around the plugin's operator table: builds ArgsViews from raw buffers,
+// calls an operator body exactly as Camel's executors do - op(withView, normView, ctx)
+// (src/passes/sched/nodevm/nodevm.cpp:588) - and hands the result back as raw buffers.  The
+// argument and result structs have the layout of the oracle's reference driver, so one Python
+// front end drives both the reference module and this plugin.
+#include "camel/core/error/runtime.h"
+#include "camel/core/mm.h"
+#include "camel/core/operator.h"
+#include "camel/core/rtdata/array.h"
+#include "camel/core/type/composite/array.h"
+#include "device_tensor.h"
+#include "tensor_ops.h"
+#include "type.h"
+
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+using camel::tensor::TensorObject;
+using camel::tensor::TensorType;
+namespace mm = camel::core::mm;
+using camel::core::type::ArrayType;
+using camel::core::type::Type;
+using camel::core::type::TypeCode;
+
+namespace {
+
+struct VecArgsView final : ArgsView {
+    std::vector<slot_t> slots;
+    std::vector<Type *> types;
+    size_t size() const override { return slots.size(); }
+    slot_t slot(size_t i) const override { return slots[i]; }
+    void setSlot(size_t i, slot_t v) override { slots[i] = v; }
+    TypeCode code(size_t i) const override { return types[i]->code(); }
+    Type *type(size_t i) const override { return types[i]; }
+};
+
+// Object headers of the arguments live in malloc blocks that are released after the call.
+class ScratchAllocator final : public mm::IAllocator {
+  public:
+    void *alloc(size_t size, size_t) override {
+        auto *base = static_cast<std::byte *>(std::calloc(1, size + 64));
+        if (!base)
+            return nullptr;
+        blocks_.push_back(base);
+        return base + 64;
+    }
+    void free(void *) override {}
+    void releaseAll() {
+        for (auto *b : blocks_)
+            std::free(b);
+        blocks_.clear();
+    }
+
+  private:
+    std::vector<std::byte *> blocks_;
+};
+
+ScratchAllocator g_scratch;
+void *g_lastOut = nullptr;
+
+TypeCode dtypeCode(int d) { return d == 0 ? TypeCode::Float32 : (d == 1 ? TypeCode::Int64 : TypeCode::Bool); }
+Type *dtypeType(int d) { return d == 0 ? Type::Float32() : (d == 1 ? Type::Int64() : Type::Bool()); }
+
+Type *tensorTypeFor(int dtype) {
+    static Type *cache[3] = {nullptr, nullptr, nullptr};
+    int k                 = dtype < 0 || dtype > 2 ? 2 : dtype;
+    if (!cache[k])
+        cache[k] = TensorType::Dynamic(dtypeType(k));
+    return cache[k];
+}
+
+} // namespace
+
+extern "C" {
+
+// kind (low byte): 0 tensor, 1 int64, 2 float64, 3 float32, 4 int32, 5 bool, 6 int64 array;
+// kind | 0x100 places the argument in the `with` list instead of the `norm` list.
+struct camel_host_arg {
+    int32_t kind, dtype, rank, pad_;
+    const int64_t *shape;
+    const void *data;
+    double f64;
+    int64_t i64;
+};
+
+struct camel_host_out {
+    int32_t kind, dtype, rank, pad_; // kind: 0 tensor, 1 float64, 2 int64 array, 3 null
+    int64_t shape[8];
+    uint64_t numel;
+    const void *data; // owned by the harness until the next call
+    double f64;
+    double seconds;
+};
+
+int camel_ref_call(const char *op, int nargs, const camel_host_arg *args, camel_host_out *out, char *err, int errlen) {
+    auto fail = [&](int rc, const std::string &msg) {
+        if (err && errlen > 0) {
+            std::strncpy(err, msg.c_str(), static_cast<size_t>(errlen) - 1);
+            err[errlen - 1] = '\0';
+        }
+        return rc;
+    };
+    try {
+        // everything the previous call created is garbage now
+        g_scratch.releaseAll();
+        camel::tensor::releaseAllDeviceBuffers();
+        std::free(g_lastOut);
+        g_lastOut = nullptr;
+
+        static const auto ops = getTensorOpsMap();
+        auto it               = ops.find(op);
+        if (it == ops.end())
+            return fail(2, std::string("unknown operator: ") + op);
+
+        VecArgsView with, norm;
+        for (int i = 0; i < nargs; ++i) {
+            const camel_host_arg &a = args[i];
+            VecArgsView &dst        = (a.kind & 0x100) ? with : norm;
+            switch (a.kind & 0xff) {
+            case 0: {
+                std::span<const int64_t> shape(a.shape, static_cast<size_t>(a.rank));
+                TensorObject *t = TensorObject::fromHost(dtypeCode(a.dtype), shape, a.data, g_scratch);
+                dst.slots.push_back(camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(t)));
+                dst.types.push_back(tensorTypeFor(a.dtype));
+                break;
+            }
+            case 1:
+                dst.slots.push_back(camel::core::rtdata::toSlot<int64_t>(a.i64));
+                dst.types.push_back(Type::Int64());
+                break;
+            case 2:
+                dst.slots.push_back(camel::core::rtdata::toSlot<double>(a.f64));
+                dst.types.push_back(Type::Float64());
+                break;
+            case 3:
+                dst.slots.push_back(camel::core::rtdata::toSlot<float>(static_cast<float>(a.f64)));
+                dst.types.push_back(Type::Float32());
+                break;
+            case 4:
+                dst.slots.push_back(camel::core::rtdata::toSlot<int32_t>(static_cast<int32_t>(a.i64)));
+                dst.types.push_back(Type::Int32());
+                break;
+            case 5:
+                dst.slots.push_back(camel::core::rtdata::toSlot<bool>(a.i64 != 0));
+                dst.types.push_back(Type::Bool());
+                break;
+            case 6: {
+                ::Array *arr = ::Array::create(g_scratch, static_cast<size_t>(a.rank));
+                for (int k = 0; k < a.rank; ++k)
+                    arr->set<int64_t>(static_cast<size_t>(k), a.shape[k]);
+                dst.slots.push_back(camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(arr)));
+                static Type *intArray = ArrayType::create(Type::Int64());
+                dst.types.push_back(intArray);
+                break;
+            }
+            default:
+                return fail(2, "bad argument kind");
+            }
+        }
+
+        camel::core::context::Context *nullCtx = nullptr; // no operator body touches the context
+        auto t0       = std::chrono::steady_clock::now();
+        slot_t result = it->second(with, norm, *nullCtx);
+        ct_sync();
+        auto t1 = std::chrono::steady_clock::now();
+
+        std::memset(out, 0, sizeof(*out));
+        out->seconds  = std::chrono::duration<double>(t1 - t0).count();
+        std::string n = op;
+        if (n == "sum" || n == "idx" || n == "idx2d") {
+            out->kind = 1;
+            out->f64  = camel::core::rtdata::fromSlot<double>(result);
+        } else if (n == "shape") {
+            auto *arr = camel::core::rtdata::fromSlot<::Array *>(result);
+            out->kind = 2;
+            out->rank = static_cast<int32_t>(arr->size());
+            for (size_t k = 0; k < arr->size() && k < 8; ++k)
+                out->shape[k] = arr->get<int64_t>(k);
+        } else if (n == "show") {
+            out->kind = 3;
+        } else {
+            auto *t    = camel::core::rtdata::fromSlot<TensorObject *>(result);
+            out->kind  = 0;
+            out->dtype = static_cast<int32_t>(t->ctDType());
+            out->rank  = static_cast<int32_t>(t->rank());
+            for (size_t k = 0; k < t->rank() && k < 8; ++k)
+                out->shape[k] = t->dim(k);
+            out->numel = t->numel();
+            if (t->byteSize() > 0) {
+                g_lastOut = std::malloc(t->byteSize());
+                std::memcpy(g_lastOut, t->rawData(), t->byteSize());
+            }
+            out->data = g_lastOut;
+            t->invalidateHost();
+        }
+        ct_status async = ct_check();
+        if (async != CT_OK)
+            return fail(1, ct_last_error());
+        return 0;
+    } catch (const camel::core::error::RuntimeFault &f) {
+        std::string msg;
+        for (const auto &s : f.formatArgs())
+            msg += s;
+        if (msg.empty())
+            msg = f.what();
+        return fail(1, msg);
+    } catch (const std::exception &e) {
+        return fail(1, e.what());
+    }
+}
+
+int camel_ref_list_ops(char *buf, int buflen) {
+    std::string s;
+    for (const auto &kv : getTensorOpsMap())
+        s += kv.first + "\n";
+    if (static_cast<int>(s.size()) + 1 > buflen)
+        return -static_cast<int>(s.size()) - 1;
+    std::memcpy(buf, s.c_str(), s.size() + 1);
+    return static_cast<int>(s.size());
+}
+
+int camel_ref_list_groups(char *buf, int buflen) {
+    std::string s;
+    for (const auto &g : getTensorOperatorGroups())
+        for (const auto &[uri, resolver] : g->resolvers())
+            s += g->name() + "\t" + uri + "\t" + resolver->signature() + "\n";
+    if (static_cast<int>(s.size()) + 1 > buflen)
+        return -static_cast<int>(s.size()) - 1;
+    std::memcpy(buf, s.c_str(), s.size() + 1);
+    return static_cast<int>(s.size());
+}
+
+} // extern "C"

@@ -250,12 +250,14 @@ empty = zeros  # tensorEmpty also zero-initialises (runtime.cpp:614-617)
 
 
 def ones(shape) -> Tensor:
-    return full(shape, 1.0)
+    return full(shape, 1.0)  # always Float32 (operators.cpp:991-1001)
 
 
 def full(shape, value: Number) -> Tensor:
-    t = Tensor(L.F32, _shape_arg(shape))
-    check(lib.ct_fill(L.F32, float(value), t.numel, t.ptr))
+    # the tensor's dtype follows the value's type (operators.cpp:1003-1014): int -> Int64, ...
+    dt = _scalar_dtype(value)
+    t = Tensor(dt, _shape_arg(shape))
+    check(lib.ct_fill(dt, float(value), t.numel, t.ptr))
     return t
 
 

@@ -260,14 +260,25 @@ class Float32(float):
     """Marks a scalar as Camel float32 (plain Python floats are float64)."""
 
 
+class With:
+    """Marks an argument as a `with` parameter (`op<w, b>(x)`): the plugin's added operators
+    take their weights that way; the reference's own operators have none."""
+
+    def __init__(self, value):
+        self.value = value
+
+
 class Reference:
     """Calls `tensor:<op>` of the compiled reference.  Arguments: numpy arrays (tensors),
     Python int (Int64) / float (Float64) / bool scalars, Float32(...), IntArray([...])."""
 
-    def __init__(self):
-        if not REF_LIB.exists():
-            raise OracleError(f"{REF_LIB} not built (run `make -C oracle ref` where the reference checkout is)")
-        self.lib = C.CDLL(str(REF_LIB))
+    def __init__(self, lib_path=None):
+        """lib_path: another library with the same driver entry points (the plugin's own test
+        harness, camel_b200/host/_build/libcamel_tensor_host_test.so); default: the reference."""
+        path = Path(lib_path) if lib_path else REF_LIB
+        if not path.exists():
+            raise OracleError(f"{path} not built (run `make -C oracle ref` where the reference checkout is)")
+        self.lib = C.CDLL(str(path))
         self.last_seconds = 0.0
 
     @staticmethod
@@ -288,6 +299,9 @@ class Reference:
         keep, cargs = [], (_Arg * len(args))()
         for i, a in enumerate(args):
             x = cargs[i]
+            in_with = isinstance(a, With)
+            if in_with:
+                a = a.value
             if isinstance(a, np.ndarray):
                 arr, dt = norm(a)
                 shp = (C.c_int64 * max(1, arr.ndim))(*arr.shape)
@@ -307,6 +321,8 @@ class Reference:
                 x.kind, x.f64 = 2, float(a)
             else:
                 raise OracleError(f"unsupported argument {type(a)}")
+            if in_with:
+                x.kind |= 0x100
         out, err = _Out(), C.create_string_buffer(512)
         rc = self.lib.camel_ref_call(op.encode(), len(args), cargs, C.byref(out), err, 512)
         if rc:

@@ -76,7 +76,7 @@ class PortBackend:
         return self.p.full(oracle.F32, 0.0, tuple(shape))
 
     def full(self, shape, v):
-        return self.p.full(oracle.F32, v, tuple(shape))
+        return self.p.full(oracle.scalar_dtype(v), v, tuple(shape))  # dtype follows the value's type
 
     def eye(self, n):
         return self.p.eye(n)
@@ -159,7 +159,7 @@ class RefBackend:
         return self.r.call("zeros", IntArray(shape))
 
     def full(self, shape, v):
-        return self.r.call("full", IntArray(shape), float(v))
+        return self.r.call("full", IntArray(shape), v)
 
     def eye(self, n):
         return self.r.call("eye", int(n))
@@ -304,7 +304,8 @@ def build_cases():
 
     @case("constructors")
     def _(be):
-        return [be.zeros([3, 5]), be.ones([2, 3, 4]), be.full([7], 2.5), be.full([2, 2], -1), be.eye(1), be.eye(9),
+        return [be.zeros([3, 5]), be.ones([2, 3, 4]), be.full([7], 2.5), be.full([2, 2], -1), be.full([3], True),
+                be.eye(1), be.eye(9),
                 be.range(0, 10, 1), be.range(2, 11, 3), be.range(10, 0, -3), be.range(5, 5, 1), be.zeros([0, 4])]
 
     # -- contractions: tolerance-checked on the GPU, bit-exact between the CPU checkers

@@ -1,0 +1,139 @@
+"""The C++ host side of the plugin (camel_b200/host): `tensor.cmo` and its operator tables.
+
+CPU: the built plugin exports the two entry points Camel's loader looks up
+(src/core/module/dynamic.cpp:83-126), its registration table equals the reference's, entry by
+entry, and operators refuse to run without a GPU.
+GPU: every parity case of tests/cases.py through the plugin's real operator bodies
+(`operator_t(with, norm, ctx)` over an ArgsView, as the graph executors call them), compared with
+the CPU oracle under the same bars as the C-ABI tests.
+
+The libraries are built by camel_b200/host/Makefile where the reference headers are; the built
+files travel with the repository snapshot.
+"""
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle
+from cases import CASES, PortBackend, RefBackend
+from oracle import IntArray, With
+
+ROOT = Path(__file__).resolve().parents[1]
+BUILD = ROOT / "camel_b200" / "host" / "_build"
+CMO = BUILD / "tensor.cmo"
+HARNESS = BUILD / "libcamel_tensor_host_test.so"
+
+needs_build = pytest.mark.skipif(not HARNESS.exists(), reason="camel_b200/host/_build not built (needs the reference headers)")
+
+
+@pytest.fixture(scope="module")
+def plugin():
+    return oracle.Reference(HARNESS)
+
+
+@needs_build
+def test_cmo_exports_loader_entry_points():
+    syms = subprocess.run(["nm", "-D", "--defined-only", str(CMO)], capture_output=True, text=True).stdout
+    assert " T camel_module_abi_version" in syms
+    assert " T camel_module_create" in syms
+
+
+@needs_build
+def test_registration_table_equals_reference(plugin):
+    """Group, URI and signature string of all 37 reference entries, in order; the plugin's own
+    operators come after them."""
+    ref = [tuple(l.split("\t")) for l in (ROOT / "tests/golden/operator_table.tsv").read_text().splitlines()]
+    mine = plugin.groups()
+    assert mine[: len(ref)] == ref
+    extra = {u for _, u, _ in mine[len(ref):]}
+    assert extra == {"tensor:relu", "tensor:softmax", "tensor:dense", "tensor:dense_relu", "tensor:dense_softmax",
+                     "tensor:conv2d", "tensor:conv2d_relu", "tensor:maxpool2d", "tensor:flatten"}
+    ops = set(plugin.ops())
+    assert {u.split(":")[1] for _, u, _ in mine} == ops
+    if oracle.Reference.available():
+        assert set(oracle.ref().ops()) <= ops
+
+
+@needs_build
+def test_no_gpu_no_result(plugin):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(oracle.OracleError, match="no CUDA device"):
+        plugin.call("add", np.ones(4, np.float32), np.ones(4, np.float32))
+
+
+class PluginBackend(RefBackend):
+    """The reference's operator names on the plugin's tables; relu / softmax / dense are the
+    plugin's fused operators instead of the compositions."""
+
+    name = "plugin"
+
+    def __init__(self, plugin):
+        self.r = plugin
+
+    def relu(self, a):
+        return self.r.call("relu", a)
+
+    def softmax(self, a):
+        return self.r.call("softmax", a)
+
+    def dense(self, x, w, b, act):
+        if b is None:
+            y = self.r.call("matmul", x, w)
+            return self.r.call("relu", y) if act == "relu" else y
+        return self.r.call("dense_relu" if act == "relu" else "dense", With(w), With(np.asarray(b, np.float32)), x)
+
+
+@needs_build
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,fn", CASES, ids=[c[0] for c in CASES])
+def test_plugin_operators_match_oracle(name, fn, plugin, golden):
+    from test_gpu_parity import compare_outputs
+
+    got = fn(PluginBackend(plugin))
+    ref = fn(PortBackend())
+    assert len(got) == len(ref)
+    for i, (g, r) in enumerate(zip(got, ref)):
+        compare_outputs(name, g, r, f"{name}[{i}] vs oracle")
+        compare_outputs(name, g, golden[f"{name}/{i}"], f"{name}[{i}] vs golden")
+
+
+@needs_build
+@pytest.mark.gpu
+def test_plugin_errors_shapes_and_new_operators(plugin):
+    a = np.arange(12, dtype=np.float32).reshape(3, 4)
+    with pytest.raises(oracle.OracleError, match="Division by zero"):
+        plugin.call("divide", a, np.zeros((3, 4), np.float32))
+    with pytest.raises(oracle.OracleError, match="log: input must be positive"):
+        plugin.call("log", a)
+    with pytest.raises(oracle.OracleError, match="matching shapes"):
+        plugin.call("add", a, a.T.copy())
+    with pytest.raises(oracle.OracleError, match="matmul dimension mismatch"):
+        plugin.call("matmul", a, a)
+    assert plugin.call("shape", a) == [3, 4]
+    assert plugin.call("idx2d", a, 2, 1) == 9.0
+    assert plugin.call("sum", a) == 66.0
+    assert plugin.call("full", IntArray([2, 2]), 3).dtype == np.int64  # dtype follows the value's type
+    assert plugin.call("range", 5).tolist() == [0, 1, 2, 3, 4]
+
+    rng = np.random.default_rng(21)
+    p = oracle.port()
+    x = rng.standard_normal((2, 16, 12, 12)).astype(np.float32)
+    w = (rng.standard_normal((32, 16, 3, 3)) * 0.1).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, 32).astype(np.float32)
+    got = plugin.call("conv2d_relu", With(w), With(b), With(1), With(1), x)
+    ref = p.conv2d(x, w, b, 1, 1, 1)
+    assert got.shape == ref.shape
+    assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) <= 1e-5
+    pooled = plugin.call("maxpool2d", got, 2)
+    assert pooled.tobytes() == p.maxpool2d(got, 2).tobytes()
+    flat = plugin.call("flatten", pooled)
+    assert flat.shape == (2, 32 * 6 * 6)
+    logits_w = rng.uniform(-0.05, 0.05, (flat.shape[1], 10)).astype(np.float32)
+    probs = plugin.call("dense_softmax", With(logits_w), With(np.zeros(10, np.float32)), flat)
+    ref_probs = p.softmax_rows(p.dense(flat, logits_w, np.zeros(10, np.float32), 0))
+    assert np.max(np.abs(probs - ref_probs)) <= 1e-5
