@@ -31,6 +31,8 @@ struct DeviceState {
     size_t reduce_ws_bytes = 0;
     void *gemm_ws        = nullptr; // split operand planes of the tensor-core GEMM
     size_t gemm_ws_bytes = 0;
+    void *splitk_ws      = nullptr; // partial outputs of the split-K GEMM
+    size_t splitk_ws_bytes = 0;
     void *stage_ws[3]    = {nullptr, nullptr, nullptr}; // device staging of the *_host forms
     size_t stage_ws_bytes[3] = {0, 0, 0};
 };

@@ -42,7 +42,38 @@ __device__ __forceinline__ double exp_from_f32(double x) {
     return p * scale;
 }
 
-__device__ __forceinline__ float exp_f32(float x) { return (float)exp_from_f32((double)x); }
+// float32 in, float32 out.  The common range |x| <= 87 (result a normal float32) takes a path
+// without clamps or special cases and scales by adding k to the exponent field; everything else
+// (NaN, results that overflow, underflow or are subnormal) goes through exp_from_f32.  The
+// operators built on this are bound by instruction issue, so every instruction counts.
+__device__ __forceinline__ float exp_f32(float xf) {
+    if (fabsf(xf) <= 87.0f) {
+        const double kLog2e = 1.4426950408889634074;
+        const double kLn2Hi = 6.93147180369123816490e-01;
+        const double kLn2Lo = 1.90821492927058770002e-10;
+        const double kMagic = 6755399441055744.0;
+        double x  = (double)xf;
+        double t  = fma(x, kLog2e, kMagic);
+        int k     = __double2loint(t);
+        double kd = t - kMagic;
+        double r  = fma(-kd, kLn2Hi, x);
+        r         = fma(-kd, kLn2Lo, r);
+        double p  = 1.0 / 39916800.0;
+        p         = fma(p, r, 1.0 / 3628800.0);
+        p         = fma(p, r, 1.0 / 362880.0);
+        p         = fma(p, r, 1.0 / 40320.0);
+        p         = fma(p, r, 1.0 / 5040.0);
+        p         = fma(p, r, 1.0 / 720.0);
+        p         = fma(p, r, 1.0 / 120.0);
+        p         = fma(p, r, 1.0 / 24.0);
+        p         = fma(p, r, 1.0 / 6.0);
+        p         = fma(p, r, 0.5);
+        p         = fma(p, r, 1.0);
+        p         = fma(p, r, 1.0);
+        return (float)__hiloint2double(__double2hiint(p) + (k << 20), __double2loint(p));
+    }
+    return (float)exp_from_f32((double)xf);
+}
 
 // log tables: for m in [1, 2], j = round((m - 1) * 128), c_j = 1 + j/128:
 // rc[j] = 1/c_j, lc[j] = log(c_j), with lc[128] the same double as ln 2 so that values just

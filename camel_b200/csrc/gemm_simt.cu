@@ -195,9 +195,10 @@ __global__ void __launch_bounds__(256) gemm_skinny_smem_kernel(
     // staged transposed [n][k] and already widened to float64: the float32 -> float64
     // conversions run on the slow special-function pipe, so they are paid once per weight
     // and block here instead of once per multiply-add
-    for (int64_t i = threadIdx.x; i < k * n; i += 256) {
-        int64_t kk = i / n, j = i - kk * n;
-        w_s[j * k + kk] = (double)w[i];
+    const int total = (int)(k * n); // <= 25600 by the dispatch condition
+    for (int i = threadIdx.x; i < total; i += 256) {
+        int kk = i / n, j = i - kk * n;
+        w_s[(int64_t)j * k + kk] = (double)w[i];
     }
     __syncthreads();
     const int lane     = threadIdx.x & 31;
@@ -211,19 +212,33 @@ __global__ void __launch_bounds__(256) gemm_skinny_smem_kernel(
         for (int j = 0; j < N_MAX; ++j)
             acc[j] = 0.0;
         if (vec) {
-            for (int64_t kk = (int64_t)lane * 4; kk < k; kk += 128) {
-                float4 q = __ldcs(reinterpret_cast<const float4 *>(xr + kk));
-                double x0 = (double)q.x, x1 = (double)q.y, x2 = (double)q.z, x3 = (double)q.w;
+            // eight 128-bit loads in flight per lane before any arithmetic: with few resident warps
+            // the row would otherwise be one load-latency per 128 values of k
+            constexpr int kChunk = 8;
+            for (int64_t kk0 = (int64_t)lane * 4; kk0 < k; kk0 += 128 * kChunk) {
+                float4 q[kChunk];
 #pragma unroll
-                for (int j = 0; j < N_MAX; ++j)
-                    if (j < n) {
-                        const double2 *wp = reinterpret_cast<const double2 *>(w_s + (int64_t)j * k + kk);
-                        double2 wa = wp[0], wb = wp[1];
-                        acc[j] += x0 * wa.x;
-                        acc[j] += x1 * wa.y;
-                        acc[j] += x2 * wb.x;
-                        acc[j] += x3 * wb.y;
-                    }
+                for (int c = 0; c < kChunk; ++c) {
+                    int64_t kk = kk0 + (int64_t)c * 128;
+                    q[c]       = kk < k ? __ldcs(reinterpret_cast<const float4 *>(xr + kk)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int c = 0; c < kChunk; ++c) {
+                    int64_t kk = kk0 + (int64_t)c * 128;
+                    if (kk >= k)
+                        break;
+                    double x0 = (double)q[c].x, x1 = (double)q[c].y, x2 = (double)q[c].z, x3 = (double)q[c].w;
+#pragma unroll
+                    for (int j = 0; j < N_MAX; ++j)
+                        if (j < n) {
+                            const double2 *wp = reinterpret_cast<const double2 *>(w_s + (int64_t)j * k + kk);
+                            double2 wa = wp[0], wb = wp[1];
+                            acc[j] += x0 * wa.x;
+                            acc[j] += x1 * wa.y;
+                            acc[j] += x2 * wb.x;
+                            acc[j] += x3 * wb.y;
+                        }
+                }
             }
         } else {
             for (int64_t kk = lane; kk < k; kk += 32) {

@@ -70,6 +70,7 @@ struct GemmParams {
     int64_t out_batch_stride; // elements between consecutive outputs of the batch
     int bias_per_row;         // bias indexed by output row (conv: one per output channel)
     uint32_t *flags;
+    int kb_per_split;         // > 0: split-K, k-blocks per slice (slices take the batch index)
     int tile_n;               // output columns per tile: BN, or th*wo for the implicit-GEMM conv
     // implicit-GEMM convolution (conv != 0): the B operand is the NHWC input itself, fetched by
     // 4-D TMA boxes shifted by the filter tap, instead of a materialised patch matrix
@@ -255,7 +256,12 @@ __global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
-    const int nkb        = p.num_k_blocks;
+    // split-K (kb_per_split > 0): the leading block index selects a slice of the k-blocks instead
+    // of a batch entry; every slice writes its own partial output, summed by a second kernel
+    const int kb_first = p.kb_per_split > 0 ? tz * p.kb_per_split : 0;
+    const int kb_left  = p.num_k_blocks - kb_first;
+    const int nkb      = p.kb_per_split > 0 ? (kb_left < p.kb_per_split ? kb_left : p.kb_per_split) : p.num_k_blocks;
+    const int bz       = p.kb_per_split > 0 ? 0 : tz; // batch coordinate of the B operand
     const int chunk      = p.chunk_blocks;
     const int num_chunks = (nkb + chunk - 1) / chunk;
 
@@ -271,7 +277,7 @@ __global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
                 uint32_t full = smem_u32(&bar_full[s]);
                 uint32_t dst  = stage_addr(s);
                 mbar_expect_tx(full, (uint32_t)(C::kPlanes * (C::kABytes + p.tile_n * ROW_B)));
-                int32_t kc = kb * C::kBlockK;
+                int32_t kc = (kb_first + kb) * C::kBlockK;
                 tma_load_2d(dst, &map_a_hi, full, kc, tm * BM);
                 dst += C::kABytes;
                 if (MODE == MODE_3X) {
@@ -289,10 +295,10 @@ __global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
                     if (MODE == MODE_3X)
                         tma_load_4d(dst, &map_b_lo, full, c0, w0, h0, tz);
                 } else {
-                    tma_load_3d(dst, &map_b_hi, full, kc, tn * BN, tz);
+                    tma_load_3d(dst, &map_b_hi, full, kc, tn * BN, bz);
                     dst += C::kBBytes;
                     if (MODE == MODE_3X)
-                        tma_load_3d(dst, &map_b_lo, full, kc, tn * BN, tz);
+                        tma_load_3d(dst, &map_b_lo, full, kc, tn * BN, bz);
                 }
                 issued = kb + 1;
             }
@@ -532,8 +538,11 @@ template <int BN, int MODE>
 ct_status launch_gemm(
     DeviceState *st, const void *a_hi, const void *a_lo, const void *b_hi, const void *b_lo,
     int64_t m, int64_t n, int64_t kp, const float *bias, int act, float *out, int batch,
-    int64_t out_batch_stride, int bias_per_row, const ConvGeom *cg) {
+    int64_t out_batch_stride, int bias_per_row, const ConvGeom *cg, int splits = 1) {
     using C = Cfg<BN, MODE>;
+    // split-K: `splits` slices of the k range, each writing m*n partial sums `out_batch_stride`
+    // apart; the operand maps keep their own (single) batch entry
+    const int grid_batch = splits > 1 ? splits : batch;
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
     CT_TRY(make_plane_map(&ma_hi, a_hi, C::kElem, m, kp, BM, 0));
     if (cg)
@@ -566,6 +575,7 @@ ct_status launch_gemm(
     p.bias_per_row = bias_per_row;
     p.flags        = st->flags_dev;
     p.tile_n       = BN;
+    p.kb_per_split = splits > 1 ? (p.num_k_blocks + splits - 1) / splits : 0;
     p.conv         = 0;
     p.conv_cblocks = p.conv_kw = p.conv_pad = p.conv_th = 0;
     if (cg) {
@@ -579,7 +589,7 @@ ct_status launch_gemm(
         if (p.tile_n > BN || (p.tile_n & 15) != 0)
             return fail(CT_ERR_INVALID, "conv2d: internal tile shape %d not usable", p.tile_n);
     }
-    int64_t tiles  = (int64_t)p.tiles_m * p.tiles_n * batch;
+    int64_t tiles  = (int64_t)p.tiles_m * p.tiles_n * grid_batch;
     if (tiles > 0x7fffffffll)
         return fail(CT_ERR_TOO_LARGE, "gemm: too many tiles");
     static bool attr_set = false;
@@ -597,6 +607,25 @@ ct_status launch_gemm(
 
 } // namespace
 
+namespace {
+// out[i] = act(sum_z partial[z][i] + bias[i % n]), slices added in ascending order.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(
+    const float *__restrict__ partial, int splits, int64_t total, int64_t n, const float *__restrict__ bias,
+    int act, float *__restrict__ out) {
+    int64_t step = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+        float v = partial[i];
+        for (int z = 1; z < splits; ++z)
+            v = __fadd_rn(v, partial[(int64_t)z * total + i]);
+        if (bias)
+            v = __fadd_rn(v, bias[i % n]);
+        if (act == CT_ACT_RELU)
+            v = __fmul_rn(v, v > 0.0f ? 1.0f : 0.0f);
+        out[i] = v;
+    }
+}
+} // namespace
+
 // Contraction over prepared operand planes: out[z][m][n] = act(A[m][kp] . B[z][n][kp]^T + bias).
 ct_status gemm_planes(
     DeviceState *st, int mode, const void *a_hi, const void *a_lo, const void *b_hi,
@@ -609,6 +638,40 @@ ct_status gemm_planes(
         wide = atoi(getenv("CAMEL_TENSOR_BN")) == 256;
     if (conv)
         wide = conv->th * conv->wo > 128;
+    // Few output tiles and a long reduction (e.g. a 12544 -> 128 layer): slice k across CTAs so
+    // that the whole machine works, partial sums in a workspace, one pass to add them up.
+    if (!conv && batch == 1 && !bias_per_row && !getenv("CAMEL_TENSOR_NO_SPLITK")) {
+        const int kblock  = mode == MODE_3X ? 32 : 64;
+        const int nkb     = (int)(kp / kblock);
+        int64_t tiles     = ((m + BM - 1) / BM) * ((n + (wide ? 255 : 127)) / (wide ? 256 : 128));
+        int splits        = (int)(st->sm_count / (tiles > 0 ? tiles : 1));
+        if (splits > nkb / 8)
+            splits = nkb / 8;
+        if (splits > 32)
+            splits = 32;
+        if (tiles * 2 <= st->sm_count && splits >= 2) {
+            int per = (nkb + splits - 1) / splits;
+            splits  = (nkb + per - 1) / per; // no empty slice
+            size_t bytes = (size_t)splits * m * n * sizeof(float);
+            CT_TRY(ensure_ws(&st->splitk_ws, &st->splitk_ws_bytes, bytes));
+            float *partial = static_cast<float *>(st->splitk_ws);
+#define CT_SPLIT_ARGS st, a_hi, a_lo, b_hi, b_lo, m, n, kp, nullptr, CT_ACT_NONE, partial, 1, m * n, 0, nullptr, splits
+            if (mode == MODE_3X)
+                CT_TRY(wide ? launch_gemm<256, MODE_3X>(CT_SPLIT_ARGS) : launch_gemm<128, MODE_3X>(CT_SPLIT_ARGS));
+            else
+                CT_TRY(wide ? launch_gemm<256, MODE_BF>(CT_SPLIT_ARGS) : launch_gemm<128, MODE_BF>(CT_SPLIT_ARGS));
+#undef CT_SPLIT_ARGS
+            int64_t total  = m * n;
+            int64_t blocks = (total + 255) / 256;
+            int64_t cap    = (int64_t)st->sm_count * 16;
+            if (blocks > cap)
+                blocks = cap;
+            ProfScope prof("gemm_splitk_reduce");
+            splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(partial, splits, total, n, bias, act, out);
+            CT_LAUNCH_CHECK("splitk_reduce");
+            return CT_OK;
+        }
+    }
 #define CT_GEMM_ARGS st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row, conv
     if (mode == MODE_3X)
         return wide ? launch_gemm<256, MODE_3X>(CT_GEMM_ARGS) : launch_gemm<128, MODE_3X>(CT_GEMM_ARGS);
@@ -772,6 +835,7 @@ ct_status launch_static(
     p.bias_per_row     = 0;
     p.flags            = s->flags;
     p.tile_n           = BN;
+    p.kb_per_split     = 0;
     p.conv             = 0;
     p.conv_cblocks = p.conv_kw = p.conv_pad = p.conv_th = 0;
     CT_CUDA(cudaFuncSetAttribute(

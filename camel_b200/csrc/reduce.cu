@@ -404,6 +404,69 @@ __global__ void __launch_bounds__(THREADS) softmax_rows_kernel(const float *in, 
     }
 }
 
+// Wide rows (cols a multiple of 4, 16-byte aligned rows, cols <= 4 * V4 * THREADS): the same
+// three phases with 128-bit loads and stores, and register use capped so that at least two
+// blocks share an SM - while one block sits in a reduction the other streams.
+template <int V4, int THREADS>
+__global__ void __launch_bounds__(THREADS, 2)
+    softmax_rows_wide_kernel(const float *__restrict__ in, int64_t rows, int64_t cols, float *__restrict__ out) {
+    constexpr int WARPS = THREADS / 32;
+    __shared__ float s_max[WARPS];
+    __shared__ double s_sum[WARPS];
+    const int64_t row = blockIdx.x;
+    const float4 *r   = reinterpret_cast<const float4 *>(in + row * cols);
+    float4 *o         = reinterpret_cast<float4 *>(out + row * cols);
+    const int nvec    = (int)(cols >> 2);
+    float4 v[V4];
+    float best = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < V4; ++k) {
+        int j = k * THREADS + threadIdx.x;
+        v[k]  = j < nvec ? __ldcs(r + j) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        best  = fmaxf(best, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
+    }
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1)
+        best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o2));
+    if ((threadIdx.x & 31) == 0)
+        s_max[threadIdx.x >> 5] = best;
+    __syncthreads();
+    float m = s_max[threadIdx.x & (WARPS - 1)];
+#pragma unroll
+    for (int o2 = WARPS / 2; o2 > 0; o2 >>= 1)
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o2));
+    float first = in[row * cols];
+    if (first != first)
+        m = first; // a NaN first element seeds the reference's scan and is never replaced
+    double acc = 0.0;
+#pragma unroll
+    for (int k = 0; k < V4; ++k) {
+        int j = k * THREADS + threadIdx.x;
+        if (j < nvec) {
+            v[k].x = exp_f32(__fsub_rn(v[k].x, m));
+            v[k].y = exp_f32(__fsub_rn(v[k].y, m));
+            v[k].z = exp_f32(__fsub_rn(v[k].z, m));
+            v[k].w = exp_f32(__fsub_rn(v[k].w, m));
+            acc += ((double)v[k].x + (double)v[k].y) + ((double)v[k].z + (double)v[k].w);
+        }
+    }
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0)
+        s_sum[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    double total = s_sum[threadIdx.x & (WARPS - 1)];
+#pragma unroll
+    for (int o2 = WARPS / 2; o2 > 0; o2 >>= 1)
+        total += __shfl_xor_sync(0xffffffffu, total, o2);
+    const float d = (float)total;
+#pragma unroll
+    for (int k = 0; k < V4; ++k) {
+        int j = k * THREADS + threadIdx.x;
+        if (j < nvec)
+            __stcs(o + j, make_float4(__fdiv_rn(v[k].x, d), __fdiv_rn(v[k].y, d), __fdiv_rn(v[k].z, d), __fdiv_rn(v[k].w, d)));
+    }
+}
+
 // Several short rows per block: one warp per row, row kept in registers.
 template <int PER_LANE>
 __global__ void __launch_bounds__(256) softmax_rows_warp_kernel(const float *in, int64_t rows, int64_t cols, float *out) {
@@ -598,7 +661,14 @@ ct_status ct_softmax_rows(const float *in, int64_t rows, int64_t cols, float *ou
         softmax_rows_warp_kernel<4><<<wblocks, 256, 0, stream()>>>(in, rows, cols, out);
     else if (cols <= 512)
         softmax_rows_warp_kernel<16><<<wblocks, 256, 0, stream()>>>(in, rows, cols, out);
-    else if (cols <= 2048)
+    else if (cols <= 8192 && (cols & 3) == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0) {
+        if (cols <= 2048)
+            softmax_rows_wide_kernel<1, 512><<<(unsigned)rows, 512, 0, stream()>>>(in, rows, cols, out);
+        else if (cols <= 4096)
+            softmax_rows_wide_kernel<2, 512><<<(unsigned)rows, 512, 0, stream()>>>(in, rows, cols, out);
+        else
+            softmax_rows_wide_kernel<4, 512><<<(unsigned)rows, 512, 0, stream()>>>(in, rows, cols, out);
+    } else if (cols <= 2048)
         softmax_rows_kernel<8, 256><<<(unsigned)rows, 256, 0, stream()>>>(in, rows, cols, out);
     else if (cols <= 8192)
         softmax_rows_kernel<8, 1024><<<(unsigned)rows, 1024, 0, stream()>>>(in, rows, cols, out);

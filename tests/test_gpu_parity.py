@@ -195,7 +195,21 @@ def _ref_matmul_f64(a, b):
     return (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
 
 
-@pytest.mark.parametrize("m,k,n", [(512, 512, 512), (384, 1000, 640), (1024, 784, 1024), (2048, 4096, 512)])
+def test_dense_split_k(T):
+    """Few output tiles, long reduction: the k range is sliced across CTAs and the partial sums
+    are added (with bias and relu) by a second kernel."""
+    rng = np.random.default_rng(12)
+    x = rng.uniform(0, 1, (300, 3000)).astype(np.float32)
+    w = rng.uniform(-0.05, 0.05, (3000, 100)).astype(np.float32)
+    b = rng.uniform(-0.5, 0.5, 100).astype(np.float32)
+    ref = np.maximum((x.astype(np.float64) @ w.astype(np.float64) + b).astype(np.float32), 0)
+    got = T.dense(T.from_numpy(x), T.from_numpy(w), T.from_numpy(b), "relu").numpy()
+    T.check_async()
+    assert _rel_err(got, ref) <= GEMM_TOL
+
+
+@pytest.mark.parametrize("m,k,n", [(512, 512, 512), (384, 1000, 640), (1024, 784, 1024), (2048, 4096, 512),
+                                   (256, 4096, 128), (130, 9000, 257)])
 def test_gemm_3xtf32_large(T, m, k, n):
     """Sizes past what the scalar oracle finishes quickly: numpy float64 matmul rounded once is
     the same function (the oracle agrees with it to the last bit on the sizes of tests/cases.py
@@ -345,6 +359,19 @@ def test_cnn_forward_cfg4_slice(T):
     srt = np.sort(logits, axis=1)
     decided = (srt[:, -1] - srt[:, -2]) > 1e-4 * np.max(np.abs(logits))
     assert np.array_equal(arg[decided], arg_ref[decided])
+
+
+def test_softmax_wide_rows(T):
+    """Row widths that take the 128-bit block kernels, incl. a NaN first element and -inf."""
+    rng = np.random.default_rng(31)
+    for shape in ((3, 516), (5, 2048), (2, 4100), (3, 8192), (2, 8196)):
+        x = rng.uniform(-8, 8, shape).astype(np.float32)
+        x[0, 5] = -np.inf
+        if shape[0] > 2:
+            x[2, 0] = np.nan
+        ref = oracle.port().softmax_rows(x)
+        got = T.softmax(T.from_numpy(x)).numpy()
+        compare_outputs("softmax_rows", got, ref, f"softmax {shape}")
 
 
 def test_maxpool2d(T):
