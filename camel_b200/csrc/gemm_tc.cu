@@ -656,11 +656,13 @@ ct_status gemm_planes(
             CT_TRY(ensure_ws(&st->splitk_ws, &st->splitk_ws_bytes, bytes));
             float *partial = static_cast<float *>(st->splitk_ws);
 #define CT_SPLIT_ARGS st, a_hi, a_lo, b_hi, b_lo, m, n, kp, nullptr, CT_ACT_NONE, partial, 1, m * n, 0, nullptr, splits
+            ct_status launched;
             if (mode == MODE_3X)
-                CT_TRY(wide ? launch_gemm<256, MODE_3X>(CT_SPLIT_ARGS) : launch_gemm<128, MODE_3X>(CT_SPLIT_ARGS));
+                launched = wide ? launch_gemm<256, MODE_3X>(CT_SPLIT_ARGS) : launch_gemm<128, MODE_3X>(CT_SPLIT_ARGS);
             else
-                CT_TRY(wide ? launch_gemm<256, MODE_BF>(CT_SPLIT_ARGS) : launch_gemm<128, MODE_BF>(CT_SPLIT_ARGS));
+                launched = wide ? launch_gemm<256, MODE_BF>(CT_SPLIT_ARGS) : launch_gemm<128, MODE_BF>(CT_SPLIT_ARGS);
 #undef CT_SPLIT_ARGS
+            CT_TRY(launched);
             int64_t total  = m * n;
             int64_t blocks = (total + 255) / 256;
             int64_t cap    = (int64_t)st->sm_count * 16;
