@@ -196,9 +196,21 @@ __global__ void __launch_bounds__(256) gemm_skinny_smem_kernel(
     // conversions run on the slow special-function pipe, so they are paid once per weight
     // and block here instead of once per multiply-add
     const int total = (int)(k * n); // <= 25600 by the dispatch condition
-    for (int i = threadIdx.x; i < total; i += 256) {
-        int kk = i / n, j = i - kk * n;
-        w_s[(int64_t)j * k + kk] = (double)w[i];
+    for (int base = threadIdx.x; base < total; base += 256 * 8) {
+        float tmp[8]; // eight independent loads in flight per thread, then the scattered stores
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            int i  = base + u * 256;
+            tmp[u] = i < total ? __ldg(w + i) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            int i = base + u * 256;
+            if (i < total) {
+                int kk = i / n, j = i - kk * n;
+                w_s[(int64_t)j * k + kk] = (double)tmp[u];
+            }
+        }
     }
     __syncthreads();
     const int lane     = threadIdx.x & 31;

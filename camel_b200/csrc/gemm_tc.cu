@@ -42,12 +42,18 @@ constexpr int ROW_B    = 128; // bytes of one operand row per k-block (= swizzle
 constexpr int MODE_3X  = 0;
 constexpr int MODE_BF  = 1;
 
-template <int BN, int MODE> struct Cfg {
+// RB = bytes of one operand row per k-block = swizzle span of the shared-memory tiles (128 or
+// 64).  A k-block of 64-byte rows halves the stage, so twice as many stages fit: with 96 KB
+// stages (BN = 256, 3xTF32, RB = 128) only two fit and the MMA warp waits on every TMA round
+// trip; four 48 KB stages cover that latency.
+template <int BN, int MODE, int RB = ROW_B> struct Cfg {
+    static constexpr int kRowB       = RB;
+    static constexpr int kKSteps     = RB / 32; // MMAs along k per k-block (32 bytes of k each)
     static constexpr int kElem       = MODE == MODE_3X ? 4 : 2;
-    static constexpr int kBlockK     = ROW_B / kElem; // elements of k per k-block
+    static constexpr int kBlockK     = RB / kElem; // elements of k per k-block
     static constexpr int kPlanes     = MODE == MODE_3X ? 2 : 1;
-    static constexpr int kABytes     = BM * ROW_B;
-    static constexpr int kBBytes     = BN * ROW_B;
+    static constexpr int kABytes     = BM * RB;
+    static constexpr int kBBytes     = BN * RB;
     static constexpr int kStageBytes = kPlanes * (kABytes + kBBytes);
     static constexpr int kStages     = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
     static constexpr int kEpiWarps   = BN / 32; // 128 accumulator columns per thread
@@ -182,12 +188,12 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(
 
 // ---- main kernel ------------------------------------------------------------------------
 
-template <int BN, int MODE>
-__global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
+template <int BN, int MODE, int RB = ROW_B>
+__global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel(
     const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
     const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
     const GemmParams p) {
-    using C = Cfg<BN, MODE>;
+    using C = Cfg<BN, MODE, RB>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full[C::kStages];
     __shared__ uint64_t bar_empty[C::kStages];
@@ -276,7 +282,7 @@ __global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
                     break;
                 uint32_t full = smem_u32(&bar_full[s]);
                 uint32_t dst  = stage_addr(s);
-                mbar_expect_tx(full, (uint32_t)(C::kPlanes * (C::kABytes + p.tile_n * ROW_B)));
+                mbar_expect_tx(full, (uint32_t)(C::kPlanes * (C::kABytes + p.tile_n * C::kRowB)));
                 int32_t kc = (kb_first + kb) * C::kBlockK;
                 tma_load_2d(dst, &map_a_hi, full, kc, tm * BM);
                 dst += C::kABytes;
@@ -343,10 +349,10 @@ __global__ void __launch_bounds__(Cfg<BN, MODE>::kThreads, 1) gemm_tc_kernel(
                     uint32_t a_lo = a_hi + C::kABytes;
                     uint32_t b_hi = a_hi + C::kPlanes * C::kABytes;
                     uint32_t b_lo = b_hi + C::kBBytes;
-                    uint64_t da_hi = smem_desc_k_sw128(a_hi), db_hi = smem_desc_k_sw128(b_hi);
-                    uint64_t da_lo = smem_desc_k_sw128(a_lo), db_lo = smem_desc_k_sw128(b_lo);
+                    uint64_t da_hi = smem_desc_k<RB>(a_hi), db_hi = smem_desc_k<RB>(b_hi);
+                    uint64_t da_lo = smem_desc_k<RB>(a_lo), db_lo = smem_desc_k<RB>(b_lo);
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
+                    for (int kk = 0; kk < C::kKSteps; ++kk) {
                         uint64_t adv = (uint64_t)(kk * 32 >> 4);
                         if (MODE == MODE_3X) {
                             // small terms first, then the leading term
@@ -483,19 +489,19 @@ ct_status encode_fn(EncodeTiledFn *out) {
 // 128-byte swizzle, out-of-range rows read as zero.
 ct_status make_plane_map(
     CUtensorMap *map, const void *base, int elem_bytes, int64_t rows, int64_t kp, int box_rows,
-    int batch /* 0: rank-2 map; >= 1: rank-3 map [batch][rows][kp] */) {
+    int batch /* 0: rank-2 map; >= 1: rank-3 map [batch][rows][kp] */, int row_bytes = ROW_B) {
     EncodeTiledFn fn;
     CT_TRY(encode_fn(&fn));
     cuuint64_t dims[3]    = {(cuuint64_t)kp, (cuuint64_t)rows, (cuuint64_t)(batch > 0 ? batch : 1)};
     cuuint64_t strides[2] = {(cuuint64_t)kp * (cuuint64_t)elem_bytes,
                              (cuuint64_t)kp * (cuuint64_t)elem_bytes * (cuuint64_t)rows};
-    cuuint32_t box[3]     = {(cuuint32_t)(ROW_B / elem_bytes), (cuuint32_t)box_rows, 1};
+    cuuint32_t box[3]     = {(cuuint32_t)(row_bytes / elem_bytes), (cuuint32_t)box_rows, 1};
     cuuint32_t estr[3]    = {1, 1, 1};
     CUtensorMapDataType dt =
         elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     CUresult r = fn(
         map, dt, batch > 0 ? 3 : 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
@@ -505,19 +511,20 @@ ct_status make_plane_map(
 // Tensor map over NHWC input planes [batch][h][w][c_pad] (channels contiguous); box = 32 channels
 // (one k-block) x wo columns x th rows of one image, 128-byte swizzle.  Written to shared memory
 // the box is th*wo rows of 128 bytes: the K-major B tile of th*wo output pixels.
-ct_status make_conv_map(CUtensorMap *map, const void *base, int elem_bytes, const ConvGeom &g, int batch) {
+ct_status make_conv_map(
+    CUtensorMap *map, const void *base, int elem_bytes, const ConvGeom &g, int batch, int row_bytes = ROW_B) {
     EncodeTiledFn fn;
     CT_TRY(encode_fn(&fn));
     cuuint64_t row        = (cuuint64_t)g.c_pad * (cuuint64_t)elem_bytes;
     cuuint64_t dims[4]    = {(cuuint64_t)g.c_pad, (cuuint64_t)g.w, (cuuint64_t)g.h, (cuuint64_t)batch};
     cuuint64_t strides[3] = {row, row * (cuuint64_t)g.w, row * (cuuint64_t)g.w * (cuuint64_t)g.h};
-    cuuint32_t box[4]     = {(cuuint32_t)(ROW_B / elem_bytes), (cuuint32_t)g.wo, (cuuint32_t)g.th, 1};
+    cuuint32_t box[4]     = {(cuuint32_t)(row_bytes / elem_bytes), (cuuint32_t)g.wo, (cuuint32_t)g.th, 1};
     cuuint32_t estr[4]    = {1, 1, 1, 1};
     CUtensorMapDataType dt =
         elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     CUresult r = fn(
         map, dt, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled (conv) failed with code %d", (int)r);
@@ -534,27 +541,27 @@ int chunk_blocks_setting() {
     return v;
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, int RB = ROW_B>
 ct_status launch_gemm(
     DeviceState *st, const void *a_hi, const void *a_lo, const void *b_hi, const void *b_lo,
     int64_t m, int64_t n, int64_t kp, const float *bias, int act, float *out, int batch,
     int64_t out_batch_stride, int bias_per_row, const ConvGeom *cg, int splits = 1) {
-    using C = Cfg<BN, MODE>;
+    using C = Cfg<BN, MODE, RB>;
     // split-K: `splits` slices of the k range, each writing m*n partial sums `out_batch_stride`
     // apart; the operand maps keep their own (single) batch entry
     const int grid_batch = splits > 1 ? splits : batch;
     CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
-    CT_TRY(make_plane_map(&ma_hi, a_hi, C::kElem, m, kp, BM, 0));
+    CT_TRY(make_plane_map(&ma_hi, a_hi, C::kElem, m, kp, BM, 0, RB));
     if (cg)
-        CT_TRY(make_conv_map(&mb_hi, b_hi, C::kElem, *cg, batch));
+        CT_TRY(make_conv_map(&mb_hi, b_hi, C::kElem, *cg, batch, RB));
     else
-        CT_TRY(make_plane_map(&mb_hi, b_hi, C::kElem, n, kp, BN, batch));
+        CT_TRY(make_plane_map(&mb_hi, b_hi, C::kElem, n, kp, BN, batch, RB));
     if (MODE == MODE_3X) {
-        CT_TRY(make_plane_map(&ma_lo, a_lo, C::kElem, m, kp, BM, 0));
+        CT_TRY(make_plane_map(&ma_lo, a_lo, C::kElem, m, kp, BM, 0, RB));
         if (cg)
-            CT_TRY(make_conv_map(&mb_lo, b_lo, C::kElem, *cg, batch));
+            CT_TRY(make_conv_map(&mb_lo, b_lo, C::kElem, *cg, batch, RB));
         else
-            CT_TRY(make_plane_map(&mb_lo, b_lo, C::kElem, n, kp, BN, batch));
+            CT_TRY(make_plane_map(&mb_lo, b_lo, C::kElem, n, kp, BN, batch, RB));
     } else {
         ma_lo = ma_hi;
         mb_lo = mb_hi;
@@ -563,7 +570,7 @@ ct_status launch_gemm(
     p.m            = m;
     p.n            = n;
     p.num_k_blocks = (int)(kp / C::kBlockK);
-    p.chunk_blocks = chunk_blocks_setting();
+    p.chunk_blocks = chunk_blocks_setting() * (ROW_B / RB); // same k extent per drain
     p.tiles_m      = (int)((m + BM - 1) / BM);
     p.tiles_n      = (int)((n + BN - 1) / BN);
     p.bias         = bias;
@@ -595,11 +602,11 @@ ct_status launch_gemm(
     static bool attr_set = false;
     if (!attr_set) {
         CT_CUDA(cudaFuncSetAttribute(
-            gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+            gemm_tc_kernel<BN, MODE, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
         attr_set = true;
     }
     ProfScope prof("gemm_tc");
-    gemm_tc_kernel<BN, MODE><<<(unsigned)tiles, C::kThreads, C::kSmemBytes, stream()>>>(
+    gemm_tc_kernel<BN, MODE, RB><<<(unsigned)tiles, C::kThreads, C::kSmemBytes, stream()>>>(
         ma_hi, ma_lo, mb_hi, mb_lo, p);
     CT_LAUNCH_CHECK("gemm_tc");
     return CT_OK;
@@ -675,8 +682,14 @@ ct_status gemm_planes(
         }
     }
 #define CT_GEMM_ARGS st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row, conv
-    if (mode == MODE_3X)
+    if (mode == MODE_3X) {
+        // 128 x 256 tiles of two float32 planes: 64-byte k-blocks give four 48 KB stages instead
+        // of two 96 KB ones (CAMEL_TENSOR_ROWB=128 selects the wide k-block for comparison)
+        static const bool narrow = !(getenv("CAMEL_TENSOR_ROWB") && atoi(getenv("CAMEL_TENSOR_ROWB")) == 128);
+        if (wide && narrow)
+            return launch_gemm<256, MODE_3X, 64>(CT_GEMM_ARGS);
         return wide ? launch_gemm<256, MODE_3X>(CT_GEMM_ARGS) : launch_gemm<128, MODE_3X>(CT_GEMM_ARGS);
+    }
     return wide ? launch_gemm<256, MODE_BF>(CT_GEMM_ARGS) : launch_gemm<128, MODE_BF>(CT_GEMM_ARGS);
 #undef CT_GEMM_ARGS
 }

@@ -220,6 +220,20 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr) {
     return d;
 }
 
+// Same for tiles whose rows are ROW_BYTES = 128 or 64 bytes wide, written by TMA with the
+// matching swizzle (SWIZZLE_128B: layout type 2, SWIZZLE_64B: layout type 4); 8-row groups are
+// 8 * ROW_BYTES apart.
+template <int ROW_BYTES> __device__ __forceinline__ uint64_t smem_desc_k(uint32_t smem_addr) {
+    static_assert(ROW_BYTES == 128 || ROW_BYTES == 64, "operand rows are 128 or 64 bytes");
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)((8 * ROW_BYTES) >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)(ROW_BYTES == 128 ? 2 : 4) << 61;
+    return d;
+}
+
 // Instruction descriptor, dense, float32 accumulator, both operands K-major.
 // ab_format: 0 f16, 1 bf16, 2 tf32.  Fields: c format [4,6) = 1 (f32), a format [7,10),
 // b format [10,13), n >> 3 [17,23), m >> 4 [24,29).
