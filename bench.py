@@ -224,6 +224,7 @@ class Workload:
     unit = ""
     dominant = "gemm_tc"
     bound = "tensor"
+    scaling = "weak"
 
     def units_per_step(self):  # in the metric's unit numerator
         raise NotImplementedError
@@ -354,6 +355,73 @@ class GemmWorkload(Workload):
     def config(self):
         return {"workload": f"gemm fp32 M=N=K={self.n} U(-1,1) (BASELINE configs[4] per-GPU problem)",
                 "precision": self.precision}
+
+
+class ShardedGemmWorkload(Workload):
+    """BASELINE configs[4] as one job: C = A.B with M=N=K=n, A split by rows over the ranks, B
+    replicated (placed once, outside the timed region), every rank ends up with all of C.  The
+    only exchange is the all-gather of C row blocks (NCCL over NVLink); it is issued per row panel
+    on a side stream so that panel j travels while panel j+1 is computed.  Strong scaling."""
+
+    name, metric, unit, scaling = "gemm_sharded", "gemm_fp32_tflops", "TFLOP/s", "strong"
+    PANELS = 4
+
+    def __init__(self, torch, dist, T, n, world, rank):
+        self.torch, self.dist, self.T, self.n, self.world, self.rank = torch, dist, T, n, world, rank
+        dev = torch.device("cuda")
+        g = torch.Generator(device=dev)
+        g.manual_seed(5)
+        a_full = torch.rand((n, n), generator=g, device=dev, dtype=torch.float32) * 2 - 1
+        self.b_t = torch.rand((n, n), generator=g, device=dev, dtype=torch.float32) * 2 - 1
+        self.rows = n // world
+        self.a_t = a_full[rank * self.rows:(rank + 1) * self.rows].contiguous()
+        del a_full
+        self.c_t = torch.empty((n, n), device=dev, dtype=torch.float32)  # the gathered product
+        self.panel_rows = self.rows // self.PANELS
+        self.side = torch.cuda.Stream()
+        torch.cuda.synchronize()
+        self.h2d = self.d2h = 0
+
+    def _gather(self, j):
+        """All-gather of panel j: rank r's rows land at their place in the full C."""
+        pr = self.panel_rows
+        mine = self.c_t[self.rank * self.rows + j * pr: self.rank * self.rows + (j + 1) * pr]
+        outs = [self.c_t[r * self.rows + j * pr: r * self.rows + (j + 1) * pr] for r in range(self.world)]
+        self.dist.all_gather(outs, mine)
+
+    def step(self):
+        from camel_b200._lib import check, lib
+        torch, n, pr = self.torch, self.n, self.panel_rows
+        for j in range(self.PANELS):
+            a_ptr = self.a_t.data_ptr() + j * pr * n * 4
+            c_ptr = self.c_t.data_ptr() + (self.rank * self.rows + j * pr) * n * 4
+            check(lib.ct_matmul(0, a_ptr, 0, self.b_t.data_ptr(), pr, n, n, c_ptr))
+            if self.world > 1:
+                done = torch.cuda.Event()
+                done.record()
+                with torch.cuda.stream(self.side):
+                    self.side.wait_event(done)
+                    self._gather(j)
+        if self.world > 1:
+            torch.cuda.current_stream().wait_stream(self.side)
+
+    def e2e_step(self):
+        self.step()
+
+    def units_per_step(self):
+        return 2.0 * self.n ** 3 / self.world / 1e12
+
+    def algorithmic_per_step(self):
+        return 2.0 * self.n ** 3 / self.world
+
+    def resident_bytes(self):
+        return 3 * self.n * self.n * 4
+
+    def config(self):
+        return {"workload": f"gemm fp32 M=N=K={self.n}, A row-sharded over {self.world} ranks, C all-gathered "
+                            f"in {self.PANELS} row panels overlapped with compute (BASELINE configs[4])",
+                "precision": "3xtf32", "e2e": "same as value: operands are resident by construction",
+                "parallelism": f"{self.world} ranks, rows of A and C sharded, NCCL all-gather of C on a side stream"}
 
 
 class ConvWorkload(Workload):
@@ -592,6 +660,8 @@ def run_gpu(args, rank, world):
         wl = MlpWorkload(torch, T, args.batch or 4096, use_graph=not args.eager)
     elif args.workload == "gemm":
         wl = GemmWorkload(torch, T, args.size, args.precision)
+    elif args.workload == "gemm_sharded":
+        wl = ShardedGemmWorkload(torch, dist, T, args.size, world, rank)
     elif args.workload == "conv":
         wl = ConvWorkload(torch, T, args.batch or 256)
     elif args.workload == "cnn":
@@ -699,10 +769,10 @@ def run_gpu(args, rank, world):
         cpu = cpu_baseline(args) if world == 1 and not args.no_cpu_baseline else None
         line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, f32 accumulate)"
+                "scaling": wl.scaling, "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, f32 accumulate)"
                 if args.precision != "bf16" else "bf16 in / f32 accumulate", "data": "synthetic",
-                "config": {**wl.config(), "l2": "flushed between steps" if flush is not None else "inputs larger than L2",
-                           "parallelism": f"{world} ranks, independent shards, no data-path collective"},
+                "config": {"parallelism": f"{world} ranks, independent shards, no data-path collective",
+                           **wl.config(), "l2": "flushed between steps" if flush is not None else "inputs larger than L2"},
                 "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                         "steps": e2e_steps, "wall_s": e2e_wall},
                 "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks}
@@ -744,7 +814,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="mlp", choices=["mlp", "gemm", "conv", "cnn", "add", "relu", "exp", "log", "mul", "scale", "gt", "sum",
+    ap.add_argument("--workload", default="mlp", choices=["mlp", "gemm", "gemm_sharded", "conv", "cnn", "add", "relu", "exp", "log", "mul", "scale", "gt", "sum",
                              "softmax"])
     ap.add_argument("--size", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=0)
