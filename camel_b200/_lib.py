@@ -48,6 +48,18 @@ PROTOTYPES = {
     "ct_h2d": (_int, [_vp, _vp, _sz]),
     "ct_d2h": (_int, [_vp, _vp, _sz]),
     "ct_d2d": (_int, [_vp, _vp, _sz]),
+    "ct_host_alloc": (_int, [C.POINTER(_vp), _sz]),
+    "ct_host_free": (_int, [_vp]),
+    "ct_h2d_async": (_int, [_vp, _vp, _sz]),
+    "ct_d2h_async": (_int, [_vp, _vp, _sz]),
+    "ct_stream_create": (_int, [C.POINTER(_vp)]),
+    "ct_stream_destroy": (_int, [_vp]),
+    "ct_event_create": (_int, [C.POINTER(_vp)]),
+    "ct_event_destroy": (_int, [_vp]),
+    "ct_event_record": (_int, [_vp]),
+    "ct_stream_wait_event": (_int, [_vp]),
+    "ct_event_sync": (_int, [_vp]),
+    "ct_event_elapsed_ms": (_int, [_vp, _vp, C.POINTER(C.c_float)]),
     "ct_result_dtype": (_int, [_int, _int, _int]),
     "ct_binary": (_int, [_int, _int, _vp, _int, _vp, _u64, _vp]),
     "ct_binary_scalar": (_int, [_int, _int, _vp, _dbl, _int, _int, _u64, _vp]),

@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(256) conv2d_small_c_kernel(
 #pragma unroll
             for (int u = 0; u < KD; ++u)
                 if (u < kdim)
-                    acc += (double)patch[u] * wr[u];
+                    acc = __fma_rn((double)patch[u], wr[u], acc); // exact product: same bits as mul, add
             if (bias)
                 acc += (double)bias[o];
             float v = (float)acc;

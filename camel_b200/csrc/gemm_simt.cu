@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(
 #pragma unroll
         for (int j = 0; j < N_MAX; ++j)
             if (j < n)
-                acc[j] += xv * (double)__ldg(wr + j);
+                acc[j] = __fma_rn(xv, (double)__ldg(wr + j), acc[j]); // float32 x float32 is exact in float64: same bits as mul, add
     }
 #pragma unroll
     for (int j = 0; j < N_MAX; ++j) {
@@ -133,28 +133,12 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(
         argmax[row] = best_idx;
 }
 
-// Finishes one output row held as per-lane partial sums: butterfly reduction, then bias,
-// activation, and (for softmax) the row softmax / argmax across the first n lanes.
-template <int N_MAX>
-__device__ __forceinline__ void skinny_finish_row(
-    double (&acc)[N_MAX], const float *__restrict__ bias, int64_t row, int n, int act, int lane,
-    float *__restrict__ out, int64_t *__restrict__ argmax) {
-#pragma unroll
-    for (int j = 0; j < N_MAX; ++j) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-            acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
-    }
-    float logit = 0.0f;
-#pragma unroll
-    for (int j = 0; j < N_MAX; ++j) {
-        if (j == lane && j < n) {
-            double v = acc[j];
-            if (bias)
-                v += (double)bias[j]; // the bias is the last term of the float64 sum
-            logit = (float)v;
-        }
-    }
+// Lane j < n holds the rounded logit of column j of one row: activation, and for softmax the
+// row softmax / argmax with the reference's scan semantics (element 0 seeds, a later element
+// wins only on strict '>').  Called by a whole warp.
+__device__ __forceinline__ void skinny_finish_logit(
+    float logit, int64_t row, int n, int act, int lane, float *__restrict__ out,
+    int64_t *__restrict__ argmax) {
     bool live = lane < n;
     if (act == CT_ACT_RELU)
         logit = __fmul_rn(logit, logit > 0.0f ? 1.0f : 0.0f);
@@ -181,6 +165,31 @@ __device__ __forceinline__ void skinny_finish_row(
         out[row * n + lane] = __fdiv_rn(e, d);
     if (argmax && lane == 0)
         argmax[row] = best_idx;
+}
+
+// Finishes one output row held as per-lane partial sums: butterfly reduction, then bias,
+// activation, and (for softmax) the row softmax / argmax across the first n lanes.
+template <int N_MAX>
+__device__ __forceinline__ void skinny_finish_row(
+    double (&acc)[N_MAX], const float *__restrict__ bias, int64_t row, int n, int act, int lane,
+    float *__restrict__ out, int64_t *__restrict__ argmax) {
+#pragma unroll
+    for (int j = 0; j < N_MAX; ++j) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    }
+    float logit = 0.0f;
+#pragma unroll
+    for (int j = 0; j < N_MAX; ++j) {
+        if (j == lane && j < n) {
+            double v = acc[j];
+            if (bias)
+                v += (double)bias[j]; // the bias is the last term of the float64 sum
+            logit = (float)v;
+        }
+    }
+    skinny_finish_logit(logit, row, n, act, lane, out, argmax);
 }
 
 // Same contraction with the whole weight matrix [k][n] staged once per block in shared memory
@@ -245,10 +254,10 @@ __global__ void __launch_bounds__(256) gemm_skinny_smem_kernel(
                         if (j < n) {
                             const double2 *wp = reinterpret_cast<const double2 *>(w_s + (int64_t)j * k + kk);
                             double2 wa = wp[0], wb = wp[1];
-                            acc[j] += x0 * wa.x;
-                            acc[j] += x1 * wa.y;
-                            acc[j] += x2 * wb.x;
-                            acc[j] += x3 * wb.y;
+                            acc[j] = __fma_rn(x0, wa.x, acc[j]);
+                            acc[j] = __fma_rn(x1, wa.y, acc[j]);
+                            acc[j] = __fma_rn(x2, wb.x, acc[j]);
+                            acc[j] = __fma_rn(x3, wb.y, acc[j]);
                         }
                 }
             }
@@ -258,7 +267,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_smem_kernel(
 #pragma unroll
                 for (int j = 0; j < N_MAX; ++j)
                     if (j < n)
-                        acc[j] += xd * w_s[(int64_t)j * k + kk];
+                        acc[j] = __fma_rn(xd, w_s[(int64_t)j * k + kk], acc[j]);
             }
         }
         skinny_finish_row<N_MAX>(acc, bias, row, n, act, lane, out, argmax);
@@ -279,6 +288,158 @@ ct_status launch_skinny_smem(
         blocks = cap;
     gemm_skinny_smem_kernel<N_MAX><<<(unsigned)blocks, 256, smem, stream()>>>(a, b, bias, m, k, n, act, out, argmax);
     CT_LAUNCH_CHECK("gemm_skinny_smem");
+    return CT_OK;
+}
+
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src) {
+    uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+
+// Waits until at most `pending` of this thread's committed copy groups are still in flight.
+__device__ __forceinline__ void cp_async_wait_pending(int pending) {
+    switch (pending) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+    }
+}
+
+// Row-tiled variant for the classifier layer of a large batch.  A block owns 32 rows; warp s owns
+// the k-slice [s*ks, (s+1)*ks) and lane r owns row r, so every weight read is one broadcast
+// shared-memory wavefront for 32 rows (the warp-per-row kernel above re-reads the whole weight
+// matrix from shared memory for every row, which bounds it).  The activations of a slice arrive
+// by 16-byte asynchronous copies in 32-wide k chunks, each its own commit group, so arithmetic on
+// chunk c overlaps the arrival of the later chunks; the weights of the slice are widened to
+// float64 once per block.  NP = ceil(n/2) column pairs; the float64 partial sums of the eight
+// slices are added in slice order, then bias, activation and softmax / argmax as above.
+template <int NP>
+__global__ void __launch_bounds__(256, 1) gemm_skinny_tile_kernel(
+    const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+    int64_t m, int k, int n, int ks, int act, float *__restrict__ out, int64_t *__restrict__ argmax) {
+    constexpr int NE = 2 * NP;
+    extern __shared__ __align__(16) unsigned char skinny_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int xs_stride = ks + 4; // floats; (ks + 4) / 4 is odd, so 128-bit row reads spread over the banks
+    float *xs           = reinterpret_cast<float *>(skinny_smem) + (size_t)warp * 32 * xs_stride;
+    double *ws = reinterpret_cast<double *>(skinny_smem + (size_t)8 * 32 * xs_stride * sizeof(float)) +
+                 (size_t)warp * ks * NE;
+    const int64_t row0 = (int64_t)blockIdx.x * 32;
+    const int k0       = warp * ks;
+    int klen           = k - k0;
+    klen               = klen < 0 ? 0 : (klen > ks ? ks : klen);
+    const int nchunks  = (klen + 31) >> 5;
+    // activations: chunk c covers k0 + [32c, 32c+32) of the block's 32 rows; eight lanes copy one row's 128 bytes
+    for (int c = 0; c < nchunks; ++c) {
+        for (int idx = lane; idx < 256; idx += 32) {
+            int r = idx >> 3, kk = c * 32 + (idx & 7) * 4;
+            if (kk < klen && row0 + r < m)
+                cp_async_16(xs + r * xs_stride + kk, x + (row0 + r) * k + k0 + kk);
+        }
+        cp_async_commit();
+    }
+    // weights of the slice: w[(k0 + kk) * n + j] -> ws[kk * NE + j], widened once
+    {
+        const float *wsrc = w + (int64_t)k0 * n;
+        const int total   = klen * n;
+        for (int base = lane; base < total; base += 32 * 8) {
+            float tmp[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                int i  = base + u * 32;
+                tmp[u] = i < total ? __ldg(wsrc + i) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                int i = base + u * 32;
+                if (i < total) {
+                    int kk = i / n, j = i - kk * n;
+                    ws[kk * NE + j] = (double)tmp[u];
+                }
+            }
+        }
+        if (n < NE)
+            for (int kk = lane; kk < klen; kk += 32)
+                ws[kk * NE + n] = 0.0;
+    }
+    __syncwarp();
+    double acc[NE];
+#pragma unroll
+    for (int j = 0; j < NE; ++j)
+        acc[j] = 0.0;
+    const float *xrow = xs + lane * xs_stride;
+    for (int c = 0; c < nchunks; ++c) {
+        cp_async_wait_pending(nchunks - 1 - c);
+        __syncwarp();
+        int kend = (c + 1) * 32 < klen ? (c + 1) * 32 : klen;
+        for (int kk = c * 32; kk < kend; kk += 4) {
+            float4 q     = *reinterpret_cast<const float4 *>(xrow + kk);
+            double xd[4] = {(double)q.x, (double)q.y, (double)q.z, (double)q.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const double2 *wp = reinterpret_cast<const double2 *>(ws + (kk + u) * NE);
+#pragma unroll
+                for (int j = 0; j < NP; ++j) {
+                    double2 wv = wp[j];
+                    // float32 x float32 is exact in float64, so the fused form rounds like mul, add
+                    acc[2 * j]     = __fma_rn(xd[u], wv.x, acc[2 * j]);
+                    acc[2 * j + 1] = __fma_rn(xd[u], wv.y, acc[2 * j + 1]);
+                }
+            }
+        }
+    }
+    __syncthreads(); // every warp is done with its activations: the region becomes the partial sums
+    double *red = reinterpret_cast<double *>(skinny_smem);
+#pragma unroll
+    for (int j = 0; j < NE; ++j)
+        red[((size_t)warp * 32 + lane) * NE + j] = acc[j];
+    __syncthreads();
+    for (int r = warp * 4; r < warp * 4 + 4; ++r) {
+        if (row0 + r >= m)
+            break;
+        float logit = 0.0f;
+        if (lane < n) {
+            double v = 0.0;
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                v += red[((size_t)s * 32 + r) * NE + lane];
+            if (bias)
+                v += (double)bias[lane];
+            logit = (float)v;
+        }
+        skinny_finish_logit(logit, row0 + r, n, act, lane, out, argmax);
+    }
+}
+
+// Slice length of the tiled kernel: a multiple of 8 so that (ks + 4) / 4 is odd.
+inline int skinny_tile_slice(int64_t k) { return (int)((((k + 7) / 8) + 7) / 8 * 8); }
+
+inline size_t skinny_tile_smem(int64_t k, int np) {
+    int ks    = skinny_tile_slice(k);
+    size_t xs = (size_t)8 * 32 * (ks + 4) * sizeof(float);
+    size_t ws = (size_t)8 * ks * 2 * np * sizeof(double);
+    size_t rd = (size_t)8 * 32 * 2 * np * sizeof(double);
+    return (xs > rd ? xs : rd) + ws;
+}
+
+template <int NP>
+ct_status launch_skinny_tile(
+    const float *a, const float *b, const float *bias, int64_t m, int64_t k, int n, int act, float *out,
+    int64_t *argmax) {
+    size_t smem = skinny_tile_smem(k, NP);
+    if (smem > 48 * 1024)
+        CT_CUDA(cudaFuncSetAttribute(
+            gemm_skinny_tile_kernel<NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    gemm_skinny_tile_kernel<NP><<<(unsigned)((m + 31) / 32), 256, smem, stream()>>>(
+        a, b, bias, m, (int)k, n, skinny_tile_slice(k), act, out, argmax);
+    CT_LAUNCH_CHECK("gemm_skinny_tile");
     return CT_OK;
 }
 
@@ -306,6 +467,20 @@ ct_status gemm_f32_skinny(
         return fail(CT_ERR_INVALID, "skinny GEMM takes at most 32 output columns");
     unsigned blocks = (unsigned)((m + 7) / 8);
     ProfScope prof("gemm_skinny");
+    const int np = (int)((n + 1) / 2);
+    if (m >= 256 && n <= 16 && k >= 32 && (k & 3) == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
+        k <= (1 << 20) && skinny_tile_smem(k, np) <= 220 * 1024) {
+        switch (np) {
+        case 1: return launch_skinny_tile<1>(a, b, bias, m, k, (int)n, act, out, argmax);
+        case 2: return launch_skinny_tile<2>(a, b, bias, m, k, (int)n, act, out, argmax);
+        case 3: return launch_skinny_tile<3>(a, b, bias, m, k, (int)n, act, out, argmax);
+        case 4: return launch_skinny_tile<4>(a, b, bias, m, k, (int)n, act, out, argmax);
+        case 5: return launch_skinny_tile<5>(a, b, bias, m, k, (int)n, act, out, argmax);
+        case 6: return launch_skinny_tile<6>(a, b, bias, m, k, (int)n, act, out, argmax);
+        case 7: return launch_skinny_tile<7>(a, b, bias, m, k, (int)n, act, out, argmax);
+        default: return launch_skinny_tile<8>(a, b, bias, m, k, (int)n, act, out, argmax);
+        }
+    }
     if ((size_t)k * n * sizeof(double) <= 200 * 1024 && k > 0) {
         if (n <= 8)
             return launch_skinny_smem<8>(st, a, b, bias, m, k, (int)n, act, out, argmax);

@@ -225,6 +225,109 @@ ct_status ct_d2d(void *dst_dev, const void *src_dev, size_t bytes) {
     return CT_OK;
 }
 
+ct_status ct_host_alloc(void **ptr_host, size_t bytes) {
+    if (!ptr_host)
+        return fail(CT_ERR_INVALID, "ptr_host is null");
+    DeviceState *st;
+    CT_TRY(current(&st));
+    *ptr_host = nullptr;
+    if (bytes == 0)
+        return CT_OK;
+    CT_CUDA(cudaHostAlloc(ptr_host, bytes, cudaHostAllocDefault));
+    return CT_OK;
+}
+
+ct_status ct_host_free(void *ptr_host) {
+    if (!ptr_host)
+        return CT_OK;
+    CT_CUDA(cudaFreeHost(ptr_host));
+    return CT_OK;
+}
+
+ct_status ct_h2d_async(void *dst_dev, const void *src_host_pinned, size_t bytes) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (bytes == 0)
+        return CT_OK;
+    CT_CUDA(cudaMemcpyAsync(dst_dev, src_host_pinned, bytes, cudaMemcpyHostToDevice, stream()));
+    return CT_OK;
+}
+
+ct_status ct_d2h_async(void *dst_host_pinned, const void *src_dev, size_t bytes) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (bytes == 0)
+        return CT_OK;
+    CT_CUDA(cudaMemcpyAsync(dst_host_pinned, src_dev, bytes, cudaMemcpyDeviceToHost, stream()));
+    return CT_OK;
+}
+
+ct_status ct_stream_create(void **stream_out) {
+    if (!stream_out)
+        return fail(CT_ERR_INVALID, "stream_out is null");
+    DeviceState *st;
+    CT_TRY(current(&st));
+    cudaStream_t s = nullptr;
+    CT_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *stream_out = s;
+    return CT_OK;
+}
+
+ct_status ct_stream_destroy(void *s) {
+    if (!s)
+        return CT_OK;
+    if (stream() == static_cast<cudaStream_t>(s))
+        return fail(CT_ERR_INVALID, "ct_stream_destroy: the stream is the current one");
+    CT_CUDA(cudaStreamDestroy(static_cast<cudaStream_t>(s)));
+    return CT_OK;
+}
+
+ct_status ct_event_create(void **event_out) {
+    if (!event_out)
+        return fail(CT_ERR_INVALID, "event_out is null");
+    DeviceState *st;
+    CT_TRY(current(&st));
+    cudaEvent_t e = nullptr;
+    CT_CUDA(cudaEventCreate(&e));
+    *event_out = e;
+    return CT_OK;
+}
+
+ct_status ct_event_destroy(void *event) {
+    if (!event)
+        return CT_OK;
+    CT_CUDA(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+    return CT_OK;
+}
+
+ct_status ct_event_record(void *event) {
+    if (!event)
+        return fail(CT_ERR_INVALID, "event is null");
+    CT_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), stream()));
+    return CT_OK;
+}
+
+ct_status ct_stream_wait_event(void *event) {
+    if (!event)
+        return fail(CT_ERR_INVALID, "event is null");
+    CT_CUDA(cudaStreamWaitEvent(stream(), static_cast<cudaEvent_t>(event), 0));
+    return CT_OK;
+}
+
+ct_status ct_event_sync(void *event) {
+    if (!event)
+        return fail(CT_ERR_INVALID, "event is null");
+    CT_CUDA(cudaEventSynchronize(static_cast<cudaEvent_t>(event)));
+    return CT_OK;
+}
+
+ct_status ct_event_elapsed_ms(void *start_event, void *end_event, float *ms_out) {
+    if (!start_event || !end_event || !ms_out)
+        return fail(CT_ERR_INVALID, "ct_event_elapsed_ms: null argument");
+    CT_CUDA(cudaEventElapsedTime(ms_out, static_cast<cudaEvent_t>(start_event), static_cast<cudaEvent_t>(end_event)));
+    return CT_OK;
+}
+
 ct_dtype ct_result_dtype(ct_binary_op op, ct_dtype lhs, ct_dtype rhs) {
     if (op == CT_DIV || op == CT_POW)
         return CT_F32;

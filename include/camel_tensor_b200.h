@@ -109,6 +109,28 @@ ct_status ct_h2d(void *dst_dev, const void *src_host, size_t bytes);
 ct_status ct_d2h(void *dst_host, const void *src_dev, size_t bytes);
 ct_status ct_d2d(void *dst_dev, const void *src_dev, size_t bytes);
 
+/* ---- streaming across the graph boundary --------------------------------------------
+ * The reference keeps tensors in host memory, so it has no counterpart of these: they exist
+ * because the storage moved to the device and a batch now has to cross PCIe on its way in and
+ * out.  ct_h2d/ct_d2h above wait for the copy; the _async forms only enqueue it on the current
+ * stream and need page-locked host memory (ct_host_alloc) that stays valid until the stream has
+ * passed the copy.  With three streams (copy in, compute, copy out) and events between them the
+ * copy of batch i+1 overlaps the kernels of batch i and the read-back of batch i-1.
+ * A stream handle is what ct_set_stream takes; events are recorded on, and waited for by, the
+ * current stream. */
+ct_status ct_host_alloc(void **ptr_host, size_t bytes);
+ct_status ct_host_free(void *ptr_host);
+ct_status ct_h2d_async(void *dst_dev, const void *src_host_pinned, size_t bytes);
+ct_status ct_d2h_async(void *dst_host_pinned, const void *src_dev, size_t bytes);
+ct_status ct_stream_create(void **stream_out);
+ct_status ct_stream_destroy(void *stream);
+ct_status ct_event_create(void **event_out);
+ct_status ct_event_destroy(void *event);
+ct_status ct_event_record(void *event);       /* on the current stream */
+ct_status ct_stream_wait_event(void *event);  /* the current stream waits; the host does not */
+ct_status ct_event_sync(void *event);         /* the host waits */
+ct_status ct_event_elapsed_ms(void *start_event, void *end_event, float *ms_out);
+
 /* Result dtype of a binary operator: promoteTensorTypes (runtime.cpp:570-580) with the
  * Divide/Power -> Float32 override (runtime.cpp:781-784). */
 ct_dtype ct_result_dtype(ct_binary_op op, ct_dtype lhs, ct_dtype rhs);

@@ -208,6 +208,36 @@ def test_dense_split_k(T):
     assert _rel_err(got, ref) <= GEMM_TOL
 
 
+@pytest.mark.parametrize("m,k,n,act", [(300, 1000, 10, "softmax"), (257, 36, 7, "relu"), (1024, 1024, 10, "softmax"),
+                                       (4096, 128, 10, "softmax"), (512, 2048, 16, None), (260, 40, 1, None),
+                                       (512, 1100, 3, "softmax")])
+def test_dense_few_columns_row_tiled(T, m, k, n, act):
+    """Classifier-layer shapes (n <= 16, many rows): float64 accumulation, so logits agree with
+    float64-matmul-rounded-once to the last bit except where the summation order shows (<= 1 ulp),
+    rows past a multiple of 32 and slices past k are masked, argmax is exact."""
+    rng = np.random.default_rng(m * 7 + k + n)
+    x = rng.uniform(0, 1, (m, k)).astype(np.float32)
+    w = rng.uniform(-0.1, 0.1, (k, n)).astype(np.float32)
+    b = rng.uniform(-0.5, 0.5, n).astype(np.float32)
+    logits = (x.astype(np.float64) @ w.astype(np.float64) + b).astype(np.float32)
+    if act == "softmax":
+        got, arg = T.dense(T.from_numpy(x), T.from_numpy(w), T.from_numpy(b), "softmax", with_argmax=True)
+        got, arg = got.numpy(), arg.numpy()
+        T.check_async()
+        e = np.exp((logits - logits.max(axis=1, keepdims=True)).astype(np.float64))
+        ref = (e / e.sum(axis=1, keepdims=True)).astype(np.float32)
+        assert np.max(np.abs(got - ref)) <= 1e-6
+        srt = np.sort(logits, axis=1)
+        decided = (srt[:, -1] - srt[:, -2] > 1e-6) if n > 1 else np.ones(m, bool)
+        assert np.array_equal(arg[decided], np.argmax(logits, axis=1)[decided])
+    else:
+        got = T.dense(T.from_numpy(x), T.from_numpy(w), T.from_numpy(b), act).numpy()
+        T.check_async()
+        ref = np.maximum(logits, 0) if act == "relu" else logits
+        ulp = np.spacing(np.maximum(np.abs(ref), np.float32(1e-3)))
+        assert np.all(np.abs(got - ref) <= ulp)
+
+
 @pytest.mark.parametrize("m,k,n", [(512, 512, 512), (384, 1000, 640), (1024, 784, 1024), (2048, 4096, 512),
                                    (256, 4096, 128), (130, 9000, 257)])
 def test_gemm_3xtf32_large(T, m, k, n):
@@ -428,3 +458,33 @@ def test_graph_replay_matches_eager(T):
         assert arg_g.tobytes() == arg_e.numpy().tobytes()
     T.check_async()
     del warm
+
+
+def test_host_pipeline_streams_batches(T):
+    """Seven host batches through a depth-2 pipeline (copy in, recorded forward, copy out on three
+    streams): every batch's results equal the call-by-call run on the same bytes, in order."""
+    from camel_b200 import pipeline
+    from camel_b200._lib import F32
+
+    rng = np.random.default_rng(9)
+    w1 = T.from_numpy(rng.uniform(-0.2, 0.2, (96, 160)).astype(np.float32))
+    b1 = T.from_numpy(rng.uniform(-0.1, 0.1, 160).astype(np.float32))
+    w2 = T.from_numpy(rng.uniform(-0.2, 0.2, (160, 10)).astype(np.float32))
+
+    def forward(inp):
+        h = T.dense(inp, w1, b1, "relu")
+        return T.dense(h, w2, None, "softmax", with_argmax=True)
+
+    pipe = pipeline.HostPipeline(forward, F32, (300, 96), depth=2)
+    ins = [pipeline.pinned_array((300, 96), np.float32) for _ in range(7)]
+    for buf in ins:
+        buf.array[...] = rng.uniform(0, 1, (300, 96)).astype(np.float32)
+    outs = [(pipeline.pinned_array((300, 10), np.float32), pipeline.pinned_array((300,), np.int64)) for _ in range(7)]
+    ms = pipe.run([b.ptr for b in ins], [(p.ptr, a.ptr) for p, a in outs])
+    assert ms > 0.0
+    for buf, (p, a) in zip(ins, outs):
+        probs_e, arg_e = forward(T.from_numpy(buf.array.copy()))
+        assert p.array.tobytes() == probs_e.numpy().tobytes()
+        assert a.array.tobytes() == arg_e.numpy().tobytes()
+    T.check_async()
+    pipe.close()
