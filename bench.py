@@ -344,7 +344,9 @@ class MlpWorkload(Workload):
 
     def config(self):
         return {"workload": "mlp_forward 784-1024-1024-10 relu,relu,softmax+argmax (BASELINE configs[1])",
-                "batch_per_gpu": self.batch, "precision": "3xtf32"}
+                "batch_per_gpu": self.batch, "precision": "3xtf32",
+                "weights": "tensor-core layout kept with each weight tensor (built at first use)"
+                if self.T._weight_cache else "transposed and split at every call"}
 
 
 class GemmWorkload(Workload):
@@ -415,35 +417,30 @@ class ShardedGemmWorkload(Workload):
         g.manual_seed(5)
         a_full = torch.rand((n, n), generator=g, device=dev, dtype=torch.float32) * 2 - 1
         self.b_t = torch.rand((n, n), generator=g, device=dev, dtype=torch.float32) * 2 - 1
-        self.rows = n // world
-        self.a_t = a_full[rank * self.rows:(rank + 1) * self.rows].contiguous()
+        from camel_b200 import sharding
+        self.sharding = sharding
+        self.row0, self.rows = sharding.row_shard(n, world, rank)
+        self.a_t = a_full[self.row0:self.row0 + self.rows].contiguous()
         del a_full
         self.c_t = torch.empty((n, n), device=dev, dtype=torch.float32)  # the gathered product
-        self.panel_rows = self.rows // self.PANELS
+        self.plan = sharding.panel_plan(self.rows, self.PANELS)
         self.side = torch.cuda.Stream()
         torch.cuda.synchronize()
         self.h2d = self.d2h = 0
 
-    def _gather(self, j):
-        """All-gather of panel j: rank r's rows land at their place in the full C."""
-        pr = self.panel_rows
-        mine = self.c_t[self.rank * self.rows + j * pr: self.rank * self.rows + (j + 1) * pr]
-        outs = [self.c_t[r * self.rows + j * pr: r * self.rows + (j + 1) * pr] for r in range(self.world)]
-        self.dist.all_gather(outs, mine)
-
     def step(self):
         from camel_b200._lib import check, lib
-        torch, n, pr = self.torch, self.n, self.panel_rows
-        for j in range(self.PANELS):
-            a_ptr = self.a_t.data_ptr() + j * pr * n * 4
-            c_ptr = self.c_t.data_ptr() + (self.rank * self.rows + j * pr) * n * 4
+        torch, n = self.torch, self.n
+        for off, pr in self.plan:
+            a_ptr = self.a_t.data_ptr() + off * n * 4
+            c_ptr = self.c_t.data_ptr() + (self.row0 + off) * n * 4
             check(lib.ct_matmul(0, a_ptr, 0, self.b_t.data_ptr(), pr, n, n, c_ptr))
             if self.world > 1:
                 done = torch.cuda.Event()
                 done.record()
                 with torch.cuda.stream(self.side):
                     self.side.wait_event(done)
-                    self._gather(j)
+                    self.sharding.gather_panel(self.dist, self.c_t, self.rows, off, pr, self.rank, self.world)
         if self.world > 1:
             torch.cuda.current_stream().wait_stream(self.side)
 
@@ -675,7 +672,9 @@ class CnnWorkload(Workload):
 
     def config(self):
         return {"workload": "cnn_forward conv32-conv64-pool-dense128-dense10 on 1x28x28 (BASELINE configs[3])",
-                "batch_per_gpu": self.batch, "precision": "3xtf32"}
+                "batch_per_gpu": self.batch, "precision": "3xtf32",
+                "weights": "tensor-core layout kept with each weight tensor (built at first use)"
+                if self.T._weight_cache else "transposed and split at every call"}
 
 
 def run_gpu(args, rank, world):
@@ -697,6 +696,7 @@ def run_gpu(args, rank, world):
     check(lib.ct_set_stream(None))  # legacy default stream: ordered with torch's default stream
     if args.precision == "bf16":
         check(lib.ct_set_precision(_lib.PREC_BF16))
+    T.set_weight_cache(not args.no_weight_cache)
 
     if args.workload == "mlp":
         wl = MlpWorkload(torch, T, args.batch or 4096, use_graph=not args.eager)
@@ -784,11 +784,8 @@ def run_gpu(args, rank, world):
     T.check_async()
 
     def reduce_max(v):
-        if dist is None:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        from camel_b200 import sharding
+        return sharding.reduce_max(dist, torch, v, "cuda")
 
     ms = reduce_max(ms)
     e2e_ms = reduce_max(max(e2e_ms_dev, 0.0))
@@ -875,6 +872,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ref-workers", type=int, default=0, help="processes of the reference arm (0: one per core, max 32)")
     ap.add_argument("--eager", action="store_true", help="do not replay the forward pass as a CUDA graph")
+    ap.add_argument("--no-weight-cache", action="store_true",
+                    help="transpose and split the weights of every dense layer at every call instead of once per tensor")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

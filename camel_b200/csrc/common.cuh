@@ -94,9 +94,22 @@ inline size_t dtype_size(int dt) { return dt == CT_F32 ? 4 : (dt == CT_I64 ? 8 :
 inline bool valid_dtype(int dt) { return dt == CT_F32 || dt == CT_I64 || dt == CT_BOOL; }
 
 // Entry points of the other translation units used across files.
+// The B operand of a float32 GEMM already in the layout the tensor-core kernel reads: transposed
+// [n][kp] hi/lo planes (3xTF32) or one bf16 plane, built once from a [k][n] weight matrix.
+struct PackedWeights {
+    uint32_t magic;
+    int mode;
+    int device;
+    int64_t k, n, kp;
+    const float *src; // the matrix the planes were built from
+    void *base;       // one device allocation holding the planes
+    void *hi, *lo;
+};
+constexpr uint32_t kPackedMagic = 0x43545057u; // "CTPW"
+
 ct_status gemm_f32_tc(
     DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
-    int64_t n, int act, float *out);
+    int64_t n, int act, float *out, const PackedWeights *packed = nullptr);
 // Geometry of a stride-1 convolution run as an implicit GEMM over NHWC input planes.
 struct ConvGeom {
     int c_pad;  // channels rounded up to the k-block

@@ -264,6 +264,12 @@ ct_status ct_matmul(
 ct_status ct_dense(
     const float *x, const float *w, const float *bias, int64_t m, int64_t k, int64_t n,
     ct_activation act, float *out, int64_t *argmax) {
+    return ct_dense_packed(x, w, nullptr, bias, m, k, n, act, out, argmax);
+}
+
+ct_status ct_dense_packed(
+    const float *x, const float *w, const void *packed, const float *bias, int64_t m, int64_t k,
+    int64_t n, ct_activation act, float *out, int64_t *argmax) {
     DeviceState *st;
     CT_TRY(current(&st));
     if (m < 0 || k < 0 || n < 0)
@@ -278,7 +284,7 @@ ct_status ct_dense(
         return gemm_f32_skinny(st, x, w, bias, m, k, n, act, out, argmax);
     int gemm_act = act == CT_ACT_RELU ? CT_ACT_RELU : CT_ACT_NONE;
     CT_TRY(clear_flags(st));
-    CT_TRY(gemm_f32_tc(st, x, w, bias, m, k, n, gemm_act, out));
+    CT_TRY(gemm_f32_tc(st, x, w, bias, m, k, n, gemm_act, out, static_cast<const PackedWeights *>(packed)));
     if (act == CT_ACT_SOFTMAX) {
         // wide classifier: logits are complete rows in `out`; finish in place
         if (argmax)

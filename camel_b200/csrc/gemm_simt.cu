@@ -167,6 +167,38 @@ __device__ __forceinline__ void skinny_finish_logit(
         argmax[row] = best_idx;
 }
 
+// The same for two rows at once, one per half-warp: `sub` is the lane within its half.
+__device__ __forceinline__ void skinny_finish_logit_half(
+    float logit, int64_t row, bool row_valid, int n, int act, int sub, float *__restrict__ out,
+    int64_t *__restrict__ argmax) {
+    bool live = sub < n && row_valid;
+    if (act == CT_ACT_RELU)
+        logit = __fmul_rn(logit, logit > 0.0f ? 1.0f : 0.0f);
+    if (act != CT_ACT_SOFTMAX) {
+        if (live)
+            out[row * n + sub] = logit;
+        return;
+    }
+    float best   = __shfl_sync(0xffffffffu, logit, 0, 16);
+    int best_idx = 0;
+    for (int j = 1; j < n; ++j) {
+        float v = __shfl_sync(0xffffffffu, logit, j, 16);
+        if (v > best) {
+            best     = v;
+            best_idx = j;
+        }
+    }
+    float e  = sub < n ? exp_f32(__fsub_rn(logit, best)) : 0.0f;
+    double s = 0.0;
+    for (int j = 0; j < n; ++j)
+        s += (double)__shfl_sync(0xffffffffu, e, j, 16);
+    float d = (float)s;
+    if (live)
+        out[row * n + sub] = __fdiv_rn(e, d);
+    if (argmax && sub == 0 && row_valid)
+        argmax[row] = best_idx;
+}
+
 // Finishes one output row held as per-lane partial sums: butterfly reduction, then bias,
 // activation, and (for softmax) the row softmax / argmax across the first n lanes.
 template <int N_MAX>
@@ -318,10 +350,23 @@ __device__ __forceinline__ void cp_async_wait_pending(int pending) {
 // matrix from shared memory for every row, which bounds it).  The activations of a slice arrive
 // by 16-byte asynchronous copies in 32-wide k chunks, each its own commit group, so arithmetic on
 // chunk c overlaps the arrival of the later chunks; the weights of the slice are widened to
-// float64 once per block.  NP = ceil(n/2) column pairs; the float64 partial sums of the eight
+// float64 once per block.  NP = ceil(n/2) column pairs; the float64 partial sums of the sixteen
 // slices are added in slice order, then bias, activation and softmax / argmax as above.
+constexpr int kSkinnyWarps = 16; // k-slices per block
+
+#ifdef CT_GEMM_TRACE
+__device__ unsigned long long g_skinny_trace[1024 * 8];
+#define SK_STAMP(slot)                                                                     \
+    do {                                                                                   \
+        if (threadIdx.x == 0 && blockIdx.x < 1024)                                         \
+            g_skinny_trace[blockIdx.x * 8 + (slot)] = (unsigned long long)clock64();       \
+    } while (0)
+#else
+#define SK_STAMP(slot) do { } while (0)
+#endif
+
 template <int NP>
-__global__ void __launch_bounds__(256, 1) gemm_skinny_tile_kernel(
+__global__ void __launch_bounds__(32 * kSkinnyWarps, 1) gemm_skinny_tile_kernel(
     const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
     int64_t m, int k, int n, int ks, int act, float *__restrict__ out, int64_t *__restrict__ argmax) {
     constexpr int NE = 2 * NP;
@@ -329,13 +374,38 @@ __global__ void __launch_bounds__(256, 1) gemm_skinny_tile_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int xs_stride = ks + 4; // floats; (ks + 4) / 4 is odd, so 128-bit row reads spread over the banks
     float *xs           = reinterpret_cast<float *>(skinny_smem) + (size_t)warp * 32 * xs_stride;
-    double *ws = reinterpret_cast<double *>(skinny_smem + (size_t)8 * 32 * xs_stride * sizeof(float)) +
+    double *ws = reinterpret_cast<double *>(skinny_smem + (size_t)kSkinnyWarps * 32 * xs_stride * sizeof(float)) +
                  (size_t)warp * ks * NE;
     const int64_t row0 = (int64_t)blockIdx.x * 32;
     const int k0       = warp * ks;
     int klen           = k - k0;
     klen               = klen < 0 ? 0 : (klen > ks ? ks : klen);
     const int nchunks  = (klen + 31) >> 5;
+    SK_STAMP(0);
+    // weights of the slice, w[(k0 + kk) * n + j] -> ws[kk * NE + j], widened once.  The first round of
+    // loads is issued before the activation copies so that its latency passes while those are issued.
+    const float *wsrc    = w + (int64_t)k0 * n;
+    const int total      = klen * n;
+    constexpr int kLoads = 20; // independent loads in flight per lane: one round for 64 x 10 weights
+    float tmp[kLoads];
+    auto load_round = [&](int base) {
+#pragma unroll
+        for (int u = 0; u < kLoads; ++u) {
+            int i  = base + u * 32;
+            tmp[u] = i < total ? __ldg(wsrc + i) : 0.0f;
+        }
+    };
+    auto store_round = [&](int base) {
+#pragma unroll
+        for (int u = 0; u < kLoads; ++u) {
+            int i = base + u * 32;
+            if (i < total) {
+                int kk = i / n, j = i - kk * n;
+                ws[kk * NE + j] = (double)tmp[u];
+            }
+        }
+    };
+    load_round(lane);
     // activations: chunk c covers k0 + [32c, 32c+32) of the block's 32 rows; eight lanes copy one row's 128 bytes
     for (int c = 0; c < nchunks; ++c) {
         for (int idx = lane; idx < 256; idx += 32) {
@@ -345,31 +415,17 @@ __global__ void __launch_bounds__(256, 1) gemm_skinny_tile_kernel(
         }
         cp_async_commit();
     }
-    // weights of the slice: w[(k0 + kk) * n + j] -> ws[kk * NE + j], widened once
-    {
-        const float *wsrc = w + (int64_t)k0 * n;
-        const int total   = klen * n;
-        for (int base = lane; base < total; base += 32 * 8) {
-            float tmp[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                int i  = base + u * 32;
-                tmp[u] = i < total ? __ldg(wsrc + i) : 0.0f;
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                int i = base + u * 32;
-                if (i < total) {
-                    int kk = i / n, j = i - kk * n;
-                    ws[kk * NE + j] = (double)tmp[u];
-                }
-            }
-        }
-        if (n < NE)
-            for (int kk = lane; kk < klen; kk += 32)
-                ws[kk * NE + n] = 0.0;
+    SK_STAMP(1);
+    store_round(lane);
+    for (int base = lane + 32 * kLoads; base < total; base += 32 * kLoads) {
+        load_round(base);
+        store_round(base);
     }
+    if (n < NE)
+        for (int kk = lane; kk < klen; kk += 32)
+            ws[kk * NE + n] = 0.0;
     __syncwarp();
+    SK_STAMP(2);
     double acc[NE];
 #pragma unroll
     for (int j = 0; j < NE; ++j)
@@ -378,7 +434,10 @@ __global__ void __launch_bounds__(256, 1) gemm_skinny_tile_kernel(
     for (int c = 0; c < nchunks; ++c) {
         cp_async_wait_pending(nchunks - 1 - c);
         __syncwarp();
+        if (c == 0)
+            SK_STAMP(3);
         int kend = (c + 1) * 32 < klen ? (c + 1) * 32 : klen;
+#pragma unroll 2
         for (int kk = c * 32; kk < kend; kk += 4) {
             float4 q     = *reinterpret_cast<const float4 *>(xrow + kk);
             double xd[4] = {(double)q.x, (double)q.y, (double)q.z, (double)q.w};
@@ -395,37 +454,46 @@ __global__ void __launch_bounds__(256, 1) gemm_skinny_tile_kernel(
             }
         }
     }
+    SK_STAMP(4);
     __syncthreads(); // every warp is done with its activations: the region becomes the partial sums
     double *red = reinterpret_cast<double *>(skinny_smem);
 #pragma unroll
     for (int j = 0; j < NE; ++j)
         red[((size_t)warp * 32 + lane) * NE + j] = acc[j];
     __syncthreads();
-    for (int r = warp * 4; r < warp * 4 + 4; ++r) {
-        if (row0 + r >= m)
-            break;
-        float logit = 0.0f;
-        if (lane < n) {
+    SK_STAMP(5);
+    // two rows per warp, one per half-warp; lane (sub) j < n of a half finishes column j
+    static_assert(kSkinnyWarps == 16, "the finish phase maps one row to each half-warp");
+    {
+        const int sub = lane & 15;
+        const int r   = warp * 2 + (lane >> 4);
+        float logit   = 0.0f;
+        if (sub < n) {
+            double part[kSkinnyWarps];
+#pragma unroll
+            for (int s = 0; s < kSkinnyWarps; ++s)
+                part[s] = red[((size_t)s * 32 + r) * NE + sub];
             double v = 0.0;
 #pragma unroll
-            for (int s = 0; s < 8; ++s)
-                v += red[((size_t)s * 32 + r) * NE + lane];
+            for (int s = 0; s < kSkinnyWarps; ++s)
+                v += part[s];
             if (bias)
-                v += (double)bias[lane];
+                v += (double)bias[sub];
             logit = (float)v;
         }
-        skinny_finish_logit(logit, row0 + r, n, act, lane, out, argmax);
+        skinny_finish_logit_half(logit, row0 + r, row0 + r < m, n, act, sub, out, argmax);
     }
+    SK_STAMP(6);
 }
 
 // Slice length of the tiled kernel: a multiple of 8 so that (ks + 4) / 4 is odd.
-inline int skinny_tile_slice(int64_t k) { return (int)((((k + 7) / 8) + 7) / 8 * 8); }
+inline int skinny_tile_slice(int64_t k) { return (int)((((k + kSkinnyWarps - 1) / kSkinnyWarps) + 7) / 8 * 8); }
 
 inline size_t skinny_tile_smem(int64_t k, int np) {
     int ks    = skinny_tile_slice(k);
-    size_t xs = (size_t)8 * 32 * (ks + 4) * sizeof(float);
-    size_t ws = (size_t)8 * ks * 2 * np * sizeof(double);
-    size_t rd = (size_t)8 * 32 * 2 * np * sizeof(double);
+    size_t xs = (size_t)kSkinnyWarps * 32 * (ks + 4) * sizeof(float);
+    size_t ws = (size_t)kSkinnyWarps * ks * 2 * np * sizeof(double);
+    size_t rd = (size_t)kSkinnyWarps * 32 * 2 * np * sizeof(double);
     return (xs > rd ? xs : rd) + ws;
 }
 
@@ -437,7 +505,7 @@ ct_status launch_skinny_tile(
     if (smem > 48 * 1024)
         CT_CUDA(cudaFuncSetAttribute(
             gemm_skinny_tile_kernel<NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    gemm_skinny_tile_kernel<NP><<<(unsigned)((m + 31) / 32), 256, smem, stream()>>>(
+    gemm_skinny_tile_kernel<NP><<<(unsigned)((m + 31) / 32), 32 * kSkinnyWarps, smem, stream()>>>(
         a, b, bias, m, (int)k, n, skinny_tile_slice(k), act, out, argmax);
     CT_LAUNCH_CHECK("gemm_skinny_tile");
     return CT_OK;
@@ -499,3 +567,9 @@ ct_status gemm_f32_skinny(
 }
 
 } // namespace ct
+
+#ifdef CT_GEMM_TRACE
+extern "C" int ct_debug_skinny_trace(unsigned long long *host, int count) {
+    return (int)cudaMemcpyFromSymbol(host, ct::g_skinny_trace, sizeof(unsigned long long) * (size_t)count);
+}
+#endif

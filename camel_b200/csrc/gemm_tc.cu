@@ -61,6 +61,10 @@ template <int BN, int MODE, int RB = ROW_B> struct Cfg {
     static constexpr int kTmemCols   = 2 * BN;
     static constexpr int kSmemBytes  = kStages * kStageBytes + 1024;
     static constexpr uint32_t kIdesc = make_idesc(MODE == MODE_3X ? 2u : 1u, BM, BN);
+    // epilogue staging in the idle pipeline stages: 32 rows of 128 floats per warp, rows padded by 16 bytes
+    static constexpr int kEpiRowBytes   = 128 * 4 + 16;
+    static constexpr int kEpiStageBytes = 32 * kEpiRowBytes;
+    static_assert(kEpiWarps * kEpiStageBytes <= kStages * kStageBytes, "epilogue staging must fit in the stages");
 };
 
 struct GemmParams {
@@ -188,6 +192,24 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(
 
 // ---- main kernel ------------------------------------------------------------------------
 
+// Optional per-CTA timeline (SM clock stamps) for tuning; compiled in only with -DCT_GEMM_TRACE.
+#ifdef CT_GEMM_TRACE
+__device__ unsigned long long g_gemm_trace[1024 * 16];
+#define CT_STAMP(slot)                                                        \
+    do {                                                                      \
+        if (blockIdx.x < 1024)                                                \
+            g_gemm_trace[blockIdx.x * 16 + (slot)] = (unsigned long long)clock64(); \
+    } while (0)
+#define CT_STAMP_NS(slot)                                                     \
+    do {                                                                      \
+        if (blockIdx.x < 1024)                                                \
+            g_gemm_trace[blockIdx.x * 16 + (slot)] = globaltimer_ns();        \
+    } while (0)
+#else
+#define CT_STAMP(slot) do { } while (0)
+#define CT_STAMP_NS(slot) do { } while (0)
+#endif
+
 template <int BN, int MODE, int RB = ROW_B>
 __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel(
     const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
@@ -209,8 +231,11 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
 
     // If an earlier CTA of this launch already timed out, do not start: the launch has failed
     // and the remaining CTAs should drain at once instead of each waiting out its own budget.
-    if (threadIdx.x == 0)
+    if (threadIdx.x == 0) {
+        CT_STAMP(0);
+        CT_STAMP_NS(8);
         abort_flag_s = *reinterpret_cast<volatile uint32_t *>(p.flags + FLAG_TIMEOUT) != 0 ? 1 : 0;
+    }
     __syncthreads();
     if (abort_flag_s)
         return;
@@ -261,6 +286,8 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
+    if (threadIdx.x == 0)
+        CT_STAMP(1);
 
     // split-K (kb_per_split > 0): the leading block index selects a slice of the k-blocks instead
     // of a batch entry; every slice writes its own partial output, summed by a second kernel
@@ -345,6 +372,8 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
                         break;
                     }
                     tc_fence_after_sync();
+                    if (kb == 0)
+                        CT_STAMP(2);
                     uint32_t a_hi = stage_addr(s);
                     uint32_t a_lo = a_hi + C::kABytes;
                     uint32_t b_hi = a_hi + C::kPlanes * C::kABytes;
@@ -369,6 +398,7 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
                 if (ok)
                     tc_commit(smem_u32(&bar_tmem_full[buf]));
             }
+            CT_STAMP(3);
             if (!ok || *abort_flag) {
                 // unwind: wait until every MMA issued so far has retired
                 tc_commit(smem_u32(&bar_done));
@@ -393,6 +423,8 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
             ok       = __all_sync(0xffffffffu, got);
             if (!ok)
                 break;
+            if (c == num_chunks - 1 && warp == 2 && lane == 0)
+                CT_STAMP(4);
             tc_fence_after_sync();
             uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128);
 #pragma unroll
@@ -409,11 +441,63 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
             if (lane == 0)
                 mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
         }
+        if (warp == 2 && lane == 0)
+            CT_STAMP(5);
         if (ok) {
             int64_t row  = (int64_t)tm * BM + quarter * 32 + lane;
             int64_t col0 = (int64_t)tn * p.tile_n + half * 128;
             int64_t lim  = (int64_t)(tn + 1) * p.tile_n < p.n ? (int64_t)(tn + 1) * p.tile_n : p.n;
-            if (row < p.m) {
+            float *out_z = p.out + (int64_t)tz * p.out_batch_stride;
+            if ((p.ldc & 3) == 0 && (col0 & 3) == 0 && (reinterpret_cast<uintptr_t>(out_z) & 15u) == 0) {
+                // A thread holds 128 consecutive columns of one row, so storing straight from the
+                // registers writes 32 scattered 16-byte pieces per instruction, and the tile's store
+                // then takes longer than 300 k-steps of the main loop.  The pipeline stages are idle by
+                // now (every MMA has retired): each warp parks its 32 x 128 block there, rows padded to
+                // 528 bytes so that neither phase has bank conflicts, and writes it out with one row
+                // (512 contiguous bytes) per instruction.  Lane l owns columns 4l..4l+3 in that phase,
+                // so the column bias is read once per lane.
+                uint8_t *stg = smem_raw + (smem_base - smem_u32(smem_raw)) + (uint32_t)ew * C::kEpiStageBytes;
+                float4 *mine = reinterpret_cast<float4 *>(stg + lane * C::kEpiRowBytes);
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    mine[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+                __syncwarp();
+                const int64_t col = col0 + lane * 4;
+                float b4[4]       = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (p.bias && !p.bias_per_row) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (col + q < lim)
+                            b4[q] = p.bias[col + q];
+                }
+                const int64_t row0 = (int64_t)tm * BM + quarter * 32;
+#pragma unroll 4
+                for (int i = 0; i < 32; ++i) {
+                    if (row0 + i >= p.m)
+                        break;
+                    float4 q4 = *reinterpret_cast<const float4 *>(stg + i * C::kEpiRowBytes + lane * 16);
+                    float v[4] = {q4.x, q4.y, q4.z, q4.w};
+                    const float rb = (p.bias && p.bias_per_row) ? p.bias[row0 + i] : 0.0f;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float x = v[q];
+                        if (p.bias)
+                            x = __fadd_rn(x, p.bias_per_row ? rb : b4[q]);
+                        if (p.act == CT_ACT_RELU)
+                            x = __fmul_rn(x, x > 0.0f ? 1.0f : 0.0f);
+                        v[q] = x;
+                    }
+                    float *dst = out_z + (row0 + i) * p.ldc;
+                    if (col + 3 < lim) {
+                        *reinterpret_cast<float4 *>(dst + col) = make_float4(v[0], v[1], v[2], v[3]);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (col + q < lim)
+                                dst[col + q] = v[q];
+                    }
+                }
+            } else if (row < p.m) {
                 float *dst      = p.out + (int64_t)tz * p.out_batch_stride + row * p.ldc;
                 const float rb  = (p.bias && p.bias_per_row) ? p.bias[row] : 0.0f;
                 const bool vec4 = (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
@@ -445,12 +529,18 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
         }
     }
 
+    if (warp == 2 && lane == 0)
+        CT_STAMP(6);
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+    if (threadIdx.x == 0) {
+        CT_STAMP(7);
+        CT_STAMP_NS(9);
     }
     if (threadIdx.x == 0 && *abort_flag)
         atomicExch(p.flags + FLAG_TIMEOUT, 1u + (uint32_t)blockIdx.x);
@@ -733,7 +823,7 @@ constexpr int64_t kMaxDim = 1ll << 30;
 
 ct_status gemm_f32_tc(
     DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
-    int64_t n, int act, float *out) {
+    int64_t n, int act, float *out, const PackedWeights *packed) {
     if (m == 0 || n == 0)
         return CT_OK;
     if (m > kMaxDim || n > kMaxDim || k > kMaxDim)
@@ -747,17 +837,33 @@ ct_status gemm_f32_tc(
         kp = kblock; // k == 0: one all-zero k-block gives C = act(bias)
     // workspace: [A hi][A lo][B hi][B lo], each plane 1024-byte aligned
     auto align_up       = [](size_t v) { return (v + 1023) & ~(size_t)1023; };
+    if (packed) {
+        int dev = -1;
+        CT_CUDA(cudaGetDevice(&dev));
+        if (packed->magic != kPackedMagic || packed->mode != mode || packed->k != k || packed->n != n ||
+            packed->kp != kp || packed->src != b || packed->device != dev)
+            return fail(
+                CT_ERR_INVALID,
+                "dense: the packed weights were built from another matrix, shape, precision or device");
+    }
     size_t a_plane      = align_up((size_t)m * kp * elem);
-    size_t b_plane      = align_up((size_t)n * kp * elem);
+    size_t b_plane      = packed ? 0 : align_up((size_t)n * kp * elem);
     size_t total        = planes * (a_plane + b_plane);
     CT_TRY(ensure_ws(&st->gemm_ws, &st->gemm_ws_bytes, total));
     uint8_t *ws = static_cast<uint8_t *>(st->gemm_ws);
     void *a_hi = ws, *a_lo = ws + a_plane;
     void *b_hi = ws + planes * a_plane, *b_lo = ws + planes * a_plane + b_plane;
+    if (packed) {
+        b_hi = packed->hi;
+        b_lo = packed->lo;
+    }
 
     {
         ProfScope prof("gemm_prepass");
         CT_TRY(split_rows_planes(st, mode, a, m, k, kp, a_hi, a_lo));
+    }
+    if (!packed) {
+        ProfScope prof("gemm_prepass");
         dim3 grid((unsigned)((n + 31) / 32), (unsigned)(kp / 32));
         if (grid.y > 65535)
             return fail(CT_ERR_TOO_LARGE, "gemm: k too large for the operand pre-pass");
@@ -769,6 +875,72 @@ ct_status gemm_f32_tc(
     }
 
     return gemm_planes(st, mode, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, 1, 0, 0);
+}
+
+// ---- packed weights -----------------------------------------------------------------------
+
+extern "C" ct_status ct_weights_pack(const float *w, int64_t k, int64_t n, void **packed_out) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (!packed_out)
+        return fail(CT_ERR_INVALID, "ct_weights_pack: packed_out is null");
+    *packed_out = nullptr;
+    if (k <= 0 || n <= 0 || !w)
+        return fail(CT_ERR_INVALID, "ct_weights_pack: empty or null matrix");
+    if (n > kMaxDim || k > kMaxDim)
+        return fail(CT_ERR_TOO_LARGE, "ct_weights_pack: dimension too large");
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    CT_CUDA(cudaStreamIsCapturing(stream(), &cap));
+    if (cap != cudaStreamCaptureStatusNone)
+        return fail(CT_ERR_INVALID, "ct_weights_pack: cannot run while calls are being recorded");
+    const int mode   = ct_get_precision() == CT_PREC_BF16 ? MODE_BF : MODE_3X;
+    const int elem   = mode == MODE_3X ? 4 : 2;
+    const int planes = mode == MODE_3X ? 2 : 1;
+    const int kblock = ROW_B / elem;
+    const int64_t kp = (k + kblock - 1) / kblock * kblock;
+    const size_t plane = ((size_t)n * kp * elem + 1023) & ~(size_t)1023;
+    dim3 grid((unsigned)((n + 31) / 32), (unsigned)(kp / 32));
+    if (grid.y > 65535)
+        return fail(CT_ERR_TOO_LARGE, "ct_weights_pack: k too large for the operand pre-pass");
+    void *base = nullptr;
+    CT_TRY(ct_alloc(&base, plane * planes));
+    void *hi = base, *lo = static_cast<uint8_t *>(base) + plane;
+    {
+        ProfScope prof("weights_pack");
+        if (mode == MODE_3X)
+            split_transpose_kernel<MODE_3X><<<grid, 256, 0, stream()>>>(w, k, n, kp, hi, lo);
+        else
+            split_transpose_kernel<MODE_BF><<<grid, 256, 0, stream()>>>(w, k, n, kp, hi, lo);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            ct_free(base);
+            return cuda_fail(e, "weights_pack");
+        }
+        count_launch(1);
+    }
+    // the handle may be used from any stream afterwards: finish the one-time pass here
+    cudaError_t se = cudaStreamSynchronize(stream());
+    if (se != cudaSuccess) {
+        ct_free(base);
+        return cuda_fail(se, "weights_pack");
+    }
+    int dev = -1;
+    CT_CUDA(cudaGetDevice(&dev));
+    PackedWeights *pw = new PackedWeights{kPackedMagic, mode, dev, k, n, kp, w, base, hi, lo};
+    *packed_out       = pw;
+    return CT_OK;
+}
+
+extern "C" ct_status ct_weights_free(void *packed) {
+    if (!packed)
+        return CT_OK;
+    PackedWeights *pw = static_cast<PackedWeights *>(packed);
+    if (pw->magic != kPackedMagic)
+        return fail(CT_ERR_INVALID, "ct_weights_free: not a packed-weights handle");
+    pw->magic    = 0;
+    ct_status st = ct_free(pw->base);
+    delete pw;
+    return st;
 }
 
 // ---- matmul without any allocation --------------------------------------------------------
@@ -922,3 +1094,9 @@ extern "C" ct_status ct_matmul_f32_static(
             status_dev, s->flags + FLAG_TIMEOUT, sizeof(uint32_t), cudaMemcpyDeviceToDevice, stream()));
     return CT_OK;
 }
+
+#ifdef CT_GEMM_TRACE
+extern "C" int ct_debug_gemm_trace(unsigned long long *host, int count) {
+    return (int)cudaMemcpyFromSymbol(host, ct::g_gemm_trace, sizeof(unsigned long long) * (size_t)count);
+}
+#endif

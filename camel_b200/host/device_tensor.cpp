@@ -5,7 +5,9 @@
 #include <mutex>
 #include <ostream>
 #include <stdexcept>
+#include <map>
 #include <unordered_set>
+#include <utility>
 
 namespace camel::tensor {
 
@@ -14,6 +16,10 @@ using type::TypeCode;
 namespace {
 std::mutex g_registryMutex;
 std::unordered_set<void *> g_deviceBuffers;
+// (device buffer, precision) -> packed form of a weight tensor.  A device buffer is written once,
+// when its tensor is created, and lives until releaseAllDeviceBuffers, so the address identifies
+// the contents.
+std::map<std::pair<void *, int>, void *> g_packedWeights;
 
 void *allocDevice(size_t bytes) {
     void *p = nullptr;
@@ -41,9 +47,26 @@ void ctCheck(ct_status status) {
 
 void releaseAllDeviceBuffers() {
     std::lock_guard<std::mutex> lock(g_registryMutex);
+    for (auto &entry : g_packedWeights)
+        ct_weights_free(entry.second);
+    g_packedWeights.clear();
     for (void *p : g_deviceBuffers)
         ct_free(p);
     g_deviceBuffers.clear();
+}
+
+const void *packedWeightsFor(const TensorObject *w, int64_t k, int64_t n) {
+    if (n <= 32 || k <= 0 || w->dtype() != TypeCode::Float32)
+        return nullptr; // narrow outputs read the matrix itself
+    const auto key = std::make_pair(const_cast<void *>(w->deviceData()), static_cast<int>(ct_get_precision()));
+    std::lock_guard<std::mutex> lock(g_registryMutex);
+    auto it = g_packedWeights.find(key);
+    if (it != g_packedWeights.end())
+        return it->second;
+    void *handle = nullptr;
+    ctCheck(ct_weights_pack(static_cast<const float *>(w->deviceData()), k, n, &handle));
+    g_packedWeights.emplace(key, handle);
+    return handle;
 }
 
 size_t liveDeviceBuffers() {

@@ -100,6 +100,11 @@ type::TypeCode fromCtDType(ct_dtype dt);
 // (modules/tensor/operators.cpp:103-109).
 void ctCheck(ct_status status);
 
+// Tensor-core layout of a weight tensor (ct_weights_pack), built at its first use as the `with`
+// argument of dense and kept until the device buffers are released; nullptr where dense does not
+// take one.  Tensors are immutable values, so the layout never goes stale.
+const void *packedWeightsFor(const TensorObject *w, int64_t k, int64_t n);
+
 // Releases every device buffer created so far (module unload / explicit scope end).
 void releaseAllDeviceBuffers();
 size_t liveDeviceBuffers();

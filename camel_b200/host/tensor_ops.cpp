@@ -322,9 +322,9 @@ slot_t denseBody(ArgsView &with, ArgsView &norm, ct_activation act) {
             throw std::invalid_argument("dense: bias must have one value per output column");
         int64_t outShape[2] = {m, n};
         TensorObject *out   = newTensor(TypeCode::Float32, outShape);
-        ctn::ctCheck(ct_dense(
+        ctn::ctCheck(ct_dense_packed(
             static_cast<const float *>(x->deviceData()), static_cast<const float *>(w->deviceData()),
-            b ? static_cast<const float *>(b->deviceData()) : nullptr, m, k, n, act,
+            ctn::packedWeightsFor(w, k, n), b ? static_cast<const float *>(b->deviceData()) : nullptr, m, k, n, act,
             static_cast<float *>(out->deviceData()), nullptr));
         return wrap(out);
     });

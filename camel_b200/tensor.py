@@ -42,9 +42,10 @@ def _normalize_np(a: np.ndarray) -> tuple[np.ndarray, int]:
 class Tensor:
     """Device-resident counterpart of TensorObject (modules/tensor/runtime.h:55-109)."""
 
-    __slots__ = ("dtype", "shape", "ptr", "_owns", "_keep")
+    __slots__ = ("dtype", "shape", "ptr", "_owns", "_keep", "_packed")
 
     def __init__(self, dtype: int, shape: Sequence[int], ptr: int | None = None, keep=None):
+        self._packed = None  # {precision: handle} once the tensor has served as the weights of dense()
         self.dtype = dtype
         self.shape = tuple(int(d) for d in shape)
         for d in self.shape:
@@ -60,7 +61,18 @@ class Tensor:
             self.ptr = ptr
             self._owns = False
 
+    def invalidate(self) -> None:
+        """Drops what was derived from the contents (packed weights).  Tensors are immutable
+        values, as in the reference; code that overwrites a buffer through the raw C ABI calls this."""
+        packed, self._packed = getattr(self, "_packed", None), None
+        for handle in (packed or {}).values():
+            try:
+                lib.ct_weights_free(handle)
+            except Exception:
+                pass
+
     def __del__(self):
+        self.invalidate()
         if getattr(self, "_owns", False) and self.ptr:
             try:
                 lib.ct_free(self.ptr)
@@ -442,9 +454,39 @@ def dense(x: Tensor, w: Tensor, b: Tensor | None = None, activation: str | None 
         raise _invalid("dense: unknown activation")
     out = Tensor(L.F32, (m, n))
     am = Tensor(L.I64, (m,)) if with_argmax else None
-    check(lib.ct_dense(x.ptr, w.ptr, b.ptr if b is not None else None, m, k, n, _ACT[activation],
-                       out.ptr, am.ptr if am is not None else None))
+    check(lib.ct_dense_packed(x.ptr, w.ptr, _packed_weights(w, m, k, n), b.ptr if b is not None else None,
+                              m, k, n, _ACT[activation], out.ptr, am.ptr if am is not None else None))
     return (out, am) if with_argmax else out
+
+
+_weight_cache = True
+_recording = 0
+
+
+def set_weight_cache(on: bool) -> None:
+    """dense() keeps the tensor-core layout of a weight tensor with the tensor (built at its first
+    use with at least 128 rows of input) unless this is switched off."""
+    global _weight_cache
+    _weight_cache = bool(on)
+
+
+def _packed_weights(w: Tensor, m: int, k: int, n: int):
+    """Handle of w's packed form under the current precision, or None where the call does not use
+    one: narrow outputs read w itself, small problems take other kernels, and nothing is packed
+    while calls are being recorded (the handle would belong to the recording)."""
+    if not _weight_cache or n <= 32 or m < 128 or k == 0:
+        return None
+    prec = int(lib.ct_get_precision())
+    if w._packed is not None and prec in w._packed:
+        return w._packed[prec]
+    if _recording:
+        return None
+    handle = C.c_void_p()
+    check(lib.ct_weights_pack(w.ptr, k, n, C.byref(handle)))
+    if w._packed is None:
+        w._packed = {}
+    w._packed[prec] = handle
+    return handle
 
 
 def conv2d(x: Tensor, w: Tensor, b: Tensor | None = None, stride: int = 1, pad: int = 0,
@@ -499,10 +541,14 @@ class Graph:
         self.keep = None
 
     def __enter__(self):
+        global _recording
         check(lib.ct_graph_begin())
+        _recording += 1
         return self
 
     def __exit__(self, exc_type, exc, tb):
+        global _recording
+        _recording -= 1
         status = lib.ct_graph_end(C.byref(self.handle))
         if exc_type is None:
             check(status)

@@ -220,6 +220,21 @@ ct_status ct_dense(
     const float *x_dev, const float *w_dev, const float *bias_dev, int64_t m, int64_t k,
     int64_t n, ct_activation act, float *out_dev, int64_t *argmax_dev);
 
+/* Weights that are multiplied many times (the layers of a network) can be handed over once in the
+ * layout the tensor-core GEMM reads: ct_weights_pack transposes and splits a [k][n] float32 matrix
+ * under the current precision and returns a handle; ct_dense_packed is ct_dense with that handle
+ * and skips the per-call pre-pass over the weights (packed == NULL: exactly ct_dense).  The
+ * handle must come from the same w_dev, k, n, precision and device, else CT_ERR_INVALID; the
+ * caller keeps w_dev unchanged and alive (shapes with n <= 32 read w_dev itself).  Tensors of the
+ * reference are immutable values (every operator returns a new tensor), which is what makes
+ * caching by tensor sound; the reference itself has no counterpart of these two calls.
+ * ct_weights_pack cannot be recorded into a graph. */
+ct_status ct_weights_pack(const float *w_dev, int64_t k, int64_t n, void **packed_out);
+ct_status ct_weights_free(void *packed);
+ct_status ct_dense_packed(
+    const float *x_dev, const float *w_dev, const void *packed, const float *bias_dev, int64_t m,
+    int64_t k, int64_t n, ct_activation act, float *out_dev, int64_t *argmax_dev);
+
 /* conv2d, NCHW input [n,c,h,w], OIHW weights [k_out,c,kh,kw], zero padding, then + bias and
  * activation (NONE or RELU).  No reference counterpart (the reference has no conv operator);
  * arithmetic follows the reference's style: one accumulation per output over (c,kh,kw). */

@@ -460,6 +460,45 @@ def test_graph_replay_matches_eager(T):
     del warm
 
 
+def test_dense_packed_weights(T):
+    """The tensor-core layout of a weight tensor is built once and kept with the tensor: same bytes
+    as the per-call pre-pass, in both precisions; a handle from another matrix is refused."""
+    import ctypes as C
+
+    import camel_b200
+    from camel_b200._lib import check, lib
+
+    rng = np.random.default_rng(21)
+    x = T.from_numpy(rng.uniform(0, 1, (300, 200)).astype(np.float32))
+    w_np = rng.uniform(-0.1, 0.1, (200, 150)).astype(np.float32)
+    b = T.from_numpy(rng.uniform(-0.1, 0.1, 150).astype(np.float32))
+    for prec in (camel_b200._lib.PREC_3XTF32, camel_b200._lib.PREC_BF16):
+        check(lib.ct_set_precision(prec))
+        try:
+            T.set_weight_cache(False)
+            plain = T.dense(x, T.from_numpy(w_np), b, "relu").numpy()
+            T.set_weight_cache(True)
+            w = T.from_numpy(w_np)
+            first = T.dense(x, w, b, "relu").numpy()
+            assert w._packed is not None and prec in w._packed
+            second = T.dense(x, w, b, "relu").numpy()
+            T.check_async()
+            assert plain.tobytes() == first.tobytes() == second.tobytes()
+            if prec == camel_b200._lib.PREC_3XTF32:
+                w3x = w
+        finally:
+            check(lib.ct_set_precision(camel_b200._lib.PREC_3XTF32))
+            T.set_weight_cache(True)
+    other = T.from_numpy(w_np)
+    out = T.Tensor(0, (300, 150))
+    with pytest.raises(camel_b200.CamelTensorError, match="packed weights"):
+        check(lib.ct_dense_packed(x.ptr, other.ptr, w3x._packed[camel_b200._lib.PREC_3XTF32], None, 300, 200, 150, 0,
+                                  out.ptr, None))
+    h = C.c_void_p()
+    with pytest.raises(camel_b200.CamelTensorError):
+        check(lib.ct_weights_pack(None, 4, 4, C.byref(h)))
+
+
 def test_host_pipeline_streams_batches(T):
     """Seven host batches through a depth-2 pipeline (copy in, recorded forward, copy out on three
     streams): every batch's results equal the call-by-call run on the same bytes, in order."""
