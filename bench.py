@@ -6,11 +6,15 @@ configurations; no dataset is used):
   mlp    3-layer MLP forward, batch 4096, 784->1024->1024->10, relu/relu/softmax+argmax
          (metric: samples/s) - the default
   gemm   one fp32 GEMM M=N=K (default 16384, --size), 3xTF32 (or --precision bf16)
+  gemm_sharded  the same product with the rows of A split over the ranks and C all-gathered in
+         row panels on a side stream while the next panel computes (strong scaling)
   conv   conv2d 256x64x56x56 * 128x64x3x3, pad 1, + bias + relu
-  add    elementwise add of 2^28 float32 (HBM-bound)
+  cnn    conv32-conv64-pool-dense128-dense10 forward on 1x28x28 images, batch 8192
+  add, mul, scale, relu, gt, exp, log, sum, softmax   2^28 float32 (HBM-bound)
 
 Under torchrun every rank runs the same per-GPU workload on its own shard (weak scaling, no
-data-path collective: samples / row blocks are independent); rank 0 prints ONE JSON line.
+data-path collective: samples / row blocks are independent; gemm_sharded is the exception);
+rank 0 prints ONE JSON line.
 `--impl reference` times the reference's own CPU operators (oracle/_ref) on a bounded sample.
 """
 from __future__ import annotations
@@ -232,6 +236,12 @@ class Workload:
     def algorithmic_per_step(self):  # flops (tensor) or bytes (hbm) of the dominant kernel
         raise NotImplementedError
 
+    def ncu_traffic(self):
+        """(DRAM bytes per launch of the dominant kernel from an ncu capture, where it came from).
+        The figures are constants copied from the summaries under profiles/: a profiler never runs
+        inside the bench."""
+        return None, "no ncu capture of this shape"
+
 
 class _Pinned:
     """Page-locked host buffer from the library's own allocator (ct_host_alloc)."""
@@ -339,6 +349,12 @@ class MlpWorkload(Workload):
     def algorithmic_per_step(self):
         return 2.0 * self.batch * (784 * 1024 + 1024 * 1024)  # the two tensor-core layers
 
+    def ncu_traffic(self):
+        if self.batch != 4096:
+            return None, "captured at batch 4096 only"
+        return 38.1e6, ("profiles/mlp_forward_launch_list_and_gemm.md: 43.4 MB (k=1024) and 32.9 MB (k=784) per "
+                        "launch = the operand planes read once; the result stays in L2")
+
     def resident_bytes(self):
         return self.x.nbytes + sum(t.nbytes for t in self.w) + 2 * self.batch * 1024 * 4
 
@@ -392,6 +408,12 @@ class GemmWorkload(Workload):
 
     def algorithmic_per_step(self):
         return 2.0 * self.n ** 3
+
+    def ncu_traffic(self):
+        if self.n == 4096:
+            return 690.7e6, "profiles/gemm_tc_kernel_gemm4096.md (335 MB algorithmic: operand tiles re-read 2.1x)"
+        return None, ("captured at 4096^3 only: the re-read factor depends on how the raster groups fit in L2 "
+                      "and does not scale with the flops")
 
     def resident_bytes(self):
         return 3 * self.n * self.n * 4
@@ -490,6 +512,14 @@ class ConvWorkload(Workload):
     def algorithmic_per_step(self):
         return self.flops
 
+    def ncu_traffic(self):
+        # batch-32 capture: 52.1 MB read = the NHWC and weight planes once; reads scale with the batch,
+        # and at full size the whole result goes to DRAM (at batch 32 most of it was still in L2)
+        reads = 52.1e6 * self.batch / 32.0
+        writes = self.batch * 128 * 56 * 56 * 4.0
+        return reads + writes, ("profiles/conv2d_and_elementwise_kernels.md: reads scaled from the batch-32 capture "
+                                "by the batch, writes = the size of the result")
+
     def resident_bytes(self):
         return self.h2d + self.d2h
 
@@ -530,6 +560,10 @@ class AddWorkload(Workload):
 
     def algorithmic_per_step(self):
         return 12.0 * self.n
+
+    def ncu_traffic(self):
+        return 12.0 * self.n, ("profiles/conv2d_and_elementwise_kernels.md: the 2^26 capture moved its algorithmic "
+                               "12 B/element (reads exact, the tail of the writes still in L2); scaled by n")
 
     def resident_bytes(self):
         return 12 * self.n
@@ -608,6 +642,12 @@ class HbmWorkload(Workload):
 
     def algorithmic_per_step(self):
         return float(self.bpe) * self.n
+
+    def ncu_traffic(self):
+        if self.op in ("exp", "softmax"):
+            return float(self.bpe) * self.n, ("profiles/conv2d_and_elementwise_kernels.md: the 2^26 capture read and "
+                                               "wrote every element once (8 B/element); scaled by n")
+        return None, "no ncu capture of this operator"
 
     def resident_bytes(self):
         return self.bpe * self.n
@@ -811,8 +851,10 @@ def run_gpu(args, rank, world):
             peak, peak_note = pk["hbm_gbs"], f"{pk['source']} STREAM-style copy"
             achieved = alg / (dom_ms / 1e3) / 1e9 if dom_ms > 0 else 0.0
             runit = "GB/s"
+        traffic, traffic_note = wl.ncu_traffic() if args.precision != "bf16" else (None, "no ncu capture in bf16 mode")
         roofline = {"bound": wl.bound, "kernel": wl.dominant, "achieved": achieved, "peak": peak, "unit": runit,
-                    "frac": achieved / peak if peak else None, "traffic": None, "peak_note": peak_note,
+                    "frac": achieved / peak if peak else None, "traffic": traffic, "traffic_unit": "bytes per launch",
+                    "traffic_note": traffic_note, "peak_note": peak_note,
                     "launches_per_step": launches_per_step, "avg_launch_ms": dom_ms}
         cpu = cpu_baseline(args) if world == 1 and not args.no_cpu_baseline else None
         line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
