@@ -1,9 +1,13 @@
 // Library state: error text, device/stream selection, storage entry points.
 #include "common.cuh"
 
+#include <cctype>
+#include <cstdio>
 #include <cstring>
 #include <mutex>
 #include <vector>
+
+#include <sched.h>
 
 namespace ct {
 
@@ -114,6 +118,45 @@ ct_status fetch_flags(DeviceState *st) {
     return CT_OK;
 }
 
+} // namespace ct
+
+namespace ct {
+namespace {
+// CPUs local to a GPU, from /sys/bus/pci/devices/<bus id>/local_cpulist ("0-31,64-95").
+bool local_cpus_of_device(int dev, cpu_set_t *set) {
+    char bus[32] = {0};
+    if (cudaDeviceGetPCIBusId(bus, (int)sizeof(bus), dev) != cudaSuccess)
+        return false;
+    for (char *c = bus; *c; ++c)
+        *c = (char)tolower((unsigned char)*c);
+    char path[128];
+    snprintf(path, sizeof(path), "/sys/bus/pci/devices/%s/local_cpulist", bus);
+    FILE *f = fopen(path, "r");
+    if (!f)
+        return false;
+    char line[4096] = {0};
+    bool got        = fgets(line, sizeof(line), f) != nullptr;
+    fclose(f);
+    if (!got)
+        return false;
+    CPU_ZERO(set);
+    int count = 0;
+    for (char *p = line; *p;) {
+        if (!isdigit((unsigned char)*p)) {
+            ++p;
+            continue;
+        }
+        long a = strtol(p, &p, 10), b = a;
+        if (*p == '-')
+            b = strtol(p + 1, &p, 10);
+        for (long c = a; c <= b && c < CPU_SETSIZE; ++c) {
+            CPU_SET((int)c, set);
+            ++count;
+        }
+    }
+    return count > 0;
+}
+} // namespace
 } // namespace ct
 
 using namespace ct;
@@ -233,7 +276,25 @@ ct_status ct_host_alloc(void **ptr_host, size_t bytes) {
     *ptr_host = nullptr;
     if (bytes == 0)
         return CT_OK;
-    CT_CUDA(cudaHostAlloc(ptr_host, bytes, cudaHostAllocDefault));
+    // Page-locked pages land on the memory node of the CPU that allocates them.  On a two-socket host
+    // a buffer on the far socket crosses the inter-socket link on every copy and several GPUs then
+    // share that link; so the calling thread is moved, for the duration of the allocation, onto the
+    // CPUs that are local to the current GPU (as sysfs reports them), where the process is allowed there.
+    cpu_set_t saved, local;
+    bool moved = false;
+    int dev    = -1;
+    if (cudaGetDevice(&dev) == cudaSuccess && sched_getaffinity(0, sizeof(saved), &saved) == 0 &&
+        local_cpus_of_device(dev, &local)) {
+        cpu_set_t both;
+        CPU_AND(&both, &saved, &local);
+        if (CPU_COUNT(&both) > 0 && !CPU_EQUAL(&both, &saved))
+            moved = sched_setaffinity(0, sizeof(both), &both) == 0;
+    }
+    cudaError_t e = cudaHostAlloc(ptr_host, bytes, cudaHostAllocDefault);
+    if (moved)
+        sched_setaffinity(0, sizeof(saved), &saved);
+    if (e != cudaSuccess)
+        return cuda_fail(e, "cudaHostAlloc");
     return CT_OK;
 }
 
