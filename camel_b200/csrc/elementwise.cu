@@ -479,48 +479,19 @@ template <int OP> ct_status unary(const float *t, uint64_t n, float *o, uint32_t
     return launch_map(n - done, Unary<OP, false>{t, o, flags, done}, name);
 }
 
-// ---- log: table-driven, tables staged in shared memory --------------------------------
-
-__device__ double g_log_rc[kLogTableSize];
-__device__ double g_log_lc[kLogTableSize];
-
-// Fills the tables once per device from the host's libm (the values the reference's host
-// would use), so that log(c_j) and ln 2 are consistent doubles.
-ct_status ensure_log_tables(DeviceState *st) {
-    static std::mutex mu;
-    static bool done[16] = {};
-    std::lock_guard<std::mutex> lock(mu);
-    if (done[st->device])
-        return CT_OK;
-    double rc[kLogTableSize], lc[kLogTableSize];
-    for (int j = 0; j < kLogTableSize; ++j) {
-        double c = 1.0 + j / 128.0;
-        rc[j]    = 1.0 / c;
-        lc[j]    = std::log(c);
-    }
-    lc[kLogTableSize - 1] = 0.693147180559945309417;
-    CT_CUDA(cudaMemcpyToSymbol(g_log_rc, rc, sizeof(rc)));
-    CT_CUDA(cudaMemcpyToSymbol(g_log_lc, lc, sizeof(lc)));
-    done[st->device] = true;
-    return CT_OK;
-}
+// ---- log ------------------------------------------------------------------------------
 
 // tensorLog (runtime.cpp:1029-1045): any x <= 0 raises the flag (the reference throws there).
 __global__ void __launch_bounds__(kThreads) log_kernel(
     const float *__restrict__ in, float *__restrict__ out, uint64_t n, int vec, uint32_t *flags) {
-    __shared__ double rc[kLogTableSize];
-    __shared__ double lc[kLogTableSize];
-    for (int j = threadIdx.x; j < kLogTableSize; j += kThreads) {
-        rc[j] = g_log_rc[j];
-        lc[j] = g_log_lc[j];
-    }
-    __syncthreads();
     auto one = [&](float x) -> float {
+        if (x >= 1.17549435e-38f && x <= 3.4028234663852886e38f)
+            return log_f32_normal(x, 0); // the common case behind one range test
         if (x <= 0.0f) {
             flags[FLAG_LOG_DOMAIN] = 1;
             return 0.0f;
         }
-        return (float)log_from_f32((double)x, rc, lc);
+        return log_f32_pos(x);
     };
     if (vec) {
         uint64_t nv   = n / kVec;
@@ -788,7 +759,6 @@ ct_status ct_log(const float *in, uint64_t n, float *out) {
         return CT_OK;
     if (!in || !out)
         return fail(CT_ERR_INVALID, "ct_log: null pointer");
-    CT_TRY(ensure_log_tables(st));
     CT_TRY(clear_flags(st));
     {
         uint64_t per_block = (uint64_t)kThreads * kUnroll * kVec;

@@ -546,6 +546,322 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
         atomicExch(p.flags + FLAG_TIMEOUT, 1u + (uint32_t)blockIdx.x);
 }
 
+// ---- the same pipeline, many short tiles per CTA ------------------------------------------
+//
+// When a tile's whole k range fits one accumulation (k <= 1024: conv2d with a few hundred
+// channel-taps, batched layers), the kernel above spends as long before and after the main loop
+// (barrier and TMEM set-up, first operands, final store: ~7 us) as in it.  Here one CTA per SM
+// walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...: the TMA ring and the two TMEM accumulators
+// carry on across tiles, so the producer is already fetching tile i+1 while tile i computes, and
+// the epilogue warps drain and store tile i (from registers, through their own staging area)
+// while the MMA warp fills the other accumulator with tile i+1.
+template <int BN, int MODE> struct StreamCfg {
+    using C = Cfg<BN, MODE, 64>;
+    static constexpr int kEpiCols      = 64; // columns staged at a time
+    static constexpr int kEpiRowBytes  = kEpiCols * 4 + 16;
+    static constexpr int kEpiWarpBytes = 32 * kEpiRowBytes;
+    static constexpr int kEpiBytes     = C::kEpiWarps * kEpiWarpBytes;
+    static constexpr int kStagesFit    = (226 * 1024 - 1024 - kEpiBytes) / C::kStageBytes;
+    static constexpr int kStages       = kStagesFit > 8 ? 8 : kStagesFit;
+    static constexpr int kSmemBytes    = kStages * C::kStageBytes + kEpiBytes + 1024;
+    static_assert(kStages >= 2, "at least two pipeline stages");
+};
+
+__device__ __forceinline__ void tile_coords(const GemmParams &p, int tile, int &tm, int &tn, int &tz) {
+    int per_batch  = p.tiles_m * p.tiles_n;
+    tz             = tile / per_batch;
+    int bid        = tile - tz * per_batch;
+    int group_size = 16 * p.tiles_n;
+    int g          = bid / group_size;
+    int first_m    = g * 16;
+    int gm         = p.tiles_m - first_m < 16 ? p.tiles_m - first_m : 16;
+    int in_group   = bid - g * group_size;
+    tm             = first_m + in_group % gm;
+    tn             = in_group / gm;
+}
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(Cfg<BN, MODE, 64>::kThreads, 1) gemm_tc_stream_kernel(
+    const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+    const GemmParams p, const int total_tiles) {
+    constexpr int RB = 64;
+    using C          = Cfg<BN, MODE, RB>;
+    using S          = StreamCfg<BN, MODE>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full[S::kStages];
+    __shared__ uint64_t bar_empty[S::kStages];
+    __shared__ uint64_t bar_tmem_full[2];
+    __shared__ uint64_t bar_tmem_empty[2];
+    __shared__ uint64_t bar_done;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag_s;
+    volatile int *abort_flag = &abort_flag_s;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0)
+        abort_flag_s = *reinterpret_cast<volatile uint32_t *>(p.flags + FLAG_TIMEOUT) != 0 ? 1 : 0;
+    __syncthreads();
+    if (abort_flag_s)
+        return;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    auto stage_addr          = [&](int s) { return smem_base + (uint32_t)s * C::kStageBytes; };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::kStages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bar_tmem_full[b]), 1);
+            mbar_init(smem_u32(&bar_tmem_empty[b]), C::kEpiWarps);
+        }
+        mbar_init(smem_u32(&bar_done), 1);
+        mbar_fence_init();
+        prefetch_tensormap(&map_a_hi);
+        prefetch_tensormap(&map_b_hi);
+        if (MODE == MODE_3X) {
+            prefetch_tensormap(&map_a_lo);
+            prefetch_tensormap(&map_b_lo);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    const int nkb            = p.num_k_blocks;
+
+    if (warp == 0) {
+        // ===== TMA producer: k-blocks numbered across tiles =====
+        if (lane == 0) {
+            int kbg = 0; // k-blocks issued so far
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                int tm, tn, tz;
+                tile_coords(p, tile, tm, tn, tz);
+                for (int kb = 0; kb < nkb; ++kb, ++kbg) {
+                    int s       = kbg % S::kStages;
+                    uint32_t ph = (uint32_t)(kbg / S::kStages) & 1u;
+                    if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    uint32_t full = smem_u32(&bar_full[s]);
+                    uint32_t dst  = stage_addr(s);
+                    mbar_expect_tx(full, (uint32_t)(C::kPlanes * (C::kABytes + p.tile_n * C::kRowB)));
+                    int32_t kc = kb * C::kBlockK;
+                    tma_load_2d(dst, &map_a_hi, full, kc, tm * BM);
+                    dst += C::kABytes;
+                    if (MODE == MODE_3X) {
+                        tma_load_2d(dst, &map_a_lo, full, kc, tm * BM);
+                        dst += C::kABytes;
+                    }
+                    if (p.conv) {
+                        int rs = kb / p.conv_cblocks, cb = kb - rs * p.conv_cblocks;
+                        int r = rs / p.conv_kw, sx = rs - r * p.conv_kw;
+                        int32_t c0 = cb * C::kBlockK, w0 = sx - p.conv_pad, h0 = tn * p.conv_th + r - p.conv_pad;
+                        tma_load_4d(dst, &map_b_hi, full, c0, w0, h0, tz);
+                        dst += C::kBBytes;
+                        if (MODE == MODE_3X)
+                            tma_load_4d(dst, &map_b_lo, full, c0, w0, h0, tz);
+                    } else {
+                        tma_load_3d(dst, &map_b_hi, full, kc, tn * BN, tz);
+                        dst += C::kBBytes;
+                        if (MODE == MODE_3X)
+                            tma_load_3d(dst, &map_b_lo, full, kc, tn * BN, tz);
+                    }
+                }
+            }
+            if (*abort_flag) {
+                // unwind: let the copies still in flight land before the CTA goes away
+                int first = kbg - S::kStages < 0 ? 0 : kbg - S::kStages;
+                for (int k2 = first; k2 < kbg; ++k2) {
+                    uint32_t bar = smem_u32(&bar_full[k2 % S::kStages]);
+                    uint32_t ph  = (uint32_t)(k2 / S::kStages) & 1u;
+                    uint64_t t0  = globaltimer_ns();
+                    while (!mbar_try_wait(bar, ph) && globaltimer_ns() - t0 < kWaitBudgetNs) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer: accumulator buffer i & 1 for the CTA's i-th tile =====
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(MODE == MODE_3X ? 2u : 1u, BM, (uint32_t)p.tile_n);
+            int kbg = 0, i = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++i) {
+                int buf = i & 1;
+                if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), (((uint32_t)i >> 1) & 1u) ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
+                bool first      = true;
+                for (int kb = 0; kb < nkb; ++kb, ++kbg) {
+                    int s       = kbg % S::kStages;
+                    uint32_t ph = (uint32_t)(kbg / S::kStages) & 1u;
+                    if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    uint32_t a_hi = stage_addr(s);
+                    uint32_t a_lo = a_hi + C::kABytes;
+                    uint32_t b_hi = a_hi + C::kPlanes * C::kABytes;
+                    uint32_t b_lo = b_hi + C::kBBytes;
+                    uint64_t da_hi = smem_desc_k<RB>(a_hi), db_hi = smem_desc_k<RB>(b_hi);
+                    uint64_t da_lo = smem_desc_k<RB>(a_lo), db_lo = smem_desc_k<RB>(b_lo);
+#pragma unroll
+                    for (int kk = 0; kk < C::kKSteps; ++kk) {
+                        uint64_t adv = (uint64_t)(kk * 32 >> 4);
+                        if (MODE == MODE_3X) {
+                            mma_tf32(d_tmem, da_lo + adv, db_hi + adv, idesc, first ? 0u : 1u);
+                            mma_tf32(d_tmem, da_hi + adv, db_lo + adv, idesc, 1u);
+                            mma_tf32(d_tmem, da_hi + adv, db_hi + adv, idesc, 1u);
+                        } else {
+                            mma_f16(d_tmem, da_hi + adv, db_hi + adv, idesc, first ? 0u : 1u);
+                        }
+                        first = false;
+                    }
+                    tc_commit(smem_u32(&bar_empty[s]));
+                }
+                if (ok)
+                    tc_commit(smem_u32(&bar_tmem_full[buf]));
+            }
+            if (!ok || *abort_flag) {
+                tc_commit(smem_u32(&bar_done));
+                uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(smem_u32(&bar_done), 0) && globaltimer_ns() - t0 < kWaitBudgetNs) {
+                }
+            }
+        }
+    } else {
+        // ===== epilogue: drain tile i to registers, release the accumulator, then store =====
+        const int ew      = warp - 2;
+        const int quarter = warp & 3;
+        const int half    = ew >> 2;
+        uint8_t *stg = smem_raw + (smem_base - smem_u32(smem_raw)) + (uint32_t)S::kStages * C::kStageBytes +
+                       (uint32_t)ew * S::kEpiWarpBytes;
+        int i = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++i) {
+            int tm, tn, tz;
+            tile_coords(p, tile, tm, tn, tz);
+            const int buf = i & 1;
+            bool got = mbar_wait(smem_u32(&bar_tmem_full[buf]), ((uint32_t)i >> 1) & 1u, abort_flag);
+            if (!__all_sync(0xffffffffu, got))
+                break;
+            tc_fence_after_sync();
+            float acc[128];
+            uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + g * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    acc[g * 32 + j] = __uint_as_float(r[j]);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+
+            const int64_t row0 = (int64_t)tm * BM + quarter * 32;
+            const int64_t col0 = (int64_t)tn * p.tile_n + half * 128;
+            const int64_t lim  = (int64_t)(tn + 1) * p.tile_n < p.n ? (int64_t)(tn + 1) * p.tile_n : p.n;
+            float *out_z       = p.out + (int64_t)tz * p.out_batch_stride;
+            if ((p.ldc & 3) == 0 && (col0 & 3) == 0 && (reinterpret_cast<uintptr_t>(out_z) & 15u) == 0) {
+                // 64 columns at a time through the warp's staging block (rows padded to 272 bytes);
+                // written out two rows (2 x 256 contiguous bytes) per instruction
+                const int sub = lane & 15, rr = lane >> 4;
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    if (col0 + h2 * 64 >= lim)
+                        break;
+                    float4 *mine = reinterpret_cast<float4 *>(stg + lane * S::kEpiRowBytes);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        mine[j] = make_float4(acc[h2 * 64 + 4 * j], acc[h2 * 64 + 4 * j + 1], acc[h2 * 64 + 4 * j + 2],
+                                              acc[h2 * 64 + 4 * j + 3]);
+                    __syncwarp();
+                    const int64_t col = col0 + h2 * 64 + sub * 4;
+                    float b4[4]       = {0.0f, 0.0f, 0.0f, 0.0f};
+                    if (p.bias && !p.bias_per_row) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (col + q < lim)
+                                b4[q] = p.bias[col + q];
+                    }
+#pragma unroll 4
+                    for (int it = 0; it < 16; ++it) {
+                        const int r_in = it * 2 + rr;
+                        if (row0 + r_in < p.m) {
+                            float4 q4 = *reinterpret_cast<const float4 *>(stg + r_in * S::kEpiRowBytes + sub * 16);
+                            float v[4] = {q4.x, q4.y, q4.z, q4.w};
+                            const float rb = (p.bias && p.bias_per_row) ? p.bias[row0 + r_in] : 0.0f;
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                float x = v[q];
+                                if (p.bias)
+                                    x = __fadd_rn(x, p.bias_per_row ? rb : b4[q]);
+                                if (p.act == CT_ACT_RELU)
+                                    x = __fmul_rn(x, x > 0.0f ? 1.0f : 0.0f);
+                                v[q] = x;
+                            }
+                            float *dst = out_z + (row0 + r_in) * p.ldc;
+                            if (col + 3 < lim) {
+                                *reinterpret_cast<float4 *>(dst + col) = make_float4(v[0], v[1], v[2], v[3]);
+                            } else {
+#pragma unroll
+                                for (int q = 0; q < 4; ++q)
+                                    if (col + q < lim)
+                                        dst[col + q] = v[q];
+                            }
+                        }
+                    }
+                    __syncwarp(); // the block is rewritten by the next half / tile
+                }
+            } else if (row0 + lane < p.m) {
+                const int64_t row = row0 + lane;
+                float *dst        = out_z + row * p.ldc;
+                const float rb    = (p.bias && p.bias_per_row) ? p.bias[row] : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 128; ++j) {
+                    int64_t col = col0 + j;
+                    if (col < lim) {
+                        float x = acc[j];
+                        if (p.bias)
+                            x = __fadd_rn(x, p.bias_per_row ? rb : p.bias[col]);
+                        if (p.act == CT_ACT_RELU)
+                            x = __fmul_rn(x, x > 0.0f ? 1.0f : 0.0f);
+                        dst[col] = x;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag)
+        atomicExch(p.flags + FLAG_TIMEOUT, 1u + (uint32_t)blockIdx.x);
+}
+
 } // namespace
 
 // ---- host side --------------------------------------------------------------------------
@@ -689,6 +1005,25 @@ ct_status launch_gemm(
     int64_t tiles  = (int64_t)p.tiles_m * p.tiles_n * grid_batch;
     if (tiles > 0x7fffffffll)
         return fail(CT_ERR_TOO_LARGE, "gemm: too many tiles");
+    if constexpr (RB == 64) {
+        // more tiles than SMs, each with a k range short enough for one accumulation (k <= 1024,
+        // the error stays at the level of the chunked form): one CTA per SM walks the tiles
+        static const bool streaming = !getenv("CAMEL_TENSOR_NO_STREAM");
+        if (streaming && splits == 1 && p.num_k_blocks <= 64 && tiles > st->sm_count) {
+            using S = StreamCfg<BN, MODE>;
+            static bool stream_attr_set = false;
+            if (!stream_attr_set) {
+                CT_CUDA(cudaFuncSetAttribute(
+                    gemm_tc_stream_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes));
+                stream_attr_set = true;
+            }
+            ProfScope prof("gemm_tc");
+            gemm_tc_stream_kernel<BN, MODE><<<(unsigned)st->sm_count, C::kThreads, S::kSmemBytes, stream()>>>(
+                ma_hi, ma_lo, mb_hi, mb_lo, p, (int)tiles);
+            CT_LAUNCH_CHECK("gemm_tc_stream");
+            return CT_OK;
+        }
+    }
     static bool attr_set = false;
     if (!attr_set) {
         CT_CUDA(cudaFuncSetAttribute(

@@ -407,8 +407,8 @@ __global__ void __launch_bounds__(THREADS) softmax_rows_kernel(const float *in, 
 // Wide rows (cols a multiple of 4, 16-byte aligned rows, cols <= 4 * V4 * THREADS): the same
 // three phases with 128-bit loads and stores, and register use capped so that at least two
 // blocks share an SM - while one block sits in a reduction the other streams.
-template <int V4, int THREADS>
-__global__ void __launch_bounds__(THREADS, 2)
+template <int V4, int THREADS, int MIN_BLOCKS = 2>
+__global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
     softmax_rows_wide_kernel(const float *__restrict__ in, int64_t rows, int64_t cols, float *__restrict__ out) {
     constexpr int WARPS = THREADS / 32;
     __shared__ float s_max[WARPS];
@@ -443,10 +443,10 @@ __global__ void __launch_bounds__(THREADS, 2)
     for (int k = 0; k < V4; ++k) {
         int j = k * THREADS + threadIdx.x;
         if (j < nvec) {
-            v[k].x = exp_f32(__fsub_rn(v[k].x, m));
-            v[k].y = exp_f32(__fsub_rn(v[k].y, m));
-            v[k].z = exp_f32(__fsub_rn(v[k].z, m));
-            v[k].w = exp_f32(__fsub_rn(v[k].w, m));
+            v[k].x = exp_f32_nonpos(__fsub_rn(v[k].x, m));
+            v[k].y = exp_f32_nonpos(__fsub_rn(v[k].y, m));
+            v[k].z = exp_f32_nonpos(__fsub_rn(v[k].z, m));
+            v[k].w = exp_f32_nonpos(__fsub_rn(v[k].w, m));
             acc += ((double)v[k].x + (double)v[k].y) + ((double)v[k].z + (double)v[k].w);
         }
     }
@@ -458,12 +458,14 @@ __global__ void __launch_bounds__(THREADS, 2)
 #pragma unroll
     for (int o2 = WARPS / 2; o2 > 0; o2 >>= 1)
         total += __shfl_xor_sync(0xffffffffu, total, o2);
-    const float d = (float)total;
+    const float d  = (float)total;
+    const float rd = __frcp_rn(d);
 #pragma unroll
     for (int k = 0; k < V4; ++k) {
         int j = k * THREADS + threadIdx.x;
         if (j < nvec)
-            __stcs(o + j, make_float4(__fdiv_rn(v[k].x, d), __fdiv_rn(v[k].y, d), __fdiv_rn(v[k].z, d), __fdiv_rn(v[k].w, d)));
+            __stcs(o + j, make_float4(div_small_by(v[k].x, d, rd), div_small_by(v[k].y, d, rd),
+                                      div_small_by(v[k].z, d, rd), div_small_by(v[k].w, d, rd)));
     }
 }
 
