@@ -31,6 +31,7 @@ PROTOTYPES = {
     "ct_version": (C.c_char_p, []),
     "ct_device_count": (_int, [C.POINTER(_int)]),
     "ct_set_device": (_int, [_int]),
+    "ct_get_device": (_int, [C.POINTER(_int)]),
     "ct_set_stream": (_int, [_vp]),
     "ct_sync": (_int, []),
     "ct_check": (_int, []),
@@ -79,6 +80,8 @@ PROTOTYPES = {
     "ct_eye": (_int, [_i64, _vp]),
     "ct_arange": (_int, [_i64, _i64, _i64, _vp]),
     "ct_matmul": (_int, [_int, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
+    "ct_matmul_tn": (_int, [_vp, _vp, _i64, _i64, _i64, _vp]),
+    "ct_scaled_sub": (_int, [_vp, _vp, _dbl, _u64, _vp]),
     "ct_dense": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),
     "ct_weights_pack": (_int, [_vp, _i64, _i64, C.POINTER(_vp)]),
     "ct_weights_free": (_int, [_vp]),

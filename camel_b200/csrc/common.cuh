@@ -10,6 +10,8 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
+#include <utility>
 
 namespace ct {
 
@@ -76,6 +78,38 @@ ct_status fetch_flags(DeviceState *st);
             return ::ct::cuda_fail(e__, name);                                                     \
     } while (0)
 
+// Programmatic dependent launch.  A chain of short kernels (the layers of an MLP: 8-40 us each)
+// otherwise pays, at every boundary, the drain of one grid, the launch of the next and its set-up.
+// A kernel launched with launch_dependent() may be scheduled while its predecessor in the stream
+// is still running; it must execute griddep_wait() before it touches any global memory (the wait
+// returns once the predecessor grid has completed and its writes are visible), so only its set-up
+// (barrier initialisation, TMEM allocation, descriptor prefetch, index arithmetic) overlaps.  A
+// kernel lets its successor start early with griddep_launch_dependents(); without that call the
+// successor starts when the grid ends, as usual.  CAMEL_TENSOR_NO_PDL=1 turns the attribute off.
+#ifdef __CUDACC__
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(
+    void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args &&...args) {
+    static const bool enabled = getenv("CAMEL_TENSOR_NO_PDL") == nullptr;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim          = grid;
+    cfg.blockDim         = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream           = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs    = attr;
+    cfg.numAttrs = enabled ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#endif
+
 // When profiling is on (ct_profile_enable), brackets the launches made in its scope with CUDA
 // events on the launching stream, filed under `name` (a string literal).
 class ProfScope {
@@ -109,7 +143,7 @@ constexpr uint32_t kPackedMagic = 0x43545057u; // "CTPW"
 
 ct_status gemm_f32_tc(
     DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
-    int64_t n, int act, float *out, const PackedWeights *packed = nullptr);
+    int64_t n, int act, float *out, const PackedWeights *packed = nullptr, bool a_is_km = false);
 // Geometry of a stride-1 convolution run as an implicit GEMM over NHWC input planes.
 struct ConvGeom {
     int c_pad;  // channels rounded up to the k-block

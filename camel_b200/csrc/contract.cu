@@ -261,6 +261,29 @@ ct_status ct_matmul(
     return matmul_generic(adt, a, bdt, b, m, k, n, out);
 }
 
+ct_status ct_matmul_tn(const float *a_km, const float *b, int64_t m, int64_t k, int64_t n, float *out) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (m < 0 || k < 0 || n < 0)
+        return fail(CT_ERR_INVALID, "matmul: negative dimension");
+    if (m == 0 || n == 0)
+        return CT_OK;
+    if (!out || (k > 0 && (!a_km || !b)))
+        return fail(CT_ERR_INVALID, "matmul: null pointer");
+    if (n <= 32 || m * n * (k > 0 ? k : 1) < kTinyMacs) {
+        // shapes the tensor-core kernel does not take: materialise the transpose, then as ct_matmul
+        void *at = nullptr;
+        CT_TRY(ct_alloc(&at, (size_t)(m * k > 0 ? m * k : 1) * sizeof(float)));
+        ct_status s = k > 0 ? ct_transpose(CT_F32, a_km, k, m, at) : CT_OK;
+        if (s == CT_OK)
+            s = ct_matmul(CT_F32, at, CT_F32, b, m, k, n, out);
+        ct_status f = ct_free(at);
+        return s != CT_OK ? s : f;
+    }
+    CT_TRY(clear_flags(st));
+    return gemm_f32_tc(st, a_km, b, nullptr, m, k, n, CT_ACT_NONE, out, nullptr, /*a_is_km=*/true);
+}
+
 ct_status ct_dense(
     const float *x, const float *w, const float *bias, int64_t m, int64_t k, int64_t n,
     ct_activation act, float *out, int64_t *argmax) {

@@ -479,6 +479,32 @@ template <int OP> ct_status unary(const float *t, uint64_t n, float *o, uint32_t
     return launch_map(n - done, Unary<OP, false>{t, o, flags, done}, name);
 }
 
+// ---- w - g * lr in one pass (the parameter update of the reference's training loops) ------
+
+// Same roundings as the two operators it replaces: t = float(double(g) * lr) (tensor * scalar,
+// runtime.cpp:795-812), then float(double(w) - double(t)) = the IEEE float32 difference.
+template <bool VEC> struct ScaledSub {
+    const float *w;
+    const float *g;
+    float *o;
+    double lr;
+    uint64_t offset;
+    __device__ float one(float wv, float gv) const { return __fsub_rn(wv, (float)((double)gv * lr)); }
+    __device__ void operator()(uint64_t i) const {
+        if (VEC) {
+            VecT<float> a = load_vec<float>(w, i);
+            VecT<float> b = load_vec<float>(g, i);
+            VecT<float> c;
+#pragma unroll
+            for (int k = 0; k < kVec; ++k)
+                c.v[k] = one(a.v[k], b.v[k]);
+            store_vec(o, i, c);
+        } else {
+            o[i + offset] = one(w[i + offset], g[i + offset]);
+        }
+    }
+};
+
 // ---- log ------------------------------------------------------------------------------
 
 // tensorLog (runtime.cpp:1029-1045): any x <= 0 raises the flag (the reference throws there).
@@ -774,6 +800,22 @@ ct_status ct_log(const float *in, uint64_t n, float *out) {
     if (st->flags_host[FLAG_LOG_DOMAIN])
         return fail(CT_ERR_LOG_DOMAIN, "log: input must be positive");
     return CT_OK;
+}
+
+ct_status ct_scaled_sub(const float *w, const float *g, double lr, uint64_t n, float *out) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (n == 0)
+        return CT_OK;
+    if (!w || !g || !out)
+        return fail(CT_ERR_INVALID, "ct_scaled_sub: null pointer");
+    uint64_t nv = 0;
+    if (aligned16(w) && aligned16(g) && aligned16(out)) {
+        nv = n / kVec;
+        CT_TRY(launch_map(nv, ScaledSub<true>{w, g, out, lr, 0}, "scaled_sub"));
+    }
+    uint64_t done = nv * kVec;
+    return launch_map(n - done, ScaledSub<false>{w, g, out, lr, done}, "scaled_sub");
 }
 
 ct_status ct_relu(const float *in, uint64_t n, float *out) {

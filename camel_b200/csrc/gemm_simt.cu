@@ -381,6 +381,8 @@ __global__ void __launch_bounds__(32 * kSkinnyWarps, 1) gemm_skinny_tile_kernel(
     int klen           = k - k0;
     klen               = klen < 0 ? 0 : (klen > ks ? ks : klen);
     const int nchunks  = (klen + 31) >> 5;
+    griddep_launch_dependents();
+    griddep_wait(); // activations (and possibly weights) come from the previous kernel
     SK_STAMP(0);
     // weights of the slice, w[(k0 + kk) * n + j] -> ws[kk * NE + j], widened once.  The first round of
     // loads is issued before the activation copies so that its latency passes while those are issued.
@@ -505,8 +507,9 @@ ct_status launch_skinny_tile(
     if (smem > 48 * 1024)
         CT_CUDA(cudaFuncSetAttribute(
             gemm_skinny_tile_kernel<NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    gemm_skinny_tile_kernel<NP><<<(unsigned)((m + 31) / 32), 32 * kSkinnyWarps, smem, stream()>>>(
-        a, b, bias, m, (int)k, n, skinny_tile_slice(k), act, out, argmax);
+    CT_CUDA(launch_dependent(
+        gemm_skinny_tile_kernel<NP>, dim3((unsigned)((m + 31) / 32)), dim3(32 * kSkinnyWarps), smem, stream(), a, b, bias,
+        m, (int)k, n, skinny_tile_slice(k), act, out, argmax));
     CT_LAUNCH_CHECK("gemm_skinny_tile");
     return CT_OK;
 }

@@ -120,6 +120,8 @@ template <int MODE>
 __global__ void __launch_bounds__(256) split_rows_vec_kernel(
     const float *__restrict__ in, int64_t rows, int64_t k, int64_t kp, void *__restrict__ p_hi,
     void *__restrict__ p_lo, int in_vec_ok) {
+    griddep_launch_dependents();
+    griddep_wait(); // the input may be the previous kernel's output, the planes its operands
     const int64_t c = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
     if (c >= kp)
         return;
@@ -228,6 +230,7 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    griddep_launch_dependents();
 
     // If an earlier CTA of this launch already timed out, do not start: the launch has failed
     // and the remaining CTAs should drain at once instead of each waiting out its own budget.
@@ -288,6 +291,9 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
     const uint32_t tmem_base = tmem_base_slot;
     if (threadIdx.x == 0)
         CT_STAMP(1);
+    // everything above is set-up that does not depend on earlier kernels; the operands and the
+    // output may
+    griddep_wait();
 
     // split-K (kb_per_split > 0): the leading block index selects a slice of the k-blocks instead
     // of a batch entry; every slice writes its own partial output, summed by a second kernel
@@ -1031,8 +1037,9 @@ ct_status launch_gemm(
         attr_set = true;
     }
     ProfScope prof("gemm_tc");
-    gemm_tc_kernel<BN, MODE, RB><<<(unsigned)tiles, C::kThreads, C::kSmemBytes, stream()>>>(
-        ma_hi, ma_lo, mb_hi, mb_lo, p);
+    CT_CUDA(launch_dependent(
+        gemm_tc_kernel<BN, MODE, RB>, dim3((unsigned)tiles), dim3(C::kThreads), (size_t)C::kSmemBytes, stream(), ma_hi,
+        ma_lo, mb_hi, mb_lo, p));
     CT_LAUNCH_CHECK("gemm_tc");
     return CT_OK;
 }
@@ -1146,9 +1153,9 @@ ct_status split_rows_planes(
     dim3 grid((unsigned)((kp / 4 + 255) / 256), (unsigned)(rows < 65535 ? rows : 65535));
     int vec_ok = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0;
     if (mode == MODE_3X)
-        split_rows_vec_kernel<MODE_3X><<<grid, 256, 0, stream()>>>(in, rows, k, kp, hi, lo, vec_ok);
+        CT_CUDA(launch_dependent(split_rows_vec_kernel<MODE_3X>, grid, dim3(256), 0, stream(), in, rows, k, kp, hi, lo, vec_ok));
     else
-        split_rows_vec_kernel<MODE_BF><<<grid, 256, 0, stream()>>>(in, rows, k, kp, hi, lo, vec_ok);
+        CT_CUDA(launch_dependent(split_rows_vec_kernel<MODE_BF>, grid, dim3(256), 0, stream(), in, rows, k, kp, hi, lo, vec_ok));
     CT_LAUNCH_CHECK("split_rows");
     return CT_OK;
 }
@@ -1158,7 +1165,7 @@ constexpr int64_t kMaxDim = 1ll << 30;
 
 ct_status gemm_f32_tc(
     DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
-    int64_t n, int act, float *out, const PackedWeights *packed) {
+    int64_t n, int act, float *out, const PackedWeights *packed, bool a_is_km) {
     if (m == 0 || n == 0)
         return CT_OK;
     if (m > kMaxDim || n > kMaxDim || k > kMaxDim)
@@ -1193,7 +1200,19 @@ ct_status gemm_f32_tc(
         b_lo = packed->lo;
     }
 
-    {
+    if (a_is_km) {
+        // A is stored [k][m] (the product is A^T . B): its planes [m][kp] come out of the same
+        // transposing pass that prepares B, so no transposed copy of A is ever written
+        ProfScope prof("gemm_prepass");
+        dim3 grid((unsigned)((m + 31) / 32), (unsigned)(kp / 32));
+        if (grid.y > 65535)
+            return fail(CT_ERR_TOO_LARGE, "gemm: k too large for the operand pre-pass");
+        if (mode == MODE_3X)
+            split_transpose_kernel<MODE_3X><<<grid, 256, 0, stream()>>>(a, k, m, kp, a_hi, a_lo);
+        else
+            split_transpose_kernel<MODE_BF><<<grid, 256, 0, stream()>>>(a, k, m, kp, a_hi, a_lo);
+        CT_LAUNCH_CHECK("split_transpose");
+    } else {
         ProfScope prof("gemm_prepass");
         CT_TRY(split_rows_planes(st, mode, a, m, k, kp, a_hi, a_lo));
     }

@@ -194,6 +194,15 @@ ct_status ct_set_device(int device) {
     return current(&st);
 }
 
+ct_status ct_get_device(int *device_host) {
+    if (!device_host)
+        return fail(CT_ERR_INVALID, "device_host is null");
+    DeviceState *st;
+    CT_TRY(current(&st));
+    *device_host = st->device;
+    return CT_OK;
+}
+
 ct_status ct_set_stream(void *s) {
     g_stream.store(static_cast<cudaStream_t>(s));
     return CT_OK;

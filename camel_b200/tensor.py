@@ -61,6 +61,15 @@ class Tensor:
             self.ptr = ptr
             self._owns = False
 
+    def __dlpack__(self, stream=None, **_unused):
+        """DLPack export of the device buffer itself (no copy); see camel_b200.dlpack."""
+        from . import dlpack
+        return dlpack.to_dlpack(self)
+
+    def __dlpack_device__(self):
+        from . import dlpack
+        return (dlpack.kDLCUDA, dlpack.current_device())
+
     def invalidate(self) -> None:
         """Drops what was derived from the contents (packed weights).  Tensors are immutable
         values, as in the reference; code that overwrites a buffer through the raw C ABI calls this."""
@@ -238,6 +247,38 @@ def matmul(lhs: Tensor, rhs: Tensor) -> Tensor:
     n = rhs.shape[1]
     out = Tensor(lib.ct_result_dtype(L.ADD, lhs.dtype, rhs.dtype), (m, n))
     check(lib.ct_matmul(lhs.dtype, lhs.ptr, rhs.dtype, rhs.ptr, m, k, n, out.ptr))
+    return out
+
+
+def matmul_tn(lhs: Tensor, rhs: Tensor) -> Tensor:
+    """transpose(lhs) @ rhs without the transposed copy (the gradient of test/run/nn/mnist.cml:39);
+    float tensors, same bytes as matmul(transpose(lhs), rhs)."""
+    if not (_is_tensor(lhs) and _is_tensor(rhs)):
+        raise _invalid("Expected Tensor argument")
+    if lhs.rank != 2 or rhs.rank != 2:
+        raise _invalid("matmul currently only supports rank-2 tensors")
+    if lhs.shape[0] != rhs.shape[0]:
+        raise _invalid("matmul dimension mismatch")
+    _require_float(lhs, "matmul_tn")
+    _require_float(rhs, "matmul_tn")
+    k, m = lhs.shape
+    n = rhs.shape[1]
+    out = Tensor(L.F32, (m, n))
+    check(lib.ct_matmul_tn(lhs.ptr, rhs.ptr, m, k, n, out.ptr))
+    return out
+
+
+def scaled_sub(w: Tensor, g: Tensor, lr: float) -> Tensor:
+    """w - lr * g in one pass (the update of test/run/nn/mnist.cml:40), same bytes as
+    subtract(w, multiply(g, lr))."""
+    if not (_is_tensor(w) and _is_tensor(g)):
+        raise _invalid("Expected Tensor argument")
+    if w.shape != g.shape:
+        raise _invalid("Tensor binary operations currently require matching shapes")
+    _require_float(w, "scaled_sub")
+    _require_float(g, "scaled_sub")
+    out = Tensor(L.F32, w.shape)
+    check(lib.ct_scaled_sub(w.ptr, g.ptr, float(lr), w.numel, out.ptr))
     return out
 
 

@@ -70,6 +70,7 @@ const char *ct_last_error(void);
 const char *ct_version(void);
 ct_status ct_device_count(int *count_host);
 ct_status ct_set_device(int device);
+ct_status ct_get_device(int *device_host);
 /* stream is a cudaStream_t passed as void*; NULL selects the legacy default stream. */
 ct_status ct_set_stream(void *stream);
 ct_status ct_sync(void);
@@ -211,6 +212,14 @@ ct_status ct_arange(int64_t start, int64_t step, int64_t count, int64_t *out_dev
 ct_status ct_matmul(
     ct_dtype a_dtype, const void *a_dev, ct_dtype b_dtype, const void *b_dev, int64_t m,
     int64_t k, int64_t n, void *out_dev);
+
+/* The two fused forms the reference's training loops call for (test/run/nn/mnist.cml:39-40:
+ * `transpose(X) @ (probs - y)` and `W - lr * g`), each with the roundings of the operator chain it
+ * replaces.  ct_matmul_tn: out[m,n] = A^T . B with A stored [k][m]; identical to ct_transpose
+ * followed by ct_matmul, without the transposed copy.  ct_scaled_sub: out = w - float(double(g) * lr)
+ * (tensor * scalar, then tensor - tensor).  No single reference function corresponds to either. */
+ct_status ct_matmul_tn(const float *a_km_dev, const float *b_dev, int64_t m, int64_t k, int64_t n, float *out_dev);
+ct_status ct_scaled_sub(const float *w_dev, const float *g_dev, double lr, uint64_t numel, float *out_dev);
 
 /* dense<w,b>(x) = act(x . w + b): the bias idiom concat(x, ones, 1) @ concat(w, b, 0) of
  * test/run/nn/lr.cml:19-21 with the activation fused into the GEMM epilogue.  bias_dev may be

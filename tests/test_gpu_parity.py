@@ -500,6 +500,59 @@ def test_exp_log_float32_paths_against_float64_rounded_once(T):
     assert got[y == 1.0][0] == 0.0 and got[np.isinf(y)][0] == np.inf and np.isnan(got[np.isnan(y)]).all()
 
 
+def test_training_step_fused_forms(T):
+    """transpose(X) @ G and W - lr * g as single calls give the bytes of the operator chains of
+    test/run/nn/mnist.cml:39-40 (tensor-core, few-column and tiny shapes; odd lengths)."""
+    rng = np.random.default_rng(55)
+    for k, m, n in ((512, 784, 64), (300, 200, 10), (37, 5, 3), (1000, 130, 257)):
+        a = T.from_numpy(rng.uniform(-1, 1, (k, m)).astype(np.float32))
+        b = T.from_numpy(rng.uniform(-1, 1, (k, n)).astype(np.float32))
+        got = T.matmul_tn(a, b).numpy()
+        ref = T.matmul(T.transpose(a), b).numpy()
+        T.check_async()
+        assert got.shape == (m, n) and got.tobytes() == ref.tobytes()
+    for count in (100003, 4096, 5):
+        w = rng.uniform(-1, 1, count).astype(np.float32)
+        g = rng.uniform(-3, 3, count).astype(np.float32)
+        lr = 0.01 / 512
+        got = T.scaled_sub(T.from_numpy(w), T.from_numpy(g), lr).numpy()
+        chain = T.subtract(T.from_numpy(w), T.multiply(T.from_numpy(g), lr)).numpy()
+        T.check_async()
+        host = w - (g.astype(np.float64) * lr).astype(np.float32)
+        assert got.tobytes() == chain.tobytes() == host.tobytes()
+
+
+def test_dlpack_zero_copy_with_torch(T):
+    """Device tensors cross to torch and back through DLPack without a copy (same device pointer)."""
+    import torch
+
+    from camel_b200 import dlpack
+
+    rng = np.random.default_rng(44)
+    a = rng.uniform(-1, 1, (37, 19)).astype(np.float32)
+    t = T.from_numpy(a)
+    tt = torch.from_dlpack(t)
+    assert tt.is_cuda and tt.data_ptr() == t.ptr and tuple(tt.shape) == (37, 19)
+    assert np.array_equal(tt.cpu().numpy(), a)
+    tt.mul_(2.0)  # the same memory: visible on our side
+    torch.cuda.synchronize()
+    assert np.array_equal(t.numpy(), a * 2)
+    del tt
+
+    src = torch.arange(12, dtype=torch.int64, device="cuda").reshape(3, 4)
+    u = dlpack.from_dlpack(src)
+    assert u.ptr == src.data_ptr() and u.shape == (3, 4)
+    got = T.add(u, u).numpy()
+    T.check_async()
+    assert np.array_equal(got, 2 * np.arange(12).reshape(3, 4))
+    with pytest.raises(ValueError, match="dense row-major"):
+        dlpack.from_dlpack(src.t())
+    with pytest.raises(ValueError, match="float32, int64"):
+        dlpack.from_dlpack(torch.zeros(4, dtype=torch.float16, device="cuda"))
+    mask = dlpack.from_dlpack(torch.tensor([True, False, True], device="cuda"))
+    assert mask.dtype == 2 and mask.numpy().astype(np.uint8).tolist() == [1, 0, 1]
+
+
 def test_dense_packed_weights(T):
     """The tensor-core layout of a weight tensor is built once and kept with the tensor: same bytes
     as the per-call pre-pass, in both precisions; a handle from another matrix is refused."""
