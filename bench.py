@@ -203,10 +203,14 @@ def run_reference(args, rank):
     kind, units, _, desc = results[0]
     t = max(r[2] for r in results)  # the slowest shard bounds the step
     value = units * workers / t
-    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": 0, "steps": steps,
+    # the same workload description as the GPU arm prints for this --workload
+    workload = {"mlp": "mlp_forward 784-1024-1024-10 relu,relu,softmax+argmax (BASELINE configs[1])",
+                "gemm": f"gemm fp32 M=N=K={args.size} U(-1,1) (BASELINE configs[4] per-GPU problem)"}[args.workload]
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": steps,
             "warmup": warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f64-accumulate/f32", "data": "synthetic",
-            "config": {"workload": args.workload, "note": "reference CPU operators, bounded sample per process"},
+            "vs_baseline": None, "dtype": "f32 (float64 accumulate, the reference's arithmetic)", "data": "synthetic",
+            "config": {"workload": workload, "batch_per_gpu": 4096 if args.workload == "mlp" else None,
+                       "note": "the reference's CPU operators on the host cores, a bounded sample per step and process"},
             "cpu_baseline": {"value": value, "unit": unit, "cores": workers, "kind": kind,
                              "sample": desc + f"; {workers} processes (the kernels themselves are single-threaded)",
                              "host_cores_available": cores},

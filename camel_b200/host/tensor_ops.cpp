@@ -4,7 +4,7 @@
 // (modules/tensor/operators.h:31-63, operators.cpp:160-583), so programs resolve and dispatch
 // exactly as before; each body unpacks its ArgsView the way the reference body does and then
 // calls one function of the C ABI (include/camel_tensor_b200.h) instead of looping on the host.
-// Six operators are added on top (relu, softmax, dense*, conv2d*, maxpool2d, flatten).
+// Operators added on top: relu, softmax, dense*, conv2d*, maxpool2d, flatten, matmul_tn, scaled_sub.
 #include "tensor_ops.h"
 
 #include "camel/core/error/runtime.h"
@@ -629,6 +629,42 @@ CT_OP(__tensor_flatten__) {
         int64_t shape[2]  = {rows, rows ? static_cast<int64_t>(x->numel()) / rows : 0};
         TensorObject *out = newTensor(x->dtype(), shape);
         ctn::ctCheck(ct_d2d(out->deviceData(), x->deviceData(), x->byteSize()));
+        return wrap(out);
+    });
+}
+
+// transpose(a) @ b in one call (test/run/nn/mnist.cml:39), float tensors.
+CT_OP(__tensor_matmul_tn__) {
+    CT_UNUSED;
+    return guarded([&]() -> slot_t {
+        TensorObject *a = requireFloat(tensorArg(norm, 0), "matmul_tn");
+        TensorObject *b = requireFloat(tensorArg(norm, 1), "matmul_tn");
+        if (a->rank() != 2 || b->rank() != 2)
+            throw std::invalid_argument("matmul currently only supports rank-2 tensors");
+        if (a->dim(0) != b->dim(0))
+            throw std::invalid_argument("matmul dimension mismatch");
+        int64_t shape[2]  = {a->dim(1), b->dim(1)};
+        TensorObject *out = newTensor(TypeCode::Float32, shape);
+        ctn::ctCheck(ct_matmul_tn(
+            static_cast<const float *>(a->deviceData()), static_cast<const float *>(b->deviceData()), a->dim(1),
+            a->dim(0), b->dim(1), static_cast<float *>(out->deviceData())));
+        return wrap(out);
+    });
+}
+
+// w - lr * g in one pass (test/run/nn/mnist.cml:40), float tensors of one shape.
+CT_OP(__tensor_scaled_sub__) {
+    CT_UNUSED;
+    return guarded([&]() -> slot_t {
+        TensorObject *w = requireFloat(tensorArg(norm, 0), "scaled_sub");
+        TensorObject *g = requireFloat(tensorArg(norm, 1), "scaled_sub");
+        if (!w->sameShape(g))
+            throw std::invalid_argument("Tensor binary operation requires matching shapes");
+        double lr         = scalarValue(norm, 2);
+        TensorObject *out = newTensor(TypeCode::Float32, std::span<const int64_t>(w->shape(), w->rank()));
+        ctn::ctCheck(ct_scaled_sub(
+            static_cast<const float *>(w->deviceData()), static_cast<const float *>(g->deviceData()), lr, w->numel(),
+            static_cast<float *>(out->deviceData())));
         return wrap(out);
     });
 }

@@ -132,6 +132,12 @@ std::optional<Type *> convCheck(const type_vec_t &w, const type_vec_t &n) {
                ? some(tensorOf())
                : std::nullopt;
 }
+std::optional<Type *> matmulTnCheck(const type_vec_t &, const type_vec_t &n) {
+    return n.size() == 2 && isTensor(n[0]) && isTensor(n[1]) ? some(tensorOf()) : std::nullopt;
+}
+std::optional<Type *> scaledSubCheck(const type_vec_t &, const type_vec_t &n) {
+    return n.size() == 3 && isTensor(n[0]) && isTensor(n[1]) && isScalar(n[2]) ? some(tensorOf()) : std::nullopt;
+}
 std::optional<Type *> poolCheck(const type_vec_t &, const type_vec_t &n) {
     return n.size() == 2 && isTensor(n[0]) && isInt(n[1]) ? some(tensorOf()) : std::nullopt;
 }
@@ -168,6 +174,7 @@ std::unordered_map<std::string, operator_t> getTensorOpsMap() {
         {"dense_relu", __tensor_dense_relu__}, {"dense_softmax", __tensor_dense_softmax__},
         {"conv2d", __tensor_conv2d__}, {"conv2d_relu", __tensor_conv2d_relu__},
         {"maxpool2d", __tensor_maxpool2d__}, {"flatten", __tensor_flatten__},
+        {"matmul_tn", __tensor_matmul_tn__}, {"scaled_sub", __tensor_scaled_sub__},
     };
 }
 
@@ -224,6 +231,9 @@ const std::vector<oper_group_ptr_t> &getTensorOperatorGroups() {
                                "<w: Tensor, b: Tensor, stride: int, pad: int>(x: Tensor) => Tensor", convCheck}}),
         group("maxpool2d", {{"tensor:maxpool2d", 0, 2, "(t: Tensor, window: int) => Tensor", poolCheck}}),
         group("flatten", {{"tensor:flatten", 0, 1, kUnarySig, unaryCheck}}),
+        group("matmul_tn", {{"tensor:matmul_tn", 0, 2, "(a: Tensor, b: Tensor) => Tensor", matmulTnCheck}}),
+        group("scaled_sub",
+              {{"tensor:scaled_sub", 0, 3, "(w: Tensor, g: Tensor, lr: number) => Tensor", scaledSubCheck}}),
     };
     return groups;
 }

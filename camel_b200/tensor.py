@@ -274,7 +274,7 @@ def scaled_sub(w: Tensor, g: Tensor, lr: float) -> Tensor:
     if not (_is_tensor(w) and _is_tensor(g)):
         raise _invalid("Expected Tensor argument")
     if w.shape != g.shape:
-        raise _invalid("Tensor binary operations currently require matching shapes")
+        raise _invalid("Tensor binary operation requires matching shapes")
     _require_float(w, "scaled_sub")
     _require_float(g, "scaled_sub")
     out = Tensor(L.F32, w.shape)

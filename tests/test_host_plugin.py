@@ -49,7 +49,8 @@ def test_registration_table_equals_reference(plugin):
     assert mine[: len(ref)] == ref
     extra = {u for _, u, _ in mine[len(ref):]}
     assert extra == {"tensor:relu", "tensor:softmax", "tensor:dense", "tensor:dense_relu", "tensor:dense_softmax",
-                     "tensor:conv2d", "tensor:conv2d_relu", "tensor:maxpool2d", "tensor:flatten"}
+                     "tensor:conv2d", "tensor:conv2d_relu", "tensor:maxpool2d", "tensor:flatten",
+                     "tensor:matmul_tn", "tensor:scaled_sub"}
     ops = set(plugin.ops())
     assert {u.split(":")[1] for _, u, _ in mine} == ops
     if oracle.Reference.available():
@@ -137,3 +138,14 @@ def test_plugin_errors_shapes_and_new_operators(plugin):
     probs = plugin.call("dense_softmax", With(logits_w), With(np.zeros(10, np.float32)), flat)
     ref_probs = p.softmax_rows(p.dense(flat, logits_w, np.zeros(10, np.float32), 0))
     assert np.max(np.abs(probs - ref_probs)) <= 1e-5
+
+    # the two fused forms of the training loop equal the operator chains they replace
+    xs = rng.uniform(0, 1, (300, 200)).astype(np.float32)
+    gs = rng.uniform(-1, 1, (300, 64)).astype(np.float32)
+    grad = plugin.call("matmul_tn", xs, gs)
+    assert grad.tobytes() == plugin.call("matmul", plugin.call("transpose", xs), gs).tobytes()
+    w0 = rng.uniform(-1, 1, (200, 64)).astype(np.float32)
+    upd = plugin.call("scaled_sub", w0, grad, 0.01 / 300)
+    assert upd.tobytes() == plugin.call("subtract", w0, plugin.call("multiply", grad, 0.01 / 300)).tobytes()
+    with pytest.raises(oracle.OracleError, match="matching shapes"):
+        plugin.call("scaled_sub", w0, xs, 0.1)
