@@ -85,11 +85,86 @@ __device__ __forceinline__ float exp_f32(float x) {
     return (float)exp_from_f32((double)x);
 }
 
-// The same for arguments known to be <= 0 or NaN (x - max of a softmax row): one range test.
+// For arguments known to be <= 0 or NaN (x - max of a softmax row): one range test, and the plain
+// form of the same evaluation (degree-4 fit, no residual terms: 18 instructions instead of 28).
+// Still never more than 1 ulp from float(exp(double(x))), identical for 90.6 % of inputs instead of
+// 98.9 %.  A softmax output is this value divided by a rounded sum of such values and rounded
+// again, so its last bits are not the reference's either way (measured: at most 4 ulp, 1e-5
+// relative is the bar), while the wide softmax kernel is bound by instruction issue and gains
+// a fifth in speed from the shorter form.
+__device__ __forceinline__ float exp_f32_plain(float x) { // -87 <= x <= 87, not NaN
+    {
+        const float kMagic = 12582912.0f;
+        const float t  = __fmaf_rn(x, __int_as_float(0x3fb8aa3b), kMagic);
+        const float nf = __fsub_rn(t, kMagic);
+        const int ni   = __float_as_int(t) - 0x4B400000;
+        float r        = __fmaf_rn(nf, -0.693145751953125f, x);
+        r              = __fmaf_rn(nf, -__int_as_float(0x35bfbe8e), r);
+        float q        = __int_as_float(0x3ab6a194);
+        q              = __fmaf_rn(q, r, __int_as_float(0x3c0905ba));
+        q              = __fmaf_rn(q, r, __int_as_float(0x3d2aaa75));
+        q              = __fmaf_rn(q, r, __int_as_float(0x3e2aaa6e));
+        q              = __fmaf_rn(q, r, 0.5f);
+        const float s  = __fmaf_rn(__fmul_rn(r, r), q, r);
+        const float p  = __fadd_rn(1.0f, s);
+        return __int_as_float(__float_as_int(p) + (ni << 23));
+    }
+}
+
 __device__ __forceinline__ float exp_f32_nonpos(float x) {
     if (x >= -87.0f)
-        return exp_f32_core(x);
+        return exp_f32_plain(x);
     return (float)exp_from_f32((double)x);
+}
+
+// ---- two float32 lanes per instruction (sm_100: add / mul / fma .f32x2, IEEE round-to-nearest
+// per lane), for kernels that are bound by instruction issue ----
+typedef unsigned long long f32x2;
+
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float &a, float &b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__host__ __device__ constexpr f32x2 dup2(uint32_t bits) { return ((f32x2)bits << 32) | (f32x2)bits; }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// exp_f32_plain on two values (both in [-87, 87], not NaN): the same operations in the same
+// order, so the same bits, in 11 two-lane instructions plus two integer ones per lane.
+__device__ __forceinline__ f32x2 exp_f32_plain2(f32x2 x) {
+    const f32x2 t  = fma2(x, dup2(0x3fb8aa3bu), dup2(0x4B400000u));   // x log2e + 1.5 * 2^23
+    const f32x2 nf = add2(t, dup2(0xCB400000u));                       // - 1.5 * 2^23
+    f32x2 r        = fma2(nf, dup2(0xBF317200u), x);                   // - n * 0.693145751953125
+    r              = fma2(nf, dup2(0xB5BFBE8Eu), r);                   // - n * (ln2 - hi)
+    f32x2 q        = fma2(dup2(0x3ab6a194u), r, dup2(0x3c0905bau));
+    q              = fma2(q, r, dup2(0x3d2aaa75u));
+    q              = fma2(q, r, dup2(0x3e2aaa6eu));
+    q              = fma2(q, r, dup2(0x3f000000u));
+    const f32x2 s  = fma2(mul2(r, r), q, r);
+    const f32x2 p  = add2(dup2(0x3f800000u), s);
+    // 2^n: the low bits of t hold n (biased by a constant whose low nine bits are zero)
+    float t0, t1, p0, p1;
+    unpack2(t, t0, t1);
+    unpack2(p, p0, p1);
+    return pack2(__int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23)),
+                 __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23)));
 }
 
 // e / d for many numerators and one denominator (a softmax row): with r = __frcp_rn(d), the

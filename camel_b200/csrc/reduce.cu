@@ -443,10 +443,19 @@ __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
     for (int k = 0; k < V4; ++k) {
         int j = k * THREADS + threadIdx.x;
         if (j < nvec) {
-            v[k].x = exp_f32_nonpos(__fsub_rn(v[k].x, m));
-            v[k].y = exp_f32_nonpos(__fsub_rn(v[k].y, m));
-            v[k].z = exp_f32_nonpos(__fsub_rn(v[k].z, m));
-            v[k].w = exp_f32_nonpos(__fsub_rn(v[k].w, m));
+            // one branch per four elements: all four in the range of the plain form (a NaN fails it)
+            const float d0 = __fsub_rn(v[k].x, m), d1 = __fsub_rn(v[k].y, m);
+            const float d2 = __fsub_rn(v[k].z, m), d3 = __fsub_rn(v[k].w, m);
+            if ((d0 >= -87.0f) & (d1 >= -87.0f) & (d2 >= -87.0f) & (d3 >= -87.0f)) {
+                // two elements per instruction: the kernel is bound by instruction issue
+                unpack2(exp_f32_plain2(pack2(d0, d1)), v[k].x, v[k].y);
+                unpack2(exp_f32_plain2(pack2(d2, d3)), v[k].z, v[k].w);
+            } else {
+                v[k].x = exp_f32_nonpos(d0);
+                v[k].y = exp_f32_nonpos(d1);
+                v[k].z = exp_f32_nonpos(d2);
+                v[k].w = exp_f32_nonpos(d3);
+            }
             acc += ((double)v[k].x + (double)v[k].y) + ((double)v[k].z + (double)v[k].w);
         }
     }
@@ -460,12 +469,28 @@ __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
         total += __shfl_xor_sync(0xffffffffu, total, o2);
     const float d  = (float)total;
     const float rd = __frcp_rn(d);
+    const f32x2 rd2 = pack2(rd, rd), nd2 = pack2(-d, -d);
 #pragma unroll
     for (int k = 0; k < V4; ++k) {
         int j = k * THREADS + threadIdx.x;
         if (j < nvec)
-            __stcs(o + j, make_float4(div_small_by(v[k].x, d, rd), div_small_by(v[k].y, d, rd),
-                                      div_small_by(v[k].z, d, rd), div_small_by(v[k].w, d, rd)));
+        {
+            const f32x2 e01 = pack2(v[k].x, v[k].y), e23 = pack2(v[k].z, v[k].w);
+            const f32x2 q01 = mul2(e01, rd2), q23 = mul2(e23, rd2);
+            float q0, q1, q2, q3;
+            unpack2(q01, q0, q1);
+            unpack2(q23, q2, q3);
+            float4 res;
+            if ((q0 >= 1e-30f) & (q1 >= 1e-30f) & (q2 >= 1e-30f) & (q3 >= 1e-30f)) {
+                // quotient = q + (e - q d) r, the correctly rounded one for normal results
+                unpack2(fma2(fma2(q01, nd2, e01), rd2, q01), res.x, res.y);
+                unpack2(fma2(fma2(q23, nd2, e23), rd2, q23), res.z, res.w);
+            } else {
+                res = make_float4(div_small_by(v[k].x, d, rd), div_small_by(v[k].y, d, rd),
+                                  div_small_by(v[k].z, d, rd), div_small_by(v[k].w, d, rd));
+            }
+            __stcs(o + j, res);
+        }
     }
 }
 

@@ -148,8 +148,9 @@ def compare_outputs(name, got, ref, label):
         return 0.0
     if ref.dtype == np.float32 and name.startswith(ULP_CASES):
         d = ulp_distance(got, ref)
-        # exp, log, pow: within 1 ulp.  softmax divides an exp (<= 1 ulp) by a sum of them and rounds again: 2.
-        bar = 2 if name.startswith("softmax_rows") else 1
+        # exp, log, pow: within 1 ulp.  softmax divides an exp (<= 1 ulp) by a rounded sum of them and
+        # rounds again: up to 4 ulp (4.8e-7 relative; the path is specified to 1e-5)
+        bar = 4 if name.startswith("softmax_rows") else 1
         assert d.max() <= bar, f"{label}: {int(d.max())} ulp apart at {np.unravel_index(d.argmax(), d.shape)}"
         return float(np.mean(d == 0))
     raise AssertionError(f"{label}: not bit-exact")
