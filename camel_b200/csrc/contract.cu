@@ -177,6 +177,68 @@ __global__ void __launch_bounds__(256) conv2d_small_c_kernel(
     }
 }
 
+// One input channel, 3x3, stride 1 (the first layer of a CNN on grey images).  A thread owns four
+// horizontally adjacent outputs: their patches overlap in a 3 x 6 window, which is loaded once and
+// widened to float64 once, and every filter value read from shared memory then feeds four
+// multiply-adds.  With one output per thread (the kernel above) each multiply-add needs its own
+// 8-byte broadcast read and the layer is bound by the return bandwidth of shared memory (128 B per
+// clock and SM), four times above what writing the result costs.  Same arithmetic: float64
+// accumulation in (r, s) order, bias last, one rounding.
+__global__ void __launch_bounds__(256) conv2d_c1_3x3_kernel(
+    const float *__restrict__ x, const float *__restrict__ wt, const float *__restrict__ bias,
+    int64_t n, int64_t h, int64_t w, int ko, int64_t pad, int64_t ho, int64_t wo, int act,
+    float *__restrict__ out) {
+    extern __shared__ double w_s[]; // [ko][9]
+    for (int i = threadIdx.x; i < ko * 9; i += 256)
+        w_s[i] = (double)wt[i];
+    __syncthreads();
+    const int64_t quads = wo >> 2; // wo is a multiple of 4
+    const int64_t pix   = ho * wo;
+    const int64_t total = n * ho * quads;
+    const int64_t step  = (int64_t)gridDim.x * 256;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+        const int64_t qx = i % quads, oy = (i / quads) % ho, img = i / (quads * ho);
+        const int64_t ox = qx * 4;
+        double patch[3][6];
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            const int64_t iy  = oy - pad + r;
+            const bool row_ok = iy >= 0 && iy < h;
+            const float *src  = x + (img * h + (row_ok ? iy : 0)) * w;
+#pragma unroll
+            for (int s = 0; s < 6; ++s) {
+                const int64_t ix = ox - pad + s;
+                patch[r][s]      = (row_ok && ix >= 0 && ix < w) ? (double)__ldg(src + ix) : 0.0;
+            }
+        }
+        float *dst = out + img * ko * pix + oy * wo + ox;
+        for (int o = 0; o < ko; ++o) {
+            const double *wr = w_s + o * 9;
+            double acc[4]    = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+            for (int r = 0; r < 3; ++r)
+#pragma unroll
+                for (int s = 0; s < 3; ++s) {
+                    const double wv = wr[r * 3 + s];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        acc[j] = __fma_rn(patch[r][s + j], wv, acc[j]); // exact product: same bits as mul, add
+                }
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                double a = acc[j];
+                if (bias)
+                    a += (double)bias[o];
+                v[j] = (float)a;
+                if (act == CT_ACT_RELU)
+                    v[j] = __fmul_rn(v[j], v[j] > 0.0f ? 1.0f : 0.0f);
+            }
+            *reinterpret_cast<float4 *>(dst + (int64_t)o * pix) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    }
+}
+
 // maxpool, window == stride: one thread per output, strict '>' from the window's first element.
 __global__ void __launch_bounds__(256) maxpool2d_kernel(
     const float *__restrict__ x, int64_t planes, int64_t h, int64_t w, int64_t win, int64_t ho,
@@ -362,6 +424,14 @@ ct_status ct_conv2d(
         return fail(CT_ERR_INVALID, "conv2d: null pointer");
     int64_t kdim = c * kh * kw;
     int64_t pix  = ho * wo;
+    if (c == 1 && kh == 3 && kw == 3 && stride == 1 && (wo & 3) == 0 && (pix & 3) == 0 && ko * 72 <= 48 * 1024 &&
+        (reinterpret_cast<uintptr_t>(out) & 15u) == 0 && !getenv("CAMEL_TENSOR_NO_CONV_C1")) {
+        ProfScope prof("conv_small_c");
+        conv2d_c1_3x3_kernel<<<capped_blocks(st, n * ho * (wo >> 2), 16), 256, (size_t)ko * 72, stream()>>>(
+            x, w, bias, n, h, wd, (int)ko, pad, ho, wo, act, out);
+        CT_LAUNCH_CHECK("conv2d_c1_3x3");
+        return CT_OK;
+    }
     if (kdim <= kSmallPatch && ko * kdim * 8 <= 48 * 1024 && ko <= 0x7fffffff) {
         ProfScope prof("conv_small_c");
         unsigned blocks = capped_blocks(st, n * pix, 16);
