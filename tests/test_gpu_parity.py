@@ -413,8 +413,11 @@ def test_softmax_wide_rows(T):
 
 def test_maxpool2d(T):
     rng = np.random.default_rng(4)
-    for shape, win in (((3, 5, 28, 28), 2), ((2, 3, 9, 12), 3), ((1, 1, 7, 7), 2)):
+    for shape, win in (((3, 5, 28, 28), 2), ((2, 3, 9, 12), 3), ((1, 1, 7, 7), 2), ((2, 3, 10, 30), 2),
+                       ((4, 2, 6, 8), 2)):
         x = rng.standard_normal(shape).astype(np.float32)
+        x[0, 0, 0, 0] = np.nan  # a NaN that opens a window stays; one that does not never wins
+        x[-1, -1, 1, 3] = np.nan
         ref = oracle.port().maxpool2d(x, win)
         got = T.maxpool2d(T.from_numpy(x), win).numpy()
         assert got.tobytes() == ref.tobytes()
