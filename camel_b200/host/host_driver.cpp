@@ -3,6 +3,7 @@
 // (src/passes/sched/nodevm/nodevm.cpp:588) - and hands the result back as raw buffers.  The
 // argument and result structs have the layout of the oracle's reference driver, so one Python
 // front end drives both the reference module and this plugin.
+#include "dlpack.h"
 #include "camel/core/error/runtime.h"
 #include "camel/core/mm.h"
 #include "camel/core/operator.h"
@@ -220,6 +221,37 @@ int camel_ref_list_ops(char *buf, int buflen) {
         return -static_cast<int>(s.size()) - 1;
     std::memcpy(buf, s.c_str(), s.size() + 1);
     return static_cast<int>(s.size());
+}
+
+// DLPack round trip of a float32 matrix, for the tests: host -> tensor -> device export (must be
+// the tensor's own buffer, kDLCUDA) -> import (device copy) -> host export -> import -> host.
+// Returns 0, or a negative step number; out_host receives the matrix after both round trips.
+int camel_host_dlpack_roundtrip(const float *host, int64_t rows, int64_t cols, float *out_host, char *err, int errlen) {
+    try {
+        int64_t shape[2] = {rows, cols};
+        TensorObject *t  = TensorObject::fromHost(TypeCode::Float32, shape, host, g_scratch);
+        camel::tensor::DLManagedTensor *dev = camel::tensor::tensorToDLPackDevice(t);
+        if (dev->dl_tensor.device.device_type != camel::tensor::kDLCUDA || dev->dl_tensor.data != t->deviceData() ||
+            dev->dl_tensor.ndim != 2 || dev->dl_tensor.shape[0] != rows || dev->dl_tensor.shape[1] != cols)
+            return -1;
+        TensorObject *u = camel::tensor::tensorFromDLPackCopy(dev, g_scratch);
+        dev->deleter(dev);
+        if (u->deviceData() == t->deviceData())
+            return -2;
+        camel::tensor::DLManagedTensor *cpu = camel::tensor::tensorToDLPackCopy(u);
+        if (cpu->dl_tensor.device.device_type != camel::tensor::kDLCPU)
+            return -3;
+        TensorObject *v = camel::tensor::tensorFromDLPackCopy(cpu, g_scratch);
+        cpu->deleter(cpu);
+        std::memcpy(out_host, v->rawData(), v->byteSize());
+        return 0;
+    } catch (const std::exception &e) {
+        if (err && errlen > 0) {
+            std::strncpy(err, e.what(), static_cast<size_t>(errlen) - 1);
+            err[errlen - 1] = '\0';
+        }
+        return -9;
+    }
 }
 
 int camel_ref_list_groups(char *buf, int buflen) {

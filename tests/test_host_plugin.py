@@ -149,3 +149,21 @@ def test_plugin_errors_shapes_and_new_operators(plugin):
     assert upd.tobytes() == plugin.call("subtract", w0, plugin.call("multiply", grad, 0.01 / 300)).tobytes()
     with pytest.raises(oracle.OracleError, match="matching shapes"):
         plugin.call("scaled_sub", w0, xs, 0.1)
+
+
+@needs_build
+@pytest.mark.gpu
+def test_plugin_dlpack_device_export_and_import():
+    """tensorToDLPackDevice hands out the tensor's own device buffer (kDLCUDA); import copies on
+    the device; the reference's host-copy pair still works; the data survives both round trips."""
+    import ctypes as C
+
+    lib = C.CDLL(str(HARNESS))
+    lib.camel_host_dlpack_roundtrip.restype = C.c_int
+    lib.camel_host_dlpack_roundtrip.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_char_p, C.c_int]
+    a = np.random.default_rng(7).uniform(-1, 1, (37, 19)).astype(np.float32)
+    out = np.zeros_like(a)
+    err = C.create_string_buffer(512)
+    rc = lib.camel_host_dlpack_roundtrip(a.ctypes.data, 37, 19, out.ctypes.data, err, 512)
+    assert rc == 0, (rc, err.value.decode())
+    assert out.tobytes() == a.tobytes()
