@@ -207,9 +207,17 @@ __device__ unsigned long long g_gemm_trace[1024 * 16];
         if (blockIdx.x < 1024)                                                \
             g_gemm_trace[blockIdx.x * 16 + (slot)] = globaltimer_ns();        \
     } while (0)
+#define CT_CLOCK() clock64()
+#define CT_ACCUM(slot, cycles)                                                \
+    do {                                                                      \
+        if (blockIdx.x < 1024)                                                \
+            g_gemm_trace[blockIdx.x * 16 + (slot)] += (unsigned long long)(cycles); \
+    } while (0)
 #else
 #define CT_STAMP(slot) do { } while (0)
 #define CT_STAMP_NS(slot) do { } while (0)
+#define CT_CLOCK() 0ll
+#define CT_ACCUM(slot, cycles) do { } while (0)
 #endif
 
 template <int BN, int MODE, int RB = ROW_B>
@@ -868,6 +876,271 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, 64>::kThreads, 1) gemm_tc_stream
         atomicExch(p.flags + FLAG_TIMEOUT, 1u + (uint32_t)blockIdx.x);
 }
 
+// ---- conv2d with at most 64 output channels: pixels on the rows ----------------------------
+//
+// With the output channels on the 128 accumulator rows, a layer of 64 (or 32) filters spends half
+// (or three quarters) of every MMA on zero rows.  Here the operands trade places: the A tile is a
+// block of th*wo <= 128 output pixels (the shifted NHWC box, one per filter tap and channel block),
+// the B tile the 64 filter rows of the weight planes, N = 64.  The accumulator then holds
+// [pixel][channel]; a thread owns one pixel, and for a fixed channel the 32 lanes of a warp write 32
+// consecutive pixels of that channel's NCHW plane: coalesced without any staging.  Same streaming
+// structure as above (one CTA per SM walks the tiles, two TMEM accumulators).
+struct ConvSwapParams {
+    int ko;            // output channels (<= 64)
+    int n_mma;         // ko rounded up to 16: the MMA's N
+    int num_k_blocks;  // taps * channel blocks
+    int cblocks, kw, pad, th, wo;
+    int rows;          // th * wo pixels per tile (<= 128)
+    int tiles_y;       // ceil(ho / th)
+    int64_t pix;       // ho * wo
+    const float *bias;
+    int act;
+    float *out;        // [batch][ko][pix]
+    uint32_t *flags;
+};
+
+template <int MODE> struct SwapCfg {
+    // 128-byte operand rows (32 float32 channels per k-block).  Measured on the 32 -> 64 channel
+    // layer of the CNN: 64-byte rows (twice as many, half as large copies) are a third slower, also
+    // with the filter planes kept resident in shared memory, so neither variant is kept.
+    static constexpr int kRowB       = 128;
+    static constexpr int kKSteps     = kRowB / 32;
+    static constexpr int kBN         = 64;
+    static constexpr int kElem       = MODE == MODE_3X ? 4 : 2;
+    static constexpr int kBlockK     = kRowB / kElem;
+    static constexpr int kPlanes     = MODE == MODE_3X ? 2 : 1;
+    static constexpr int kABytes     = BM * kRowB;
+    static constexpr int kBBytes     = kBN * kRowB;
+    static constexpr int kStageBytes = kPlanes * (kABytes + kBBytes);
+    static constexpr int kStages     = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+    static constexpr int kThreads    = 64 + 4 * 32;
+    static constexpr int kTmemCols   = 2 * kBN;
+    static constexpr int kSmemBytes  = kStages * kStageBytes + 1024;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(SwapCfg<MODE>::kThreads, 1) conv_swap_stream_kernel(
+    const __grid_constant__ CUtensorMap map_x_hi, const __grid_constant__ CUtensorMap map_x_lo,
+    const __grid_constant__ CUtensorMap map_w_hi, const __grid_constant__ CUtensorMap map_w_lo,
+    const ConvSwapParams p, const int total_tiles) {
+    using S = SwapCfg<MODE>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full[S::kStages];
+    __shared__ uint64_t bar_empty[S::kStages];
+    __shared__ uint64_t bar_tmem_full[2];
+    __shared__ uint64_t bar_tmem_empty[2];
+    __shared__ uint64_t bar_done;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag_s;
+    volatile int *abort_flag = &abort_flag_s;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0)
+        abort_flag_s = *reinterpret_cast<volatile uint32_t *>(p.flags + FLAG_TIMEOUT) != 0 ? 1 : 0;
+    __syncthreads();
+    if (abort_flag_s)
+        return;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    auto stage_addr          = [&](int s) { return smem_base + (uint32_t)s * S::kStageBytes; };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::kStages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bar_tmem_full[b]), 1);
+            mbar_init(smem_u32(&bar_tmem_empty[b]), 4);
+        }
+        mbar_init(smem_u32(&bar_done), 1);
+        mbar_fence_init();
+        prefetch_tensormap(&map_x_hi);
+        prefetch_tensormap(&map_w_hi);
+        if (MODE == MODE_3X) {
+            prefetch_tensormap(&map_x_lo);
+            prefetch_tensormap(&map_w_lo);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), S::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    const int nkb            = p.num_k_blocks;
+
+    if (warp == 0) {
+        // ===== TMA producer =====
+        if (lane == 0) {
+            int kbg = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int img = tile / p.tiles_y, ty = tile - img * p.tiles_y;
+                for (int kb = 0; kb < nkb; ++kb, ++kbg) {
+                    int s       = kbg % S::kStages;
+                    uint32_t ph = (uint32_t)(kbg / S::kStages) & 1u;
+                    if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    uint32_t full = smem_u32(&bar_full[s]);
+                    uint32_t dst  = stage_addr(s);
+                    mbar_expect_tx(full, (uint32_t)(S::kPlanes * (p.rows * S::kRowB + S::kBBytes)));
+                    // k-block = (filter tap rs, channel block cb): pixels of th rows by wo columns,
+                    // shifted by the tap, the halo read as zero
+                    int rs = kb / p.cblocks, cb = kb - rs * p.cblocks;
+                    int r = rs / p.kw, sx = rs - r * p.kw;
+                    int32_t c0 = cb * S::kBlockK, w0 = sx - p.pad, h0 = ty * p.th + r - p.pad;
+                    tma_load_4d(dst, &map_x_hi, full, c0, w0, h0, img);
+                    dst += S::kABytes;
+                    if (MODE == MODE_3X) {
+                        tma_load_4d(dst, &map_x_lo, full, c0, w0, h0, img);
+                        dst += S::kABytes;
+                    }
+                    int32_t kc = kb * S::kBlockK;
+                    tma_load_2d(dst, &map_w_hi, full, kc, 0);
+                    dst += S::kBBytes;
+                    if (MODE == MODE_3X)
+                        tma_load_2d(dst, &map_w_lo, full, kc, 0);
+                }
+            }
+            if (*abort_flag) {
+                int first = kbg - S::kStages < 0 ? 0 : kbg - S::kStages;
+                for (int k2 = first; k2 < kbg; ++k2) {
+                    uint32_t bar = smem_u32(&bar_full[k2 % S::kStages]);
+                    uint32_t ph  = (uint32_t)(k2 / S::kStages) & 1u;
+                    uint64_t t0  = globaltimer_ns();
+                    while (!mbar_try_wait(bar, ph) && globaltimer_ns() - t0 < kWaitBudgetNs) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(MODE == MODE_3X ? 2u : 1u, BM, (uint32_t)p.n_mma);
+            int kbg = 0, i = 0;
+            bool ok = true;
+            long long c_start = CT_CLOCK();
+            (void)c_start;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++i) {
+                int buf = i & 1;
+                long long c0 = CT_CLOCK();
+                if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), (((uint32_t)i >> 1) & 1u) ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                CT_ACCUM(11, CT_CLOCK() - c0);
+                tc_fence_after_sync();
+                uint32_t d_tmem = tmem_base + (uint32_t)buf * S::kBN;
+                bool first      = true;
+                for (int kb = 0; kb < nkb; ++kb, ++kbg) {
+                    int s       = kbg % S::kStages;
+                    uint32_t ph = (uint32_t)(kbg / S::kStages) & 1u;
+                    long long c1 = CT_CLOCK();
+                    if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    CT_ACCUM(10, CT_CLOCK() - c1);
+                    uint32_t a_hi = stage_addr(s);
+                    uint32_t a_lo = a_hi + S::kABytes;
+                    uint32_t b_hi = a_hi + S::kPlanes * S::kABytes;
+                    uint32_t b_lo = b_hi + S::kBBytes;
+                    uint64_t da_hi = smem_desc_k<S::kRowB>(a_hi), db_hi = smem_desc_k<S::kRowB>(b_hi);
+                    uint64_t da_lo = smem_desc_k<S::kRowB>(a_lo), db_lo = smem_desc_k<S::kRowB>(b_lo);
+#pragma unroll
+                    for (int kk = 0; kk < S::kKSteps; ++kk) {
+                        uint64_t adv = (uint64_t)(kk * 32 >> 4);
+                        if (MODE == MODE_3X) {
+                            mma_tf32(d_tmem, da_lo + adv, db_hi + adv, idesc, first ? 0u : 1u);
+                            mma_tf32(d_tmem, da_hi + adv, db_lo + adv, idesc, 1u);
+                            mma_tf32(d_tmem, da_hi + adv, db_hi + adv, idesc, 1u);
+                        } else {
+                            mma_f16(d_tmem, da_hi + adv, db_hi + adv, idesc, first ? 0u : 1u);
+                        }
+                        first = false;
+                    }
+                    tc_commit(smem_u32(&bar_empty[s]));
+                }
+                if (ok)
+                    tc_commit(smem_u32(&bar_tmem_full[buf]));
+            }
+            CT_ACCUM(12, CT_CLOCK() - c_start);
+            CT_ACCUM(13, i);
+            if (!ok || *abort_flag) {
+                tc_commit(smem_u32(&bar_done));
+                uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(smem_u32(&bar_done), 0) && globaltimer_ns() - t0 < kWaitBudgetNs) {
+                }
+            }
+        }
+    } else {
+        // ===== epilogue: one pixel per thread, 64 channels =====
+        const int quarter = warp & 3;
+        int i             = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++i) {
+            const int img = tile / p.tiles_y, ty = tile - img * p.tiles_y;
+            const int buf = i & 1;
+            long long c2 = CT_CLOCK();
+            bool got = mbar_wait(smem_u32(&bar_tmem_full[buf]), ((uint32_t)i >> 1) & 1u, abort_flag);
+            if (warp == 2 && lane == 0)
+                CT_ACCUM(14, CT_CLOCK() - c2);
+            if (!__all_sync(0xffffffffu, got))
+                break;
+            tc_fence_after_sync();
+            float acc[64];
+            uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * S::kBN);
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + g * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    acc[g * 32 + j] = __uint_as_float(r[j]);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(smem_u32(&bar_tmem_empty[buf]));
+
+            const int row     = quarter * 32 + lane;                       // pixel within the tile
+            const int64_t pix = (int64_t)ty * p.th * p.wo + row;           // pixel within the image
+            if (row < p.rows && pix < p.pix) {
+                float *dst = p.out + ((int64_t)img * p.ko) * p.pix + pix;
+#pragma unroll
+                for (int ch = 0; ch < 64; ++ch) {
+                    if (ch < p.ko) {
+                        float x = acc[ch];
+                        if (p.bias)
+                            x = __fadd_rn(x, p.bias[ch]);
+                        if (p.act == CT_ACT_RELU)
+                            x = __fmul_rn(x, x > 0.0f ? 1.0f : 0.0f);
+                        dst[(int64_t)ch * p.pix] = x;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, S::kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag)
+        atomicExch(p.flags + FLAG_TIMEOUT, 1u + (uint32_t)blockIdx.x);
+}
+
 } // namespace
 
 // ---- host side --------------------------------------------------------------------------
@@ -1044,6 +1317,58 @@ ct_status launch_gemm(
     return CT_OK;
 }
 
+// conv2d with ko <= 64 output channels on the accumulator columns (conv_swap_stream_kernel).
+// w_*: weight planes [ko][kp] (tap-major k), x_*: NHWC input planes [batch][h][w][c_pad].
+template <int MODE>
+ct_status launch_conv_swap(
+    DeviceState *st, const void *w_hi, const void *w_lo, const void *x_hi, const void *x_lo, int ko, int64_t kp,
+    const float *bias, int act, float *out, int batch, const ConvGeom &g) {
+    using S = SwapCfg<MODE>;
+    CUtensorMap mx_hi, mx_lo, mw_hi, mw_lo;
+    CT_TRY(make_conv_map(&mx_hi, x_hi, S::kElem, g, batch, S::kRowB));
+    CT_TRY(make_plane_map(&mw_hi, w_hi, S::kElem, ko, kp, S::kBN, 0, S::kRowB));
+    if (MODE == MODE_3X) {
+        CT_TRY(make_conv_map(&mx_lo, x_lo, S::kElem, g, batch, S::kRowB));
+        CT_TRY(make_plane_map(&mw_lo, w_lo, S::kElem, ko, kp, S::kBN, 0, S::kRowB));
+    } else {
+        mx_lo = mx_hi;
+        mw_lo = mw_hi;
+    }
+    ConvSwapParams p;
+    p.ko           = ko;
+    p.n_mma        = (ko + 15) / 16 * 16;
+    p.num_k_blocks = (int)(kp / S::kBlockK);
+    p.cblocks      = g.c_pad / S::kBlockK;
+    p.kw           = g.kw;
+    p.pad          = g.pad;
+    p.th           = g.th;
+    p.wo           = g.wo;
+    p.rows         = g.th * g.wo;
+    p.tiles_y      = (g.ho + g.th - 1) / g.th;
+    p.pix          = (int64_t)g.ho * g.wo;
+    p.bias         = bias;
+    p.act          = act;
+    p.out          = out;
+    p.flags        = st->flags_dev;
+    if (p.rows < 1 || p.rows > BM || p.num_k_blocks < 1)
+        return fail(CT_ERR_INVALID, "conv2d: internal tile shape %d x %d not usable", g.th, g.wo);
+    int64_t tiles = (int64_t)p.tiles_y * batch;
+    if (tiles > 0x7fffffffll)
+        return fail(CT_ERR_TOO_LARGE, "conv2d: too many tiles");
+    static bool attr_set = false;
+    if (!attr_set) {
+        CT_CUDA(cudaFuncSetAttribute(
+            conv_swap_stream_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes));
+        attr_set = true;
+    }
+    unsigned grid = (unsigned)(tiles < st->sm_count ? tiles : st->sm_count);
+    ProfScope prof("gemm_tc");
+    conv_swap_stream_kernel<MODE><<<grid, S::kThreads, S::kSmemBytes, stream()>>>(
+        mx_hi, mx_lo, mw_hi, mw_lo, p, (int)tiles);
+    CT_LAUNCH_CHECK("conv_swap_stream");
+    return CT_OK;
+}
+
 } // namespace
 
 namespace {
@@ -1075,6 +1400,16 @@ ct_status gemm_planes(
     bool wide        = n > 128 && tiles256 >= st->sm_count / 2;
     if (getenv("CAMEL_TENSOR_BN"))
         wide = atoi(getenv("CAMEL_TENSOR_BN")) == 256;
+    if (conv && m <= 64 && conv->wo <= 128 && kp <= 1024 * (mode == MODE_3X ? 1 : 2) && bias_per_row == (bias ? 1 : 0) &&
+        !getenv("CAMEL_TENSOR_NO_CONV_SWAP")) {
+        // few output channels: pixels on the accumulator rows, channels on its columns; the whole k
+        // range is one accumulation, so k stays within what keeps the error at float32 level
+        ConvGeom g = *conv;
+        g.th       = 128 / g.wo < g.ho ? 128 / g.wo : g.ho;
+        if (mode == MODE_3X)
+            return launch_conv_swap<MODE_3X>(st, a_hi, a_lo, b_hi, b_lo, (int)m, kp, bias, act, out, batch, g);
+        return launch_conv_swap<MODE_BF>(st, a_hi, a_lo, b_hi, b_lo, (int)m, kp, bias, act, out, batch, g);
+    }
     if (conv)
         wide = conv->th * conv->wo > 128;
     // Few output tiles and a long reduction (e.g. a 12544 -> 128 layer): slice k across CTAs so
