@@ -22,6 +22,15 @@
 //   warps 2+ : epilogue - drain TMEM chunks into registers, then bias/activation and store
 // Every barrier wait is bounded; on a timeout the kernel raises an error word, unwinds and
 // frees its TMEM, and the host reports CT_ERR_TIMEOUT.
+//
+// Variants in this file
+//   gemm_tc_kernel          one CTA per tile; long k ranges are accumulated in chunks (see above);
+//                           few tiles with a long k are sliced along k (split-K + reduce kernel)
+//   gemm_tc_stream_kernel   many tiles with k <= 1024: one CTA per SM walks the tiles, the store of
+//                           tile i overlaps the MMAs of tile i+1 (conv2d, batched layers)
+//   conv_swap_stream_kernel conv2d with <= 64 output channels: pixels on the accumulator rows
+//   ct_weights_pack         the B planes of a weight matrix built once and reused
+//   ct_matmul_f32_static    the GEMM for callers that may not allocate device memory
 #include "common.cuh"
 #include "tc_ptx.cuh"
 #include "split.cuh"
