@@ -624,3 +624,96 @@ def test_host_pipeline_streams_batches(T):
         assert a.array.tobytes() == arg_e.numpy().tobytes()
     T.check_async()
     pipe.close()
+
+
+def test_full_size_gemm_checksum_16384(T):
+    """BASELINE configs[4] at full size (16384^3, U(-1,1), seed 5): the scalar oracle would need days,
+    so the product is checked through a property that holds at any size, (A B) 1 = A (B 1), plus 64
+    entries recomputed in float64 on the host."""
+    import torch
+
+    n = 16384
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    a = torch.rand((n, n), generator=g, device="cuda", dtype=torch.float32) * 2 - 1
+    b = torch.rand((n, n), generator=g, device="cuda", dtype=torch.float32) * 2 - 1
+    ta, tb = T.wrap_device(a.data_ptr(), 0, (n, n), keep=a), T.wrap_device(b.data_ptr(), 0, (n, n), keep=b)
+    c = T.matmul(ta, tb)
+    T.check_async()
+    ct = torch.from_dlpack(c)
+    ones = torch.ones((n, 1), device="cuda", dtype=torch.float64)
+    lhs = ct.double() @ ones
+    rhs = a.double() @ (b.double() @ ones)
+    scale = float((a.double().abs() @ (b.double().abs() @ ones)).max())
+    assert float((lhs - rhs).abs().max()) / scale <= 1e-6
+    rng = np.random.default_rng(0)
+    rows, cols = rng.integers(0, n, 64), rng.integers(0, n, 64)
+    for i, j in zip(rows.tolist(), cols.tolist()):
+        ref = float((a[i].double() * b[:, j].double()).sum())
+        bound = float((a[i].double().abs() * b[:, j].double().abs()).sum())
+        assert abs(float(ct[i, j]) - ref) <= 1e-5 * bound
+
+
+def test_full_size_mlp_rows_are_independent(T):
+    """BASELINE configs[1] at full size (batch 4096): rows 0..255 and the last 256 rows agree with
+    the same rows run as their own small batches (a row's tile neighbours do not enter its sum;
+    the small batch takes other tile shapes and a k-sliced schedule, so sums differ in order, not
+    in value beyond the contraction tolerance), and the first rows equal the oracle."""
+    rng = np.random.default_rng(1)
+
+    def kaiming(fan_in, fan_out):
+        lim = np.sqrt(6.0 / fan_in)
+        return rng.uniform(-lim, lim, (fan_in, fan_out)).astype(np.float32)
+
+    w = [kaiming(784, 1024), kaiming(1024, 1024), kaiming(1024, 10)]
+    b = [np.zeros(1024, np.float32), np.zeros(1024, np.float32), np.zeros(10, np.float32)]
+    x = np.random.default_rng(2).uniform(0, 1, (4096, 784)).astype(np.float32)
+    tw, tb = [T.from_numpy(v) for v in w], [T.from_numpy(v) for v in b]
+
+    def forward(inp):
+        h = T.dense(inp, tw[0], tb[0], "relu")
+        h = T.dense(h, tw[1], tb[1], "relu")
+        probs, arg = T.dense(h, tw[2], tb[2], "softmax", with_argmax=True)
+        return probs.numpy(), arg.numpy()
+
+    probs, arg = forward(T.from_numpy(x))
+    T.check_async()
+    assert probs.shape == (4096, 10) and arg.shape == (4096,)
+    assert np.all(np.abs(probs.sum(axis=1) - 1.0) <= 1e-5)
+    assert np.array_equal(arg, probs.argmax(axis=1)) or np.mean(arg == probs.argmax(axis=1)) > 0.999
+    for sl in (slice(0, 256), slice(4096 - 256, 4096)):
+        p_small, a_small = forward(T.from_numpy(x[sl]))
+        assert np.max(np.abs(p_small - probs[sl])) <= 2e-6
+        top2 = np.sort(probs[sl], axis=1)[:, -2:]
+        decided = top2[:, 1] - top2[:, 0] > 1e-5
+        assert np.array_equal(a_small[decided], arg[sl][decided])
+    p = oracle.port()
+    h = p.dense(x[:64], w[0], b[0], 1)
+    h = p.dense(h, w[1], b[1], 1)
+    ref = p.softmax_rows(p.dense(h, w[2], b[2], 0))
+    assert np.max(np.abs(probs[:64] - ref)) <= 1e-5
+
+
+def test_full_size_conv_linearity(T):
+    """BASELINE configs[2] geometry at full batch (256 x 64 x 56 x 56 -> 128): conv is linear in its
+    input, conv(x1 + x2) = conv(x1) + conv(x2) without bias, within the contraction tolerance, and a
+    2-image slice equals the oracle."""
+    import torch
+
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    x1 = torch.randn((256, 64, 56, 56), generator=g, device="cuda", dtype=torch.float32)
+    x2 = torch.randn((256, 64, 56, 56), generator=g, device="cuda", dtype=torch.float32)
+    wt = (torch.randn((128, 64, 3, 3), generator=g, device="cuda", dtype=torch.float32) * (2.0 / 576) ** 0.5)
+    wrap = lambda t: T.wrap_device(t.data_ptr(), 0, tuple(t.shape), keep=t)  # noqa: E731
+    tw = wrap(wt)
+    xs = x1 + x2
+    ys = torch.from_dlpack(T.conv2d(wrap(xs), tw, None, 1, 1, None))
+    y1 = torch.from_dlpack(T.conv2d(wrap(x1), tw, None, 1, 1, None))
+    y2 = torch.from_dlpack(T.conv2d(wrap(x2), tw, None, 1, 1, None))
+    T.check_async()
+    err = float((ys - (y1 + y2)).abs().max()) / float(ys.abs().max())
+    assert err <= 3e-5
+    ref = oracle.port().conv2d(x1[:2].cpu().numpy(), wt.cpu().numpy(), np.zeros(128, np.float32), 1, 1, 0)
+    got = y1[:2].cpu().numpy()
+    assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) <= 1e-5
