@@ -1,5 +1,5 @@
 // Inline-PTX wrappers for the sm_100a features the contraction kernels use: mbarriers with
-// BOUNDED waits, TMA tile loads (cp.async.bulk.tensor, never multicast), tensor memory (TMEM)
+// BOUNDED waits, TMA tile loads (cp.async.bulk.tensor; every CTA fetches its own tiles), tensor memory (TMEM)
 // allocation, tcgen05.mma / commit / ld, and the shared-memory matrix descriptors.
 #pragma once
 
