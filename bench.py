@@ -692,12 +692,16 @@ class CnnWorkload(Workload):
         self.arg_host = _pin_empty((batch,), np.int64)
         self.h2d, self.d2h = x.nbytes, batch * 48
         self.flops = 2.0 * batch * (28 * 28 * (32 * 9 + 64 * 288) + 12544 * 128 + 1280)
+        self.fuse_pool = not os.environ.get("CAMEL_BENCH_UNFUSED_POOL")
 
     def forward(self, x):
         T = self.T
         h = T.conv2d(x, self.w[0], self.b[0], 1, 1, "relu")
-        h = T.conv2d(h, self.w[1], self.b[1], 1, 1, "relu")
-        h = T.flatten(T.maxpool2d(h, 2))
+        if self.fuse_pool:  # conv + relu + 2x2 max-pool as one call (the pool in the conv's epilogue)
+            h = T.flatten(T.conv2d(h, self.w[1], self.b[1], 1, 1, "relu", pool=2))
+        else:
+            h = T.conv2d(h, self.w[1], self.b[1], 1, 1, "relu")
+            h = T.flatten(T.maxpool2d(h, 2))
         h = T.dense(h, self.w[2], self.b[2], "relu")
         return T.dense(h, self.w[3], self.b[3], "softmax", with_argmax=True)
 

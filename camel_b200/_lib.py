@@ -87,6 +87,7 @@ PROTOTYPES = {
     "ct_weights_free": (_int, [_vp]),
     "ct_dense_packed": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),
     "ct_conv2d": (_int, [_vp, _vp, _vp] + [_i64] * 9 + [_int, _vp]),
+    "ct_conv2d_maxpool2": (_int, [_vp, _vp, _vp] + [_i64] * 9 + [_int, _vp]),
     "ct_maxpool2d": (_int, [_vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "ct_matmul_f32_static": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "ct_matmul_host":(_int, [_vp, _vp, _i64, _i64, _i64, _vp]),

@@ -151,6 +151,7 @@ struct ConvGeom {
     int ho, wo; // output height / width
     int kh, kw, pad;
     int th;     // output rows per tile (th * wo <= 256, multiple of 16)
+    int pool = 0; // 2: store the 2x2 max-pool of the activated output (pixels-on-rows kernel only)
 };
 
 // mode: 0 = 3xTF32 (float32 hi/lo planes), 1 = bf16 (one plane).  With conv != nullptr the B

@@ -433,10 +433,59 @@ ct_status ct_matmul_host(
     return CT_OK;
 }
 
+// Largest even number of output rows whose pixels fit the 128 accumulator rows; the fused
+// conv + 2x2 max-pool needs at least two, even output height and width, at most 64 filters and a
+// k range of one accumulation (the conditions of the pixels-on-rows kernel).
+static int pooled_tile_rows(int64_t ho, int64_t wo) {
+    int64_t th = wo > 0 ? 128 / wo : 0;
+    if (th > ho)
+        th = ho;
+    return (int)(th & ~(int64_t)1);
+}
+
+static ct_status conv2d_run(
+    const float *x, const float *w, const float *bias, int64_t n, int64_t c, int64_t h,
+    int64_t wd, int64_t ko, int64_t kh, int64_t kw, int64_t stride, int64_t pad,
+    ct_activation act, float *out, int pool);
+
 ct_status ct_conv2d(
     const float *x, const float *w, const float *bias, int64_t n, int64_t c, int64_t h,
     int64_t wd, int64_t ko, int64_t kh, int64_t kw, int64_t stride, int64_t pad,
     ct_activation act, float *out) {
+    return conv2d_run(x, w, bias, n, c, h, wd, ko, kh, kw, stride, pad, act, out, 0);
+}
+
+ct_status ct_conv2d_maxpool2(
+    const float *x, const float *w, const float *bias, int64_t n, int64_t c, int64_t h,
+    int64_t wd, int64_t ko, int64_t kh, int64_t kw, int64_t stride, int64_t pad,
+    ct_activation act, float *out) {
+    if (n < 0 || c < 0 || h < 0 || wd < 0 || ko < 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0)
+        return fail(CT_ERR_INVALID, "conv2d: bad dimension");
+    if (h + 2 * pad < kh || wd + 2 * pad < kw)
+        return fail(CT_ERR_INVALID, "conv2d: kernel larger than padded input");
+    const int64_t ho = (h + 2 * pad - kh) / stride + 1, wo = (wd + 2 * pad - kw) / stride + 1;
+    const int kblock   = ct_get_precision() == CT_PREC_BF16 ? 64 : 32;
+    const int64_t kp_i = kh * kw * ((c + kblock - 1) / kblock * kblock);
+    const bool fused = stride == 1 && c >= 16 && ko <= 64 && ko > 0 && wo <= 128 && (wo & 1) == 0 && (ho & 1) == 0 &&
+                       kp_i <= 1024 * (kblock / 32) && pooled_tile_rows(ho, wo) >= 2 && conv_tile_rows(ho, wo) > 0 &&
+                       n > 0 && !getenv("CAMEL_TENSOR_NO_CONV_SWAP") && !getenv("CAMEL_TENSOR_CONV_IM2COL");
+    if (fused)
+        return conv2d_run(x, w, bias, n, c, h, wd, ko, kh, kw, stride, pad, act, out, 2);
+    // not a shape of the fused kernel: the convolution into a temporary, then maxpool2d
+    void *tmp      = nullptr;
+    size_t bytes   = (size_t)(n * ko * ho * wo > 0 ? n * ko * ho * wo : 1) * sizeof(float);
+    CT_TRY(ct_alloc(&tmp, bytes));
+    ct_status s = conv2d_run(x, w, bias, n, c, h, wd, ko, kh, kw, stride, pad, act, static_cast<float *>(tmp), 0);
+    if (s == CT_OK)
+        s = ct_maxpool2d(static_cast<const float *>(tmp), n, ko, ho, wo, 2, out);
+    ct_status f = ct_free(tmp);
+    return s != CT_OK ? s : f;
+}
+
+static ct_status conv2d_run(
+    const float *x, const float *w, const float *bias, int64_t n, int64_t c, int64_t h,
+    int64_t wd, int64_t ko, int64_t kh, int64_t kw, int64_t stride, int64_t pad,
+    ct_activation act, float *out, int pool) {
     DeviceState *st;
     CT_TRY(current(&st));
     if (n < 0 || c < 0 || h < 0 || wd < 0 || ko < 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0)
@@ -453,7 +502,7 @@ ct_status ct_conv2d(
         return fail(CT_ERR_INVALID, "conv2d: null pointer");
     int64_t kdim = c * kh * kw;
     int64_t pix  = ho * wo;
-    if (c == 1 && kh == 3 && kw == 3 && stride == 1 && (wo & 3) == 0 && (pix & 3) == 0 && ko * 72 <= 48 * 1024 &&
+    if (pool == 0 && c == 1 && kh == 3 && kw == 3 && stride == 1 && (wo & 3) == 0 && (pix & 3) == 0 && ko * 72 <= 48 * 1024 &&
         (reinterpret_cast<uintptr_t>(out) & 15u) == 0 && !getenv("CAMEL_TENSOR_NO_CONV_C1")) {
         ProfScope prof("conv_small_c");
         conv2d_c1_3x3_kernel<<<capped_blocks(st, n * ho * (wo >> 2), 16), 256, (size_t)ko * 72, stream()>>>(
@@ -461,7 +510,7 @@ ct_status ct_conv2d(
         CT_LAUNCH_CHECK("conv2d_c1_3x3");
         return CT_OK;
     }
-    if (kdim <= kSmallPatch && ko * kdim * 8 <= 48 * 1024 && ko <= 0x7fffffff) {
+    if (pool == 0 && kdim <= kSmallPatch && ko * kdim * 8 <= 48 * 1024 && ko <= 0x7fffffff) {
         ProfScope prof("conv_small_c");
         unsigned blocks = capped_blocks(st, n * pix, 16);
         size_t smem     = (size_t)(ko * kdim * 8);
@@ -478,7 +527,7 @@ ct_status ct_conv2d(
         CT_LAUNCH_CHECK("conv2d_small_c");
         return CT_OK;
     }
-    if (kdim * ko * pix * n < kTinyMacs * 8 || ko < 16 || pix < 64 || n > 0x7fffffff) {
+    if (pool == 0 && (kdim * ko * pix * n < kTinyMacs * 8 || ko < 16 || pix < 64 || n > 0x7fffffff)) {
         conv2d_direct_kernel<<<capped_blocks(st, total_out, 16), 256, 0, stream()>>>(
             x, w, bias, n, c, h, wd, ko, kh, kw, stride, pad, ho, wo, act, out);
         CT_LAUNCH_CHECK("conv2d_direct");
@@ -522,6 +571,7 @@ ct_status ct_conv2d(
         g.c_pad = (int)c_pad;
         g.h = (int)h, g.w = (int)wd, g.ho = (int)ho, g.wo = (int)wo;
         g.kh = (int)kh, g.kw = (int)kw, g.pad = (int)pad, g.th = th;
+        g.pool = pool; // only set for shapes ct_conv2d_maxpool2 has checked against the fused kernel
         return gemm_planes(
             st, mode, w_hi, w_lo, x_hi, x_lo, ko, pix, kp_i, bias, act, out, (int)n, ko * pix,
             bias ? 1 : 0, &g);

@@ -904,8 +904,10 @@ struct ConvSwapParams {
     int64_t pix;       // ho * wo
     const float *bias;
     int act;
-    float *out;        // [batch][ko][pix]
+    float *out;        // [batch][ko][pix], or [batch][ko][ho/2][wo/2] with pool
     uint32_t *flags;
+    int pool;          // 2: a 2x2 max-pool of the activated output is what gets stored
+    int ho;
 };
 
 template <int MODE> struct SwapCfg {
@@ -924,7 +926,10 @@ template <int MODE> struct SwapCfg {
     static constexpr int kStages     = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
     static constexpr int kThreads    = 64 + 4 * 32;
     static constexpr int kTmemCols   = 2 * kBN;
-    static constexpr int kSmemBytes  = kStages * kStageBytes + 1024;
+    // pooled epilogue: the tile's [pixel][channel] values, rows padded to 65 floats
+    static constexpr int kPoolRowF   = 65;
+    static constexpr int kPoolBytes  = BM * kPoolRowF * 4;
+    static constexpr int kSmemBytes  = kStages * kStageBytes + kPoolBytes + 1024;
 };
 
 template <int MODE>
@@ -939,6 +944,7 @@ __global__ void __launch_bounds__(SwapCfg<MODE>::kThreads, 1) conv_swap_stream_k
     __shared__ uint64_t bar_tmem_full[2];
     __shared__ uint64_t bar_tmem_empty[2];
     __shared__ uint64_t bar_done;
+    __shared__ uint64_t bar_epi; // the four epilogue warps meet here (bounded, unlike bar.sync)
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
     volatile int *abort_flag = &abort_flag_s;
@@ -965,6 +971,7 @@ __global__ void __launch_bounds__(SwapCfg<MODE>::kThreads, 1) conv_swap_stream_k
             mbar_init(smem_u32(&bar_tmem_empty[b]), 4);
         }
         mbar_init(smem_u32(&bar_done), 1);
+        mbar_init(smem_u32(&bar_epi), 4);
         mbar_fence_init();
         prefetch_tensormap(&map_x_hi);
         prefetch_tensormap(&map_w_hi);
@@ -1094,6 +1101,18 @@ __global__ void __launch_bounds__(SwapCfg<MODE>::kThreads, 1) conv_swap_stream_k
         // ===== epilogue: one pixel per thread, 64 channels =====
         const int quarter = warp & 3;
         int i             = 0;
+        uint32_t epi_phase = 0;
+        float *pool_st = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)) +
+                                                    (uint32_t)S::kStages * S::kStageBytes);
+        // all four epilogue warps arrive, then wait (bounded); false when the launch is aborting
+        auto epi_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(smem_u32(&bar_epi));
+            bool ok = mbar_wait(smem_u32(&bar_epi), epi_phase, abort_flag);
+            epi_phase ^= 1u;
+            return __all_sync(0xffffffffu, ok);
+        };
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++i) {
             const int img = tile / p.tiles_y, ty = tile - img * p.tiles_y;
             const int buf = i & 1;
@@ -1122,7 +1141,48 @@ __global__ void __launch_bounds__(SwapCfg<MODE>::kThreads, 1) conv_swap_stream_k
 
             const int row     = quarter * 32 + lane;                       // pixel within the tile
             const int64_t pix = (int64_t)ty * p.th * p.wo + row;           // pixel within the image
-            if (row < p.rows && pix < p.pix) {
+            if (p.pool) {
+                // activated values of the tile to shared memory as [pixel][channel]; then each warp
+                // takes every fourth channel and its lanes the tile's (th/2) x (wo/2) <= 32 pooled
+                // pixels: a store instruction writes consecutive pooled pixels of one channel plane.
+                // Window order and strict '>' as in maxpool2d (first element seeds, NaN never wins).
+#pragma unroll
+                for (int ch = 0; ch < 64; ++ch) {
+                    if (ch < p.ko) {
+                        float x = acc[ch];
+                        if (p.bias)
+                            x = __fadd_rn(x, p.bias[ch]);
+                        if (p.act == CT_ACT_RELU)
+                            x = __fmul_rn(x, x > 0.0f ? 1.0f : 0.0f);
+                        pool_st[row * S::kPoolRowF + ch] = x;
+                    }
+                }
+                if (!epi_sync())
+                    break;
+                const int pw = p.wo >> 1, ph = p.ho >> 1, prow0 = ty * (p.th >> 1);
+                const int pcount = (p.th >> 1) * pw;
+                if (lane < pcount) {
+                    const int py = lane / pw, px = lane - py * pw;
+                    if (prow0 + py < ph) {
+                        const float *src = pool_st + ((2 * py) * p.wo + 2 * px) * S::kPoolRowF;
+                        float *dst = p.out + (((int64_t)img * p.ko) * ph + prow0 + py) * pw + px;
+                        for (int ch = warp - 2; ch < p.ko; ch += 4) {
+                            float best = src[ch];
+                            float v1 = src[S::kPoolRowF + ch], v2 = src[p.wo * S::kPoolRowF + ch];
+                            float v3 = src[(p.wo + 1) * S::kPoolRowF + ch];
+                            if (v1 > best)
+                                best = v1;
+                            if (v2 > best)
+                                best = v2;
+                            if (v3 > best)
+                                best = v3;
+                            dst[(int64_t)ch * ph * pw] = best;
+                        }
+                    }
+                }
+                if (!epi_sync()) // the block is rewritten by the next tile
+                    break;
+            } else if (row < p.rows && pix < p.pix) {
                 float *dst = p.out + ((int64_t)img * p.ko) * p.pix + pix;
 #pragma unroll
                 for (int ch = 0; ch < 64; ++ch) {
@@ -1359,6 +1419,8 @@ ct_status launch_conv_swap(
     p.act          = act;
     p.out          = out;
     p.flags        = st->flags_dev;
+    p.pool         = g.pool;
+    p.ho           = g.ho;
     if (p.rows < 1 || p.rows > BM || p.num_k_blocks < 1)
         return fail(CT_ERR_INVALID, "conv2d: internal tile shape %d x %d not usable", g.th, g.wo);
     int64_t tiles = (int64_t)p.tiles_y * batch;
@@ -1415,10 +1477,14 @@ ct_status gemm_planes(
         // range is one accumulation, so k stays within what keeps the error at float32 level
         ConvGeom g = *conv;
         g.th       = 128 / g.wo < g.ho ? 128 / g.wo : g.ho;
+        if (g.pool)
+            g.th &= ~1; // pooling windows must not straddle tiles
         if (mode == MODE_3X)
             return launch_conv_swap<MODE_3X>(st, a_hi, a_lo, b_hi, b_lo, (int)m, kp, bias, act, out, batch, g);
         return launch_conv_swap<MODE_BF>(st, a_hi, a_lo, b_hi, b_lo, (int)m, kp, bias, act, out, batch, g);
     }
+    if (conv && conv->pool)
+        return fail(CT_ERR_INVALID, "conv2d: the fused max-pool was requested for a shape its kernel does not take");
     if (conv)
         wide = conv->th * conv->wo > 128;
     // Few output tiles and a long reduction (e.g. a 12544 -> 128 layer): slice k across CTAs so

@@ -531,7 +531,12 @@ def _packed_weights(w: Tensor, m: int, k: int, n: int):
 
 
 def conv2d(x: Tensor, w: Tensor, b: Tensor | None = None, stride: int = 1, pad: int = 0,
-           activation: str | None = None) -> Tensor:
+           activation: str | None = None, pool: int = 0) -> Tensor:
+    """conv2d, + bias, activation; with pool=2 also the 2x2 max-pool of the result (the values of
+    maxpool2d(conv2d(...), 2), without writing the full-resolution activation where the layer has
+    at most 64 filters)."""
+    if pool not in (0, 2):
+        raise _invalid("conv2d: pool must be 0 or 2")
     if x.rank != 4 or w.rank != 4:
         raise _invalid("conv2d requires rank-4 input [n,c,h,w] and weights [k,c,kh,kw]")
     if x.shape[1] != w.shape[1]:
@@ -547,6 +552,11 @@ def conv2d(x: Tensor, w: Tensor, b: Tensor | None = None, stride: int = 1, pad: 
     if h + 2 * pad < kh or wd + 2 * pad < kw or stride <= 0:
         raise _invalid("conv2d: kernel larger than padded input")
     ho, wo = (h + 2 * pad - kh) // stride + 1, (wd + 2 * pad - kw) // stride + 1
+    if pool == 2:
+        out = Tensor(L.F32, (n, ko, ho // 2, wo // 2))
+        check(lib.ct_conv2d_maxpool2(x.ptr, w.ptr, b.ptr if b is not None else None, n, c, h, wd, ko, kh, kw,
+                                     stride, pad, _ACT[activation], out.ptr))
+        return out
     out = Tensor(L.F32, (n, ko, ho, wo))
     check(lib.ct_conv2d(x.ptr, w.ptr, b.ptr if b is not None else None, n, c, h, wd, ko, kh, kw,
                         stride, pad, _ACT[activation], out.ptr))

@@ -251,6 +251,14 @@ ct_status ct_conv2d(
     const float *x_dev, const float *w_dev, const float *bias_dev, int64_t n, int64_t c,
     int64_t h, int64_t w, int64_t k_out, int64_t kh, int64_t kw, int64_t stride, int64_t pad,
     ct_activation act, float *out_dev);
+/* conv2d followed by a 2x2 max-pool (window == stride == 2), as one call: the same values as
+ * ct_conv2d then ct_maxpool2d.  For stride-1 layers with at most 64 filters the pooling happens in
+ * the convolution's epilogue and the full-resolution activation is never written; other shapes run
+ * the two steps.  out_dev is [n][k_out][h_out/2][w_out/2]. */
+ct_status ct_conv2d_maxpool2(
+    const float *x_dev, const float *w_dev, const float *bias_dev, int64_t n, int64_t c, int64_t h,
+    int64_t w, int64_t k_out, int64_t kh, int64_t kw, int64_t stride, int64_t pad, ct_activation act,
+    float *out_dev);
 
 /* maxpool2d, NCHW, window == stride, no padding.  No reference counterpart; strict '>' from
  * the window's first element, like tensorMaxAxis. */

@@ -504,6 +504,30 @@ def test_exp_log_float32_paths_against_float64_rounded_once(T):
     assert got[y == 1.0][0] == 0.0 and got[np.isinf(y)][0] == np.inf and np.isnan(got[np.isnan(y)]).all()
 
 
+@pytest.mark.parametrize("n,c,h,w,ko,kk,pad", [
+    (3, 32, 28, 28, 64, 3, 1),    # second CNN layer: fused in the convolution's epilogue
+    (40, 32, 28, 28, 64, 3, 1),   # more tiles than SMs
+    (2, 16, 12, 40, 24, 3, 1),    # wo = 40: two output rows per tile, 24 filters
+    (2, 32, 10, 10, 64, 3, 0),    # no padding: 8 x 8 output
+    (2, 32, 14, 14, 128, 3, 1),   # 128 filters: not a shape of the fused kernel (conv, then pool)
+    (2, 8, 9, 9, 16, 3, 1),       # odd output size, few channels: conv, then pool
+])
+def test_conv2d_with_fused_maxpool(T, n, c, h, w, ko, kk, pad):
+    """conv2d(..., relu, pool=2) gives the bytes of maxpool2d(conv2d(..., relu), 2), whichever
+    kernels serve the shape, including a NaN in the input (it must spread exactly as unfused)."""
+    rng = np.random.default_rng(n * 100 + c + h + ko)
+    x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    x[0, 0, 1, 1] = np.nan
+    wt = (rng.standard_normal((ko, c, kk, kk)) * np.sqrt(2.0 / (c * kk * kk))).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, ko).astype(np.float32)
+    tx, tw, tb = T.from_numpy(x), T.from_numpy(wt), T.from_numpy(b)
+    fused = T.conv2d(tx, tw, tb, 1, pad, "relu", pool=2).numpy()
+    chain = T.maxpool2d(T.conv2d(tx, tw, tb, 1, pad, "relu"), 2).numpy()
+    T.check_async()
+    assert fused.shape == chain.shape
+    assert canonical_nan(fused).tobytes() == canonical_nan(chain).tobytes()
+
+
 def test_training_step_fused_forms(T):
     """transpose(X) @ G and W - lr * g as single calls give the bytes of the operator chains of
     test/run/nn/mnist.cml:39-40 (tensor-core, few-column and tiny shapes; odd lengths)."""
