@@ -466,7 +466,11 @@ ct_status ct_conv2d_maxpool2(
     const int64_t ho = (h + 2 * pad - kh) / stride + 1, wo = (wd + 2 * pad - kw) / stride + 1;
     const int kblock   = ct_get_precision() == CT_PREC_BF16 ? 64 : 32;
     const int64_t kp_i = kh * kw * ((c + kblock - 1) / kblock * kblock);
-    const bool fused = stride == 1 && c >= 16 && ko <= 64 && ko > 0 && wo <= 128 && (wo & 1) == 0 && (ho & 1) == 0 &&
+    // only where ct_conv2d itself takes the tensor-core path (same kernel, so the same bits): not
+    // the short-patch, tiny or few-filter shapes that it serves with float64 CUDA-core kernels
+    const int64_t kdim = c * kh * kw, pix = ho * wo;
+    const bool tensor_core = kdim > kSmallPatch && !(kdim * ko * pix * n < kTinyMacs * 8 || ko < 16 || pix < 64);
+    const bool fused = tensor_core && stride == 1 && c >= 16 && ko <= 64 && ko > 0 && wo <= 128 && (wo & 1) == 0 && (ho & 1) == 0 &&
                        kp_i <= 1024 * (kblock / 32) && pooled_tile_rows(ho, wo) >= 2 && conv_tile_rows(ho, wo) > 0 &&
                        n > 0 && !getenv("CAMEL_TENSOR_NO_CONV_SWAP") && !getenv("CAMEL_TENSOR_CONV_IM2COL");
     if (fused)

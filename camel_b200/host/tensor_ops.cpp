@@ -4,7 +4,8 @@
 // (modules/tensor/operators.h:31-63, operators.cpp:160-583), so programs resolve and dispatch
 // exactly as before; each body unpacks its ArgsView the way the reference body does and then
 // calls one function of the C ABI (include/camel_tensor_b200.h) instead of looping on the host.
-// Operators added on top: relu, softmax, dense*, conv2d*, maxpool2d, flatten, matmul_tn, scaled_sub.
+// Operators added on top: relu, softmax, dense*, conv2d*, conv2d_relu_maxpool2, maxpool2d, flatten,
+// matmul_tn, scaled_sub.
 #include "tensor_ops.h"
 
 #include "camel/core/error/runtime.h"
@@ -330,7 +331,7 @@ slot_t denseBody(ArgsView &with, ArgsView &norm, ct_activation act) {
     });
 }
 
-slot_t convBody(ArgsView &with, ArgsView &norm, ct_activation act) {
+slot_t convBody(ArgsView &with, ArgsView &norm, ct_activation act, bool pool2 = false) {
     return guarded([&]() -> slot_t {
         TensorObject *x = requireFloat(tensorArg(norm, 0), "conv2d");
         TensorObject *w = requireFloat(tensorArg(with, 0), "conv2d");
@@ -347,8 +348,12 @@ slot_t convBody(ArgsView &with, ArgsView &norm, ct_activation act) {
         if (stride <= 0 || pad < 0 || h + 2 * pad < kh || wd + 2 * pad < kw)
             throw std::invalid_argument("conv2d: kernel larger than padded input");
         int64_t outShape[4] = {n, ko, (h + 2 * pad - kh) / stride + 1, (wd + 2 * pad - kw) / stride + 1};
-        TensorObject *out   = newTensor(TypeCode::Float32, outShape);
-        ctn::ctCheck(ct_conv2d(
+        if (pool2) {
+            outShape[2] /= 2;
+            outShape[3] /= 2;
+        }
+        TensorObject *out = newTensor(TypeCode::Float32, outShape);
+        ctn::ctCheck((pool2 ? ct_conv2d_maxpool2 : ct_conv2d)(
             static_cast<const float *>(x->deviceData()), static_cast<const float *>(w->deviceData()),
             static_cast<const float *>(b->deviceData()), n, c, h, wd, ko, kh, kw, stride, pad, act,
             static_cast<float *>(out->deviceData())));
@@ -603,6 +608,7 @@ CT_OP(__tensor_dense_relu__) { (void)ctx; return denseBody(with, norm, CT_ACT_RE
 CT_OP(__tensor_dense_softmax__) { (void)ctx; return denseBody(with, norm, CT_ACT_SOFTMAX); }
 CT_OP(__tensor_conv2d__) { (void)ctx; return convBody(with, norm, CT_ACT_NONE); }
 CT_OP(__tensor_conv2d_relu__) { (void)ctx; return convBody(with, norm, CT_ACT_RELU); }
+CT_OP(__tensor_conv2d_relu_maxpool2__) { (void)ctx; return convBody(with, norm, CT_ACT_RELU, true); }
 
 CT_OP(__tensor_maxpool2d__) {
     CT_UNUSED;

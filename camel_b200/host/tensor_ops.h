@@ -53,6 +53,7 @@ CAMEL_TENSOR_DECLARE(__tensor_conv2d__)
 CAMEL_TENSOR_DECLARE(__tensor_conv2d_relu__)
 CAMEL_TENSOR_DECLARE(__tensor_maxpool2d__)
 CAMEL_TENSOR_DECLARE(__tensor_flatten__)
+CAMEL_TENSOR_DECLARE(__tensor_conv2d_relu_maxpool2__)
 CAMEL_TENSOR_DECLARE(__tensor_matmul_tn__)
 CAMEL_TENSOR_DECLARE(__tensor_scaled_sub__)
 #undef CAMEL_TENSOR_DECLARE

@@ -175,6 +175,7 @@ std::unordered_map<std::string, operator_t> getTensorOpsMap() {
         {"conv2d", __tensor_conv2d__}, {"conv2d_relu", __tensor_conv2d_relu__},
         {"maxpool2d", __tensor_maxpool2d__}, {"flatten", __tensor_flatten__},
         {"matmul_tn", __tensor_matmul_tn__}, {"scaled_sub", __tensor_scaled_sub__},
+        {"conv2d_relu_maxpool2", __tensor_conv2d_relu_maxpool2__},
     };
 }
 
@@ -231,6 +232,9 @@ const std::vector<oper_group_ptr_t> &getTensorOperatorGroups() {
                                "<w: Tensor, b: Tensor, stride: int, pad: int>(x: Tensor) => Tensor", convCheck}}),
         group("maxpool2d", {{"tensor:maxpool2d", 0, 2, "(t: Tensor, window: int) => Tensor", poolCheck}}),
         group("flatten", {{"tensor:flatten", 0, 1, kUnarySig, unaryCheck}}),
+        group("conv2d_relu_maxpool2",
+              {{"tensor:conv2d_relu_maxpool2", 4, 1,
+                "<w: Tensor, b: Tensor, stride: int, pad: int>(x: Tensor) => Tensor", convCheck}}),
         group("matmul_tn", {{"tensor:matmul_tn", 0, 2, "(a: Tensor, b: Tensor) => Tensor", matmulTnCheck}}),
         group("scaled_sub",
               {{"tensor:scaled_sub", 0, 3, "(w: Tensor, g: Tensor, lr: number) => Tensor", scaledSubCheck}}),

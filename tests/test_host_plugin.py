@@ -50,7 +50,7 @@ def test_registration_table_equals_reference(plugin):
     extra = {u for _, u, _ in mine[len(ref):]}
     assert extra == {"tensor:relu", "tensor:softmax", "tensor:dense", "tensor:dense_relu", "tensor:dense_softmax",
                      "tensor:conv2d", "tensor:conv2d_relu", "tensor:maxpool2d", "tensor:flatten",
-                     "tensor:matmul_tn", "tensor:scaled_sub"}
+                     "tensor:matmul_tn", "tensor:scaled_sub", "tensor:conv2d_relu_maxpool2"}
     ops = set(plugin.ops())
     assert {u.split(":")[1] for _, u, _ in mine} == ops
     if oracle.Reference.available():
@@ -132,6 +132,8 @@ def test_plugin_errors_shapes_and_new_operators(plugin):
     assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) <= 1e-5
     pooled = plugin.call("maxpool2d", got, 2)
     assert pooled.tobytes() == p.maxpool2d(got, 2).tobytes()
+    fused = plugin.call("conv2d_relu_maxpool2", With(w), With(b), With(1), With(1), x)
+    assert fused.tobytes() == pooled.tobytes()
     flat = plugin.call("flatten", pooled)
     assert flat.shape == (2, 32 * 6 * 6)
     logits_w = rng.uniform(-0.05, 0.05, (flat.shape[1], 10)).astype(np.float32)
