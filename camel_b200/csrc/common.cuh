@@ -43,6 +43,19 @@ void set_error(const char *fmt, ...);
 ct_status fail(ct_status code, const char *fmt, ...);
 ct_status cuda_fail(cudaError_t e, const char *what);
 
+// The reference's Taskflow scheduler calls operators from up to 32 threads at once
+// (src/passes/sched/taskflow/taskflow.h:79-80).  An entry point may enqueue several kernels that
+// share a cached workspace or the device error words; those sequences must not interleave on the
+// stream, so every compute entry point holds this lock (recursive: entry points call each other)
+// while it enqueues.  Device work itself stays asynchronous.
+class OpLock {
+  public:
+    OpLock();
+    ~OpLock();
+    OpLock(const OpLock &)            = delete;
+    OpLock &operator=(const OpLock &) = delete;
+};
+
 // Current device state (initialised on first use) and stream of the calling process.
 ct_status current(DeviceState **out);
 cudaStream_t stream();
@@ -86,6 +99,10 @@ ct_status fetch_flags(DeviceState *st);
 // (barrier initialisation, TMEM allocation, descriptor prefetch, index arithmetic) overlaps.  A
 // kernel lets its successor start early with griddep_launch_dependents(); without that call the
 // successor starts when the grid ends, as usual.  CAMEL_TENSOR_NO_PDL=1 turns the attribute off.
+// While per-kernel event brackets are on (ct_profile_enable) kernels are launched the ordinary way,
+// so that a bracket times one kernel alone and not its overlap with the neighbours.
+bool profiling_enabled();
+
 #ifdef __CUDACC__
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch_dependents() {
@@ -105,7 +122,7 @@ inline cudaError_t launch_dependent(
     attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs    = attr;
-    cfg.numAttrs = enabled ? 1 : 0;
+    cfg.numAttrs = enabled && !profiling_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 #endif

@@ -329,6 +329,7 @@ extern "C" {
 ct_status ct_matmul(
     ct_dtype adt, const void *a, ct_dtype bdt, const void *b, int64_t m, int64_t k, int64_t n,
     void *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (!valid_dtype(adt) || !valid_dtype(bdt))
@@ -353,6 +354,7 @@ ct_status ct_matmul(
 }
 
 ct_status ct_matmul_tn(const float *a_km, const float *b, int64_t m, int64_t k, int64_t n, float *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (m < 0 || k < 0 || n < 0)
@@ -384,6 +386,7 @@ ct_status ct_dense(
 ct_status ct_dense_packed(
     const float *x, const float *w, const void *packed, const float *bias, int64_t m, int64_t k,
     int64_t n, ct_activation act, float *out, int64_t *argmax) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (m < 0 || k < 0 || n < 0)
@@ -410,6 +413,7 @@ ct_status ct_dense_packed(
 
 ct_status ct_matmul_host(
     const float *a, const float *b, int64_t m, int64_t k, int64_t n, float *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (m < 0 || k < 0 || n < 0)
@@ -490,6 +494,7 @@ static ct_status conv2d_run(
     const float *x, const float *w, const float *bias, int64_t n, int64_t c, int64_t h,
     int64_t wd, int64_t ko, int64_t kh, int64_t kw, int64_t stride, int64_t pad,
     ct_activation act, float *out, int pool) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (n < 0 || c < 0 || h < 0 || wd < 0 || ko < 0 || kh <= 0 || kw <= 0 || stride <= 0 || pad < 0)
@@ -608,6 +613,7 @@ static ct_status conv2d_run(
 
 ct_status ct_maxpool2d(
     const float *x, int64_t n, int64_t c, int64_t h, int64_t w, int64_t window, float *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (n < 0 || c < 0 || h < 0 || w < 0 || window <= 0)

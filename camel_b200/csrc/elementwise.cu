@@ -611,6 +611,7 @@ extern "C" {
 ct_status ct_binary(
     ct_binary_op op, ct_dtype ldt, const void *l, ct_dtype rdt, const void *r, uint64_t n,
     void *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (op < CT_ADD || op > CT_POW || !valid_dtype(ldt) || !valid_dtype(rdt))
@@ -669,6 +670,7 @@ ct_status ct_binary(
 ct_status ct_binary_scalar(
     ct_binary_op op, ct_dtype tdt, const void *t, double scalar, ct_dtype sdt, int left,
     uint64_t n, void *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (op < CT_ADD || op > CT_POW || !valid_dtype(tdt) || !valid_dtype(sdt))
@@ -729,6 +731,7 @@ ct_status ct_binary_scalar(
 ct_status ct_compare(
     ct_compare_op op, ct_dtype ldt, const void *l, ct_dtype rdt, const void *r, uint64_t n,
     uint8_t *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (op < CT_LT || op > CT_EQ || !valid_dtype(ldt) || !valid_dtype(rdt))
@@ -750,6 +753,7 @@ ct_status ct_compare(
 ct_status ct_compare_scalar(
     ct_compare_op op, ct_dtype tdt, const void *t, double scalar, int left, uint64_t n,
     uint8_t *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (op < CT_LT || op > CT_EQ || !valid_dtype(tdt))
@@ -769,6 +773,7 @@ ct_status ct_compare_scalar(
 }
 
 ct_status ct_exp(const float *in, uint64_t n, float *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (n == 0)
@@ -779,6 +784,7 @@ ct_status ct_exp(const float *in, uint64_t n, float *out) {
 }
 
 ct_status ct_log(const float *in, uint64_t n, float *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (n == 0)
@@ -803,6 +809,7 @@ ct_status ct_log(const float *in, uint64_t n, float *out) {
 }
 
 ct_status ct_scaled_sub(const float *w, const float *g, double lr, uint64_t n, float *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (n == 0)
@@ -819,6 +826,7 @@ ct_status ct_scaled_sub(const float *w, const float *g, double lr, uint64_t n, f
 }
 
 ct_status ct_relu(const float *in, uint64_t n, float *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (n == 0)
@@ -829,6 +837,7 @@ ct_status ct_relu(const float *in, uint64_t n, float *out) {
 }
 
 ct_status ct_fill(ct_dtype dt, double value, uint64_t n, void *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (!valid_dtype(dt))
@@ -848,6 +857,7 @@ ct_status ct_fill(ct_dtype dt, double value, uint64_t n, void *out) {
 }
 
 ct_status ct_eye(int64_t size, float *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (size < 0)
@@ -858,6 +868,7 @@ ct_status ct_eye(int64_t size, float *out) {
 }
 
 ct_status ct_arange(int64_t start, int64_t step, int64_t count, int64_t *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (step == 0)
@@ -869,6 +880,7 @@ ct_status ct_arange(int64_t start, int64_t step, int64_t count, int64_t *out) {
 
 ct_status ct_binary_host(
     ct_binary_op op, const float *lhs, const float *rhs, uint64_t n, float *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (n == 0)

@@ -1359,7 +1359,8 @@ ct_status launch_gemm(
         static const bool streaming = !getenv("CAMEL_TENSOR_NO_STREAM");
         if (streaming && splits == 1 && p.num_k_blocks <= 64 && tiles > st->sm_count) {
             using S = StreamCfg<BN, MODE>;
-            static bool stream_attr_set = false;
+            static bool stream_attr_set_dev[16] = {}; // the attribute belongs to a device's context
+            bool &stream_attr_set       = stream_attr_set_dev[st->device & 15];
             if (!stream_attr_set) {
                 CT_CUDA(cudaFuncSetAttribute(
                     gemm_tc_stream_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes));
@@ -1372,7 +1373,8 @@ ct_status launch_gemm(
             return CT_OK;
         }
     }
-    static bool attr_set = false;
+    static bool attr_set_dev[16] = {}; // the attribute belongs to a device's context
+    bool &attr_set = attr_set_dev[st->device & 15];
     if (!attr_set) {
         CT_CUDA(cudaFuncSetAttribute(
             gemm_tc_kernel<BN, MODE, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
@@ -1426,7 +1428,8 @@ ct_status launch_conv_swap(
     int64_t tiles = (int64_t)p.tiles_y * batch;
     if (tiles > 0x7fffffffll)
         return fail(CT_ERR_TOO_LARGE, "conv2d: too many tiles");
-    static bool attr_set = false;
+    static bool attr_set_dev[16] = {}; // the attribute belongs to a device's context
+    bool &attr_set = attr_set_dev[st->device & 15];
     if (!attr_set) {
         CT_CUDA(cudaFuncSetAttribute(
             conv_swap_stream_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes));
@@ -1644,6 +1647,7 @@ ct_status gemm_f32_tc(
 // ---- packed weights -----------------------------------------------------------------------
 
 extern "C" ct_status ct_weights_pack(const float *w, int64_t k, int64_t n, void **packed_out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (!packed_out)

@@ -22,6 +22,7 @@ using namespace ct;
 extern "C" {
 
 ct_status ct_graph_begin(void) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (g_capturing)

@@ -306,6 +306,7 @@ ct_status reduce_axis_typed(const T *in, int64_t rows, int64_t cols, int axis, O
 
 template <int KIND, typename OT>
 ct_status reduce_axis(int dt, const void *in, int64_t rows, int64_t cols, int64_t axis, OT *out, const char *name) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (!valid_dtype(dt))
@@ -637,6 +638,7 @@ using namespace ct;
 extern "C" {
 
 ct_status ct_sum(ct_dtype dt, const void *in, uint64_t n, double *result) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (!valid_dtype(dt) || !result)
@@ -670,6 +672,7 @@ ct_status ct_argmax_axis(ct_dtype dt, const void *in, int64_t rows, int64_t cols
 }
 
 ct_status ct_softmax_rows(const float *in, int64_t rows, int64_t cols, float *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (rows < 0 || cols < 0)
@@ -706,6 +709,7 @@ ct_status ct_softmax_rows(const float *in, int64_t rows, int64_t cols, float *ou
 }
 
 ct_status ct_transpose(ct_dtype dt, const void *in, int64_t rows, int64_t cols, void *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (!valid_dtype(dt) || rows < 0 || cols < 0)
@@ -736,6 +740,7 @@ ct_status ct_transpose(ct_dtype dt, const void *in, int64_t rows, int64_t cols, 
 ct_status ct_concat(
     ct_dtype dt, const void *lhs, const void *rhs, uint64_t outer, uint64_t lhs_axis,
     uint64_t rhs_axis, uint64_t inner, void *out) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     if (!valid_dtype(dt))

@@ -21,6 +21,12 @@ std::atomic<uint64_t> g_launches{0};
 std::atomic<int> g_precision{CT_PREC_3XTF32};
 } // namespace
 
+namespace {
+std::recursive_mutex g_op_mutex;
+}
+OpLock::OpLock() { g_op_mutex.lock(); }
+OpLock::~OpLock() { g_op_mutex.unlock(); }
+
 void set_error(const char *fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -434,6 +440,8 @@ std::atomic<int> g_prof_on{0};
 std::mutex g_prof_mutex;
 std::vector<ProfRecord> g_prof;
 } // namespace
+
+bool profiling_enabled() { return g_prof_on.load(std::memory_order_relaxed) != 0; }
 
 ProfScope::ProfScope(const char *name) : name_(name), e0_(nullptr), e1_(nullptr) {
     if (!g_prof_on.load(std::memory_order_relaxed))

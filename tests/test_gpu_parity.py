@@ -528,6 +528,48 @@ def test_conv2d_with_fused_maxpool(T, n, c, h, w, ko, kk, pad):
     assert canonical_nan(fused).tobytes() == canonical_nan(chain).tobytes()
 
 
+def test_entry_points_from_many_threads(T):
+    """The reference's Taskflow scheduler calls operators from up to 32 threads at once.  Entry
+    points that enqueue several kernels over a shared workspace must not interleave: eight threads
+    run different dense / softmax / sum calls concurrently and get the single-threaded bytes."""
+    import threading
+
+    rng = np.random.default_rng(77)
+    jobs = []
+    for i in range(8):
+        m, k, n = 200 + 37 * i, 96 + 32 * i, 64 + 48 * i
+        x = T.from_numpy(rng.uniform(0, 1, (m, k)).astype(np.float32))
+        w = T.from_numpy(rng.uniform(-0.2, 0.2, (k, n)).astype(np.float32))
+        b = T.from_numpy(rng.uniform(-0.1, 0.1, n).astype(np.float32))
+        jobs.append((x, w, b))
+
+    def work(job):
+        x, w, b = job
+        h = T.dense(x, w, b, "relu")
+        return T.softmax(h).numpy(), T.sum(h)
+
+    expected = [work(j) for j in jobs]
+    T.check_async()
+    results, errors = [None] * len(jobs), []
+
+    def runner(idx):
+        try:
+            for _ in range(20):
+                results[idx] = work(jobs[idx])
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=runner, args=(i,)) for i in range(len(jobs))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    T.check_async()
+    assert not errors, errors
+    for (p_exp, s_exp), (p_got, s_got) in zip(expected, results):
+        assert p_got.tobytes() == p_exp.tobytes() and s_got == s_exp
+
+
 def test_training_step_fused_forms(T):
     """transpose(X) @ G and W - lr * g as single calls give the bytes of the operator chains of
     test/run/nn/mnist.cml:39-40 (tensor-core, few-column and tiny shapes; odd lengths)."""
