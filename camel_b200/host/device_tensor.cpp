@@ -156,6 +156,28 @@ TensorObject *TensorObject::fromHost(
 
 ct_dtype TensorObject::ctDType() const { return toCtDType(dtype_); }
 
+void TensorObject::deferCompare(const TensorObject *src, ct_compare_op op, double scalar, bool tensorOnLeft) {
+    deferred_.src          = src->deviceData(); // a finished buffer: a deferred source is evaluated here
+    deferred_.srcDType     = src->ctDType();
+    deferred_.op           = op;
+    deferred_.scalar       = scalar;
+    deferred_.tensorOnLeft = tensorOnLeft ? 1 : 0;
+    pending_.store(true, std::memory_order_release);
+}
+
+void TensorObject::materialise() const {
+    if (!pending_.load(std::memory_order_acquire))
+        return;
+    static std::mutex once;
+    std::lock_guard<std::mutex> lock(once);
+    if (!pending_.load(std::memory_order_relaxed))
+        return;
+    const DeferredCompare &d = deferred_;
+    ctCheck(ct_compare_scalar(
+        d.op, d.srcDType, d.src, d.scalar, d.tensorOnLeft ? 0 : 1, numel_, static_cast<uint8_t *>(dev_)));
+    pending_.store(false, std::memory_order_release);
+}
+
 bool TensorObject::sameShape(const TensorObject *other) const {
     if (!other || rank_ != other->rank_)
         return false;
@@ -171,7 +193,7 @@ const std::byte *TensorObject::rawData() const {
         if (!host_)
             throw std::bad_alloc();
         if (byteSize_ > 0)
-            ctCheck(ct_d2h(host_, dev_, static_cast<size_t>(byteSize_)));
+            ctCheck(ct_d2h(host_, deviceData(), static_cast<size_t>(byteSize_)));
     }
     return host_;
 }
@@ -207,7 +229,7 @@ bool TensorObject::equals(const rtdata::Object *other, const type::Type *, bool)
 rtdata::Object *TensorObject::clone(mm::IAllocator &allocator, const type::Type *, bool) const {
     TensorObject *copy = create(dtype_, std::span<const int64_t>(shape_, rank_), allocator, false);
     if (byteSize_ > 0)
-        ctCheck(ct_d2d(copy->dev_, dev_, static_cast<size_t>(byteSize_)));
+        ctCheck(ct_d2d(copy->dev_, deviceData(), static_cast<size_t>(byteSize_)));
     return copy;
 }
 

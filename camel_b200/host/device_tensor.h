@@ -17,6 +17,7 @@
 #include "camel/core/type/base.h"
 #include "camel_tensor_b200.h"
 
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <span>
@@ -54,9 +55,34 @@ class TensorObject : public rtdata::Object {
     int64_t dim(size_t index) const { return shape_[index]; }
     bool sameShape(const TensorObject *other) const;
 
-    // Device payload (never null for numel > 0).
-    void *deviceData() { return dev_; }
-    const void *deviceData() const { return dev_; }
+    // Device payload (never null for numel > 0).  A deferred comparison (below) is evaluated
+    // first, so every reader sees the finished mask.
+    void *deviceData() {
+        materialise();
+        return dev_;
+    }
+    const void *deviceData() const {
+        materialise();
+        return dev_;
+    }
+
+    // `t > s`, `t < s`, ... against a scalar may stay unevaluated until somebody reads the mask.
+    // The reference's programs write relu as `h * (h > 0)` (test/run/nn/svm.cml:31): multiply sees
+    // the deferred `h > 0` and runs one relu kernel (8 bytes per element instead of 14 for the two
+    // operators), and the mask is never written unless something else asks for it.  The source is
+    // remembered by its device buffer, which neither moves nor dies before the module is unloaded.
+    struct DeferredCompare {
+        const void *src = nullptr; // device buffer of the compared tensor; set once, by deferCompare
+        ct_dtype srcDType = CT_F32;
+        ct_compare_op op  = CT_GT;
+        double scalar     = 0.0;
+        int tensorOnLeft  = 1;
+    };
+    void deferCompare(const TensorObject *src, ct_compare_op op, double scalar, bool tensorOnLeft);
+    // The record of a comparison that has not run yet, or nullptr.  Operators run on many threads:
+    // the flag is the only field written after deferCompare, and materialise() is serialised.
+    const DeferredCompare *deferred() const { return pending_.load(std::memory_order_acquire) ? &deferred_ : nullptr; }
+    void materialise() const;
 
     // Host view of the payload: copies device -> host on first use after a device write.
     const std::byte *rawData() const;
@@ -81,6 +107,8 @@ class TensorObject : public rtdata::Object {
     uint64_t numel_;
     uint64_t byteSize_;
     void *dev_;
+    DeferredCompare deferred_;
+    mutable std::atomic<bool> pending_{false};
     mutable std::byte *host_; // malloc'd mirror, nullptr while stale
     int64_t *shape_;
     int64_t dims_[]; // rank_ entries, in the same allocation as the header

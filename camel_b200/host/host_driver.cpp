@@ -254,6 +254,57 @@ int camel_host_dlpack_roundtrip(const float *host, int64_t rows, int64_t cols, f
     }
 }
 
+// The relu idiom of the reference's programs, `h * (h > threshold)`, as one operator chain on one
+// tensor, for the tests.  out_product receives the product, out_mask the comparison (read after the
+// product).  Returns 1 if the comparison was still unevaluated after the multiply (so the multiply
+// did not read it), 0 if the multiply evaluated it, negative on error.
+int camel_host_relu_idiom(const float *host, int64_t n, double threshold, int mask_first, float *out_product,
+                          uint8_t *out_mask, char *err, int errlen) {
+    try {
+        static const auto ops = getTensorOpsMap();
+        int64_t shape[1]      = {n};
+        TensorObject *h       = TensorObject::fromHost(TypeCode::Float32, shape, host, g_scratch);
+        camel::core::context::Context *nullCtx = nullptr;
+        Type *f32Tensor                        = tensorTypeFor(0);
+
+        VecArgsView with, cmp;
+        cmp.slots.push_back(camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(h)));
+        cmp.types.push_back(f32Tensor);
+        cmp.slots.push_back(camel::core::rtdata::toSlot<double>(threshold));
+        cmp.types.push_back(Type::Float64());
+        slot_t maskSlot = ops.at("gt")(with, cmp, *nullCtx);
+        auto *mask      = camel::core::rtdata::fromSlot<TensorObject *>(maskSlot);
+
+        VecArgsView mul;
+        auto push = [&](TensorObject *t, int dtype) {
+            mul.slots.push_back(camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(t)));
+            mul.types.push_back(tensorTypeFor(dtype));
+        };
+        if (mask_first) {
+            push(mask, 2);
+            push(h, 0);
+        } else {
+            push(h, 0);
+            push(mask, 2);
+        }
+        auto *prod   = camel::core::rtdata::fromSlot<TensorObject *>(ops.at("multiply")(with, mul, *nullCtx));
+        int deferred = mask->deferred() != nullptr ? 1 : 0;
+        if (prod->dtype() != TypeCode::Float32 || prod->numel() != static_cast<uint64_t>(n))
+            return -1;
+        std::memcpy(out_product, prod->rawData(), prod->byteSize());
+        std::memcpy(out_mask, mask->rawData(), mask->byteSize());
+        if (mask->deferred() != nullptr)
+            return -2;
+        return deferred;
+    } catch (const std::exception &e) {
+        if (err && errlen > 0) {
+            std::strncpy(err, e.what(), static_cast<size_t>(errlen) - 1);
+            err[errlen - 1] = '\0';
+        }
+        return -9;
+    }
+}
+
 int camel_ref_list_groups(char *buf, int buflen) {
     std::string s;
     for (const auto &g : getTensorOperatorGroups())

@@ -215,6 +215,21 @@ slot_t binaryBody(ArgsView &norm, ct_binary_op op, bool lhsMustBeTensor) {
             TensorObject *a = tensorArg(norm, 0), *b = tensorArg(norm, 1);
             if (!a->sameShape(b))
                 throw std::invalid_argument("Tensor binary operation requires matching shapes");
+            if (op == CT_MUL) {
+                // h * (h > 0) with the comparison still deferred: one relu kernel, same bits
+                auto reluOf = [](TensorObject *h, TensorObject *mask) {
+                    const auto *d = mask->deferred();
+                    return d && h->dtype() == TypeCode::Float32 && d->src == h->deviceData() && d->op == CT_GT &&
+                           d->tensorOnLeft && d->scalar == 0.0;
+                };
+                TensorObject *h = reluOf(a, b) ? a : (reluOf(b, a) ? b : nullptr);
+                if (h) {
+                    TensorObject *out = newTensor(TypeCode::Float32, shapeOf(h));
+                    ctn::ctCheck(ct_relu(static_cast<const float *>(h->deviceData()), h->numel(),
+                                         static_cast<float *>(out->deviceData())));
+                    return wrap(out);
+                }
+            }
             ct_dtype odt      = ct_result_dtype(op, a->ctDType(), b->ctDType());
             TensorObject *out = newTensor(ctn::fromCtDType(odt), shapeOf(a));
             ctn::ctCheck(ct_binary(op, a->ctDType(), a->deviceData(), b->ctDType(), b->deviceData(), a->numel(),
@@ -253,8 +268,7 @@ slot_t compareBody(ArgsView &norm, ct_compare_op op, bool arraysAllowed) {
         TensorObject *t   = fetch(ti);
         double s          = scalarValue(norm, si);
         TensorObject *out = newTensor(TypeCode::Bool, shapeOf(t));
-        ctn::ctCheck(ct_compare_scalar(op, t->ctDType(), t->deviceData(), s, lt ? 0 : 1, t->numel(),
-                                       static_cast<uint8_t *>(out->deviceData())));
+        out->deferCompare(t, op, s, lt); // evaluated when the mask is first read (see device_tensor.h)
         return wrap(out);
     });
 }
