@@ -187,6 +187,9 @@ ct_status split_rows_planes(
 ct_status gemm_f32_skinny(
     DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
     int64_t n, int act, float *out, int64_t *argmax);
+// out[m][n] = A^T . B with A stored [k][m], n <= 32 (float64 accumulation, two launches)
+ct_status gemm_f32_tn_skinny(
+    DeviceState *st, const float *a_km, const float *b, int64_t m, int64_t k, int64_t n, float *out);
 ct_status matmul_generic(
     int adt, const void *a, int bdt, const void *b, int64_t m, int64_t k, int64_t n, void *out);
 

@@ -324,6 +324,46 @@ unsigned capped_blocks(DeviceState *st, int64_t total, int per_sm) {
 
 using namespace ct;
 
+namespace ct {
+
+// matmul with k == 1 is an outer product: out[i][j] = float(0.0 + double(a[i]) * double(b[j])), one
+// exact product rounded once.  The reference's programs broadcast a column this way
+// (`v[n, 1] @ ones([1, k])`, test/run/nn/mnist.cml:18), so it has to return v exactly, which a
+// split-precision tensor-core product does not.  Bound by the write of the result.
+template <bool VEC>
+__global__ void __launch_bounds__(256) outer_product_kernel(
+    const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out, int64_t n, int64_t total) {
+    int64_t step = (int64_t)gridDim.x * 256;
+    auto one     = [](float x, float y) { return (float)(0.0 + (double)x * (double)y); };
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+        if (VEC) { // n % 4 == 0: four neighbours of one row
+            int64_t r = (i * 4) / n, c = i * 4 - r * n;
+            float x   = a[r];
+            float4 y  = *reinterpret_cast<const float4 *>(b + c);
+            float4 o  = make_float4(one(x, y.x), one(x, y.y), one(x, y.z), one(x, y.w));
+            *reinterpret_cast<float4 *>(out + i * 4) = o;
+        } else {
+            int64_t r = i / n, c = i - r * n;
+            out[i]    = one(a[r], b[c]);
+        }
+    }
+}
+
+static ct_status outer_product(DeviceState *st, const float *a, const float *b, int64_t m, int64_t n, float *out) {
+    bool vec      = (n & 3) == 0 && ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+    int64_t total = vec ? m * n / 4 : m * n;
+    int64_t want  = (total + 255) / 256, cap = (int64_t)st->sm_count * 16;
+    unsigned grid = (unsigned)(want < cap ? want : cap);
+    if (vec)
+        outer_product_kernel<true><<<grid, 256, 0, stream()>>>(a, b, out, n, total);
+    else
+        outer_product_kernel<false><<<grid, 256, 0, stream()>>>(a, b, out, n, total);
+    CT_LAUNCH_CHECK("outer_product");
+    return CT_OK;
+}
+
+} // namespace ct
+
 extern "C" {
 
 ct_status ct_matmul(
@@ -345,6 +385,8 @@ ct_status ct_matmul(
         float *of = static_cast<float *>(out);
         if (n <= 32)
             return gemm_f32_skinny(st, af, bf, nullptr, m, k, n, CT_ACT_NONE, of, nullptr);
+        if (k == 1)
+            return outer_product(st, af, bf, m, n, of);
         if (m * n * (k > 0 ? k : 1) < kTinyMacs)
             return matmul_generic(adt, a, bdt, b, m, k, n, out);
         CT_TRY(clear_flags(st));
@@ -363,8 +405,10 @@ ct_status ct_matmul_tn(const float *a_km, const float *b, int64_t m, int64_t k, 
         return CT_OK;
     if (!out || (k > 0 && (!a_km || !b)))
         return fail(CT_ERR_INVALID, "matmul: null pointer");
-    if (n <= 32 || m * n * (k > 0 ? k : 1) < kTinyMacs) {
-        // shapes the tensor-core kernel does not take: materialise the transpose, then as ct_matmul
+    if (n <= 32)
+        return gemm_f32_tn_skinny(st, a_km, b, m, k, n, out);
+    if (m * n * (k > 0 ? k : 1) < kTinyMacs) {
+        // too small for the tensor-core kernel: materialise the transpose, then as ct_matmul
         void *at = nullptr;
         CT_TRY(ct_alloc(&at, (size_t)(m * k > 0 ? m * k : 1) * sizeof(float)));
         ct_status s = k > 0 ? ct_transpose(CT_F32, a_km, k, m, at) : CT_OK;

@@ -328,6 +328,11 @@ __device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
 }
 
+__device__ __forceinline__ void cp_async_4(void *smem_dst, const void *gmem_src) {
+    unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 
 // Waits until at most `pending` of this thread's committed copy groups are still in flight.
@@ -368,7 +373,8 @@ __device__ unsigned long long g_skinny_trace[1024 * 8];
 template <int NP>
 __global__ void __launch_bounds__(32 * kSkinnyWarps, 1) gemm_skinny_tile_kernel(
     const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
-    int64_t m, int k, int n, int ks, int act, float *__restrict__ out, int64_t *__restrict__ argmax) {
+    int64_t m, int k, int n, int ks, int x_aligned, int act, float *__restrict__ out,
+    int64_t *__restrict__ argmax) {
     constexpr int NE = 2 * NP;
     extern __shared__ __align__(16) unsigned char skinny_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -410,12 +416,30 @@ __global__ void __launch_bounds__(32 * kSkinnyWarps, 1) gemm_skinny_tile_kernel(
     load_round(lane);
     // activations: chunk c covers k0 + [32c, 32c+32) of the block's 32 rows; eight lanes copy one row's 128 bytes
     for (int c = 0; c < nchunks; ++c) {
-        for (int idx = lane; idx < 256; idx += 32) {
-            int r = idx >> 3, kk = c * 32 + (idx & 7) * 4;
-            if (kk < klen && row0 + r < m)
-                cp_async_16(xs + r * xs_stride + kk, x + (row0 + r) * k + k0 + kk);
+        if (x_aligned) {
+            for (int idx = lane; idx < 256; idx += 32) {
+                int r = idx >> 3, kk = c * 32 + (idx & 7) * 4;
+                if (kk < klen && row0 + r < m)
+                    cp_async_16(xs + r * xs_stride + kk, x + (row0 + r) * k + k0 + kk);
+            }
+        } else {
+            // k is not a multiple of four (784 features and a bias column): rows start at any
+            // 4-byte address, so a warp copies the 32 floats of a row's chunk one per lane
+            const int kk = c * 32 + lane;
+            if (kk < klen)
+                for (int r = 0; r < 32 && row0 + r < m; ++r)
+                    cp_async_4(xs + r * xs_stride + kk, x + (row0 + r) * k + k0 + kk);
         }
         cp_async_commit();
+    }
+    // the arithmetic walks k in fours: zero what lies between the end of the slice and the next four
+    const int kpad = (klen + 3) & ~3;
+    if (kpad > klen) {
+        const int extra = kpad - klen;
+        for (int idx = lane; idx < 32 * extra; idx += 32)
+            xs[(idx / extra) * xs_stride + klen + idx % extra] = 0.0f;
+        for (int idx = lane; idx < extra * NE; idx += 32)
+            ws[klen * NE + idx] = 0.0;
     }
     SK_STAMP(1);
     store_round(lane);
@@ -509,7 +533,8 @@ ct_status launch_skinny_tile(
             gemm_skinny_tile_kernel<NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     CT_CUDA(launch_dependent(
         gemm_skinny_tile_kernel<NP>, dim3((unsigned)((m + 31) / 32)), dim3(32 * kSkinnyWarps), smem, stream(), a, b, bias,
-        m, (int)k, n, skinny_tile_slice(k), act, out, argmax));
+        m, (int)k, n, skinny_tile_slice(k), (int)((k & 3) == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0), act, out,
+        argmax));
     CT_LAUNCH_CHECK("gemm_skinny_tile");
     return CT_OK;
 }
@@ -529,6 +554,135 @@ ct_status matmul_generic(
     return CT_OK;
 }
 
+// ---- transposed left operand, few output columns --------------------------------------------
+//
+// out[i][j] = sum_k a_km[k][i] * b[k][j], n <= 32: the gradient of a classifier,
+// `transpose(X) @ (probs - y)` (test/run/nn/mnist.cml:39; k = samples, m = features, n = classes).
+// Both operands are read in their own row-major order, X exactly once: a thread owns R output rows
+// (columns of X, so a warp's loads are contiguous), the rows of b are widened to float64 in shared
+// memory once per block and read as broadcasts, and every product is an exact float64 FMA as in
+// the reference (operators.cpp:757-766).  The long dimension is cut into slices over the grid;
+// the slices' float64 sums are added in slice order by gemm_tn_skinny_finish_kernel, so the result
+// does not depend on scheduling.  Bound by the float64 pipe and the read of X, which are about
+// equal at n = 10.
+constexpr int kTnThreads = 128;
+constexpr int kTnChunk   = 32; // rows of b staged per step
+
+template <int NMAX, int R>
+__global__ void __launch_bounds__(kTnThreads, 4) gemm_tn_skinny_kernel(
+    const float *__restrict__ a_km, const float *__restrict__ b, int64_t m, int64_t k, int n, int64_t k_per_slice,
+    double *__restrict__ partial) {
+    __shared__ double bs[kTnChunk][NMAX];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t row0 = ((int64_t)blockIdx.x * (kTnThreads / 32) + warp) * (32 * R) + lane;
+    const int64_t k0 = (int64_t)blockIdx.y * k_per_slice;
+    const int64_t k1 = k0 + k_per_slice < k ? k0 + k_per_slice : k;
+    double acc[R][NMAX];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int j = 0; j < NMAX; ++j)
+            acc[r][j] = 0.0;
+    for (int64_t kc = k0; kc < k1; kc += kTnChunk) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < kTnChunk * NMAX; idx += kTnThreads) {
+            int kk = idx / NMAX, j = idx - kk * NMAX;
+            bs[kk][j] = (kc + kk < k1 && j < n) ? (double)b[(kc + kk) * n + j] : 0.0;
+        }
+        __syncthreads();
+        const int kn = k1 - kc < kTnChunk ? (int)(k1 - kc) : kTnChunk;
+#pragma unroll 8
+        for (int kk = 0; kk < kn; ++kk) {
+            const float *arow = a_km + (kc + kk) * m;
+            double av[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                av[r] = row0 + 32 * r < m ? (double)arow[row0 + 32 * r] : 0.0;
+#pragma unroll
+            for (int j = 0; j < NMAX; ++j) {
+                double bj = bs[kk][j];
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                    acc[r][j] = fma(av[r], bj, acc[r][j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        int64_t row = row0 + 32 * r;
+        if (row < m) {
+            double *dst = partial + ((int64_t)blockIdx.y * m + row) * n;
+#pragma unroll
+            for (int j = 0; j < NMAX; ++j)
+                if (j < n)
+                    dst[j] = acc[r][j];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) gemm_tn_skinny_finish_kernel(
+    const double *__restrict__ partial, int64_t mn, int slices, float *__restrict__ out) {
+    int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= mn)
+        return;
+    double sum = 0.0;
+    for (int s = 0; s < slices; ++s)
+        sum += partial[(int64_t)s * mn + i];
+    out[i] = (float)sum;
+}
+
+template <int NMAX, int R>
+static ct_status launch_tn_skinny(
+    DeviceState *st, const float *a_km, const float *b, int64_t m, int64_t k, int n, float *out) {
+    const int64_t rows_per_block = (int64_t)(kTnThreads / 32) * 32 * R;
+    const int64_t mblocks        = (m + rows_per_block - 1) / rows_per_block;
+    int64_t slices               = (4 * (int64_t)st->sm_count + mblocks - 1) / mblocks; // four blocks per SM
+    const int64_t most           = (k + 4 * kTnChunk - 1) / (4 * kTnChunk); // at least four chunks per slice
+    if (slices > most)
+        slices = most;
+    if (slices < 1)
+        slices = 1;
+    if (slices > 65535)
+        slices = 65535;
+    int64_t k_per_slice = (k + slices - 1) / slices;
+    k_per_slice         = (k_per_slice + kTnChunk - 1) / kTnChunk * kTnChunk;
+    if (k_per_slice < kTnChunk)
+        k_per_slice = kTnChunk;
+    slices = k > 0 ? (k + k_per_slice - 1) / k_per_slice : 1;
+    CT_TRY(ensure_ws(&st->splitk_ws, &st->splitk_ws_bytes, (size_t)slices * m * n * sizeof(double)));
+    auto *partial = static_cast<double *>(st->splitk_ws);
+    dim3 grid((unsigned)mblocks, (unsigned)slices);
+    gemm_tn_skinny_kernel<NMAX, R><<<grid, kTnThreads, 0, stream()>>>(a_km, b, m, k, n, k_per_slice, partial);
+    CT_LAUNCH_CHECK("gemm_tn_skinny");
+    const int64_t mn = m * n;
+    gemm_tn_skinny_finish_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, stream()>>>(partial, mn, (int)slices, out);
+    CT_LAUNCH_CHECK("gemm_tn_skinny_finish");
+    return CT_OK;
+}
+
+ct_status gemm_f32_tn_skinny(
+    DeviceState *st, const float *a_km, const float *b, int64_t m, int64_t k, int64_t n, float *out) {
+    if (m == 0 || n == 0)
+        return CT_OK;
+    if (n > 32 || m > 0x7fffffffll * 64)
+        return fail(CT_ERR_INVALID, "transposed skinny GEMM takes at most 32 output columns");
+    ProfScope prof("gemm_skinny");
+    switch ((n + 1) / 2) {
+    case 1: return launch_tn_skinny<2, 4>(st, a_km, b, m, k, (int)n, out);
+    case 2: return launch_tn_skinny<4, 4>(st, a_km, b, m, k, (int)n, out);
+    case 3: return launch_tn_skinny<6, 4>(st, a_km, b, m, k, (int)n, out);
+    case 4: return launch_tn_skinny<8, 4>(st, a_km, b, m, k, (int)n, out);
+    case 5: return launch_tn_skinny<10, 4>(st, a_km, b, m, k, (int)n, out);
+    case 6: return launch_tn_skinny<12, 4>(st, a_km, b, m, k, (int)n, out);
+    case 7: return launch_tn_skinny<14, 4>(st, a_km, b, m, k, (int)n, out);
+    case 8: return launch_tn_skinny<16, 4>(st, a_km, b, m, k, (int)n, out);
+    default: break;
+    }
+    if (n <= 24)
+        return launch_tn_skinny<24, 2>(st, a_km, b, m, k, (int)n, out);
+    return launch_tn_skinny<32, 2>(st, a_km, b, m, k, (int)n, out);
+}
+
 ct_status gemm_f32_skinny(
     DeviceState *st, const float *a, const float *b, const float *bias, int64_t m, int64_t k,
     int64_t n, int act, float *out, int64_t *argmax) {
@@ -539,8 +693,7 @@ ct_status gemm_f32_skinny(
     unsigned blocks = (unsigned)((m + 7) / 8);
     ProfScope prof("gemm_skinny");
     const int np = (int)((n + 1) / 2);
-    if (m >= 256 && n <= 16 && k >= 32 && (k & 3) == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
-        k <= (1 << 20) && skinny_tile_smem(k, np) <= 220 * 1024) {
+    if (m >= 256 && n <= 16 && k >= 32 && k <= (1 << 20) && skinny_tile_smem(k, np) <= 220 * 1024) {
         switch (np) {
         case 1: return launch_skinny_tile<1>(a, b, bias, m, k, (int)n, act, out, argmax);
         case 2: return launch_skinny_tile<2>(a, b, bias, m, k, (int)n, act, out, argmax);

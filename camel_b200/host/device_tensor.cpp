@@ -8,6 +8,7 @@
 #include <map>
 #include <unordered_set>
 #include <utility>
+#include <vector>
 
 namespace camel::tensor {
 
@@ -20,6 +21,9 @@ std::unordered_set<void *> g_deviceBuffers;
 // when its tensor is created, and lives until releaseAllDeviceBuffers, so the address identifies
 // the contents.
 std::map<std::pair<void *, int>, void *> g_packedWeights;
+// The expression records of all tensors, released with the device buffers.
+std::vector<Expr *> g_exprs;
+std::atomic<int> g_lazy{-1}; // -1: not read from the environment yet
 
 void *allocDevice(size_t bytes) {
     void *p = nullptr;
@@ -53,6 +57,9 @@ void releaseAllDeviceBuffers() {
     for (void *p : g_deviceBuffers)
         ct_free(p);
     g_deviceBuffers.clear();
+    for (Expr *e : g_exprs)
+        delete e;
+    g_exprs.clear();
 }
 
 const void *packedWeightsFor(const TensorObject *w, int64_t k, int64_t n) {
@@ -124,8 +131,8 @@ TypeCode fromCtDType(ct_dtype dt) {
 }
 
 TensorObject::TensorObject(TypeCode dtype, uint32_t rank, uint64_t numel, uint64_t byteSize)
-    : dtype_(dtype), rank_(rank), numel_(numel), byteSize_(byteSize), dev_(nullptr), host_(nullptr),
-      shape_(nullptr) {}
+    : dtype_(dtype), rank_(rank), numel_(numel), byteSize_(byteSize), expr_(nullptr),
+      host_(nullptr), shape_(nullptr) {}
 
 TensorObject *
 TensorObject::create(TypeCode dtype, std::span<const int64_t> shape, mm::IAllocator &allocator, bool zeroInit) {
@@ -140,9 +147,20 @@ TensorObject::create(TypeCode dtype, std::span<const int64_t> shape, mm::IAlloca
     t->shape_ = t->dims_;
     if (!shape.empty())
         std::memcpy(t->dims_, shape.data(), shape.size() * sizeof(int64_t));
-    t->dev_ = allocDevice(static_cast<size_t>(bytes));
+    auto *e  = new Expr;
+    e->bytes = bytes;
+    e->dtype = toCtDType(dtype);
+    e->rank  = static_cast<uint32_t>(shape.size());
+    e->numel = numel;
+    e->rows  = shape.empty() ? 1 : shape[0];
+    e->cols  = shape.size() == 2 ? shape[1] : (e->rows ? static_cast<int64_t>(numel) / e->rows : 0);
+    t->expr_ = e;
+    {
+        std::lock_guard<std::mutex> lock(g_registryMutex);
+        g_exprs.push_back(e);
+    }
     if (zeroInit && numel > 0)
-        ctCheck(ct_fill(toCtDType(dtype), 0.0, numel, t->dev_));
+        ctCheck(ct_fill(toCtDType(dtype), 0.0, numel, t->deviceData()));
     return t;
 }
 
@@ -150,32 +168,136 @@ TensorObject *TensorObject::fromHost(
     TypeCode dtype, std::span<const int64_t> shape, const void *hostData, mm::IAllocator &allocator) {
     TensorObject *t = create(dtype, shape, allocator, false);
     if (t->byteSize_ > 0)
-        ctCheck(ct_h2d(t->dev_, hostData, static_cast<size_t>(t->byteSize_)));
+        ctCheck(ct_h2d(t->deviceData(), hostData, static_cast<size_t>(t->byteSize_)));
     return t;
 }
 
 ct_dtype TensorObject::ctDType() const { return toCtDType(dtype_); }
 
-void TensorObject::deferCompare(const TensorObject *src, ct_compare_op op, double scalar, bool tensorOnLeft) {
-    deferred_.src          = src->deviceData(); // a finished buffer: a deferred source is evaluated here
-    deferred_.srcDType     = src->ctDType();
-    deferred_.op           = op;
-    deferred_.scalar       = scalar;
-    deferred_.tensorOnLeft = tensorOnLeft ? 1 : 0;
-    pending_.store(true, std::memory_order_release);
+// ---- deferred device expressions ---------------------------------------------------------
+
+std::recursive_mutex &exprMutex() {
+    static std::recursive_mutex m;
+    return m;
 }
 
-void TensorObject::materialise() const {
-    if (!pending_.load(std::memory_order_acquire))
-        return;
+bool lazyEvaluation() {
+    int v = g_lazy.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char *env = std::getenv("CAMEL_TENSOR_EAGER");
+        v               = (env && env[0] && env[0] != '0') ? 0 : 1;
+        g_lazy.store(v, std::memory_order_relaxed);
+    }
+    return v != 0;
+}
+
+void setLazyEvaluation(bool on) { g_lazy.store(on ? 1 : 0, std::memory_order_relaxed); }
+
+void *bufferOf(Expr *e) {
     static std::mutex once;
     std::lock_guard<std::mutex> lock(once);
-    if (!pending_.load(std::memory_order_relaxed))
+    void *p = e->out.load(std::memory_order_relaxed);
+    if (!p) {
+        p = allocDevice(static_cast<size_t>(e->bytes));
+        e->out.store(p, std::memory_order_release);
+    }
+    return p;
+}
+
+void defer(TensorObject *out, ExprKind kind, const TensorObject *a, const TensorObject *b, int op, double scalar,
+           ct_dtype scalarDType, int tensorOnLeft) {
+    Expr *e         = out->expr();
+    e->kind         = kind;
+    e->a            = a ? a->expr() : nullptr;
+    e->b            = b ? b->expr() : nullptr;
+    e->op           = op;
+    e->scalar       = scalar;
+    e->scalarDType  = scalarDType;
+    e->tensorOnLeft = tensorOnLeft;
+    e->pending.store(true, std::memory_order_release);
+    if (!lazyEvaluation()) {
+        evaluate(e);
+        e->kind = ExprKind::Value; // no record: nothing downstream is fused
+        e->a = e->b = nullptr;
+    }
+}
+
+void evaluate(Expr *e) {
+    if (!e || !e->pending.load(std::memory_order_acquire))
         return;
-    const DeferredCompare &d = deferred_;
-    ctCheck(ct_compare_scalar(
-        d.op, d.srcDType, d.src, d.scalar, d.tensorOnLeft ? 0 : 1, numel_, static_cast<uint8_t *>(dev_)));
-    pending_.store(false, std::memory_order_release);
+    std::lock_guard<std::recursive_mutex> lock(exprMutex());
+    if (!e->pending.load(std::memory_order_relaxed))
+        return;
+    Expr *a = e->a, *b = e->b;
+    auto buf = [](Expr *x) { return bufferOf(x); };
+    auto f32 = [](Expr *x) { return static_cast<const float *>(bufferOf(x)); };
+    ct_status status = CT_OK;
+    if (e->numel == 0) {
+        e->pending.store(false, std::memory_order_release);
+        return;
+    }
+    switch (e->kind) {
+    case ExprKind::Value:
+        break;
+    case ExprKind::CompareScalar:
+        evaluate(a);
+        status = ct_compare_scalar(static_cast<ct_compare_op>(e->op), a->dtype, buf(a), e->scalar,
+                                   e->tensorOnLeft ? 0 : 1, e->numel, static_cast<uint8_t *>(buf(e)));
+        break;
+    case ExprKind::ScaleByScalar:
+        evaluate(a);
+        status = ct_binary_scalar(CT_MUL, a->dtype, buf(a), e->scalar, e->scalarDType, e->tensorOnLeft ? 0 : 1,
+                                  e->numel, buf(e));
+        break;
+    case ExprKind::Transpose:
+        evaluate(a);
+        status = ct_transpose(a->dtype, buf(a), a->rows, a->cols, buf(e));
+        break;
+    case ExprKind::MatMul:
+        if (a->kind == ExprKind::Transpose && a->pending.load(std::memory_order_relaxed) && a->a->dtype == CT_F32 &&
+            b->dtype == CT_F32) {
+            // transpose(X) @ G with the transposed copy never made (mnist.cml:39)
+            evaluate(a->a);
+            evaluate(b);
+            status = ct_matmul_tn(f32(a->a), f32(b), e->rows, a->cols, e->cols, static_cast<float *>(buf(e)));
+        } else {
+            evaluate(a);
+            evaluate(b);
+            status = ct_matmul(a->dtype, buf(a), b->dtype, buf(b), a->rows, a->cols, b->cols, buf(e));
+        }
+        break;
+    case ExprKind::Ones:
+        status = ct_fill(e->dtype, 1.0, e->numel, buf(e));
+        break;
+    case ExprKind::MaxAxis1:
+        evaluate(a);
+        status = ct_max_axis(a->dtype, buf(a), a->rows, a->cols, 1, static_cast<float *>(buf(e)));
+        break;
+    case ExprKind::SumAxis1:
+        evaluate(a);
+        status = ct_sum_axis(a->dtype, buf(a), a->rows, a->cols, 1, static_cast<float *>(buf(e)));
+        break;
+    case ExprKind::Column:
+        evaluate(a);
+        status = ct_d2d(buf(e), buf(a), static_cast<size_t>(e->numel) * 4);
+        break;
+    case ExprKind::Spread:
+        evaluate(a);
+        evaluate(b);
+        status = ct_matmul(CT_F32, buf(a), CT_F32, buf(b), a->rows, 1, b->cols, buf(e));
+        break;
+    case ExprKind::Subtract:
+        evaluate(a);
+        evaluate(b);
+        status = ct_binary(CT_SUB, a->dtype, buf(a), b->dtype, buf(b), e->numel, buf(e));
+        break;
+    case ExprKind::Exp:
+        evaluate(a);
+        status = ct_exp(f32(a), e->numel, static_cast<float *>(buf(e)));
+        break;
+    }
+    ctCheck(status); // a failed launch leaves the record pending: the next reader sees the error too
+    e->pending.store(false, std::memory_order_release);
 }
 
 bool TensorObject::sameShape(const TensorObject *other) const {
@@ -229,7 +351,7 @@ bool TensorObject::equals(const rtdata::Object *other, const type::Type *, bool)
 rtdata::Object *TensorObject::clone(mm::IAllocator &allocator, const type::Type *, bool) const {
     TensorObject *copy = create(dtype_, std::span<const int64_t>(shape_, rank_), allocator, false);
     if (byteSize_ > 0)
-        ctCheck(ct_d2d(copy->dev_, deviceData(), static_cast<size_t>(byteSize_)));
+        ctCheck(ct_d2d(copy->deviceData(), deviceData(), static_cast<size_t>(byteSize_)));
     return copy;
 }
 

@@ -20,6 +20,7 @@
 #include <atomic>
 #include <cstddef>
 #include <cstdint>
+#include <mutex>
 #include <span>
 #include <string>
 
@@ -32,6 +33,75 @@ namespace type   = camel::core::type;
 // Same enumerators as ct_binary_op / ct_compare_op, which follow modules/tensor/runtime.h:39-53.
 using BinaryOp  = ct_binary_op;
 using CompareOp = ct_compare_op;
+
+// ---- deferred device expressions ---------------------------------------------------------
+//
+// The reference's programs spell their networks with the module's small operators: relu is
+// `h * (h > 0)` (test/run/nn/svm.cml:31), softmax is ten operators with two matmul-by-ones
+// broadcasts (test/run/nn/mnist.cml:13-25), the gradient is `transpose(X) @ (probs - y)` and the
+// update `W - lr * g` (mnist.cml:39-40).  Run one by one, each of those is a pass over HBM.  So
+// the cheap, error-free operators of these idioms do not launch when they are called: they
+// allocate their result and record how to compute it (an Expr).  The record is evaluated the
+// first time anything reads the tensor's data, and an operator that closes an idiom (multiply,
+// subtract, divide, matmul) looks at the records of its operands and calls the fused entry point
+// instead (ct_relu, ct_dense with an activation, ct_softmax_rows, ct_matmul_tn, ct_scaled_sub);
+// the intermediate tensors are then never written.  Tensors are immutable values
+// (src/builtin/operators/ops.cpp:210) and device buffers live until the module is unloaded, so a
+// record can be evaluated at any later time with the same result.
+//
+// Operators that can raise a data-dependent error (divide, log, pow) are never deferred, so every
+// error is still raised by the operator that the reference raises it from.
+enum class ExprKind : uint8_t {
+    Value,         // computed when it was created (or uploaded); nothing recorded
+    CompareScalar, // a <op> scalar, Bool
+    ScaleByScalar, // a * scalar, float32
+    Transpose,     // rank-2 transpose of a
+    MatMul,        // a @ b, float32
+    Ones,          // ones(shape), float32
+    MaxAxis1,      // max(a, 1)
+    SumAxis1,      // sum(a, 1)
+    Column,        // reshape of the vector a[n] to [n, 1]
+    Spread,        // a[n, 1] @ ones[1, k]: every row's value k times (b is the ones tensor)
+    Subtract,      // a - b, float32
+    Exp,           // exp(a)
+};
+
+// One record per tensor, on the C++ heap: operands refer to each other through these, because the
+// collector moves small object headers (include/camel/core/mm/gen.h:460-520).  `kind` and the
+// operands stay after evaluation - they are facts about an immutable value - and only `pending`
+// changes.  Fields other than `pending` are written before the tensor is handed out, or under
+// exprMutex().
+struct Expr {
+    ExprKind kind = ExprKind::Value;
+    std::atomic<bool> pending{false};
+    Expr *a = nullptr, *b = nullptr;
+    std::atomic<void *> out{nullptr}; // the tensor's device buffer, allocated at first use (bufferOf)
+    uint64_t bytes = 0;
+    ct_dtype dtype = CT_F32;
+    uint32_t rank  = 0;
+    uint64_t numel = 0;
+    int64_t rows = 0, cols = 0; // of a rank-2 tensor; [n] counts as n rows of one
+    int op             = 0;     // ct_compare_op of CompareScalar
+    double scalar      = 0.0;
+    ct_dtype scalarDType = CT_F32;
+    int tensorOnLeft   = 1;
+};
+
+class TensorObject;
+
+// Serialises evaluation and every look at operand records (operators run on up to 32 threads).
+std::recursive_mutex &exprMutex();
+// Runs the kernels of a pending record (operands first); no-op when it has run.
+void evaluate(Expr *e);
+// The record's device buffer, allocated on the first call.
+void *bufferOf(Expr *e);
+// Records how `out` (freshly created, not yet visible to anyone) is computed.  With deferral
+// switched off it is computed at once and keeps no record.
+void defer(TensorObject *out, ExprKind kind, const TensorObject *a, const TensorObject *b = nullptr, int op = 0,
+           double scalar = 0.0, ct_dtype scalarDType = CT_F32, int tensorOnLeft = 1);
+// Deferral is on unless CAMEL_TENSOR_EAGER=1 is set when the module is loaded.
+bool lazyEvaluation();
+void setLazyEvaluation(bool on);
 
 class TensorObject : public rtdata::Object {
   public:
@@ -55,34 +125,18 @@ class TensorObject : public rtdata::Object {
     int64_t dim(size_t index) const { return shape_[index]; }
     bool sameShape(const TensorObject *other) const;
 
-    // Device payload (never null for numel > 0).  A deferred comparison (below) is evaluated
-    // first, so every reader sees the finished mask.
-    void *deviceData() {
-        materialise();
-        return dev_;
-    }
+    // Device payload.  The buffer is allocated when it is first asked for, so a tensor whose
+    // expression (below) is never evaluated never owns device memory; an expression that has not
+    // run yet is evaluated first, so every reader sees finished data.
+    void *deviceData() { return const_cast<void *>(static_cast<const TensorObject *>(this)->deviceData()); }
     const void *deviceData() const {
-        materialise();
-        return dev_;
+        if (expr_->pending.load(std::memory_order_acquire))
+            evaluate(expr_);
+        void *p = expr_->out.load(std::memory_order_acquire);
+        return p ? p : bufferOf(expr_);
     }
-
-    // `t > s`, `t < s`, ... against a scalar may stay unevaluated until somebody reads the mask.
-    // The reference's programs write relu as `h * (h > 0)` (test/run/nn/svm.cml:31): multiply sees
-    // the deferred `h > 0` and runs one relu kernel (8 bytes per element instead of 14 for the two
-    // operators), and the mask is never written unless something else asks for it.  The source is
-    // remembered by its device buffer, which neither moves nor dies before the module is unloaded.
-    struct DeferredCompare {
-        const void *src = nullptr; // device buffer of the compared tensor; set once, by deferCompare
-        ct_dtype srcDType = CT_F32;
-        ct_compare_op op  = CT_GT;
-        double scalar     = 0.0;
-        int tensorOnLeft  = 1;
-    };
-    void deferCompare(const TensorObject *src, ct_compare_op op, double scalar, bool tensorOnLeft);
-    // The record of a comparison that has not run yet, or nullptr.  Operators run on many threads:
-    // the flag is the only field written after deferCompare, and materialise() is serialised.
-    const DeferredCompare *deferred() const { return pending_.load(std::memory_order_acquire) ? &deferred_ : nullptr; }
-    void materialise() const;
+    // How this tensor came about (see Expr); never null, stable while the object moves.
+    Expr *expr() const { return expr_; }
 
     // Host view of the payload: copies device -> host on first use after a device write.
     const std::byte *rawData() const;
@@ -106,9 +160,7 @@ class TensorObject : public rtdata::Object {
     uint32_t rank_;
     uint64_t numel_;
     uint64_t byteSize_;
-    void *dev_;
-    DeferredCompare deferred_;
-    mutable std::atomic<bool> pending_{false};
+    Expr *expr_;
     mutable std::byte *host_; // malloc'd mirror, nullptr while stale
     int64_t *shape_;
     int64_t dims_[]; // rank_ entries, in the same allocation as the header

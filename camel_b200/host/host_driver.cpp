@@ -96,16 +96,129 @@ struct camel_host_out {
     double seconds;
 };
 
-int camel_ref_call(const char *op, int nargs, const camel_host_arg *args, camel_host_out *out, char *err, int errlen) {
-    auto fail = [&](int rc, const std::string &msg) {
-        if (err && errlen > 0) {
-            std::strncpy(err, msg.c_str(), static_cast<size_t>(errlen) - 1);
-            err[errlen - 1] = '\0';
+// Values kept between the calls of a session (below): what an operator returned, with its type.
+struct SessionValue {
+    slot_t slot;
+    Type *type;
+    int kind; // as camel_host_out.kind
+};
+static std::vector<SessionValue> g_session;
+
+static Type *intArrayType() {
+    static Type *t = ArrayType::create(Type::Int64());
+    return t;
+}
+
+// Appends the arguments to the `with` and `norm` views; returns an empty string or the complaint.
+static std::string buildArgs(int nargs, const camel_host_arg *args, VecArgsView &with, VecArgsView &norm) {
+    for (int i = 0; i < nargs; ++i) {
+        const camel_host_arg &a = args[i];
+        VecArgsView &dst        = (a.kind & 0x100) ? with : norm;
+        switch (a.kind & 0xff) {
+        case 0: {
+            std::span<const int64_t> shape(a.shape, static_cast<size_t>(a.rank));
+            TensorObject *t = TensorObject::fromHost(dtypeCode(a.dtype), shape, a.data, g_scratch);
+            dst.slots.push_back(camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(t)));
+            dst.types.push_back(tensorTypeFor(a.dtype));
+            break;
         }
-        return rc;
-    };
+        case 1:
+            dst.slots.push_back(camel::core::rtdata::toSlot<int64_t>(a.i64));
+            dst.types.push_back(Type::Int64());
+            break;
+        case 2:
+            dst.slots.push_back(camel::core::rtdata::toSlot<double>(a.f64));
+            dst.types.push_back(Type::Float64());
+            break;
+        case 3:
+            dst.slots.push_back(camel::core::rtdata::toSlot<float>(static_cast<float>(a.f64)));
+            dst.types.push_back(Type::Float32());
+            break;
+        case 4:
+            dst.slots.push_back(camel::core::rtdata::toSlot<int32_t>(static_cast<int32_t>(a.i64)));
+            dst.types.push_back(Type::Int32());
+            break;
+        case 5:
+            dst.slots.push_back(camel::core::rtdata::toSlot<bool>(a.i64 != 0));
+            dst.types.push_back(Type::Bool());
+            break;
+        case 6: {
+            ::Array *arr = ::Array::create(g_scratch, static_cast<size_t>(a.rank));
+            for (int k = 0; k < a.rank; ++k)
+                arr->set<int64_t>(static_cast<size_t>(k), a.shape[k]);
+            dst.slots.push_back(camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(arr)));
+            dst.types.push_back(intArrayType());
+            break;
+        }
+        case 7: { // the value an earlier call of the session returned
+            if (a.i64 < 0 || a.i64 >= static_cast<int64_t>(g_session.size()))
+                return "bad session handle";
+            dst.slots.push_back(g_session[static_cast<size_t>(a.i64)].slot);
+            dst.types.push_back(g_session[static_cast<size_t>(a.i64)].type);
+            break;
+        }
+        default:
+            return "bad argument kind";
+        }
+    }
+    return "";
+}
+
+static int resultKind(const std::string &op) {
+    if (op == "sum" || op == "idx" || op == "idx2d")
+        return 1;
+    if (op == "shape")
+        return 2;
+    return op == "show" ? 3 : 0;
+}
+
+// Copies a result out (a tensor through its host view: the device-to-host read of a graph boundary).
+static void exportResult(int kind, slot_t result, camel_host_out *out) {
+    out->kind = kind;
+    if (kind == 1) {
+        out->f64 = camel::core::rtdata::fromSlot<double>(result);
+    } else if (kind == 2) {
+        auto *arr = camel::core::rtdata::fromSlot<::Array *>(result);
+        out->rank = static_cast<int32_t>(arr->size());
+        for (size_t k = 0; k < arr->size() && k < 8; ++k)
+            out->shape[k] = arr->get<int64_t>(k);
+    } else if (kind == 0) {
+        auto *t    = camel::core::rtdata::fromSlot<TensorObject *>(result);
+        out->dtype = static_cast<int32_t>(t->ctDType());
+        out->rank  = static_cast<int32_t>(t->rank());
+        for (size_t k = 0; k < t->rank() && k < 8; ++k)
+            out->shape[k] = t->dim(k);
+        out->numel = t->numel();
+        std::free(g_lastOut);
+        g_lastOut = nullptr;
+        if (t->byteSize() > 0) {
+            g_lastOut = std::malloc(t->byteSize());
+            std::memcpy(g_lastOut, t->rawData(), t->byteSize());
+        }
+        out->data = g_lastOut;
+        t->invalidateHost();
+    }
+}
+
+static int failWith(char *err, int errlen, int rc, const std::string &msg) {
+    if (err && errlen > 0) {
+        std::strncpy(err, msg.c_str(), static_cast<size_t>(errlen) - 1);
+        err[errlen - 1] = '\0';
+    }
+    return rc;
+}
+
+static std::string faultText(const camel::core::error::RuntimeFault &f) {
+    std::string msg;
+    for (const auto &s : f.formatArgs())
+        msg += s;
+    return msg.empty() ? std::string(f.what()) : msg;
+}
+
+int camel_ref_call(const char *op, int nargs, const camel_host_arg *args, camel_host_out *out, char *err, int errlen) {
     try {
         // everything the previous call created is garbage now
+        g_session.clear();
         g_scratch.releaseAll();
         camel::tensor::releaseAllDeviceBuffers();
         std::free(g_lastOut);
@@ -114,103 +227,139 @@ int camel_ref_call(const char *op, int nargs, const camel_host_arg *args, camel_
         static const auto ops = getTensorOpsMap();
         auto it               = ops.find(op);
         if (it == ops.end())
-            return fail(2, std::string("unknown operator: ") + op);
+            return failWith(err, errlen, 2, std::string("unknown operator: ") + op);
 
         VecArgsView with, norm;
-        for (int i = 0; i < nargs; ++i) {
-            const camel_host_arg &a = args[i];
-            VecArgsView &dst        = (a.kind & 0x100) ? with : norm;
-            switch (a.kind & 0xff) {
-            case 0: {
-                std::span<const int64_t> shape(a.shape, static_cast<size_t>(a.rank));
-                TensorObject *t = TensorObject::fromHost(dtypeCode(a.dtype), shape, a.data, g_scratch);
-                dst.slots.push_back(camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(t)));
-                dst.types.push_back(tensorTypeFor(a.dtype));
-                break;
-            }
-            case 1:
-                dst.slots.push_back(camel::core::rtdata::toSlot<int64_t>(a.i64));
-                dst.types.push_back(Type::Int64());
-                break;
-            case 2:
-                dst.slots.push_back(camel::core::rtdata::toSlot<double>(a.f64));
-                dst.types.push_back(Type::Float64());
-                break;
-            case 3:
-                dst.slots.push_back(camel::core::rtdata::toSlot<float>(static_cast<float>(a.f64)));
-                dst.types.push_back(Type::Float32());
-                break;
-            case 4:
-                dst.slots.push_back(camel::core::rtdata::toSlot<int32_t>(static_cast<int32_t>(a.i64)));
-                dst.types.push_back(Type::Int32());
-                break;
-            case 5:
-                dst.slots.push_back(camel::core::rtdata::toSlot<bool>(a.i64 != 0));
-                dst.types.push_back(Type::Bool());
-                break;
-            case 6: {
-                ::Array *arr = ::Array::create(g_scratch, static_cast<size_t>(a.rank));
-                for (int k = 0; k < a.rank; ++k)
-                    arr->set<int64_t>(static_cast<size_t>(k), a.shape[k]);
-                dst.slots.push_back(camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(arr)));
-                static Type *intArray = ArrayType::create(Type::Int64());
-                dst.types.push_back(intArray);
-                break;
-            }
-            default:
-                return fail(2, "bad argument kind");
-            }
-        }
+        std::string complaint = buildArgs(nargs, args, with, norm);
+        if (!complaint.empty())
+            return failWith(err, errlen, 2, complaint);
 
         camel::core::context::Context *nullCtx = nullptr; // no operator body touches the context
+        int kind      = resultKind(op);
         auto t0       = std::chrono::steady_clock::now();
         slot_t result = it->second(with, norm, *nullCtx);
+        if (kind == 0) // an operator may only have recorded its work: have it run inside the timed region
+            camel::core::rtdata::fromSlot<TensorObject *>(result)->deviceData();
         ct_sync();
         auto t1 = std::chrono::steady_clock::now();
 
         std::memset(out, 0, sizeof(*out));
-        out->seconds  = std::chrono::duration<double>(t1 - t0).count();
-        std::string n = op;
-        if (n == "sum" || n == "idx" || n == "idx2d") {
-            out->kind = 1;
-            out->f64  = camel::core::rtdata::fromSlot<double>(result);
-        } else if (n == "shape") {
-            auto *arr = camel::core::rtdata::fromSlot<::Array *>(result);
-            out->kind = 2;
-            out->rank = static_cast<int32_t>(arr->size());
-            for (size_t k = 0; k < arr->size() && k < 8; ++k)
-                out->shape[k] = arr->get<int64_t>(k);
-        } else if (n == "show") {
-            out->kind = 3;
-        } else {
-            auto *t    = camel::core::rtdata::fromSlot<TensorObject *>(result);
-            out->kind  = 0;
-            out->dtype = static_cast<int32_t>(t->ctDType());
-            out->rank  = static_cast<int32_t>(t->rank());
-            for (size_t k = 0; k < t->rank() && k < 8; ++k)
-                out->shape[k] = t->dim(k);
-            out->numel = t->numel();
-            if (t->byteSize() > 0) {
-                g_lastOut = std::malloc(t->byteSize());
-                std::memcpy(g_lastOut, t->rawData(), t->byteSize());
-            }
-            out->data = g_lastOut;
-            t->invalidateHost();
-        }
+        out->seconds = std::chrono::duration<double>(t1 - t0).count();
+        exportResult(kind, result, out);
         ct_status async = ct_check();
         if (async != CT_OK)
-            return fail(1, ct_last_error());
+            return failWith(err, errlen, 1, ct_last_error());
         return 0;
     } catch (const camel::core::error::RuntimeFault &f) {
-        std::string msg;
-        for (const auto &s : f.formatArgs())
-            msg += s;
-        if (msg.empty())
-            msg = f.what();
-        return fail(1, msg);
+        return failWith(err, errlen, 1, faultText(f));
     } catch (const std::exception &e) {
-        return fail(1, e.what());
+        return failWith(err, errlen, 1, e.what());
     }
+}
+
+// ---- sessions: a chain of operator calls whose values stay on the device -------------------
+//
+// camel_ref_call uploads its arguments and reads its result back, like a program of one operator.
+// A session runs a program of many: every call's value is kept (handle = its index) and can be
+// an argument of later calls (argument kind 7), so tensors pass from operator to operator exactly
+// as they do between the nodes of a Camel graph - on the device and, where the plugin defers work,
+// unevaluated.  begin releases everything earlier calls created.
+
+int camel_host_session_begin(int lazy) {
+    g_session.clear();
+    g_scratch.releaseAll();
+    camel::tensor::releaseAllDeviceBuffers();
+    if (lazy >= 0)
+        camel::tensor::setLazyEvaluation(lazy != 0);
+    return 0;
+}
+
+// Keeps a host tensor (or scalar) as a session value without calling an operator.
+int camel_host_session_put(const camel_host_arg *arg, int64_t *handle, char *err, int errlen) {
+    try {
+        VecArgsView with, norm;
+        std::string complaint = buildArgs(1, arg, with, norm);
+        if (!complaint.empty())
+            return failWith(err, errlen, 2, complaint);
+        VecArgsView &v = norm.slots.empty() ? with : norm;
+        g_session.push_back({v.slots[0], v.types[0], (arg->kind & 0xff) == 0 ? 0 : -1});
+        *handle = static_cast<int64_t>(g_session.size()) - 1;
+        return 0;
+    } catch (const std::exception &e) {
+        return failWith(err, errlen, 1, e.what());
+    }
+}
+
+int camel_host_session_call(
+    const char *op, int nargs, const camel_host_arg *args, int64_t *handle, char *err, int errlen) {
+    try {
+        static const auto ops = getTensorOpsMap();
+        auto it               = ops.find(op);
+        if (it == ops.end())
+            return failWith(err, errlen, 2, std::string("unknown operator: ") + op);
+        VecArgsView with, norm;
+        std::string complaint = buildArgs(nargs, args, with, norm);
+        if (!complaint.empty())
+            return failWith(err, errlen, 2, complaint);
+        camel::core::context::Context *nullCtx = nullptr;
+        slot_t result = it->second(with, norm, *nullCtx);
+        int kind      = resultKind(op);
+        Type *type    = nullptr;
+        if (kind == 0)
+            type = tensorTypeFor(static_cast<int>(camel::core::rtdata::fromSlot<TensorObject *>(result)->ctDType()));
+        else if (kind == 1)
+            type = Type::Float64();
+        else if (kind == 2)
+            type = intArrayType();
+        g_session.push_back({result, type, kind});
+        *handle = static_cast<int64_t>(g_session.size()) - 1;
+        return 0;
+    } catch (const camel::core::error::RuntimeFault &f) {
+        return failWith(err, errlen, 1, faultText(f));
+    } catch (const std::exception &e) {
+        return failWith(err, errlen, 1, e.what());
+    }
+}
+
+// Reads a session value back (evaluating it if need be).
+int camel_host_session_fetch(int64_t handle, camel_host_out *out, char *err, int errlen) {
+    try {
+        if (handle < 0 || handle >= static_cast<int64_t>(g_session.size()) || g_session[handle].kind < 0)
+            return failWith(err, errlen, 2, "bad session handle");
+        std::memset(out, 0, sizeof(*out));
+        exportResult(g_session[handle].kind, g_session[handle].slot, out);
+        ct_status async = ct_check();
+        if (async != CT_OK)
+            return failWith(err, errlen, 1, ct_last_error());
+        return 0;
+    } catch (const camel::core::error::RuntimeFault &f) {
+        return failWith(err, errlen, 1, faultText(f));
+    } catch (const std::exception &e) {
+        return failWith(err, errlen, 1, e.what());
+    }
+}
+
+// Makes sure a tensor value has been computed (without reading it back) and waits for the device;
+// returns the number of kernels the library has launched so far, or -1.
+int64_t camel_host_session_finish(int64_t handle, char *err, int errlen) {
+    try {
+        if (handle >= 0 && handle < static_cast<int64_t>(g_session.size()) && g_session[handle].kind == 0)
+            camel::core::rtdata::fromSlot<TensorObject *>(g_session[handle].slot)->deviceData();
+        if (ct_sync() != CT_OK)
+            return failWith(err, errlen, -1, ct_last_error());
+        return static_cast<int64_t>(ct_launch_count());
+    } catch (const camel::core::error::RuntimeFault &f) {
+        return failWith(err, errlen, -1, faultText(f));
+    } catch (const std::exception &e) {
+        return failWith(err, errlen, -1, e.what());
+    }
+}
+
+// 1 if the tensor value still waits to be computed, 0 if it has been, -1 if it is no tensor.
+int camel_host_session_pending(int64_t handle) {
+    if (handle < 0 || handle >= static_cast<int64_t>(g_session.size()) || g_session[handle].kind != 0)
+        return -1;
+    return camel::core::rtdata::fromSlot<TensorObject *>(g_session[handle].slot)->expr()->pending.load() ? 1 : 0;
 }
 
 int camel_ref_list_ops(char *buf, int buflen) {
@@ -245,57 +394,6 @@ int camel_host_dlpack_roundtrip(const float *host, int64_t rows, int64_t cols, f
         cpu->deleter(cpu);
         std::memcpy(out_host, v->rawData(), v->byteSize());
         return 0;
-    } catch (const std::exception &e) {
-        if (err && errlen > 0) {
-            std::strncpy(err, e.what(), static_cast<size_t>(errlen) - 1);
-            err[errlen - 1] = '\0';
-        }
-        return -9;
-    }
-}
-
-// The relu idiom of the reference's programs, `h * (h > threshold)`, as one operator chain on one
-// tensor, for the tests.  out_product receives the product, out_mask the comparison (read after the
-// product).  Returns 1 if the comparison was still unevaluated after the multiply (so the multiply
-// did not read it), 0 if the multiply evaluated it, negative on error.
-int camel_host_relu_idiom(const float *host, int64_t n, double threshold, int mask_first, float *out_product,
-                          uint8_t *out_mask, char *err, int errlen) {
-    try {
-        static const auto ops = getTensorOpsMap();
-        int64_t shape[1]      = {n};
-        TensorObject *h       = TensorObject::fromHost(TypeCode::Float32, shape, host, g_scratch);
-        camel::core::context::Context *nullCtx = nullptr;
-        Type *f32Tensor                        = tensorTypeFor(0);
-
-        VecArgsView with, cmp;
-        cmp.slots.push_back(camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(h)));
-        cmp.types.push_back(f32Tensor);
-        cmp.slots.push_back(camel::core::rtdata::toSlot<double>(threshold));
-        cmp.types.push_back(Type::Float64());
-        slot_t maskSlot = ops.at("gt")(with, cmp, *nullCtx);
-        auto *mask      = camel::core::rtdata::fromSlot<TensorObject *>(maskSlot);
-
-        VecArgsView mul;
-        auto push = [&](TensorObject *t, int dtype) {
-            mul.slots.push_back(camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(t)));
-            mul.types.push_back(tensorTypeFor(dtype));
-        };
-        if (mask_first) {
-            push(mask, 2);
-            push(h, 0);
-        } else {
-            push(h, 0);
-            push(mask, 2);
-        }
-        auto *prod   = camel::core::rtdata::fromSlot<TensorObject *>(ops.at("multiply")(with, mul, *nullCtx));
-        int deferred = mask->deferred() != nullptr ? 1 : 0;
-        if (prod->dtype() != TypeCode::Float32 || prod->numel() != static_cast<uint64_t>(n))
-            return -1;
-        std::memcpy(out_product, prod->rawData(), prod->byteSize());
-        std::memcpy(out_mask, mask->rawData(), mask->byteSize());
-        if (mask->deferred() != nullptr)
-            return -2;
-        return deferred;
     } catch (const std::exception &e) {
         if (err && errlen > 0) {
             std::strncpy(err, e.what(), static_cast<size_t>(errlen) - 1);

@@ -16,6 +16,7 @@
 #include "type.h"
 
 #include <iostream>
+#include <mutex>
 #include <random>
 #include <optional>
 #include <stdexcept>
@@ -204,6 +205,96 @@ template <typename Fn> slot_t guarded(Fn &&fn) {
     }
 }
 
+// ---- closing an idiom: operators that look at how their operands came about -----------------
+
+using ctn::Expr;
+using ctn::ExprKind;
+
+bool isF32(const Expr *e) { return e->dtype == CT_F32; }
+bool stillPending(const Expr *e) { return e->pending.load(std::memory_order_relaxed); }
+const float *f32(Expr *e) { return static_cast<const float *>(ctn::bufferOf(e)); }
+
+// mask == (h > 0)
+bool isPositiveMaskOf(const Expr *mask, const Expr *h) {
+    return mask->kind == ExprKind::CompareScalar && mask->a == h && mask->op == CT_GT && mask->tensorOnLeft &&
+           mask->scalar == 0.0 && isF32(h);
+}
+
+// h * (h > 0), either order (test/run/nn/svm.cml:31): one relu pass; on top of a matmul that has
+// not run, the GEMM with relu in its epilogue.  Returns nullptr if the operands are not that.
+TensorObject *tryRelu(TensorObject *a, TensorObject *b) {
+    Expr *ea = a->expr(), *eb = b->expr();
+    Expr *h  = isPositiveMaskOf(eb, ea) ? ea : (isPositiveMaskOf(ea, eb) ? eb : nullptr);
+    if (!h)
+        return nullptr;
+    Expr *mask        = h == ea ? eb : ea;
+    TensorObject *out = newTensor(TypeCode::Float32, shapeOf(a));
+    if (h->numel == 0)
+        return out;
+    bool transposedLhs = h->kind == ExprKind::MatMul && h->a->kind == ExprKind::Transpose && stillPending(h->a);
+    if (h->kind == ExprKind::MatMul && stillPending(h) && !transposedLhs) {
+        ctn::evaluate(h->a);
+        ctn::evaluate(h->b);
+        ctn::ctCheck(ct_dense(f32(h->a), f32(h->b), nullptr, h->rows, h->a->cols, h->cols, CT_ACT_RELU,
+                              static_cast<float *>(out->deviceData()), nullptr));
+        // The product of the matmul was never written.  If the mask is read later it is taken from
+        // the result: (h > 0) == (h * (h > 0) > 0) for every h (-0.0, NaN and infinities included).
+        if (stillPending(mask))
+            mask->a = out->expr();
+    } else {
+        ctn::evaluate(h);
+        ctn::ctCheck(ct_relu(f32(h), h->numel, static_cast<float *>(out->deviceData())));
+    }
+    return out;
+}
+
+// w - (s * g) or w - (g * s) with the product not yet computed (mnist.cml:40): one pass.
+TensorObject *tryScaledSub(TensorObject *a, TensorObject *b) {
+    Expr *w = a->expr(), *sg = b->expr();
+    if (!(isF32(w) && sg->kind == ExprKind::ScaleByScalar && stillPending(sg) && isF32(sg->a)))
+        return nullptr;
+    TensorObject *out = newTensor(TypeCode::Float32, shapeOf(a));
+    ctn::evaluate(w);
+    ctn::evaluate(sg->a);
+    ctn::ctCheck(ct_scaled_sub(f32(w), f32(sg->a), sg->scalar, w->numel, static_cast<float *>(out->deviceData())));
+    return out;
+}
+
+// The softmax of test/run/nn/mnist.cml:13-25, recognised at its last operator:
+//   exp(L - spread(max(L, 1))) / spread(sum(exp(...), 1)),  spread(v) = reshape(v, [n, 1]) @ ones([1, k]).
+// One ct_softmax_rows pass over L; where L is a matmul that has not run, the classifier GEMM with
+// softmax fused (ct_dense).  The row sums are >= 1 (the row maximum contributes exp(0)) or NaN, so
+// the division-by-zero check of divide can never fire on this pattern.
+TensorObject *trySoftmax(TensorObject *a, TensorObject *b) {
+    Expr *num = a->expr(), *den = b->expr();
+    auto spreadOf = [](const Expr *e, ExprKind reduction) -> const Expr * {
+        if (e->kind != ExprKind::Spread || e->a->kind != ExprKind::Column || e->a->a->kind != reduction)
+            return nullptr;
+        return e->a->a->a;
+    };
+    if (num->kind != ExprKind::Exp || num->a->kind != ExprKind::Subtract)
+        return nullptr;
+    Expr *logits = num->a->a;
+    if (spreadOf(num->a->b, ExprKind::MaxAxis1) != logits || spreadOf(den, ExprKind::SumAxis1) != num)
+        return nullptr;
+    if (!isF32(logits) || logits->rank != 2 || logits->numel == 0)
+        return nullptr;
+    TensorObject *out = newTensor(TypeCode::Float32, shapeOf(a));
+    auto *dst         = static_cast<float *>(out->deviceData());
+    bool transposedLhs =
+        logits->kind == ExprKind::MatMul && logits->a->kind == ExprKind::Transpose && stillPending(logits->a);
+    if (logits->kind == ExprKind::MatMul && stillPending(logits) && !transposedLhs) {
+        ctn::evaluate(logits->a);
+        ctn::evaluate(logits->b);
+        ctn::ctCheck(ct_dense(f32(logits->a), f32(logits->b), nullptr, logits->rows, logits->a->cols, logits->cols,
+                              CT_ACT_SOFTMAX, dst, nullptr));
+    } else {
+        ctn::evaluate(logits);
+        ctn::ctCheck(ct_softmax_rows(f32(logits), logits->rows, logits->cols, dst));
+    }
+    return out;
+}
+
 // ---- generic bodies ----------------------------------------------------------------------
 
 slot_t binaryBody(ArgsView &norm, ct_binary_op op, bool lhsMustBeTensor) {
@@ -215,23 +306,18 @@ slot_t binaryBody(ArgsView &norm, ct_binary_op op, bool lhsMustBeTensor) {
             TensorObject *a = tensorArg(norm, 0), *b = tensorArg(norm, 1);
             if (!a->sameShape(b))
                 throw std::invalid_argument("Tensor binary operation requires matching shapes");
-            if (op == CT_MUL) {
-                // h * (h > 0) with the comparison still deferred: one relu kernel, same bits
-                auto reluOf = [](TensorObject *h, TensorObject *mask) {
-                    const auto *d = mask->deferred();
-                    return d && h->dtype() == TypeCode::Float32 && d->src == h->deviceData() && d->op == CT_GT &&
-                           d->tensorOnLeft && d->scalar == 0.0;
-                };
-                TensorObject *h = reluOf(a, b) ? a : (reluOf(b, a) ? b : nullptr);
-                if (h) {
-                    TensorObject *out = newTensor(TypeCode::Float32, shapeOf(h));
-                    ctn::ctCheck(ct_relu(static_cast<const float *>(h->deviceData()), h->numel(),
-                                         static_cast<float *>(out->deviceData())));
-                    return wrap(out);
-                }
+            if (op == CT_MUL || op == CT_SUB || op == CT_DIV) {
+                std::lock_guard<std::recursive_mutex> lock(ctn::exprMutex());
+                TensorObject *fused = op == CT_MUL ? tryRelu(a, b) : (op == CT_SUB ? tryScaledSub(a, b) : trySoftmax(a, b));
+                if (fused)
+                    return wrap(fused);
             }
             ct_dtype odt      = ct_result_dtype(op, a->ctDType(), b->ctDType());
             TensorObject *out = newTensor(ctn::fromCtDType(odt), shapeOf(a));
+            if (op == CT_SUB && a->dtype() == TypeCode::Float32 && b->dtype() == TypeCode::Float32) {
+                ctn::defer(out, ExprKind::Subtract, a, b); // `logits - row_max_broadcast` of the softmax idiom
+                return wrap(out);
+            }
             ctn::ctCheck(ct_binary(op, a->ctDType(), a->deviceData(), b->ctDType(), b->deviceData(), a->numel(),
                                    out->deviceData()));
             return wrap(out);
@@ -242,6 +328,10 @@ slot_t binaryBody(ArgsView &norm, ct_binary_op op, bool lhsMustBeTensor) {
         double s          = scalarValue(norm, si);
         ct_dtype odt      = lt ? ct_result_dtype(op, t->ctDType(), sdt) : ct_result_dtype(op, sdt, t->ctDType());
         TensorObject *out = newTensor(ctn::fromCtDType(odt), shapeOf(t));
+        if (op == CT_MUL && t->dtype() == TypeCode::Float32) {
+            ctn::defer(out, ExprKind::ScaleByScalar, t, nullptr, 0, s, sdt, lt ? 1 : 0); // `lr * g` of the update
+            return wrap(out);
+        }
         ctn::ctCheck(
             ct_binary_scalar(op, t->ctDType(), t->deviceData(), s, sdt, lt ? 0 : 1, t->numel(), out->deviceData()));
         return wrap(out);
@@ -268,7 +358,7 @@ slot_t compareBody(ArgsView &norm, ct_compare_op op, bool arraysAllowed) {
         TensorObject *t   = fetch(ti);
         double s          = scalarValue(norm, si);
         TensorObject *out = newTensor(TypeCode::Bool, shapeOf(t));
-        out->deferCompare(t, op, s, lt); // evaluated when the mask is first read (see device_tensor.h)
+        ctn::defer(out, ExprKind::CompareScalar, t, nullptr, op, s, CT_F32, lt ? 1 : 0); // `h > 0` of the relu idiom
         return wrap(out);
     });
 }
@@ -287,6 +377,10 @@ slot_t axisBody(ArgsView &norm, AxisKind kind, const char *name) {
         int64_t rows = t->dim(0), cols = t->dim(1);
         int64_t outShape[1] = {a == 0 ? cols : rows};
         TensorObject *out   = newTensor(kind == AxisKind::Argmax ? TypeCode::Int64 : TypeCode::Float32, outShape);
+        if (a == 1 && kind != AxisKind::Argmax && t->dtype() == TypeCode::Float32) {
+            ctn::defer(out, kind == AxisKind::Sum ? ExprKind::SumAxis1 : ExprKind::MaxAxis1, t); // softmax idiom
+            return wrap(out);
+        }
         ct_status s;
         if (kind == AxisKind::Sum)
             s = ct_sum_axis(t->ctDType(), t->deviceData(), rows, cols, a, static_cast<float *>(out->deviceData()));
@@ -299,10 +393,14 @@ slot_t axisBody(ArgsView &norm, AxisKind kind, const char *name) {
     });
 }
 
-slot_t fillBody(ArgsView &norm, TypeCode dtype, double value) {
+slot_t fillBody(ArgsView &norm, TypeCode dtype, double value, bool ones = false) {
     return guarded([&]() -> slot_t {
         auto shape        = shapeArg(norm, 0);
         TensorObject *out = newTensor(dtype, shape);
+        if (ones) {
+            ctn::defer(out, ExprKind::Ones, nullptr); // `v @ ones([1, k])` is how the programs broadcast
+            return wrap(out);
+        }
         ctn::ctCheck(ct_fill(out->ctDType(), value, out->numel(), out->deviceData()));
         return wrap(out);
     });
@@ -318,6 +416,10 @@ slot_t unaryBody(ArgsView &norm, const char *name, ct_status (*fn)(const float *
     return guarded([&]() -> slot_t {
         TensorObject *t   = requireFloat(tensorArg(norm, 0), name);
         TensorObject *out = newTensor(TypeCode::Float32, shapeOf(t));
+        if (fn == ct_exp) {
+            ctn::defer(out, ExprKind::Exp, t); // softmax idiom; exp raises no error
+            return wrap(out);
+        }
         ctn::ctCheck(fn(static_cast<const float *>(t->deviceData()), t->numel(), static_cast<float *>(out->deviceData())));
         return wrap(out);
     });
@@ -399,7 +501,7 @@ CT_OP(__tensor_exp__) { CT_UNUSED; return unaryBody(norm, "exp", ct_exp); }
 CT_OP(__tensor_log__) { CT_UNUSED; return unaryBody(norm, "log", ct_log); }
 CT_OP(__tensor_empty__) { CT_UNUSED; return fillBody(norm, TypeCode::Float32, 0.0); }
 CT_OP(__tensor_zeros__) { CT_UNUSED; return fillBody(norm, TypeCode::Float32, 0.0); }
-CT_OP(__tensor_ones__) { CT_UNUSED; return fillBody(norm, TypeCode::Float32, 1.0); }
+CT_OP(__tensor_ones__) { CT_UNUSED; return fillBody(norm, TypeCode::Float32, 1.0, true); }
 
 CT_OP(__tensor_full__) {
     CT_UNUSED;
@@ -526,6 +628,13 @@ CT_OP(__tensor_matmul__) {
             throw std::invalid_argument("matmul dimension mismatch");
         int64_t shape[2]  = {a->dim(0), b->dim(1)};
         TensorObject *out = newTensor(ctn::promoteTensorTypes(a->dtype(), b->dtype()), shape);
+        if (a->dtype() == TypeCode::Float32 && b->dtype() == TypeCode::Float32) {
+            // Deferred: multiply, divide and the readers decide whether it runs alone, with an
+            // activation in its epilogue, or without the transposed copy of its left operand.
+            bool spread = a->dim(1) == 1 && b->expr()->kind == ExprKind::Ones;
+            ctn::defer(out, spread ? ExprKind::Spread : ExprKind::MatMul, a, b);
+            return wrap(out);
+        }
         ctn::ctCheck(ct_matmul(a->ctDType(), a->deviceData(), b->ctDType(), b->deviceData(), a->dim(0), a->dim(1),
                                b->dim(1), out->deviceData()));
         return wrap(out);
@@ -540,7 +649,7 @@ CT_OP(__tensor_transpose__) {
             throw std::invalid_argument("transpose currently only supports rank-2 tensors");
         int64_t shape[2]  = {t->dim(1), t->dim(0)};
         TensorObject *out = newTensor(t->dtype(), shape);
-        ctn::ctCheck(ct_transpose(t->ctDType(), t->deviceData(), t->dim(0), t->dim(1), out->deviceData()));
+        ctn::defer(out, ExprKind::Transpose, t); // `transpose(X) @ G`: matmul reads X in place
         return wrap(out);
     });
 }
@@ -585,6 +694,10 @@ CT_OP(__tensor_reshape__) {
         if (n != t->numel())
             throw std::invalid_argument("reshape changes tensor element count");
         TensorObject *out = newTensor(t->dtype(), shape);
+        if (t->rank() == 1 && shape.size() == 2 && shape[1] == 1 && t->dtype() == TypeCode::Float32) {
+            ctn::defer(out, ExprKind::Column, t); // `reshape(row_max, [n, 1])` of the softmax idiom
+            return wrap(out);
+        }
         ctn::ctCheck(ct_d2d(out->deviceData(), t->deviceData(), t->byteSize())); // a copy, as in the reference
         return wrap(out);
     });

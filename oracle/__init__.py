@@ -296,51 +296,119 @@ class Reference:
         return [tuple(line.split("\t")) for line in buf.value.decode().splitlines() if line]
 
     def call(self, op: str, *args):
-        keep, cargs = [], (_Arg * len(args))()
-        for i, a in enumerate(args):
-            x = cargs[i]
-            in_with = isinstance(a, With)
-            if in_with:
-                a = a.value
-            if isinstance(a, np.ndarray):
-                arr, dt = norm(a)
-                shp = (C.c_int64 * max(1, arr.ndim))(*arr.shape)
-                keep += [arr, shp]
-                x.kind, x.dtype, x.rank, x.shape, x.data = 0, dt, arr.ndim, shp, arr.ctypes.data
-            elif isinstance(a, IntArray):
-                shp = (C.c_int64 * max(1, len(a.items)))(*a.items)
-                keep.append(shp)
-                x.kind, x.rank, x.shape = 6, len(a.items), shp
-            elif isinstance(a, (bool, np.bool_)):
-                x.kind, x.i64 = 5, int(a)
-            elif isinstance(a, (int, np.integer)):
-                x.kind, x.i64 = 1, int(a)
-            elif isinstance(a, Float32):
-                x.kind, x.f64 = 3, float(a)
-            elif isinstance(a, (float, np.floating)):
-                x.kind, x.f64 = 2, float(a)
-            else:
-                raise OracleError(f"unsupported argument {type(a)}")
-            if in_with:
-                x.kind |= 0x100
+        keep, cargs = _marshal(args)
         out, err = _Out(), C.create_string_buffer(512)
         rc = self.lib.camel_ref_call(op.encode(), len(args), cargs, C.byref(out), err, 512)
         if rc:
             raise OracleError(err.value.decode())
         self.last_seconds = out.seconds
-        if out.kind == 1:
-            return out.f64
-        if out.kind == 2:
-            return [out.shape[i] for i in range(out.rank)]
-        if out.kind == 3:
-            return None
-        shp = tuple(out.shape[i] for i in range(out.rank))
-        n = int(out.numel)
-        dt = _NP[out.dtype]
-        if n == 0:
-            return np.zeros(shp, dt)
-        buf = (C.c_char * (n * np.dtype(dt).itemsize)).from_address(out.data)
-        return np.frombuffer(buf, dtype=dt).reshape(shp).copy()
+        return _unmarshal(out)
+
+    def session(self, lazy: bool | None = None) -> "Session":
+        """A chain of operator calls whose values stay inside the library (the plugin's harness
+        only; the reference is driven call by call, which is the same thing for host tensors)."""
+        return Session(self.lib, lazy)
+
+
+class Handle:
+    """A value an earlier call of a Session returned."""
+
+    def __init__(self, index: int):
+        self.index = index
+
+
+def _marshal(args):
+    keep, cargs = [], (_Arg * max(1, len(args)))()
+    for i, a in enumerate(args):
+        x = cargs[i]
+        in_with = isinstance(a, With)
+        if in_with:
+            a = a.value
+        if isinstance(a, Handle):
+            x.kind, x.i64 = 7, a.index
+        elif isinstance(a, np.ndarray):
+            arr, dt = norm(a)
+            shp = (C.c_int64 * max(1, arr.ndim))(*arr.shape)
+            keep += [arr, shp]
+            x.kind, x.dtype, x.rank, x.shape, x.data = 0, dt, arr.ndim, shp, arr.ctypes.data
+        elif isinstance(a, IntArray):
+            shp = (C.c_int64 * max(1, len(a.items)))(*a.items)
+            keep.append(shp)
+            x.kind, x.rank, x.shape = 6, len(a.items), shp
+        elif isinstance(a, (bool, np.bool_)):
+            x.kind, x.i64 = 5, int(a)
+        elif isinstance(a, (int, np.integer)):
+            x.kind, x.i64 = 1, int(a)
+        elif isinstance(a, Float32):
+            x.kind, x.f64 = 3, float(a)
+        elif isinstance(a, (float, np.floating)):
+            x.kind, x.f64 = 2, float(a)
+        else:
+            raise OracleError(f"unsupported argument {type(a)}")
+        if in_with:
+            x.kind |= 0x100
+    return keep, cargs
+
+
+def _unmarshal(out: "_Out"):
+    if out.kind == 1:
+        return out.f64
+    if out.kind == 2:
+        return [out.shape[i] for i in range(out.rank)]
+    if out.kind == 3:
+        return None
+    shp = tuple(out.shape[i] for i in range(out.rank))
+    n = int(out.numel)
+    dt = _NP[out.dtype]
+    if n == 0:
+        return np.zeros(shp, dt)
+    buf = (C.c_char * (n * np.dtype(dt).itemsize)).from_address(out.data)
+    return np.frombuffer(buf, dtype=dt).reshape(shp).copy()
+
+
+class Session:
+    """Drives camel_host_session_* of the plugin's harness: `put` uploads a tensor, `call` runs an
+    operator on handles and plain arguments and returns the handle of its value, `fetch` reads a
+    value back, `finish` has a value computed and waits, returning the library's launch count.
+    Starting a session releases everything earlier calls created."""
+
+    def __init__(self, lib, lazy: bool | None = None):
+        self.lib = lib
+        lib.camel_host_session_finish.restype = C.c_int64
+        lib.camel_host_session_finish.argtypes = [C.c_int64, C.c_char_p, C.c_int]
+        lib.camel_host_session_fetch.argtypes = [C.c_int64, C.POINTER(_Out), C.c_char_p, C.c_int]
+        lib.camel_host_session_pending.argtypes = [C.c_int64]
+        lib.camel_host_session_begin(-1 if lazy is None else int(lazy))
+
+    def put(self, value) -> Handle:
+        keep, cargs = _marshal((value,))
+        h, err = C.c_int64(-1), C.create_string_buffer(512)
+        if self.lib.camel_host_session_put(cargs, C.byref(h), err, 512):
+            raise OracleError(err.value.decode())
+        return Handle(h.value)
+
+    def call(self, op: str, *args) -> Handle:
+        keep, cargs = _marshal(args)
+        h, err = C.c_int64(-1), C.create_string_buffer(512)
+        if self.lib.camel_host_session_call(op.encode(), len(args), cargs, C.byref(h), err, 512):
+            raise OracleError(err.value.decode())
+        return Handle(h.value)
+
+    def fetch(self, handle: Handle):
+        out, err = _Out(), C.create_string_buffer(512)
+        if self.lib.camel_host_session_fetch(handle.index, C.byref(out), err, 512):
+            raise OracleError(err.value.decode())
+        return _unmarshal(out)
+
+    def finish(self, handle: Handle | None = None) -> int:
+        err = C.create_string_buffer(512)
+        n = self.lib.camel_host_session_finish(-1 if handle is None else handle.index, err, 512)
+        if n < 0:
+            raise OracleError(err.value.decode())
+        return n
+
+    def pending(self, handle: Handle) -> bool:
+        return self.lib.camel_host_session_pending(handle.index) == 1
 
 
 _port = None

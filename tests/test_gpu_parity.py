@@ -213,7 +213,10 @@ def test_dense_split_k(T):
 
 @pytest.mark.parametrize("m,k,n,act", [(300, 1000, 10, "softmax"), (257, 36, 7, "relu"), (1024, 1024, 10, "softmax"),
                                        (4096, 128, 10, "softmax"), (512, 2048, 16, None), (260, 40, 1, None),
-                                       (512, 1100, 3, "softmax")])
+                                       (512, 1100, 3, "softmax"),
+                                       # k not a multiple of four: rows at any 4-byte address (784 features + bias column)
+                                       (4096, 785, 10, "softmax"), (300, 33, 10, None), (1000, 1023, 16, "relu"),
+                                       (257, 509, 5, "softmax"), (256, 34, 2, None)])
 def test_dense_few_columns_row_tiled(T, m, k, n, act):
     """Classifier-layer shapes (n <= 16, many rows): float64 accumulation, so logits agree with
     float64-matmul-rounded-once to the last bit except where the summation order shows (<= 1 ulp),
@@ -590,6 +593,45 @@ def test_training_step_fused_forms(T):
         T.check_async()
         host = w - (g.astype(np.float64) * lr).astype(np.float32)
         assert got.tobytes() == chain.tobytes() == host.tobytes()
+
+
+@pytest.mark.parametrize("k,m,n", [
+    (2048, 785, 10), (60000, 785, 10), (5000, 33, 1), (31, 1000, 2), (4097, 129, 9), (700, 12544, 10),
+    (1500, 300, 16), (999, 257, 17), (640, 64, 24), (333, 100, 25), (20000, 40, 32), (1, 7, 3),
+])
+def test_matmul_tn_few_columns(T, k, m, n):
+    """transpose(X) @ G with n <= 32 (the gradient of a classifier, mnist.cml:39) reads X in place:
+    float64 products and sums as in the reference, so the float32 result is the correctly rounded
+    one except where the summation order moves a float64 sum across a rounding boundary."""
+    rng = np.random.default_rng(k + m + n)
+    a = rng.uniform(-1, 1, (k, m)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    got = T.matmul_tn(T.from_numpy(a), T.from_numpy(b)).numpy()
+    T.check_async()
+    ref = (a.T.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+    assert got.shape == (m, n)
+    d = ulp_distance(got, ref)
+    assert d.max() <= 1 and np.mean(d == 0) >= 0.999, (int(d.max()), float(np.mean(d == 0)))
+    if k * m * n <= 3_000_000:  # the restatement itself, k ascending (operators.cpp:757-766)
+        port = oracle.port().matmul(np.ascontiguousarray(a.T), b)
+        assert np.mean(got == port) >= 0.999 and ulp_distance(got, port).max() <= 1
+
+
+def test_matmul_with_one_inner_element_is_exact(T):
+    """k == 1: one product per output, rounded once - bit-exact, also for wide outputs, where
+    larger k goes to the split-precision tensor-core kernel.  The reference's programs broadcast
+    a column with it (`v @ ones([1, k])`, mnist.cml:18)."""
+    rng = np.random.default_rng(3)
+    for m, n in ((64, 5000), (4096, 1000), (300, 33), (7, 130), (1000, 8)):
+        v = (rng.standard_normal((m, 1)) * 100).astype(np.float32)
+        v[0, 0] = -0.0
+        w = rng.standard_normal((1, n)).astype(np.float32)
+        ones = np.ones((1, n), np.float32)
+        assert T.matmul(T.from_numpy(v), T.from_numpy(ones)).numpy().tobytes() == (np.repeat(v, n, 1) + 0.0).tobytes()
+        got = T.matmul(T.from_numpy(v), T.from_numpy(w)).numpy()
+        ref = (0.0 + v.astype(np.float64) * w.astype(np.float64)).astype(np.float32)
+        assert got.tobytes() == ref.tobytes()
+    T.check_async()
 
 
 def test_dlpack_zero_copy_with_torch(T):

@@ -169,34 +169,3 @@ def test_plugin_dlpack_device_export_and_import():
     rc = lib.camel_host_dlpack_roundtrip(a.ctypes.data, 37, 19, out.ctypes.data, err, 512)
     assert rc == 0, (rc, err.value.decode())
     assert out.tobytes() == a.tobytes()
-
-
-@needs_build
-@pytest.mark.gpu
-def test_plugin_relu_idiom_runs_as_one_kernel():
-    """`h * (h > 0)` (test/run/nn/svm.cml:31): the comparison stays unevaluated, multiply runs relu,
-    and both the product and the mask (read afterwards) equal the two-operator chain; any other
-    threshold evaluates the mask inside multiply."""
-    import ctypes as C
-
-    from test_gpu_parity import canonical_nan
-
-    lib = C.CDLL(str(HARNESS))
-    fn = lib.camel_host_relu_idiom
-    fn.restype = C.c_int
-    fn.argtypes = [C.c_void_p, C.c_int64, C.c_double, C.c_int, C.c_void_p, C.c_void_p, C.c_char_p, C.c_int]
-    rng = np.random.default_rng(31)
-    h = rng.standard_normal(100_003).astype(np.float32)
-    h[:8] = [0.0, -0.0, np.nan, np.inf, -np.inf, 1e-45, -1e-45, 3.0]
-    p = oracle.port()
-    for threshold, mask_first, fused in ((0.0, 0, 1), (0.0, 1, 1), (0.5, 0, 0)):
-        prod = np.empty_like(h)
-        mask = np.empty(h.size, np.uint8)
-        err = C.create_string_buffer(512)
-        rc = fn(h.ctypes.data, h.size, threshold, mask_first, prod.ctypes.data, mask.ctypes.data, err, 512)
-        assert rc == fused, (rc, err.value.decode())
-        ref_mask = p.compare(oracle.GT, h, threshold)
-        ref = p.binary(oracle.MUL, ref_mask, h) if mask_first else p.binary(oracle.MUL, h, ref_mask)
-        assert mask.tobytes() == ref_mask.tobytes()
-        # NaN payloads are the host's or the device's own, as for every operator
-        assert canonical_nan(prod).tobytes() == canonical_nan(ref).tobytes()
