@@ -567,68 +567,171 @@ ct_status matmul_generic(
 // equal at n = 10.
 constexpr int kTnThreads = 128;
 constexpr int kTnChunk   = 32; // rows of b staged per step
+constexpr int kTnGroup   = 4;  // k steps whose operands are fetched together, one group ahead
 
-template <int NMAX, int R>
-__global__ void __launch_bounds__(kTnThreads, 4) gemm_tn_skinny_kernel(
-    const float *__restrict__ a_km, const float *__restrict__ b, int64_t m, int64_t k, int n, int64_t k_per_slice,
-    double *__restrict__ partial) {
-    __shared__ double bs[kTnChunk][NMAX];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t row0 = ((int64_t)blockIdx.x * (kTnThreads / 32) + warp) * (32 * R) + lane;
-    const int64_t k0 = (int64_t)blockIdx.y * k_per_slice;
-    const int64_t k1 = k0 + k_per_slice < k ? k0 + k_per_slice : k;
-    double acc[R][NMAX];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int j = 0; j < NMAX; ++j)
-            acc[r][j] = 0.0;
-    for (int64_t kc = k0; kc < k1; kc += kTnChunk) {
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < kTnChunk * NMAX; idx += kTnThreads) {
-            int kk = idx / NMAX, j = idx - kk * NMAX;
-            bs[kk][j] = (kc + kk < k1 && j < n) ? (double)b[(kc + kk) * n + j] : 0.0;
-        }
-        __syncthreads();
-        const int kn = k1 - kc < kTnChunk ? (int)(k1 - kc) : kTnChunk;
-#pragma unroll 8
-        for (int kk = 0; kk < kn; ++kk) {
-            const float *arow = a_km + (kc + kk) * m;
-            double av[R];
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-                av[r] = row0 + 32 * r < m ? (double)arow[row0 + 32 * r] : 0.0;
-#pragma unroll
-            for (int j = 0; j < NMAX; ++j) {
-                double bj = bs[kk][j];
-#pragma unroll
-                for (int r = 0; r < R; ++r)
-                    acc[r][j] = fma(av[r], bj, acc[r][j]);
-            }
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        int64_t row = row0 + 32 * r;
-        if (row < m) {
-            double *dst = partial + ((int64_t)blockIdx.y * m + row) * n;
-#pragma unroll
-            for (int j = 0; j < NMAX; ++j)
-                if (j < n)
-                    dst[j] = acc[r][j];
-        }
-    }
+template <int V> struct TnCount {
+    static constexpr int value = V;
+};
+
+// A read-only load that stays where it is written: the compiler may otherwise move a plain load
+// down to its first use, which undoes fetching the operands a group ahead.  0 where !ok.
+__device__ __forceinline__ float tn_load_early(const float *p, bool ok) {
+    float v;
+    asm volatile(
+        "{ .reg .pred q; setp.ne.u32 q, %2, 0; mov.f32 %0, 0f00000000; @q ld.global.nc.f32 %0, [%1]; }"
+        : "=f"(v)
+        : "l"(p), "r"((unsigned)ok));
+    return v;
 }
 
+__device__ __forceinline__ void tn_block_barrier() {
+    // a named barrier counts arriving threads, wherever in the code they arrive from: the warps of a
+    // block run differently specialised copies of the loop below
+    asm volatile("bar.sync 1, %0;" ::"n"(kTnThreads) : "memory");
+}
+
+template <int NMAX, int R>
+__global__ void __launch_bounds__(kTnThreads, 2) gemm_tn_skinny_kernel(
+    const float *__restrict__ a_km, const float *__restrict__ b, int64_t m, int64_t k, int n, int64_t k_per_slice,
+    double *__restrict__ partial) {
+    constexpr int G  = kTnGroup;
+    constexpr int BL = (kTnChunk * NMAX + kTnThreads - 1) / kTnThreads; // staged b values per thread
+    __shared__ double bs[2][kTnChunk][NMAX];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t warp_row = ((int64_t)blockIdx.x * (kTnThreads / 32) + warp) * (32 * R);
+    const int64_t row0     = warp_row + lane;
+    // 32-row groups of this warp that hold rows at all: the others cost no loads and no arithmetic
+    const int64_t left = m - warp_row;
+    const int ractive  = left <= 0 ? 0 : (left >= 32 * R ? R : (int)((left + 31) / 32));
+    const int64_t k0   = (int64_t)blockIdx.y * k_per_slice;
+    const int64_t k1   = k0 + k_per_slice < k ? k0 + k_per_slice : k;
+
+    float bnext[BL];
+    auto fetch_b = [&](int64_t kc) {
+#pragma unroll
+        for (int u = 0; u < BL; ++u) {
+            int idx = threadIdx.x + u * kTnThreads;
+            int kk = idx / NMAX, j = idx - kk * NMAX;
+            bnext[u] = (idx < kTnChunk * NMAX && kc + kk < k1 && j < n) ? __ldg(b + (kc + kk) * n + j) : 0.0f;
+        }
+    };
+    auto store_b = [&](int buf) {
+#pragma unroll
+        for (int u = 0; u < BL; ++u) {
+            int idx = threadIdx.x + u * kTnThreads;
+            if (idx < kTnChunk * NMAX)
+                (&bs[buf][0][0])[idx] = (double)bnext[u];
+        }
+    };
+
+    auto run = [&](auto count) {
+        constexpr int RA = decltype(count)::value; // 32-row groups this warp computes
+        constexpr int RN = RA > 0 ? RA : 1;
+        double acc[RN][NMAX];
+#pragma unroll
+        for (int r = 0; r < RN; ++r)
+#pragma unroll
+            for (int j = 0; j < NMAX; ++j)
+                acc[r][j] = 0.0;
+        bool rowok[RN];
+#pragma unroll
+        for (int r = 0; r < RN; ++r)
+            rowok[r] = row0 + 32 * r < m;
+        // operands of G k steps are fetched one group ahead of their use, into two register sets
+        float abuf[2][G][RN];
+        const float *pa = a_km + k0 * m + row0; // row `next` of the operand, this lane's first column
+        int64_t next    = k0;
+        auto fetch_a    = [&](float(&dst)[G][RN]) {
+            if (RA > 0) {
+#pragma unroll
+                for (int u = 0; u < G; ++u)
+#pragma unroll
+                    for (int r = 0; r < RN; ++r)
+                        dst[u][r] = tn_load_early(pa + u * m + 32 * r, next + u < k1 && rowok[r]);
+                pa += G * m;
+                next += G;
+            }
+        };
+        auto compute = [&](const float(&src)[G][RN], int buf, int g) {
+            if (RA > 0) {
+#pragma unroll
+                for (int u = 0; u < G; ++u) {
+                    double av[RN];
+#pragma unroll
+                    for (int r = 0; r < RN; ++r)
+                        av[r] = (double)src[u][r];
+#pragma unroll
+                    for (int j = 0; j < NMAX; ++j) {
+                        double bj = bs[buf][g + u][j];
+#pragma unroll
+                        for (int r = 0; r < RN; ++r)
+                            acc[r][j] = fma(av[r], bj, acc[r][j]);
+                    }
+                }
+            }
+        };
+        fetch_b(k0);
+        fetch_a(abuf[0]);
+        store_b(0);
+        tn_block_barrier();
+        int buf = 0;
+        for (int64_t kc = k0; kc < k1; kc += kTnChunk, buf ^= 1) {
+            const bool more = kc + kTnChunk < k1;
+            if (more)
+                fetch_b(kc + kTnChunk);
+#pragma unroll 1
+            for (int g = 0; g < kTnChunk; g += 2 * G) {
+                fetch_a(abuf[1]);
+                compute(abuf[0], buf, g);
+                fetch_a(abuf[0]); // may already belong to the next chunk; zeros past the slice
+                compute(abuf[1], buf, g + G);
+            }
+            if (more)
+                store_b(buf ^ 1); // nobody reads that buffer any more: all warps passed the last barrier
+            tn_block_barrier();
+        }
+        if (RA > 0) {
+#pragma unroll
+            for (int r = 0; r < RN; ++r) {
+                if (rowok[r]) {
+                    double *dst = partial + ((int64_t)blockIdx.y * m + row0 + 32 * r) * n;
+#pragma unroll
+                    for (int j = 0; j < NMAX; ++j)
+                        if (j < n)
+                            dst[j] = acc[r][j];
+                }
+            }
+        }
+    };
+    static_assert(R == 1 || R == 2 || R == 4, "row groups per warp");
+    if (ractive == R)
+        run(TnCount<R>{});
+    else if (ractive == 0)
+        run(TnCount<0>{});
+    else if (R == 4 && ractive == 3)
+        run(TnCount<(R == 4 ? 3 : 1)>{});
+    else if (R == 4 && ractive == 2)
+        run(TnCount<(R == 4 ? 2 : 1)>{});
+    else
+        run(TnCount<1>{});
+}
+
+// One warp per output element: lane l adds the slices l, l + 32, ... in that order, then the lanes'
+// sums are added in a fixed butterfly - the same order on every run.
 __global__ void __launch_bounds__(256) gemm_tn_skinny_finish_kernel(
     const double *__restrict__ partial, int64_t mn, int slices, float *__restrict__ out) {
-    int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int lane  = threadIdx.x & 31;
+    const int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) >> 5;
     if (i >= mn)
         return;
     double sum = 0.0;
-    for (int s = 0; s < slices; ++s)
+    for (int s = lane; s < slices; s += 32)
         sum += partial[(int64_t)s * mn + i];
-    out[i] = (float)sum;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1)
+        sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    if (lane == 0)
+        out[i] = (float)sum;
 }
 
 template <int NMAX, int R>
@@ -636,7 +739,8 @@ static ct_status launch_tn_skinny(
     DeviceState *st, const float *a_km, const float *b, int64_t m, int64_t k, int n, float *out) {
     const int64_t rows_per_block = (int64_t)(kTnThreads / 32) * 32 * R;
     const int64_t mblocks        = (m + rows_per_block - 1) / rows_per_block;
-    int64_t slices               = (4 * (int64_t)st->sm_count + mblocks - 1) / mblocks; // four blocks per SM
+    // one wave: two blocks fit an SM, and rounding the slice length up only takes blocks away
+    int64_t slices = 2 * (int64_t)st->sm_count / mblocks;
     const int64_t most           = (k + 4 * kTnChunk - 1) / (4 * kTnChunk); // at least four chunks per slice
     if (slices > most)
         slices = most;
@@ -655,7 +759,7 @@ static ct_status launch_tn_skinny(
     gemm_tn_skinny_kernel<NMAX, R><<<grid, kTnThreads, 0, stream()>>>(a_km, b, m, k, n, k_per_slice, partial);
     CT_LAUNCH_CHECK("gemm_tn_skinny");
     const int64_t mn = m * n;
-    gemm_tn_skinny_finish_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, stream()>>>(partial, mn, (int)slices, out);
+    gemm_tn_skinny_finish_kernel<<<(unsigned)((mn * 32 + 255) / 256), 256, 0, stream()>>>(partial, mn, (int)slices, out);
     CT_LAUNCH_CHECK("gemm_tn_skinny_finish");
     return CT_OK;
 }
@@ -673,14 +777,14 @@ ct_status gemm_f32_tn_skinny(
     case 3: return launch_tn_skinny<6, 4>(st, a_km, b, m, k, (int)n, out);
     case 4: return launch_tn_skinny<8, 4>(st, a_km, b, m, k, (int)n, out);
     case 5: return launch_tn_skinny<10, 4>(st, a_km, b, m, k, (int)n, out);
-    case 6: return launch_tn_skinny<12, 4>(st, a_km, b, m, k, (int)n, out);
-    case 7: return launch_tn_skinny<14, 4>(st, a_km, b, m, k, (int)n, out);
-    case 8: return launch_tn_skinny<16, 4>(st, a_km, b, m, k, (int)n, out);
+    case 6: return launch_tn_skinny<12, 2>(st, a_km, b, m, k, (int)n, out);
+    case 7: return launch_tn_skinny<14, 2>(st, a_km, b, m, k, (int)n, out);
+    case 8: return launch_tn_skinny<16, 2>(st, a_km, b, m, k, (int)n, out);
     default: break;
     }
     if (n <= 24)
-        return launch_tn_skinny<24, 2>(st, a_km, b, m, k, (int)n, out);
-    return launch_tn_skinny<32, 2>(st, a_km, b, m, k, (int)n, out);
+        return launch_tn_skinny<24, 1>(st, a_km, b, m, k, (int)n, out);
+    return launch_tn_skinny<32, 1>(st, a_km, b, m, k, (int)n, out);
 }
 
 ct_status gemm_f32_skinny(
