@@ -408,7 +408,9 @@ __global__ void __launch_bounds__(32 * kSkinnyWarps, 1) gemm_skinny_tile_kernel(
         for (int u = 0; u < kLoads; ++u) {
             int i = base + u * 32;
             if (i < total) {
-                int kk = i / n, j = i - kk * n;
+                // n is NE or NE - 1: divisions by constants instead of one by a run-time value
+                int kk = n == NE ? i / NE : i / (NE > 1 ? NE - 1 : 1);
+                int j  = i - kk * n;
                 ws[kk * NE + j] = (double)tmp[u];
             }
         }
@@ -426,9 +428,14 @@ __global__ void __launch_bounds__(32 * kSkinnyWarps, 1) gemm_skinny_tile_kernel(
             // k is not a multiple of four (784 features and a bias column): rows start at any
             // 4-byte address, so a warp copies the 32 floats of a row's chunk one per lane
             const int kk = c * 32 + lane;
-            if (kk < klen)
-                for (int r = 0; r < 32 && row0 + r < m; ++r)
-                    cp_async_4(xs + r * xs_stride + kk, x + (row0 + r) * k + k0 + kk);
+            if (kk < klen) {
+                const float *src = x + row0 * k + k0 + kk;
+                float *dst       = xs + kk;
+                const int rows   = m - row0 < 32 ? (int)(m - row0) : 32;
+#pragma unroll 4
+                for (int r = 0; r < rows; ++r, src += k, dst += xs_stride)
+                    cp_async_4(dst, src);
+            }
         }
         cp_async_commit();
     }
