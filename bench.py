@@ -434,7 +434,6 @@ class ShardedGemmWorkload(Workload):
     on a side stream so that panel j travels while panel j+1 is computed.  Strong scaling."""
 
     name, metric, unit, scaling = "gemm_sharded", "gemm_fp32_tflops", "TFLOP/s", "strong"
-    PANELS = 4
 
     def __init__(self, torch, dist, T, n, world, rank):
         self.torch, self.dist, self.T, self.n, self.world, self.rank = torch, dist, T, n, world, rank
@@ -445,37 +444,54 @@ class ShardedGemmWorkload(Workload):
         self.b_t = torch.rand((n, n), generator=g, device=dev, dtype=torch.float32) * 2 - 1
         from camel_b200 import sharding
         self.sharding = sharding
-        self.row0, self.rows = sharding.row_shard(n, world, rank)
-        self.a_t = a_full[self.row0:self.row0 + self.rows].contiguous()
+        _, self.rows = sharding.row_shard(n, world, rank)
+        # panel j travels while panel j+1 is computed, so only the last gather is exposed: the panels
+        # halve down to 256 rows (two row tiles; the early ones stay large enough to fill the GPU).
+        # Rows are dealt out band by band (band j = panel j of every rank), so that a gathered panel
+        # is one contiguous piece of C and its all-gather runs in place, without a staging copy.
+        plan = sharding.tapered_panel_plan(self.rows) if world > 1 else [(0, self.rows)]
+        self.bands = sharding.banded_rows(plan, world, rank)
+        self.panels = len(plan)
+        self.a_t = torch.cat([a_full[g0:g0 + cnt] for _, cnt, g0, _ in self.bands]).contiguous()
+        # a few rows of A from all over the matrix, to check the gathered product once (first warm-up step)
+        self.check_rows = torch.arange(7, n, n // 24, device=dev)[:24]
+        self.check_a = a_full[self.check_rows].double()
+        self.checked = False
         del a_full
         self.c_t = torch.empty((n, n), device=dev, dtype=torch.float32)  # the gathered product
-        # panels of at least 1024 rows: smaller GEMMs leave the last wave of tiles mostly empty
-        self.panels = max(1, min(self.PANELS, self.rows // 1024)) if world > 1 else 1
-        self.plan = sharding.panel_plan(self.rows, self.panels)
         # B is placed once: so is its tensor-core layout (transposed hi/lo planes), outside the timed region
         import ctypes as C
         from camel_b200._lib import check, lib
         self.b_packed = C.c_void_p()
         check(lib.ct_weights_pack(self.b_t.data_ptr(), n, n, C.byref(self.b_packed)))
+        self.a_packed = C.c_void_p()  # planes of this rank's rows of A: refilled every step, allocated once
         self.side = torch.cuda.Stream()
         torch.cuda.synchronize()
         self.h2d = self.d2h = 0
 
     def step(self):
+        import ctypes as C
         from camel_b200._lib import check, lib
         torch, n = self.torch, self.n
-        for off, pr in self.plan:
-            a_ptr = self.a_t.data_ptr() + off * n * 4
-            c_ptr = self.c_t.data_ptr() + (self.row0 + off) * n * 4
-            check(lib.ct_dense_packed(a_ptr, self.b_t.data_ptr(), self.b_packed, None, pr, n, n, 0, c_ptr, None))
+        check(lib.ct_rows_pack(self.a_t.data_ptr(), self.rows, n, C.byref(self.a_packed)))
+        for off, cnt, g0, band0 in self.bands:
+            check(lib.ct_matmul_packed_rows(self.a_packed, off, cnt, self.b_packed, self.c_t.data_ptr() + g0 * n * 4))
             if self.world > 1:
                 done = torch.cuda.Event()
                 done.record()
                 with torch.cuda.stream(self.side):
                     self.side.wait_event(done)
-                    self.sharding.gather_panel(self.dist, self.c_t, self.rows, off, pr, self.rank, self.world)
+                    self.sharding.gather_band(self.dist, self.c_t, band0, cnt, self.rank, self.world)
         if self.world > 1:
             torch.cuda.current_stream().wait_stream(self.side)
+        if not self.checked:  # untimed: the first warm-up step
+            self.checked = True
+            torch.cuda.synchronize()
+            ref = self.check_a @ self.b_t.double()
+            err = float((self.c_t[self.check_rows].double() - ref).abs().max() / ref.abs().max())
+            if not err <= 1e-5:
+                raise RuntimeError(f"gemm_sharded: gathered product is off by {err:.3e} of its largest entry on rank {self.rank}")
+            del ref, self.check_a
 
     def e2e_step(self):
         self.step()
@@ -491,7 +507,7 @@ class ShardedGemmWorkload(Workload):
 
     def config(self):
         return {"workload": f"gemm fp32 M=N=K={self.n}, A row-sharded over {self.world} ranks, C all-gathered "
-                            f"in {self.panels} row panels overlapped with compute, B and its tensor-core layout "
+                            f"in place in {self.panels} bands of halving size overlapped with compute, B and its tensor-core layout "
                             f"placed once (BASELINE configs[4])",
                 "precision": "3xtf32", "e2e": "same as value: operands are resident by construction",
                 "parallelism": f"{self.world} ranks, rows of A and C sharded, NCCL all-gather of C on a side stream"}

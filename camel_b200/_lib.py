@@ -85,6 +85,9 @@ PROTOTYPES = {
     "ct_dense": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),
     "ct_weights_pack": (_int, [_vp, _i64, _i64, C.POINTER(_vp)]),
     "ct_weights_free": (_int, [_vp]),
+    "ct_rows_pack": (_int, [_vp, _i64, _i64, C.POINTER(_vp)]),
+    "ct_rows_free": (_int, [_vp]),
+    "ct_matmul_packed_rows": (_int, [_vp, _i64, _i64, _vp, _vp]),
     "ct_dense_packed": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),
     "ct_conv2d": (_int, [_vp, _vp, _vp] + [_i64] * 9 + [_int, _vp]),
     "ct_conv2d_maxpool2": (_int, [_vp, _vp, _vp] + [_i64] * 9 + [_int, _vp]),

@@ -1465,6 +1465,9 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(
 } // namespace
 
 // Contraction over prepared operand planes: out[z][m][n] = act(A[m][kp] . B[z][n][kp]^T + bias).
+// set (under the entry point's lock) while a product that must not touch the shared split-K workspace is enqueued
+static bool g_no_splitk = false;
+
 ct_status gemm_planes(
     DeviceState *st, int mode, const void *a_hi, const void *a_lo, const void *b_hi,
     const void *b_lo, int64_t m, int64_t n, int64_t kp, const float *bias, int act, float *out,
@@ -1492,7 +1495,7 @@ ct_status gemm_planes(
         wide = conv->th * conv->wo > 128;
     // Few output tiles and a long reduction (e.g. a 12544 -> 128 layer): slice k across CTAs so
     // that the whole machine works, partial sums in a workspace, one pass to add them up.
-    if (!conv && batch == 1 && !bias_per_row && !getenv("CAMEL_TENSOR_NO_SPLITK")) {
+    if (!conv && batch == 1 && !bias_per_row && !g_no_splitk && !getenv("CAMEL_TENSOR_NO_SPLITK")) {
         const int kblock  = mode == MODE_3X ? 32 : 64;
         const int nkb     = (int)(kp / kblock);
         int64_t tiles     = ((m + BM - 1) / BM) * ((n + (wide ? 255 : 127)) / (wide ? 256 : 128));
@@ -1709,6 +1712,98 @@ extern "C" ct_status ct_weights_free(void *packed) {
     ct_status st = ct_free(pw->base);
     delete pw;
     return st;
+}
+
+// ---- packed left operand: split once, multiply row panels ------------------------------------
+//
+// A product whose rows are computed in several calls (the row panels of a sharded product, each
+// all-gathered while the next is computed) should not pay one launch of the operand pre-pass per
+// panel, and - since that pre-pass writes the library's one cached workspace - could not run two
+// panels at the same time.  ct_rows_pack splits the whole left operand once into planes of its
+// own; ct_matmul_packed_rows multiplies a row range of them with packed weights and touches no
+// shared workspace, so panels enqueued on different streams fill each other's last, partly empty
+// wave of tiles.
+struct PackedRows {
+    uint32_t magic;
+    int mode;
+    int device;
+    int64_t m, k, kp;
+    void *base;
+    uint8_t *hi, *lo;
+    size_t row_bytes; // bytes of one row of a plane
+};
+constexpr uint32_t kPackedRowsMagic = 0x43545052u; // "CTPR"
+
+extern "C" ct_status ct_rows_pack(const float *a, int64_t m, int64_t k, void **packed_inout) {
+    OpLock op_lock;
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (!packed_inout)
+        return fail(CT_ERR_INVALID, "ct_rows_pack: packed_inout is null");
+    if (m <= 0 || k <= 0 || !a)
+        return fail(CT_ERR_INVALID, "ct_rows_pack: empty or null matrix");
+    if (m > kMaxDim || k > kMaxDim)
+        return fail(CT_ERR_TOO_LARGE, "ct_rows_pack: dimension too large");
+    const int mode   = ct_get_precision() == CT_PREC_BF16 ? MODE_BF : MODE_3X;
+    const int elem   = mode == MODE_3X ? 4 : 2;
+    const int planes = mode == MODE_3X ? 2 : 1;
+    const int kblock = ROW_B / elem;
+    const int64_t kp = (k + kblock - 1) / kblock * kblock;
+    int dev = -1;
+    CT_CUDA(cudaGetDevice(&dev));
+    PackedRows *pr = static_cast<PackedRows *>(*packed_inout);
+    if (pr && (pr->magic != kPackedRowsMagic || pr->mode != mode || pr->m != m || pr->k != k || pr->device != dev))
+        return fail(CT_ERR_INVALID, "ct_rows_pack: the handle belongs to another shape, precision or device");
+    if (!pr) {
+        const size_t plane = ((size_t)m * kp * elem + 1023) & ~(size_t)1023;
+        void *base         = nullptr;
+        CT_TRY(ct_alloc(&base, plane * planes));
+        uint8_t *hi = static_cast<uint8_t *>(base);
+        pr          = new PackedRows{kPackedRowsMagic, mode, dev, m, k, kp, base, hi, hi + plane, (size_t)kp * elem};
+        *packed_inout = pr;
+    }
+    ProfScope prof("gemm_prepass");
+    return split_rows_planes(st, mode, a, m, k, kp, pr->hi, pr->lo);
+}
+
+extern "C" ct_status ct_rows_free(void *packed) {
+    if (!packed)
+        return CT_OK;
+    PackedRows *pr = static_cast<PackedRows *>(packed);
+    if (pr->magic != kPackedRowsMagic)
+        return fail(CT_ERR_INVALID, "ct_rows_free: not a packed-rows handle");
+    pr->magic    = 0;
+    ct_status st = ct_free(pr->base);
+    delete pr;
+    return st;
+}
+
+extern "C" ct_status ct_matmul_packed_rows(
+    const void *a_packed, int64_t row0, int64_t rows, const void *w_packed, float *out) {
+    OpLock op_lock;
+    DeviceState *st;
+    CT_TRY(current(&st));
+    const PackedRows *pr    = static_cast<const PackedRows *>(a_packed);
+    const PackedWeights *pw = static_cast<const PackedWeights *>(w_packed);
+    if (!pr || pr->magic != kPackedRowsMagic || !pw || pw->magic != kPackedMagic)
+        return fail(CT_ERR_INVALID, "ct_matmul_packed_rows: not a packed operand");
+    int dev = -1;
+    CT_CUDA(cudaGetDevice(&dev));
+    if (pr->mode != pw->mode || pr->k != pw->k || pr->kp != pw->kp || pr->device != dev || pw->device != dev)
+        return fail(CT_ERR_INVALID, "ct_matmul_packed_rows: operands of different inner size, precision or device");
+    if (row0 < 0 || rows < 0 || row0 + rows > pr->m)
+        return fail(CT_ERR_INVALID, "ct_matmul_packed_rows: row range outside the packed matrix");
+    if (rows == 0)
+        return CT_OK;
+    if (!out)
+        return fail(CT_ERR_INVALID, "ct_matmul_packed_rows: null pointer");
+    CT_TRY(clear_flags(st));
+    g_no_splitk   = true; // the split-K partial sums live in a shared workspace
+    ct_status res = gemm_planes(
+        st, pr->mode, pr->hi + (size_t)row0 * pr->row_bytes, pr->lo + (size_t)row0 * pr->row_bytes, pw->hi, pw->lo,
+        rows, pw->n, pr->kp, nullptr, CT_ACT_NONE, out, 1, 0, 0);
+    g_no_splitk = false;
+    return res;
 }
 
 // ---- matmul without any allocation --------------------------------------------------------

@@ -240,6 +240,22 @@ ct_status ct_dense(
  * ct_weights_pack cannot be recorded into a graph. */
 ct_status ct_weights_pack(const float *w_dev, int64_t k, int64_t n, void **packed_out);
 ct_status ct_weights_free(void *packed);
+
+/* The left operand packed as well, for a product whose rows are computed in several calls (the row
+ * panels of a sharded product, each sent on its way while the next is computed).  ct_rows_pack
+ * splits a [m][k] float32 matrix into planes of its own on the current stream; *packed_inout is
+ * NULL on the first call and the returned handle afterwards, whose buffers are then refilled (same
+ * shape and precision) without allocating.  ct_matmul_packed_rows computes
+ * out[rows][n] = A[row0 .. row0+rows) . W from two packed operands; it touches none of the
+ * library's cached workspaces, so calls made under different ct_set_stream streams may run at the
+ * same time (the caller orders them after the ct_rows_pack with events).  Same arithmetic as
+ * ct_dense_packed without bias, and the same bytes wherever that call does not slice k over CTAs
+ * (few output tiles and a long k), which this one never does.  No reference counterpart (operators.cpp:757-766 is the
+ * product itself). */
+ct_status ct_rows_pack(const float *a_dev, int64_t m, int64_t k, void **packed_inout);
+ct_status ct_rows_free(void *packed);
+ct_status ct_matmul_packed_rows(
+    const void *a_packed, int64_t row0, int64_t rows, const void *w_packed, float *out_dev);
 ct_status ct_dense_packed(
     const float *x_dev, const float *w_dev, const void *packed, const float *bias_dev, int64_t m,
     int64_t k, int64_t n, ct_activation act, float *out_dev, int64_t *argmax_dev);

@@ -704,6 +704,67 @@ def test_dense_packed_weights(T):
         check(lib.ct_weights_pack(None, 4, 4, C.byref(h)))
 
 
+def test_packed_rows_panels_on_two_streams(T):
+    """A left operand split once (ct_rows_pack) and multiplied in row panels of uneven size,
+    alternating between two streams, gives the bytes of the one-call product; the handle is reused
+    for new contents without allocating; ranges outside the matrix and foreign handles are refused."""
+    import ctypes as C
+
+    import camel_b200
+    from camel_b200._lib import check, lib
+
+    rng = np.random.default_rng(77)
+    m, k, n = 1100, 600, 2000  # enough tiles that the one-call product does not slice k (other summation order)
+    w = T.from_numpy(rng.uniform(-1, 1, (k, n)).astype(np.float32))
+    wp = C.c_void_p()
+    check(lib.ct_weights_pack(w.ptr, k, n, C.byref(wp)))
+    ap = C.c_void_p()
+    streams = [C.c_void_p(), C.c_void_p()]
+    for sh in streams:
+        check(lib.ct_stream_create(C.byref(sh)))
+    ev = C.c_void_p()
+    check(lib.ct_event_create(C.byref(ev)))
+    try:
+        first_handle = None
+        for seed in (1, 2):
+            a_np = np.random.default_rng(seed).uniform(-1, 1, (m, k)).astype(np.float32)
+            a = T.from_numpy(a_np)
+            whole = T.matmul(a, w).numpy()
+            check(lib.ct_rows_pack(a.ptr, m, k, C.byref(ap)))
+            first_handle = first_handle or ap.value
+            assert ap.value == first_handle  # refilled, not re-allocated
+            check(lib.ct_event_record(ev))
+            out = T.Tensor.empty((m, n)) if hasattr(T.Tensor, "empty") else T.from_numpy(np.zeros((m, n), np.float32))
+            plan = [(0, 512), (512, 256), (768, 128), (896, 204)]
+            for j, (off, rows) in enumerate(plan):
+                check(lib.ct_set_stream(streams[j % 2]))
+                check(lib.ct_stream_wait_event(ev))
+                check(lib.ct_matmul_packed_rows(ap, off, rows, wp, out.ptr + off * n * 4))
+            for sh in streams:  # the default stream waits for both lanes
+                check(lib.ct_set_stream(sh))
+                check(lib.ct_event_record(ev))
+                check(lib.ct_set_stream(None))
+                check(lib.ct_stream_wait_event(ev))
+            got = out.numpy()
+            T.check_async()
+            assert got.tobytes() == whole.tobytes()
+        with pytest.raises(camel_b200.CamelTensorError, match="row range"):
+            check(lib.ct_matmul_packed_rows(ap, 1000, 200, wp, out.ptr))
+        with pytest.raises(camel_b200.CamelTensorError, match="packed operand"):
+            check(lib.ct_matmul_packed_rows(wp, 0, 10, wp, out.ptr))
+        small = T.from_numpy(np.zeros((4, 4), np.float32))
+        with pytest.raises(camel_b200.CamelTensorError, match="another shape"):
+            check(lib.ct_rows_pack(small.ptr, 4, 4, C.byref(ap)))
+    finally:
+        check(lib.ct_set_stream(None))
+        T.sync()
+        check(lib.ct_rows_free(ap))
+        check(lib.ct_weights_free(wp))
+        check(lib.ct_event_destroy(ev))
+        for sh in streams:
+            check(lib.ct_stream_destroy(sh))
+
+
 def test_host_pipeline_streams_batches(T):
     """Seven host batches through a depth-2 pipeline (copy in, recorded forward, copy out on three
     streams): every batch's results equal the call-by-call run on the same bytes, in order."""

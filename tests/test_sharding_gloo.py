@@ -87,3 +87,69 @@ def test_sharded_product_is_reassembled_on_every_rank():
 
 def test_reduce_max_without_process_group():
     assert sharding.reduce_max(None, torch, 3.5, "cpu") == 3.5
+
+
+def test_tapered_panel_plan_covers_rows_and_shrinks():
+    from camel_b200 import sharding
+
+    for rows in (0, 1, 100, 512, 513, 1024, 2048, 4096, 16384, 2000, 3001):
+        plan = sharding.tapered_panel_plan(rows)
+        assert sum(c for _, c in plan) == rows
+        at = 0
+        for off, cnt in plan:
+            assert off == at and cnt > 0
+            at += cnt
+        sizes = [c for _, c in plan]
+        assert sizes == sorted(sizes, reverse=True)  # the exposed last gather is the smallest
+    assert [c for _, c in sharding.tapered_panel_plan(2048)] == [1024, 512, 256, 256]
+
+
+def test_banded_rows_partition_every_row_once():
+    from camel_b200 import sharding
+
+    for rows_per_rank, world in ((2048, 8), (4096, 4), (1000, 3), (96, 2)):
+        plan = sharding.tapered_panel_plan(rows_per_rank, smallest=16, unit=8)
+        seen = np.zeros(rows_per_rank * world, np.int32)
+        for rank in range(world):
+            local = 0
+            for off, cnt, g0, band0 in sharding.banded_rows(plan, world, rank):
+                assert off == local and g0 == band0 + rank * cnt
+                seen[g0:g0 + cnt] += 1
+                local += cnt
+            assert local == rows_per_rank
+        assert np.all(seen == 1)
+
+
+def _banded_rank_main(rank, world, port, n, out):
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(6)
+        a = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+        b = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+        rows = n // world
+        plan = sharding.tapered_panel_plan(rows, smallest=8, unit=4)
+        c_full = torch.full((n, n), float("nan"), dtype=torch.float32)
+        for off, cnt, g0, band0 in sharding.banded_rows(plan, world, rank):
+            block = a[g0:g0 + cnt].astype(np.float64) @ b.astype(np.float64)
+            c_full[g0:g0 + cnt] = torch.from_numpy(block.astype(np.float32))
+            sharding.gather_band(dist, c_full, band0, cnt, rank, world)
+        ref = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+        out.put((rank, bool(np.array_equal(c_full.numpy(), ref)), len(plan)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_banded_product_is_reassembled_in_place_on_every_rank():
+    world, n = 2, 96
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_banded_rank_main, args=(r, world, port, n, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(out.get(timeout=100) for _ in range(world))
+    for p in procs:
+        p.join(timeout=30)
+    assert [r[1] for r in results] == [True] * world
+    assert results[0][2] >= 3  # several bands
