@@ -470,7 +470,7 @@ __global__ void __launch_bounds__(32 * kSkinnyWarps, 1) gemm_skinny_tile_kernel(
         if (c == 0)
             SK_STAMP(3);
         int kend = (c + 1) * 32 < klen ? (c + 1) * 32 : klen;
-#pragma unroll 2
+#pragma unroll 4
         for (int kk = c * 32; kk < kend; kk += 4) {
             float4 q     = *reinterpret_cast<const float4 *>(xrow + kk);
             double xd[4] = {(double)q.x, (double)q.y, (double)q.z, (double)q.w};
