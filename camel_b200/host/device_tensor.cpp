@@ -310,20 +310,31 @@ bool TensorObject::sameShape(const TensorObject *other) const {
 }
 
 const std::byte *TensorObject::rawData() const {
-    if (!host_) {
-        host_ = static_cast<std::byte *>(std::malloc(byteSize_ ? static_cast<size_t>(byteSize_) : 1));
-        if (!host_)
+    // several operators may read the same tensor on the host at once (idx on one tensor from two
+    // scheduler threads): the mirror is made once, under a lock
+    std::byte *mirror = host_.load(std::memory_order_acquire);
+    if (mirror)
+        return mirror;
+    static std::mutex once;
+    std::lock_guard<std::mutex> lock(once);
+    mirror = host_.load(std::memory_order_relaxed);
+    if (!mirror) {
+        mirror = static_cast<std::byte *>(std::malloc(byteSize_ ? static_cast<size_t>(byteSize_) : 1));
+        if (!mirror)
             throw std::bad_alloc();
-        if (byteSize_ > 0)
-            ctCheck(ct_d2h(host_, deviceData(), static_cast<size_t>(byteSize_)));
+        if (byteSize_ > 0) {
+            ct_status status = ct_d2h(mirror, deviceData(), static_cast<size_t>(byteSize_));
+            if (status != CT_OK) {
+                std::free(mirror);
+                ctCheck(status);
+            }
+        }
+        host_.store(mirror, std::memory_order_release);
     }
-    return host_;
+    return mirror;
 }
 
-void TensorObject::invalidateHost() const {
-    std::free(host_);
-    host_ = nullptr;
-}
+void TensorObject::invalidateHost() const { std::free(host_.exchange(nullptr, std::memory_order_acq_rel)); }
 
 double TensorObject::getAsDouble(uint64_t i) const {
     const std::byte *p = rawData();

@@ -161,7 +161,7 @@ class TensorObject : public rtdata::Object {
     uint64_t numel_;
     uint64_t byteSize_;
     Expr *expr_;
-    mutable std::byte *host_; // malloc'd mirror, nullptr while stale
+    mutable std::atomic<std::byte *> host_; // malloc'd mirror, nullptr while stale
     int64_t *shape_;
     int64_t dims_[]; // rank_ entries, in the same allocation as the header
 };

@@ -17,6 +17,8 @@
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <thread>
+#include <utility>
 #include <vector>
 
 using camel::tensor::TensorObject;
@@ -360,6 +362,91 @@ int camel_host_session_pending(int64_t handle) {
     if (handle < 0 || handle >= static_cast<int64_t>(g_session.size()) || g_session[handle].kind != 0)
         return -1;
     return camel::core::rtdata::fromSlot<TensorObject *>(g_session[handle].slot)->expr()->pending.load() ? 1 : 0;
+}
+
+// The idioms of the reference's programs from many threads at once, the way the Taskflow scheduler
+// calls operators (src/passes/sched/taskflow/taskflow.cpp:157-196, up to 32 workers).  All threads
+// share one input tensor h[rows, cols] and one mask `h > 0` - whose deferred evaluation, buffer
+// allocation and host mirror they therefore race for - and each computes h * mask and the softmax
+// chain of mnist.cml:13-25 over h.  out_prod / out_probs receive every thread's results
+// ([threads][rows*cols]), out_mask the mask read at the end.  Returns 0 or the number of threads
+// that raised (the first message in err).
+int camel_host_threads_idioms(const float *host, int64_t rows, int64_t cols, int threads, float *out_prod,
+                              float *out_probs, uint8_t *out_mask, char *err, int errlen) {
+    try {
+        g_session.clear();
+        g_scratch.releaseAll();
+        camel::tensor::releaseAllDeviceBuffers();
+        camel::tensor::setLazyEvaluation(true);
+        static const auto ops = getTensorOpsMap();
+        camel::core::context::Context *nullCtx = nullptr;
+        using camel::core::rtdata::fromSlot;
+        using camel::core::rtdata::toSlot;
+        auto objSlot = [](TensorObject *t) { return toSlot(static_cast<camel::core::rtdata::Object *>(t)); };
+        int64_t shape[2] = {rows, cols};
+        TensorObject *h  = TensorObject::fromHost(TypeCode::Float32, shape, host, g_scratch);
+        Type *f32T = tensorTypeFor(0), *boolT = tensorTypeFor(2);
+        auto call = [&](const char *op, std::initializer_list<std::pair<slot_t, Type *>> args) {
+            VecArgsView with, norm;
+            for (const auto &a : args) {
+                norm.slots.push_back(a.first);
+                norm.types.push_back(a.second);
+            }
+            return ops.at(op)(with, norm, *nullCtx);
+        };
+        auto shapeSlot = [&](int64_t a, int64_t b) { // int[] argument; the allocator behind it is mutex-guarded
+            ::Array *arr = ::Array::create(mm::autoSpace(), 2);
+            arr->set<int64_t>(0, a);
+            arr->set<int64_t>(1, b);
+            return toSlot(static_cast<camel::core::rtdata::Object *>(arr));
+        };
+        slot_t hs   = objSlot(h);
+        slot_t mask = call("gt", {{hs, f32T}, {toSlot<double>(0.0), Type::Float64()}});
+        const size_t count = static_cast<size_t>(rows * cols);
+        std::vector<std::string> failures(static_cast<size_t>(threads));
+        std::vector<std::thread> pool;
+        for (int t = 0; t < threads; ++t) {
+            pool.emplace_back([&, t]() {
+                try {
+                    slot_t prod = (t & 1) ? call("multiply", {{mask, boolT}, {hs, f32T}})
+                                          : call("multiply", {{hs, f32T}, {mask, boolT}});
+                    Type *ia    = intArrayType();
+                    slot_t i1   = toSlot<int64_t>(1);
+                    slot_t rmax = call("max_axis", {{hs, f32T}, {i1, Type::Int64()}});
+                    slot_t rm2  = call("reshape", {{rmax, f32T}, {shapeSlot(rows, 1), ia}});
+                    slot_t one1 = call("ones", {{shapeSlot(1, cols), ia}});
+                    slot_t rmb  = call("matmul", {{rm2, f32T}, {one1, f32T}});
+                    slot_t stab = call("subtract", {{hs, f32T}, {rmb, f32T}});
+                    slot_t ex   = call("exp", {{stab, f32T}});
+                    slot_t rsum = call("sum_axis", {{ex, f32T}, {i1, Type::Int64()}});
+                    slot_t rs2  = call("reshape", {{rsum, f32T}, {shapeSlot(rows, 1), ia}});
+                    slot_t one2 = call("ones", {{shapeSlot(1, cols), ia}});
+                    slot_t rsb  = call("matmul", {{rs2, f32T}, {one2, f32T}});
+                    slot_t prob = call("divide", {{ex, f32T}, {rsb, f32T}});
+                    if (t % 3 == 2) // some threads read the shared mask while others still multiply by it
+                        (void)fromSlot<TensorObject *>(mask)->rawData();
+                    std::memcpy(out_prod + t * count, fromSlot<TensorObject *>(prod)->rawData(), count * 4);
+                    std::memcpy(out_probs + t * count, fromSlot<TensorObject *>(prob)->rawData(), count * 4);
+                } catch (const camel::core::error::RuntimeFault &f) {
+                    failures[static_cast<size_t>(t)] = faultText(f);
+                } catch (const std::exception &e) {
+                    failures[static_cast<size_t>(t)] = e.what();
+                }
+            });
+        }
+        for (auto &th : pool)
+            th.join();
+        std::memcpy(out_mask, fromSlot<TensorObject *>(mask)->rawData(), count);
+        int failed = 0;
+        for (const auto &f : failures)
+            if (!f.empty() && failed++ == 0)
+                failWith(err, errlen, 1, f);
+        if (ct_check() != CT_OK && failed++ == 0)
+            failWith(err, errlen, 1, ct_last_error());
+        return failed;
+    } catch (const std::exception &e) {
+        return failWith(err, errlen, -1, e.what());
+    }
 }
 
 int camel_ref_list_ops(char *buf, int buflen) {

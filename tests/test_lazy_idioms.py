@@ -269,3 +269,35 @@ def test_errors_are_raised_by_the_operator_that_owns_them(plugin):
         o.divide(a, zero)
     with pytest.raises(oracle.OracleError, match="log: input must be positive"):
         o.log(zero)
+
+
+def test_idioms_from_many_threads(plugin):
+    """Operators are called from up to 32 scheduler threads at once
+    (src/passes/sched/taskflow/taskflow.h:79-80).  24 threads share one input and one deferred mask
+    and race for its evaluation, its buffer and its host mirror; every thread must get the results
+    of the single-threaded chains."""
+    import ctypes as C
+
+    lib = plugin.lib
+    fn = lib.camel_host_threads_idioms
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p, C.c_int]
+    rows, cols, threads = 1536, 40, 24
+    h = (np.random.default_rng(8).standard_normal((rows, cols)) * 3).astype(np.float32)
+    ref = PortOps()
+    ref_mask = ref.gt(h, 0.0)
+    ref_prod = ref.multiply(h, ref_mask)
+    ref_probs, _ = softmax_program(ref, h, rows, cols)
+    from test_gpu_parity import ulp_distance
+
+    for _ in range(3):
+        prod = np.empty((threads, rows, cols), np.float32)
+        probs = np.empty((threads, rows, cols), np.float32)
+        mask = np.empty((rows, cols), np.uint8)
+        err = C.create_string_buffer(512)
+        rc = fn(h.ctypes.data, rows, cols, threads, prod.ctypes.data, probs.ctypes.data, mask.ctypes.data, err, 512)
+        assert rc == 0, (rc, err.value.decode())
+        assert mask.tobytes() == ref_mask.tobytes()
+        for t in range(threads):
+            assert prod[t].tobytes() == ref_prod.tobytes(), t
+            assert ulp_distance(probs[t], ref_probs).max() <= 4, t
