@@ -301,3 +301,41 @@ def test_idioms_from_many_threads(plugin):
         for t in range(threads):
             assert prod[t].tobytes() == ref_prod.tobytes(), t
             assert ulp_distance(probs[t], ref_probs).max() <= 4, t
+
+
+def lr_update_program(o, X, y, w, lr, m):
+    """sync func update of test/run/nn/lr.cml:23-32 (linear regression, one output column)."""
+    pred = o.matmul(X, w)
+    errors = o.subtract(pred, y)
+    dw = o.matmul(o.transpose(X), errors)
+    dw = o.multiply(2.0 / float(m), dw)
+    return o.subtract(w, o.multiply(lr, dw))
+
+
+@pytest.mark.parametrize("lazy", [True, False], ids=["deferred", "eager"])
+def test_linear_regression_update_step(plugin, lazy):
+    """predict + update of lr.cml: the bias column by concat(X, ones, 1), then two chained scalings
+    in front of the subtraction (only the outer one folds into the update)."""
+    m, d, lr = 3000, 64, 0.001
+    rng = np.random.default_rng(13)
+    X0 = rng.uniform(-1, 1, (m, d)).astype(np.float32)
+    y = rng.uniform(-1, 1, (m, 1)).astype(np.float32)
+    w = rng.uniform(-1, 1, (d + 1, 1)).astype(np.float32)
+    p = oracle.port()
+    Xb_ref = p.concat(X0, np.ones((m, 1), np.float32), 1)
+    ref = lr_update_program(PortOps(), Xb_ref, y, w, lr, m)
+
+    s = plugin.session(lazy)
+    o = SessionOps(s)
+    Xb = s.call("concat", o.tensor(X0), o.ones([m, 1]), 1)
+    before = s.finish(Xb)
+    new_w = lr_update_program(o, Xb, o.tensor(y), o.tensor(w), lr, m)
+    launches = s.finish(new_w) - before
+    got = s.fetch(new_w)
+    assert got.shape == (d + 1, 1)
+    assert np.max(np.abs(got - ref)) <= 1e-5 * max(1.0, float(np.max(np.abs(ref))))
+    assert np.array_equal(s.fetch(Xb), Xb_ref)
+    if lazy:
+        # product, difference, transposed product (two kernels), scaling and update (65 values: each a
+        # vector launch and one for the ragged tail); no transposed copy of X
+        assert launches <= 8, launches
