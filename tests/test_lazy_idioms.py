@@ -339,3 +339,37 @@ def test_linear_regression_update_step(plugin, lazy):
         # product, difference, transposed product (two kernels), scaling and update (65 values: each a
         # vector launch and one for the ragged tail); no transposed copy of X
         assert launches <= 8, launches
+
+
+def svm_program(o, X, y_adjusted, weights, bias):
+    """The forward half of svm_epoch, test/run/nn/svm.cml:26-40: the hinge loss and the masked
+    factor of its gradient.  The mask `hinge_loss > 0` is used twice: once in the relu idiom (never
+    computed for it), once times another tensor (computed there)."""
+    predictions = o.add(o.matmul(X, weights), bias)
+    margins = o.multiply(o.multiply(y_adjusted, predictions), 1.0)
+    hinge_loss = o.subtract(1.0, margins)
+    hinge_loss_positive = o.multiply(hinge_loss, o.gt(hinge_loss, 0))
+    masked = o.multiply(o.multiply(y_adjusted, -1.0), o.gt(hinge_loss, 0))
+    return hinge_loss_positive, masked
+
+
+class _PortOpsWithAdd(PortOps):
+    def add(self, a, b):
+        return self.p.binary(oracle.ADD, a, b)
+
+
+@pytest.mark.parametrize("lazy", [True, False], ids=["deferred", "eager"])
+def test_svm_hinge_chain(plugin, lazy):
+    m, d = 5000, 20
+    rng = np.random.default_rng(19)
+    X = rng.standard_normal((m, d)).astype(np.float32)
+    y = np.where(rng.uniform(size=(m, 1)) < 0.5, -1.0, 1.0).astype(np.float32)
+    w = (rng.standard_normal((d, 1)) * 0.3).astype(np.float32)
+    ref_pos, ref_masked = svm_program(_PortOpsWithAdd(), X, y, w, 0.25)
+    s = plugin.session(lazy)
+    o = SessionOps(s)
+    pos, masked = svm_program(o, o.tensor(X), o.tensor(y), o.tensor(w), 0.25)
+    got_pos, got_masked = s.fetch(pos), s.fetch(masked)
+    # one output column: the product is float64-accumulated, so everything downstream is exact
+    assert canonical_nan(got_pos).tobytes() == canonical_nan(ref_pos).tobytes()
+    assert canonical_nan(got_masked).tobytes() == canonical_nan(ref_masked).tobytes()
