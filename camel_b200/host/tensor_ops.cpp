@@ -36,15 +36,8 @@ namespace {
 
 Type *tensorType(Type *dtype = nullptr) { return TensorType::Dynamic(dtype ? dtype : Type::Float32()); }
 
-ArrayType *intArrayType() {
-    static ArrayType *instance = ArrayType::create(Type::Int64());
-    return instance;
-}
-
 bool isTensor(Type *t) { return t && t->code() == TensorType::typeCode(); }
 bool isArray(Type *t) { return t && t->code() == TypeCode::Array; }
-bool isScalar(Type *t) { return t && ctn::isSupportedTensorScalar(t->code()); }
-bool isInt(Type *t) { return t && (t->code() == TypeCode::Int32 || t->code() == TypeCode::Int64); }
 
 double scalarValue(ArgsView &args, size_t i) {
     switch (args.type(i)->code()) {
