@@ -6,12 +6,14 @@
  *
  * Pinning: every function that restates an existing reference operator is compared bit for bit
  * with the reference's own compiled code (oracle/_ref, built by the Makefile here) in
- * tests/test_oracle_vs_reference.py, and with the fixtures under tests/golden/ that were
- * produced by that compiled reference.  The operators that the reference does not have
- * (relu, softmax, dense, conv2d, maxpool2d) are pinned where a composition of reference
- * operators defines them (relu, softmax, dense); conv2d and maxpool2d have neither reference
- * code nor reference tests: PARITY UNPINNED for those two, they follow the reference's
- * arithmetic style only (double accumulation in ascending order, one rounding, strict '>').
+ * tests/test_oracle.py, and with the fixtures under tests/golden/ that were produced by that
+ * compiled reference.  The operators that the reference does not have (relu, softmax, dense,
+ * conv2d, maxpool2d) are pinned, bit for bit as well, by compositions of reference operators run
+ * on the compiled reference (tests/cases.py, RefBackend): relu, softmax and dense by the .cml
+ * idioms that define them; conv2d by one reference matmul per image over the gathered input
+ * windows with the bias as the last term (the dense idiom); maxpool2d by the reference's
+ * max(axis 0) over the gathered window elements.  In those two the gather is data movement
+ * outside the reference; every arithmetic step is the reference's.
  *
  * The reference's convention, used by every function below: read each element as double
  * (TensorObject::getAsDouble, modules/tensor/runtime.cpp:298-310), compute in double, round
@@ -370,9 +372,10 @@ int cto_dense(
     return 0;
 }
 
-/* conv2d, NCHW input, OIHW weights, zero padding, square stride: PARITY UNPINNED (no
- * reference code or test).  One double accumulator per output, terms in (c, kh, kw) ascending
- * order, padded taps skipped (they would add +0.0), bias last, one rounding, optional relu. */
+/* conv2d, NCHW input, OIHW weights, zero padding, square stride.  No reference body exists; the
+ * definition is the reference matmul (operators.cpp:757-766) over the gathered input windows:
+ * one double accumulator per output, terms in (c, kh, kw) ascending order, padded taps skipped
+ * (they would add w * 0.0), bias last, one rounding, optional relu as y * (y > 0). */
 int cto_conv2d(
     const float *x, const float *w, const float *bias, int64_t n, int64_t c, int64_t h,
     int64_t wd, int64_t ko, int64_t kh, int64_t kw, int64_t stride, int64_t pad, int activation,
@@ -413,8 +416,9 @@ int cto_conv2d(
     return 0;
 }
 
-/* maxpool2d, NCHW, window == stride, no padding: PARITY UNPINNED.  Starts from the window's
- * first element and replaces on strict '>' scanning rows then columns, as tensorMaxAxis does. */
+/* maxpool2d, NCHW, window == stride, no padding.  No reference body exists; the definition is
+ * tensorMaxAxis (runtime.cpp:924-963) over the window's elements: starts from the first element
+ * and replaces on strict '>' scanning rows then columns. */
 int cto_maxpool2d(
     const float *x, int64_t n, int64_t c, int64_t h, int64_t wd, int64_t win, float *out) {
     int64_t ho = h / win, wo = wd / win;

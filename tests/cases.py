@@ -69,6 +69,12 @@ class PortBackend:
     def dense(self, x, w, b, act):
         return self.p.dense(x, w, b, {"none": 0, "relu": 1}[act])
 
+    def conv2d(self, x, w, b, stride, pad, act):
+        return self.p.conv2d(x, w, b, stride, pad, {"none": 0, "relu": 1}[act])
+
+    def maxpool2d(self, x, win):
+        return self.p.maxpool2d(x, win)
+
     def ones(self, shape):
         return self.p.full(oracle.F32, 1.0, tuple(shape))
 
@@ -85,9 +91,43 @@ class PortBackend:
         return self.p.arange(start, stop, step)
 
 
+def conv_patches(x, kh, kw, stride, pad):
+    """Pure data movement (no arithmetic): the zero-padded input windows of one convolution as a
+    matrix per image, [n][c*kh*kw][ho*wo], rows in (c, kh, kw) ascending order."""
+    n, c, h, w = x.shape
+    ho, wo = (h + 2 * pad - kh) // stride + 1, (w + 2 * pad - kw) // stride + 1
+    xp = np.zeros((n, c, h + 2 * pad, w + 2 * pad), np.float32)
+    xp[:, :, pad:pad + h, pad:pad + w] = x
+    out = np.empty((n, c, kh, kw, ho, wo), np.float32)
+    for r in range(kh):
+        for s in range(kw):
+            out[:, :, r, s] = xp[:, :, r:r + stride * (ho - 1) + 1:stride, s:s + stride * (wo - 1) + 1:stride]
+    return out.reshape(n, c * kh * kw, ho * wo), ho, wo
+
+
+def pool_windows(x, win):
+    """Pure data movement: the win x win windows of a max-pool as [win*win][n*c*ho*wo], rows in the
+    window's scan order (rows, then columns)."""
+    n, c, h, w = x.shape
+    ho, wo = h // win, w // win
+    v = x[:, :, :ho * win, :wo * win].reshape(n, c, ho, win, wo, win)
+    return np.ascontiguousarray(v.transpose(3, 5, 0, 1, 2, 4)).reshape(win * win, n * c * ho * wo), ho, wo
+
+
 class RefBackend:
     """The reference's own operators; relu / softmax / dense by the compositions that define
-    them (test/run/nn/svm.cml:31, mnist.cml:13-25, lr.cml:19-21)."""
+    them (test/run/nn/svm.cml:31, mnist.cml:13-25, lr.cml:19-21); conv2d and maxpool2d by
+    compositions in which every arithmetic step is a reference operator:
+
+    conv2d   the input windows gathered into a patch matrix (movement only, numpy), then the dense
+             idiom of lr.cml:19-21 per image - concat(W, bias column) @ concat(patches, ones row) -
+             i.e. ONE reference matmul (operators.cpp:757-766: float64 sum over (c, kh, kw) ascending,
+             the bias the last term, one rounding), relu as `y * (y > 0)`.  A padded tap enters
+             the sum as w * 0.0, which leaves a float64 sum of finite terms unchanged.
+    maxpool  the window elements gathered as the rows of a [win*win][outputs] matrix (movement
+             only), then the reference's max(axis 0) (runtime.cpp:924-963: the first row seeds, a
+             later row replaces on strict '>').
+    """
 
     name = "ref"
 
@@ -151,6 +191,32 @@ class RefBackend:
         else:
             y = r.call("matmul", x, w)
         return self.relu(y) if act == "relu" else y
+
+    def conv2d(self, x, w, b, stride, pad, act):
+        r = self.r
+        x, w = np.asarray(x, np.float32), np.asarray(w, np.float32)
+        ko, c, kh, kw = w.shape
+        patches, ho, wo = conv_patches(x, kh, kw, stride, pad)
+        wm = w.reshape(ko, c * kh * kw)
+        if b is not None:
+            wm = r.call("concat", wm, np.asarray(b, np.float32).reshape(-1, 1), 1)
+        if x.shape[0] == 0 or ho * wo == 0:
+            return np.zeros((x.shape[0], ko, ho, wo), np.float32)
+        outs = []
+        for img in patches:
+            pm = img
+            if b is not None:
+                pm = r.call("concat", img, r.call("ones", IntArray([1, img.shape[1]])), 0)
+            y = r.call("matmul", wm, pm)
+            outs.append(self.relu(y) if act == "relu" else y)
+        return np.stack(outs).reshape(x.shape[0], ko, ho, wo)
+
+    def maxpool2d(self, x, win):
+        x = np.asarray(x, np.float32)
+        rows, ho, wo = pool_windows(x, win)
+        if rows.size == 0:
+            return np.zeros((x.shape[0], x.shape[1], ho, wo), np.float32)
+        return self.r.call("max_axis", rows, 0).reshape(x.shape[0], x.shape[1], ho, wo)
 
     def ones(self, shape):
         return self.r.call("ones", IntArray(shape))
@@ -343,10 +409,51 @@ def build_cases():
             outs += [be.dense(x, w, b, "none"), be.dense(x, w, b, "relu"), be.dense(x, w, None, "relu")]
         return outs
 
+    # -- conv2d / maxpool2d: the reference has neither; its operators composed define them (see
+    #    RefBackend).  Geometries of BASELINE configs 3 and 4 at small batch, plus ragged ones.
+    conv_geoms = [
+        # name,          n, c,  h,  w,  ko, kh, kw, stride, pad, act,   keep every k-th filter
+        ("cfg3_geometry", 1, 64, 56, 56, 128, 3, 3, 1, 1, "relu", 8),
+        ("cfg4_conv1", 3, 1, 28, 28, 32, 3, 3, 1, 1, "relu", 1),
+        ("cfg4_conv2", 2, 32, 28, 28, 64, 3, 3, 1, 1, "relu", 1),
+        ("stride2_5x5", 2, 16, 20, 20, 48, 5, 5, 2, 2, "none", 1),
+        ("nopad_ragged", 2, 5, 9, 11, 7, 3, 2, 1, 0, "relu", 1),
+        ("one_by_one", 1, 8, 6, 7, 4, 1, 1, 1, 0, "none", 1),
+        ("empty_batch", 0, 3, 8, 8, 4, 3, 3, 1, 1, "relu", 1),
+    ]
+    for (gname, n, c, h, w, ko, kh, kw, stride, pad, act, keep) in conv_geoms:
+        @case(f"conv2d_{gname}")
+        def _(be, n=n, c=c, h=h, w=w, ko=ko, kh=kh, kw=kw, stride=stride, pad=pad, act=act, keep=keep):
+            rng = np.random.default_rng(3000 + c * 7 + h + ko)
+            x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+            wt = (rng.standard_normal((ko, c, kh, kw)) * np.sqrt(2.0 / (c * kh * kw))).astype(np.float32)
+            b = rng.uniform(-0.1, 0.1, ko).astype(np.float32)
+            # every output channel is an independent sum: the wide layer is checked on every keep-th filter
+            wt, b = np.ascontiguousarray(wt[::keep]), np.ascontiguousarray(b[::keep])
+            outs = [be.conv2d(x, wt, b, stride, pad, act)]
+            if n and gname in ("cfg4_conv1", "nopad_ragged"):
+                outs.append(be.conv2d(x, wt, None, stride, pad, "none"))
+            return outs
+
+    @case("maxpool2d_windows")
+    def _(be):
+        rng = np.random.default_rng(3100)
+        outs = []
+        for shape, win in (((2, 64, 28, 28), 2), ((2, 3, 9, 12), 3), ((1, 1, 7, 7), 2), ((2, 3, 10, 30), 2),
+                           ((0, 2, 4, 4), 2)):
+            x = rng.standard_normal(shape).astype(np.float32)
+            if x.size:
+                x[0, 0, 0, 0] = np.nan       # a NaN that opens a window stays
+                x[-1, -1, 1, 1] = np.nan     # one that does not never wins
+                x[0, 0, 2, 2:4] = (0.0, -0.0)  # among equal values the first one is kept
+                x[0, 0, 3, 2:4] = (-1.0, -2.0)
+            outs.append(be.maxpool2d(x, win))
+        return outs
+
     return cases
 
 
 CASES = build_cases()
 
 # Cases whose outputs involve tensor-core contractions on the GPU (compared by tolerance there).
-TOLERANCE_CASES = {name for name, _ in CASES if name.startswith(("matmul_f32", "dense_layers"))}
+TOLERANCE_CASES = {name for name, _ in CASES if name.startswith(("matmul_f32", "dense_layers", "conv2d_"))}

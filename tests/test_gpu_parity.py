@@ -86,6 +86,13 @@ class CudaBackend:
     def dense(self, x, w, b, act):
         return self._n(self.T.dense(self._t(x), self._t(w), self._t(b) if b is not None else None, act))
 
+    def conv2d(self, x, w, b, stride, pad, act):
+        return self._n(self.T.conv2d(self._t(x), self._t(w), self._t(b) if b is not None else None, stride, pad,
+                                     None if act == "none" else act))
+
+    def maxpool2d(self, x, win):
+        return self._n(self.T.maxpool2d(self._t(x), win))
+
     def ones(self, shape):
         return self._n(self.T.ones(shape))
 

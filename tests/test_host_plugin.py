@@ -88,6 +88,13 @@ class PluginBackend(RefBackend):
             return self.r.call("relu", y) if act == "relu" else y
         return self.r.call("dense_relu" if act == "relu" else "dense", With(w), With(np.asarray(b, np.float32)), x)
 
+    def conv2d(self, x, w, b, stride, pad, act):
+        bias = np.zeros(w.shape[0], np.float32) if b is None else np.asarray(b, np.float32)  # `conv2d<w, b, stride, pad>`
+        return self.r.call("conv2d_relu" if act == "relu" else "conv2d", With(w), With(bias), With(stride), With(pad), x)
+
+    def maxpool2d(self, x, win):
+        return self.r.call("maxpool2d", x, win)
+
 
 @needs_build
 @pytest.mark.gpu
