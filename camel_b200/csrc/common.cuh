@@ -16,10 +16,17 @@
 namespace ct {
 
 // Device-side error words, read back by the entry points that must report them.
+//   words 0-1  data-dependent exceptions of one call: cleared by the entry point that checks them,
+//              read back (with a synchronisation) before it returns.
+//   word 2     sticky: written by a contraction kernel whose bounded wait ran out and by nothing
+//              else; only ct_check() (or a *_host entry point that reports it) clears it.  While it
+//              is set every later contraction kernel returns at once, so that a failed launch is
+//              not followed by products of its undefined output; no entry point clears it on the
+//              way in, and the failure is therefore still there when the host next looks.
 enum FlagWord : int {
     FLAG_DIV_ZERO   = 0, // a divisor was 0 (reference: "Division by zero")
     FLAG_LOG_DOMAIN = 1, // an input of log was <= 0
-    FLAG_TIMEOUT    = 2, // a bounded in-kernel wait ran out (value = where)
+    FLAG_TIMEOUT    = 2, // a bounded in-kernel wait ran out (value = 1 + the block that gave up)
     FLAG_COUNT      = 8
 };
 
@@ -64,10 +71,13 @@ void count_launch(unsigned n = 1);
 // Grows a cached workspace (never shrinks); contents are undefined after the call.
 ct_status ensure_ws(void **ptr, size_t *cap, size_t bytes);
 
-// Clears the device error words on the stream.
-ct_status clear_flags(DeviceState *st);
+// Clears the per-call error words (FLAG_DIV_ZERO, FLAG_LOG_DOMAIN) on the stream; the sticky
+// FLAG_TIMEOUT word is left alone.
+ct_status clear_data_flags(DeviceState *st);
 // Synchronises the stream and copies the error words to st->flags_host.
 ct_status fetch_flags(DeviceState *st);
+// After fetch_flags: reports (and clears) a recorded kernel timeout; CT_OK if there is none.
+ct_status report_timeout(DeviceState *st, const char *what);
 
 #define CT_CUDA(call)                                                                              \
     do {                                                                                           \

@@ -389,7 +389,6 @@ ct_status ct_matmul(
             return outer_product(st, af, bf, m, n, of);
         if (m * n * (k > 0 ? k : 1) < kTinyMacs)
             return matmul_generic(adt, a, bdt, b, m, k, n, out);
-        CT_TRY(clear_flags(st));
         return gemm_f32_tc(st, af, bf, nullptr, m, k, n, CT_ACT_NONE, of);
     }
     return matmul_generic(adt, a, bdt, b, m, k, n, out);
@@ -417,7 +416,6 @@ ct_status ct_matmul_tn(const float *a_km, const float *b, int64_t m, int64_t k, 
         ct_status f = ct_free(at);
         return s != CT_OK ? s : f;
     }
-    CT_TRY(clear_flags(st));
     return gemm_f32_tc(st, a_km, b, nullptr, m, k, n, CT_ACT_NONE, out, nullptr, /*a_is_km=*/true);
 }
 
@@ -444,7 +442,6 @@ ct_status ct_dense_packed(
     if (n <= 32)
         return gemm_f32_skinny(st, x, w, bias, m, k, n, act, out, argmax);
     int gemm_act = act == CT_ACT_RELU ? CT_ACT_RELU : CT_ACT_NONE;
-    CT_TRY(clear_flags(st));
     CT_TRY(gemm_f32_tc(st, x, w, bias, m, k, n, gemm_act, out, static_cast<const PackedWeights *>(packed)));
     if (act == CT_ACT_SOFTMAX) {
         // wide classifier: logits are complete rows in `out`; finish in place
@@ -475,10 +472,7 @@ ct_status ct_matmul_host(
     CT_TRY(ct_matmul(CT_F32, st->stage_ws[0], CT_F32, st->stage_ws[1], m, k, n, st->stage_ws[2]));
     CT_CUDA(cudaMemcpyAsync(out, st->stage_ws[2], ob, cudaMemcpyDeviceToHost, stream()));
     CT_TRY(fetch_flags(st));
-    if (st->flags_host[FLAG_TIMEOUT])
-        return fail(CT_ERR_TIMEOUT, "matmul: a bounded wait inside the GEMM kernel ran out (block %u)",
-                    st->flags_host[FLAG_TIMEOUT] - 1);
-    return CT_OK;
+    return report_timeout(st, "matmul");
 }
 
 // Largest even number of output rows whose pixels fit the 128 accumulator rows; the fused
@@ -520,7 +514,7 @@ ct_status ct_conv2d_maxpool2(
     const bool tensor_core = kdim > kSmallPatch && !(kdim * ko * pix * n < kTinyMacs * 8 || ko < 16 || pix < 64);
     const bool fused = tensor_core && stride == 1 && c >= 16 && ko <= 64 && ko > 0 && wo <= 128 && (wo & 1) == 0 && (ho & 1) == 0 &&
                        kp_i <= 1024 * (kblock / 32) && pooled_tile_rows(ho, wo) >= 2 && conv_tile_rows(ho, wo) > 0 &&
-                       n > 0 && !getenv("CAMEL_TENSOR_NO_CONV_SWAP") && !getenv("CAMEL_TENSOR_CONV_IM2COL");
+                       n > 0;
     if (fused)
         return conv2d_run(x, w, bias, n, c, h, wd, ko, kh, kw, stride, pad, act, out, 2);
     // not a shape of the fused kernel: the convolution into a temporary, then maxpool2d
@@ -556,7 +550,7 @@ static ct_status conv2d_run(
     int64_t kdim = c * kh * kw;
     int64_t pix  = ho * wo;
     if (pool == 0 && c == 1 && kh == 3 && kw == 3 && stride == 1 && (wo & 3) == 0 && (pix & 3) == 0 && ko * 72 <= 48 * 1024 &&
-        (reinterpret_cast<uintptr_t>(out) & 15u) == 0 && !getenv("CAMEL_TENSOR_NO_CONV_C1")) {
+        (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
         ProfScope prof("conv_small_c");
         conv2d_c1_3x3_kernel<<<capped_blocks(st, n * ho * (wo >> 2), 16), 256, (size_t)ko * 72, stream()>>>(
             x, w, bias, n, h, wd, (int)ko, pad, ho, wo, act, out);
@@ -597,7 +591,7 @@ static ct_status conv2d_run(
     // patch matrix is never materialised - each k-block is one shifted 4-D TMA box.
     const int th = (stride == 1 && c >= 16 && wo <= 256 && wd <= 0x7fffffff && h <= 0x7fffffff)
                        ? conv_tile_rows(ho, wo) : 0;
-    if (th > 0 && !getenv("CAMEL_TENSOR_CONV_IM2COL")) {
+    if (th > 0) {
         int64_t c_pad  = (c + kblock - 1) / kblock * kblock;
         int64_t taps   = kh * kw;
         int64_t kp_i   = taps * c_pad;
@@ -607,7 +601,6 @@ static ct_status conv2d_run(
         uint8_t *ws = static_cast<uint8_t *>(st->gemm_ws);
         void *w_hi = ws, *w_lo = ws + w_plane;
         void *x_hi = ws + planes * w_plane, *x_lo = ws + planes * w_plane + x_plane;
-        CT_TRY(clear_flags(st));
         {
             ProfScope prof("conv_prepass");
             int64_t wtotal = ko * kp_i;
@@ -637,7 +630,6 @@ static ct_status conv2d_run(
     uint8_t *ws = static_cast<uint8_t *>(st->gemm_ws);
     void *w_hi = ws, *w_lo = ws + w_plane;
     void *p_hi = ws + planes * w_plane, *p_lo = ws + planes * w_plane + p_plane;
-    CT_TRY(clear_flags(st));
     CT_TRY(split_rows_planes(st, mode, w, ko, kdim, kp, w_hi, w_lo));
     int64_t total = n * pix * kp;
     {

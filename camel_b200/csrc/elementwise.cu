@@ -622,7 +622,7 @@ ct_status ct_binary(
         return fail(CT_ERR_INVALID, "ct_binary: null pointer");
     bool checks = op == CT_DIV;
     if (checks)
-        CT_TRY(clear_flags(st));
+        CT_TRY(clear_data_flags(st));
     ct_status rc;
     if (ldt == CT_F32 && rdt == CT_F32) {
         const float *lf = static_cast<const float *>(l), *rf = static_cast<const float *>(r);
@@ -685,7 +685,7 @@ ct_status ct_binary_scalar(
         return fail(CT_ERR_DIV_ZERO, "Division by zero");
     bool checks = op == CT_DIV && left;
     if (checks)
-        CT_TRY(clear_flags(st));
+        CT_TRY(clear_data_flags(st));
     int odt = left ? ct_result_dtype(op, sdt, tdt) : ct_result_dtype(op, tdt, sdt);
     ct_status rc;
     if (tdt == CT_F32 && op != CT_POW && is_float_scalar_exact(scalar)) {
@@ -791,7 +791,7 @@ ct_status ct_log(const float *in, uint64_t n, float *out) {
         return CT_OK;
     if (!in || !out)
         return fail(CT_ERR_INVALID, "ct_log: null pointer");
-    CT_TRY(clear_flags(st));
+    CT_TRY(clear_data_flags(st));
     {
         uint64_t per_block = (uint64_t)kThreads * kUnroll * kVec;
         uint64_t blocks    = (n + per_block - 1) / per_block;

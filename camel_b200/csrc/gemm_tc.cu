@@ -1285,15 +1285,8 @@ ct_status make_conv_map(
     return CT_OK;
 }
 
-int chunk_blocks_setting() {
-    static int v = -1;
-    if (v < 0) {
-        const char *e = getenv("CAMEL_TENSOR_KCHUNK");
-        int x         = e ? atoi(e) : 0;
-        v             = x > 0 ? x : 8; // 8 k-blocks = 256 float32 values of k per drain
-    }
-    return v;
-}
+// k-blocks of 128-byte rows per drain of the accumulator: 8 = 256 float32 values of k
+constexpr int kChunkBlocks = 8;
 
 template <int BN, int MODE, int RB = ROW_B>
 ct_status launch_gemm(
@@ -1324,7 +1317,7 @@ ct_status launch_gemm(
     p.m            = m;
     p.n            = n;
     p.num_k_blocks = (int)(kp / C::kBlockK);
-    p.chunk_blocks = chunk_blocks_setting() * (ROW_B / RB); // same k extent per drain
+    p.chunk_blocks = kChunkBlocks * (ROW_B / RB); // same k extent per drain
     p.tiles_m      = (int)((m + BM - 1) / BM);
     p.tiles_n      = (int)((n + BN - 1) / BN);
     p.bias         = bias;
@@ -1356,8 +1349,7 @@ ct_status launch_gemm(
     if constexpr (RB == 64) {
         // more tiles than SMs, each with a k range short enough for one accumulation (k <= 1024,
         // the error stays at the level of the chunked form): one CTA per SM walks the tiles
-        static const bool streaming = !getenv("CAMEL_TENSOR_NO_STREAM");
-        if (streaming && splits == 1 && p.num_k_blocks <= 64 && tiles > st->sm_count) {
+        if (splits == 1 && p.num_k_blocks <= 64 && tiles > st->sm_count) {
             using S = StreamCfg<BN, MODE>;
             static bool stream_attr_set_dev[16] = {}; // the attribute belongs to a device's context
             bool &stream_attr_set       = stream_attr_set_dev[st->device & 15];
@@ -1475,10 +1467,7 @@ ct_status gemm_planes(
     // 128 x 256 tiles when they fill the machine, 128 x 128 otherwise
     int64_t tiles256 = ((m + BM - 1) / BM) * ((n + 255) / 256) * batch;
     bool wide        = n > 128 && tiles256 >= st->sm_count / 2;
-    if (getenv("CAMEL_TENSOR_BN"))
-        wide = atoi(getenv("CAMEL_TENSOR_BN")) == 256;
-    if (conv && m <= 64 && conv->wo <= 128 && kp <= 1024 * (mode == MODE_3X ? 1 : 2) && bias_per_row == (bias ? 1 : 0) &&
-        !getenv("CAMEL_TENSOR_NO_CONV_SWAP")) {
+    if (conv && m <= 64 && conv->wo <= 128 && kp <= 1024 * (mode == MODE_3X ? 1 : 2) && bias_per_row == (bias ? 1 : 0)) {
         // few output channels: pixels on the accumulator rows, channels on its columns; the whole k
         // range is one accumulation, so k stays within what keeps the error at float32 level
         ConvGeom g = *conv;
@@ -1495,7 +1484,7 @@ ct_status gemm_planes(
         wide = conv->th * conv->wo > 128;
     // Few output tiles and a long reduction (e.g. a 12544 -> 128 layer): slice k across CTAs so
     // that the whole machine works, partial sums in a workspace, one pass to add them up.
-    if (!conv && batch == 1 && !bias_per_row && !g_no_splitk && !getenv("CAMEL_TENSOR_NO_SPLITK")) {
+    if (!conv && batch == 1 && !bias_per_row && !g_no_splitk) {
         const int kblock  = mode == MODE_3X ? 32 : 64;
         const int nkb     = (int)(kp / kblock);
         int64_t tiles     = ((m + BM - 1) / BM) * ((n + (wide ? 255 : 127)) / (wide ? 256 : 128));
@@ -1532,11 +1521,10 @@ ct_status gemm_planes(
 #define CT_GEMM_ARGS st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row, conv
     if (mode == MODE_3X) {
         // 128 x 256 tiles of two float32 planes: 64-byte k-blocks give four 48 KB stages instead
-        // of two 96 KB ones (CAMEL_TENSOR_ROWB=128 selects the wide k-block for comparison)
-        static const bool narrow = !(getenv("CAMEL_TENSOR_ROWB") && atoi(getenv("CAMEL_TENSOR_ROWB")) == 128);
-        if (wide && narrow)
+        // of two 96 KB ones
+        if (wide)
             return launch_gemm<256, MODE_3X, 64>(CT_GEMM_ARGS);
-        return wide ? launch_gemm<256, MODE_3X>(CT_GEMM_ARGS) : launch_gemm<128, MODE_3X>(CT_GEMM_ARGS);
+        return launch_gemm<128, MODE_3X>(CT_GEMM_ARGS);
     }
     return wide ? launch_gemm<256, MODE_BF>(CT_GEMM_ARGS) : launch_gemm<128, MODE_BF>(CT_GEMM_ARGS);
 #undef CT_GEMM_ARGS
@@ -1797,7 +1785,6 @@ extern "C" ct_status ct_matmul_packed_rows(
         return CT_OK;
     if (!out)
         return fail(CT_ERR_INVALID, "ct_matmul_packed_rows: null pointer");
-    CT_TRY(clear_flags(st));
     g_no_splitk   = true; // the split-K partial sums live in a shared workspace
     ct_status res = gemm_planes(
         st, pr->mode, pr->hi + (size_t)row0 * pr->row_bytes, pr->lo + (size_t)row0 * pr->row_bytes, pw->hi, pw->lo,
@@ -1903,6 +1890,7 @@ extern "C" ct_status ct_matmul_f32_static(
     const float *a_dev, const float *b_dev, int64_t m, int64_t k, int64_t n, float *out_dev,
     uint32_t *status_dev) {
     using namespace ct;
+    OpLock op_lock; // callers on several threads that share a stream are at least enqueued one after the other
     if (m < 0 || k < 0 || n < 0)
         return fail(CT_ERR_INVALID, "matmul: negative dimension");
     if (m == 0 || n == 0) {

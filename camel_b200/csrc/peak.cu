@@ -1,0 +1,140 @@
+// Measured ceiling of the tensor pipe for the roofline of the contraction kernels.
+//
+// One CTA per SM issues tcgen05.mma (128 x 256 x 32 bytes of k) back to back on operand tiles that
+// already sit in shared memory - no TMA, no global memory, no epilogue in the loop - so the time of
+// a launch is the time the tensor pipe needs for that many MMAs and nothing else.  The GEMM and
+// conv kernels issue exactly this instruction shape; what they reach is reported against this
+// number (divided by three for the 3xTF32 scheme, which spends three MMAs per product).
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+namespace ct {
+namespace {
+
+using namespace ptx;
+
+constexpr int kPeakBN      = 256;
+constexpr int kPeakRowB    = 128;
+constexpr int kPeakABytes  = 128 * kPeakRowB;
+constexpr int kPeakBBytes  = kPeakBN * kPeakRowB;
+constexpr int kPeakSmem    = 2 * (kPeakABytes + kPeakBBytes) + 1024; // two operand sets, alternated
+constexpr int kPeakThreads = 128;
+
+// kind: 0 = kind::tf32, 1 = kind::f16 with bf16 operands
+template <int KIND>
+__global__ void __launch_bounds__(kPeakThreads, 1) mma_peak_kernel(int mma_groups, uint32_t *status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_done;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag_s;
+    const int warp = threadIdx.x >> 5;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *base            = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    // Operand values: a fixed pattern of finite numbers in (-1, 1).  Their arrangement in the
+    // swizzled tile is irrelevant here (no result is read), their being non-zero is not: an
+    // all-zero operand draws less power and would flatter the sustained figure.
+    for (int i = threadIdx.x; i < 2 * (kPeakABytes + kPeakBBytes) / 4; i += kPeakThreads) {
+        uint32_t h = (uint32_t)i * 2654435761u + blockIdx.x * 40503u;
+        float v    = ((h >> 9) & 0xffff) * (1.0f / 32768.0f) - 1.0f;
+        if (KIND == 0) {
+            reinterpret_cast<float *>(base)[i] = v;
+        } else {
+            uint32_t b = __float_as_uint(v) >> 16; // the value truncated to bf16
+            reinterpret_cast<uint32_t *>(base)[i] = b | (b << 16);
+        }
+    }
+    if (threadIdx.x == 0) {
+        abort_flag_s = 0;
+        mbar_init(smem_u32(&bar_done), 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), 2 * kPeakBN);
+        tmem_relinquish();
+    }
+    // make the generic-proxy writes of the operand tiles visible to the tensor core's async proxy
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 1 && (threadIdx.x & 31) == 0) {
+        const uint32_t idesc = make_idesc(KIND == 0 ? 2u : 1u, 128, kPeakBN);
+        for (int g = 0; g < mma_groups; ++g) {
+            const uint32_t set = smem_base + (uint32_t)(g & 1) * (kPeakABytes + kPeakBBytes);
+            const uint64_t da = smem_desc_k<kPeakRowB>(set), db = smem_desc_k<kPeakRowB>(set + kPeakABytes);
+            const uint32_t d  = tmem_base + (uint32_t)((g >> 1) & 1) * kPeakBN;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) { // four k-steps of 32 bytes per 128-byte operand row
+                const uint64_t adv = (uint64_t)(kk * 32 >> 4);
+                if (KIND == 0)
+                    mma_tf32(d, da + adv, db + adv, idesc, g < 2 && kk == 0 ? 0u : 1u);
+                else
+                    mma_f16(d, da + adv, db + adv, idesc, g < 2 && kk == 0 ? 0u : 1u);
+            }
+        }
+        tc_commit(smem_u32(&bar_done));
+        if (!mbar_wait(smem_u32(&bar_done), 0, &abort_flag_s))
+            atomicExch(status, 1u + blockIdx.x);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 2 * kPeakBN);
+    }
+}
+
+} // namespace
+} // namespace ct
+
+using namespace ct;
+
+// Runs `launches` back-to-back launches of the MMA loop (mma_groups x 4 MMAs of 128 x 256 x 8
+// (tf32) or 128 x 256 x 16 (bf16) per CTA, one CTA per SM), timed with CUDA events on the current
+// stream.  *tflops_host = dense MMA rate over the whole timed region; *ms_host its duration.
+extern "C" ct_status ct_measure_mma_peak(
+    ct_precision kind, int mma_groups, int launches, double *tflops_host, double *ms_host) {
+    OpLock op_lock;
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (mma_groups < 2 || mma_groups > (1 << 20) || launches < 1 || launches > (1 << 20))
+        return fail(CT_ERR_INVALID, "ct_measure_mma_peak: mma_groups in [2, 2^20], launches in [1, 2^20]");
+    if (kind != CT_PREC_3XTF32 && kind != CT_PREC_BF16)
+        return fail(CT_ERR_INVALID, "ct_measure_mma_peak: unknown kind");
+    // the in-kernel wait for the last MMA is bounded by one second: keep a launch far below that
+    if ((double)mma_groups * 4 * 70e-9 > 0.25)
+        return fail(CT_ERR_TOO_LARGE, "ct_measure_mma_peak: a launch of %d MMA groups would run too long", mma_groups);
+    auto kernel = kind == CT_PREC_3XTF32 ? mma_peak_kernel<0> : mma_peak_kernel<1>;
+    CT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPeakSmem));
+    CT_CUDA(cudaMemsetAsync(st->flags_dev + 3, 0, sizeof(uint32_t), stream()));
+    cudaEvent_t e0, e1;
+    CT_CUDA(cudaEventCreate(&e0));
+    CT_CUDA(cudaEventCreate(&e1));
+    kernel<<<st->sm_count, kPeakThreads, kPeakSmem, stream()>>>(mma_groups, st->flags_dev + 3); // warm-up
+    CT_LAUNCH_CHECK("mma_peak");
+    CT_CUDA(cudaEventRecord(e0, stream()));
+    for (int i = 0; i < launches; ++i) {
+        kernel<<<st->sm_count, kPeakThreads, kPeakSmem, stream()>>>(mma_groups, st->flags_dev + 3);
+        CT_LAUNCH_CHECK("mma_peak");
+    }
+    CT_CUDA(cudaEventRecord(e1, stream()));
+    CT_CUDA(cudaEventSynchronize(e1));
+    float ms = 0.0f;
+    CT_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    uint32_t bad = 0;
+    CT_CUDA(cudaMemcpy(&bad, st->flags_dev + 3, sizeof(bad), cudaMemcpyDeviceToHost));
+    if (bad)
+        return fail(CT_ERR_TIMEOUT, "ct_measure_mma_peak: the wait for the last MMA ran out (block %u)", bad - 1);
+    const double k_per_mma = kind == CT_PREC_3XTF32 ? 8.0 : 16.0;
+    const double flop = 2.0 * 128 * kPeakBN * k_per_mma * 4.0 * mma_groups * (double)st->sm_count * launches;
+    if (tflops_host)
+        *tflops_host = ms > 0 ? flop / (ms * 1e-3) / 1e12 : 0.0;
+    if (ms_host)
+        *ms_host = ms;
+    return CT_OK;
+}

@@ -4,6 +4,7 @@
 #include <cctype>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -52,20 +53,80 @@ ct_status cuda_fail(cudaError_t e, const char *what) {
 cudaStream_t stream() { return g_stream.load(); }
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+// Settings a host can give through the environment, read once, when the library is first used:
+//   CAMEL_TENSOR_PRECISION = 3xtf32 | bf16   arithmetic of the tensor-core contractions
+//   CAMEL_TENSOR_DEVICES   = "2" or "0,1,2,3" the GPU of this process: with a list, the entry at
+//                            index LOCAL_RANK (else CAMEL_TENSOR_RANK, else 0) modulo its length -
+//                            one process per GPU, each rank picking its own device from one setting
+// ct_set_precision / ct_set_device override them.  A malformed value is an error, not a default.
+ct_status settings_from_environment(int device_count, int *device_out) {
+    if (const char *p = getenv("CAMEL_TENSOR_PRECISION")) {
+        if (!strcmp(p, "3xtf32") || !strcmp(p, "3xTF32"))
+            g_precision.store(CT_PREC_3XTF32);
+        else if (!strcmp(p, "bf16") || !strcmp(p, "BF16"))
+            g_precision.store(CT_PREC_BF16);
+        else if (*p)
+            return fail(CT_ERR_INVALID, "CAMEL_TENSOR_PRECISION=%s: expected 3xtf32 or bf16", p);
+    }
+    *device_out = -1;
+    const char *d = getenv("CAMEL_TENSOR_DEVICES");
+    if (!d || !*d)
+        return CT_OK;
+    std::vector<int> list;
+    for (const char *c = d; *c;) {
+        if (*c == ',' || *c == ' ') {
+            ++c;
+            continue;
+        }
+        char *end = nullptr;
+        long v    = strtol(c, &end, 10);
+        if (end == c || v < 0 || v >= device_count)
+            return fail(CT_ERR_INVALID, "CAMEL_TENSOR_DEVICES=%s: expected device indices below %d", d, device_count);
+        list.push_back((int)v);
+        c = end;
+    }
+    if (list.empty())
+        return CT_OK;
+    long rank = 0;
+    if (const char *r = getenv("LOCAL_RANK"))
+        rank = strtol(r, nullptr, 10);
+    else if (const char *r2 = getenv("CAMEL_TENSOR_RANK"))
+        rank = strtol(r2, nullptr, 10);
+    if (rank < 0)
+        rank = 0;
+    *device_out = list[(size_t)rank % list.size()];
+    return CT_OK;
+}
+
 ct_status current(DeviceState **out) {
     int dev = g_device.load();
     if (dev < 0) {
-        int count     = 0;
-        cudaError_t e = cudaGetDeviceCount(&count);
-        if (e != cudaSuccess || count == 0) {
-            cudaGetLastError();
-            return fail(CT_ERR_NO_DEVICE, "no CUDA device: libcamel_tensor_b200 has no CPU fallback");
+        std::lock_guard<std::mutex> lock(g_mutex);
+        dev = g_device.load();
+        if (dev < 0) {
+            int count     = 0;
+            cudaError_t e = cudaGetDeviceCount(&count);
+            if (e != cudaSuccess || count == 0) {
+                cudaGetLastError();
+                return fail(CT_ERR_NO_DEVICE, "no CUDA device: libcamel_tensor_b200 has no CPU fallback");
+            }
+            int chosen = -1;
+            CT_TRY(settings_from_environment(count, &chosen));
+            if (chosen >= 0)
+                CT_CUDA(cudaSetDevice(chosen));
+            CT_CUDA(cudaGetDevice(&dev));
+            g_device.store(dev);
         }
-        CT_CUDA(cudaGetDevice(&dev));
-        g_device.store(dev);
     }
     if (dev >= 16)
         return fail(CT_ERR_INVALID, "device index %d not supported", dev);
+    // The selected device is a property of the process (ct_set_device), the CUDA "current device"
+    // one of the calling thread: a scheduler's worker threads start on device 0 whatever another
+    // thread selected.  Every entry point passes through here, so the thread is moved first.
+    int thread_dev = -1;
+    CT_CUDA(cudaGetDevice(&thread_dev));
+    if (thread_dev != dev)
+        CT_CUDA(cudaSetDevice(dev));
     DeviceState *st = &g_states[dev];
     if (!st->ready) {
         std::lock_guard<std::mutex> lock(g_mutex);
@@ -99,6 +160,15 @@ ct_status current(DeviceState **out) {
 ct_status ensure_ws(void **ptr, size_t *cap, size_t bytes) {
     if (*cap >= bytes && *ptr)
         return CT_OK;
+    // growing means cudaFree + cudaMalloc, which a stream that is being recorded cannot do
+    cudaStreamCaptureStatus cap_state = cudaStreamCaptureStatusNone;
+    CT_CUDA(cudaStreamIsCapturing(stream(), &cap_state));
+    if (cap_state != cudaStreamCaptureStatusNone)
+        return fail(
+            CT_ERR_INVALID,
+            "a workspace would have to grow to %zu bytes while calls are being recorded: run the sequence once "
+            "before ct_graph_begin",
+            bytes);
     if (*ptr) {
         CT_CUDA(cudaStreamSynchronize(stream()));
         CT_CUDA(cudaFree(*ptr));
@@ -111,9 +181,22 @@ ct_status ensure_ws(void **ptr, size_t *cap, size_t bytes) {
     return CT_OK;
 }
 
-ct_status clear_flags(DeviceState *st) {
-    CT_CUDA(cudaMemsetAsync(st->flags_dev, 0, FLAG_COUNT * sizeof(uint32_t), stream()));
+ct_status clear_data_flags(DeviceState *st) {
+    static_assert(FLAG_DIV_ZERO == 0 && FLAG_LOG_DOMAIN == 1 && FLAG_TIMEOUT == 2, "layout of the error words");
+    CT_CUDA(cudaMemsetAsync(st->flags_dev, 0, 2 * sizeof(uint32_t), stream()));
     return CT_OK;
+}
+
+ct_status report_timeout(DeviceState *st, const char *what) {
+    if (!st->flags_host[FLAG_TIMEOUT])
+        return CT_OK;
+    uint32_t where = st->flags_host[FLAG_TIMEOUT] - 1;
+    CT_CUDA(cudaMemsetAsync(st->flags_dev + FLAG_TIMEOUT, 0, sizeof(uint32_t), stream()));
+    return fail(
+        CT_ERR_TIMEOUT,
+        "%s: a bounded wait inside a contraction kernel ran out (block %u); outputs of contractions enqueued "
+        "since then are undefined",
+        what, where);
 }
 
 ct_status fetch_flags(DeviceState *st) {
@@ -417,14 +500,26 @@ ct_dtype ct_result_dtype(ct_binary_op op, ct_dtype lhs, ct_dtype rhs) {
 } // extern "C"
 
 extern "C" ct_status ct_check(void) {
+    OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
     CT_TRY(fetch_flags(st));
-    if (st->flags_host[FLAG_TIMEOUT]) {
-        uint32_t where = st->flags_host[FLAG_TIMEOUT] - 1;
-        CT_TRY(clear_flags(st));
-        return fail(CT_ERR_TIMEOUT, "a bounded wait inside a kernel ran out (block %u)", where);
-    }
+    return report_timeout(st, "ct_check");
+}
+
+// Host-side fault injection for tests of the error path: writes one of the device error words in
+// stream order, as if a kernel had raised it.  Nothing on the GPU waits, traps or faults.
+extern "C" ct_status ct_inject_status(int word, uint32_t value) {
+    OpLock op_lock;
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (word < 0 || word >= FLAG_COUNT)
+        return fail(CT_ERR_INVALID, "ct_inject_status: word %d out of range", word);
+    // the value travels inside the memset, so the call needs no host buffer that outlives it
+    if (value > 0xff)
+        return fail(CT_ERR_INVALID, "ct_inject_status: value must fit one byte");
+    CT_CUDA(cudaMemsetAsync(st->flags_dev + word, 0, sizeof(uint32_t), stream()));
+    CT_CUDA(cudaMemsetAsync(st->flags_dev + word, (int)value, 1, stream()));
     return CT_OK;
 }
 

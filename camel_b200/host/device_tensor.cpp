@@ -1,12 +1,15 @@
 #include "device_tensor.h"
 
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <ostream>
 #include <stdexcept>
 #include <map>
-#include <unordered_set>
+#include <unordered_map>
 #include <utility>
 #include <vector>
 
@@ -16,21 +19,64 @@ using type::TypeCode;
 
 namespace {
 std::mutex g_registryMutex;
-std::unordered_set<void *> g_deviceBuffers;
-// (device buffer, precision) -> packed form of a weight tensor.  A device buffer is written once,
-// when its tensor is created, and lives until releaseAllDeviceBuffers, so the address identifies
-// the contents.
-std::map<std::pair<void *, int>, void *> g_packedWeights;
-// The expression records of all tensors, released with the device buffers.
+// device buffer -> its size; the sum is g_liveBytes
+std::unordered_map<void *, uint64_t> g_deviceBuffers;
+uint64_t g_liveBytes = 0;
+// (device buffer, precision) -> packed form of a weight tensor and its size.  A device buffer is
+// written once, when its tensor is created, and the entry goes when the buffer goes, so the
+// address identifies the contents.
+struct PackedEntry {
+    void *handle;
+    uint64_t bytes;
+};
+std::map<std::pair<void *, int>, PackedEntry> g_packedWeights;
+// Every record ever made (freed at unload), and the creation log the scopes work on: the records
+// whose object header still holds its claim, in creation order.
 std::vector<Expr *> g_exprs;
+std::vector<Expr *> g_created;
+std::atomic<uint64_t> g_hostReads{0};
 std::atomic<int> g_lazy{-1}; // -1: not read from the environment yet
 
 void *allocDevice(size_t bytes) {
     void *p = nullptr;
     ctCheck(ct_alloc(&p, bytes));
     std::lock_guard<std::mutex> lock(g_registryMutex);
-    g_deviceBuffers.insert(p);
+    g_deviceBuffers.emplace(p, bytes);
+    g_liveBytes += bytes;
     return p;
+}
+
+void freeDevice(void *p) {
+    std::lock_guard<std::mutex> lock(g_registryMutex);
+    for (int prec = 0; prec < 2; ++prec) {
+        auto it = g_packedWeights.find(std::make_pair(p, prec));
+        if (it != g_packedWeights.end()) {
+            ct_weights_free(it->second.handle);
+            g_liveBytes -= it->second.bytes;
+            g_packedWeights.erase(it);
+        }
+    }
+    auto it = g_deviceBuffers.find(p);
+    if (it != g_deviceBuffers.end()) {
+        g_liveBytes -= it->second;
+        g_deviceBuffers.erase(it);
+        ct_free(p); // stream-ordered: kernels already enqueued on the stream still see the data
+    }
+}
+
+// One user of the record's buffer is gone (the object header at the end of its scope, or a
+// deferred computation that has run or will never run).  Call under exprMutex().
+void dropUser(Expr *e) {
+    if (!e || e->users.fetch_sub(1, std::memory_order_acq_rel) != 1)
+        return;
+    e->dead.store(true, std::memory_order_release);
+    if (void *buf = e->out.exchange(nullptr, std::memory_order_acq_rel))
+        freeDevice(buf);
+    std::free(e->host.exchange(nullptr, std::memory_order_acq_rel));
+    if (e->pending.exchange(false, std::memory_order_acq_rel)) { // it will never run: its operands are free of it
+        dropUser(e->a);
+        dropUser(e->b);
+    }
 }
 
 uint64_t product(std::span<const int64_t> shape) {
@@ -50,29 +96,93 @@ void ctCheck(ct_status status) {
 }
 
 void releaseAllDeviceBuffers() {
+    std::lock_guard<std::recursive_mutex> exprLock(exprMutex());
     std::lock_guard<std::mutex> lock(g_registryMutex);
     for (auto &entry : g_packedWeights)
-        ct_weights_free(entry.second);
+        ct_weights_free(entry.second.handle);
     g_packedWeights.clear();
-    for (void *p : g_deviceBuffers)
-        ct_free(p);
+    for (auto &entry : g_deviceBuffers)
+        ct_free(entry.first);
     g_deviceBuffers.clear();
-    for (Expr *e : g_exprs)
+    g_liveBytes = 0;
+    for (Expr *e : g_exprs) {
+        std::free(e->host.load(std::memory_order_relaxed));
         delete e;
+    }
     g_exprs.clear();
+    g_created.clear();
 }
+
+uint64_t beginScope() {
+    std::lock_guard<std::mutex> lock(g_registryMutex);
+    return g_created.size();
+}
+
+void endScope(uint64_t token, std::span<TensorObject *const> keep) {
+    std::lock_guard<std::recursive_mutex> exprLock(exprMutex());
+    std::vector<Expr *> ended;
+    {
+        std::lock_guard<std::mutex> lock(g_registryMutex);
+        if (token > g_created.size())
+            throw std::invalid_argument("endScope: the scope has already been ended by an enclosing one");
+        ended.assign(g_created.begin() + static_cast<std::ptrdiff_t>(token), g_created.end());
+        g_created.resize(static_cast<size_t>(token));
+        for (Expr *e : ended)
+            for (TensorObject *k : keep)
+                if (k && k->expr() == e) {
+                    g_created.push_back(e); // passes to the enclosing scope
+                    break;
+                }
+    }
+    for (Expr *e : ended) {
+        bool kept = false;
+        for (TensorObject *k : keep)
+            kept = kept || (k && k->expr() == e);
+        if (!kept)
+            dropUser(e); // the object header's claim
+    }
+}
+
+void releaseTensor(TensorObject *t) {
+    if (!t)
+        return;
+    std::lock_guard<std::recursive_mutex> exprLock(exprMutex());
+    Expr *e = t->expr();
+    {
+        std::lock_guard<std::mutex> lock(g_registryMutex);
+        auto it = std::find(g_created.rbegin(), g_created.rend(), e); // recent values are near the end
+        if (it == g_created.rend())
+            return; // its header's claim has been dropped before
+        g_created.erase(std::next(it).base());
+    }
+    dropUser(e);
+}
+
+uint64_t liveDeviceBytes() {
+    std::lock_guard<std::mutex> lock(g_registryMutex);
+    return g_liveBytes;
+}
+
+uint64_t hostReadCopies() { return g_hostReads.load(std::memory_order_relaxed); }
 
 const void *packedWeightsFor(const TensorObject *w, int64_t k, int64_t n) {
     if (n <= 32 || k <= 0 || w->dtype() != TypeCode::Float32)
         return nullptr; // narrow outputs read the matrix itself
-    const auto key = std::make_pair(const_cast<void *>(w->deviceData()), static_cast<int>(ct_get_precision()));
+    const int prec = static_cast<int>(ct_get_precision());
+    const auto key = std::make_pair(const_cast<void *>(w->deviceData()), prec);
     std::lock_guard<std::mutex> lock(g_registryMutex);
     auto it = g_packedWeights.find(key);
     if (it != g_packedWeights.end())
-        return it->second;
+        return it->second.handle;
     void *handle = nullptr;
     ctCheck(ct_weights_pack(static_cast<const float *>(w->deviceData()), k, n, &handle));
-    g_packedWeights.emplace(key, handle);
+    // size of the packed planes, for the books: [n][k rounded up to the k-block], two float32
+    // planes (3xTF32) or one bf16 plane, each rounded up to 1 KiB
+    const int64_t kblock = prec == CT_PREC_BF16 ? 64 : 32, elem = prec == CT_PREC_BF16 ? 2 : 4;
+    const uint64_t plane = (static_cast<uint64_t>(n) * ((k + kblock - 1) / kblock * kblock) * elem + 1023) & ~1023ull;
+    const uint64_t bytes = plane * (prec == CT_PREC_BF16 ? 1 : 2);
+    g_packedWeights.emplace(key, PackedEntry{handle, bytes});
+    g_liveBytes += bytes;
     return handle;
 }
 
@@ -131,8 +241,7 @@ TypeCode fromCtDType(ct_dtype dt) {
 }
 
 TensorObject::TensorObject(TypeCode dtype, uint32_t rank, uint64_t numel, uint64_t byteSize)
-    : dtype_(dtype), rank_(rank), numel_(numel), byteSize_(byteSize), expr_(nullptr),
-      host_(nullptr), shape_(nullptr) {}
+    : dtype_(dtype), rank_(rank), numel_(numel), byteSize_(byteSize), expr_(nullptr), shape_(nullptr) {}
 
 TensorObject *
 TensorObject::create(TypeCode dtype, std::span<const int64_t> shape, mm::IAllocator &allocator, bool zeroInit) {
@@ -158,6 +267,7 @@ TensorObject::create(TypeCode dtype, std::span<const int64_t> shape, mm::IAlloca
     {
         std::lock_guard<std::mutex> lock(g_registryMutex);
         g_exprs.push_back(e);
+        g_created.push_back(e);
     }
     if (zeroInit && numel > 0)
         ctCheck(ct_fill(toCtDType(dtype), 0.0, numel, t->deviceData()));
@@ -198,6 +308,8 @@ void *bufferOf(Expr *e) {
     std::lock_guard<std::mutex> lock(once);
     void *p = e->out.load(std::memory_order_relaxed);
     if (!p) {
+        if (e->dead.load(std::memory_order_acquire))
+            throw std::runtime_error("Tensor used after the scope that created it has ended");
         p = allocDevice(static_cast<size_t>(e->bytes));
         e->out.store(p, std::memory_order_release);
     }
@@ -214,6 +326,11 @@ void defer(TensorObject *out, ExprKind kind, const TensorObject *a, const Tensor
     e->scalar       = scalar;
     e->scalarDType  = scalarDType;
     e->tensorOnLeft = tensorOnLeft;
+    // until it has run, the record is a user of its operands' buffers
+    if (e->a)
+        e->a->users.fetch_add(1, std::memory_order_acq_rel);
+    if (e->b)
+        e->b->users.fetch_add(1, std::memory_order_acq_rel);
     e->pending.store(true, std::memory_order_release);
     if (!lazyEvaluation()) {
         evaluate(e);
@@ -234,6 +351,8 @@ void evaluate(Expr *e) {
     ct_status status = CT_OK;
     if (e->numel == 0) {
         e->pending.store(false, std::memory_order_release);
+        dropUser(a);
+        dropUser(b);
         return;
     }
     switch (e->kind) {
@@ -298,6 +417,24 @@ void evaluate(Expr *e) {
     }
     ctCheck(status); // a failed launch leaves the record pending: the next reader sees the error too
     e->pending.store(false, std::memory_order_release);
+    dropUser(a); // it has run: its operands are free of it (the pointers stay, as facts)
+    dropUser(b);
+}
+
+void rebindOperand(Expr *e, int which, Expr *to) {
+    std::lock_guard<std::recursive_mutex> lock(exprMutex());
+    Expr *&slot = which == 0 ? e->a : e->b;
+    if (slot == to)
+        return;
+    if (e->pending.load(std::memory_order_acquire)) {
+        if (to)
+            to->users.fetch_add(1, std::memory_order_acq_rel);
+        Expr *old = slot;
+        slot      = to;
+        dropUser(old);
+    } else {
+        slot = to;
+    }
 }
 
 bool TensorObject::sameShape(const TensorObject *other) const {
@@ -312,29 +449,34 @@ bool TensorObject::sameShape(const TensorObject *other) const {
 const std::byte *TensorObject::rawData() const {
     // several operators may read the same tensor on the host at once (idx on one tensor from two
     // scheduler threads): the mirror is made once, under a lock
-    std::byte *mirror = host_.load(std::memory_order_acquire);
+    std::byte *mirror = expr_->host.load(std::memory_order_acquire);
     if (mirror)
         return mirror;
     static std::mutex once;
     std::lock_guard<std::mutex> lock(once);
-    mirror = host_.load(std::memory_order_relaxed);
+    mirror = expr_->host.load(std::memory_order_relaxed);
     if (!mirror) {
         mirror = static_cast<std::byte *>(std::malloc(byteSize_ ? static_cast<size_t>(byteSize_) : 1));
         if (!mirror)
             throw std::bad_alloc();
         if (byteSize_ > 0) {
+            // the graph boundary: one device-to-host copy, then the device's error record - a
+            // contraction whose bounded wait ran out must not hand its undefined output to the host
             ct_status status = ct_d2h(mirror, deviceData(), static_cast<size_t>(byteSize_));
+            if (status == CT_OK)
+                status = ct_check();
             if (status != CT_OK) {
                 std::free(mirror);
                 ctCheck(status);
             }
+            g_hostReads.fetch_add(1, std::memory_order_relaxed);
         }
-        host_.store(mirror, std::memory_order_release);
+        expr_->host.store(mirror, std::memory_order_release);
     }
     return mirror;
 }
 
-void TensorObject::invalidateHost() const { std::free(host_.exchange(nullptr, std::memory_order_acq_rel)); }
+void TensorObject::invalidateHost() const { std::free(expr_->host.exchange(nullptr, std::memory_order_acq_rel)); }
 
 double TensorObject::getAsDouble(uint64_t i) const {
     const std::byte *p = rawData();
@@ -366,22 +508,59 @@ rtdata::Object *TensorObject::clone(mm::IAllocator &allocator, const type::Type 
     return copy;
 }
 
+// Text form of one element, as the reference prints it (modules/tensor/runtime.cpp:417-448):
+// float32 as "% 7.0f." when integral and below 1e10 in magnitude, else "% 7.4g"; int64 right
+// aligned in 7 columns; bool as "  true" / " false".
+static std::string elementText(const TensorObject &t, uint64_t flat) {
+    char text[48];
+    switch (t.dtype()) {
+    case TypeCode::Float32: {
+        const double v = t.getAsDouble(flat);
+        const bool whole = v == std::floor(v) && std::abs(v) < 1e10;
+        std::snprintf(text, sizeof(text), whole ? "% 7.0f." : "% 7.4g", v);
+        return text;
+    }
+    case TypeCode::Int64:
+        std::snprintf(text, sizeof(text), "%7lld", static_cast<long long>(reinterpret_cast<const int64_t *>(t.rawData())[flat]));
+        return text;
+    case TypeCode::Bool:
+        return t.getAsDouble(flat) != 0.0 ? "  true" : " false";
+    default:
+        return "?";
+    }
+}
+
+// Layout of modules/tensor/runtime.cpp:484-528: the innermost dimension on one line, wrapped
+// (", newline, indent") before an element that would pass column 100; every outer dimension puts
+// its slices on lines of their own, indented by 8 columns per level.
 void TensorObject::printLevel(std::ostream &os, size_t level, uint64_t &flat) const {
+    constexpr size_t kIndentStep = 8, kMaxWidth = 100;
     if (rank_ == 0) {
-        os << getAsDouble(0);
+        os << elementText(*this, 0);
         return;
     }
+    const std::string inner((level + 1) * kIndentStep, ' ');
     os << "[";
-    for (int64_t i = 0; i < shape_[level]; ++i) {
-        if (i > 0)
-            os << ", ";
-        if (level + 1 == rank_) {
-            if (dtype_ == TypeCode::Bool)
-                os << (getAsDouble(flat) != 0.0 ? "true" : "false");
-            else
-                os << getAsDouble(flat);
-            ++flat;
-        } else {
+    if (level + 1 == rank_) {
+        size_t width = inner.size();
+        for (int64_t i = 0; i < shape_[level]; ++i) {
+            const std::string text = elementText(*this, flat++);
+            if (i > 0) {
+                if (width + 2 + text.size() > kMaxWidth) {
+                    os << ",\n" << inner;
+                    width = inner.size();
+                } else {
+                    os << ", ";
+                    width += 2;
+                }
+            }
+            os << text;
+            width += text.size();
+        }
+    } else {
+        for (int64_t i = 0; i < shape_[level]; ++i) {
+            if (i > 0)
+                os << ",\n" << inner;
             printLevel(os, level + 1, flat);
         }
     }

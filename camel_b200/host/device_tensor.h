@@ -7,9 +7,16 @@
 // the runtime reads elements (print, equals, indexing, array conversion) - those reads are the
 // graph boundaries where a device-to-host copy is due.
 //
-// The collector that owns these objects has no finalisers (include/camel/core/mm/gen.h:224-227),
-// so device buffers are tracked in a registry and released by releaseAllDeviceBuffers() when the
-// module is unloaded or a host asks for it; objects released that way must not be used again.
+// The collector that owns these objects has no finalisers and its root set is never installed
+// (include/camel/core/mm/gen.h:224-227), so nothing ever tells the module that a tensor is dead.
+// The module therefore keeps its own books: every tensor has a record (Expr) on the C++ heap that
+// owns the device buffer and the host mirror and counts who still needs the buffer - the object
+// header, and every deferred computation that has it as an operand.  A host that knows where values
+// die brackets that region with beginScope() / endScope(): endScope releases what was created
+// inside, except the values it is told to keep (and whatever those still need).  A program of
+// the reference's training loops (test/run/nn/mnist.cml:33-41) then holds device memory flat.
+// Without scopes everything lives until releaseAllDeviceBuffers() at module unload.  A tensor whose
+// scope has ended must not be used again; using it raises instead of reading freed memory.
 #pragma once
 
 #include "camel/core/mm/alloc/allocator.h"
@@ -22,6 +29,7 @@
 #include <cstdint>
 #include <mutex>
 #include <span>
+#include <vector>
 #include <string>
 
 namespace camel::tensor {
@@ -46,8 +54,8 @@ using CompareOp = ct_compare_op;
 // subtract, divide, matmul) looks at the records of its operands and calls the fused entry point
 // instead (ct_relu, ct_dense with an activation, ct_softmax_rows, ct_matmul_tn, ct_scaled_sub);
 // the intermediate tensors are then never written.  Tensors are immutable values
-// (src/builtin/operators/ops.cpp:210) and device buffers live until the module is unloaded, so a
-// record can be evaluated at any later time with the same result.
+// (src/builtin/operators/ops.cpp:210) and a pending record keeps its operands' buffers alive
+// (it counts as a user of each), so it can be evaluated at any later time with the same result.
 //
 // Operators that can raise a data-dependent error (divide, log, pow) are never deferred, so every
 // error is still raised by the operator that the reference raises it from.
@@ -68,14 +76,24 @@ enum class ExprKind : uint8_t {
 
 // One record per tensor, on the C++ heap: operands refer to each other through these, because the
 // collector moves small object headers (include/camel/core/mm/gen.h:460-520).  `kind` and the
-// operands stay after evaluation - they are facts about an immutable value - and only `pending`
-// changes.  Fields other than `pending` are written before the tensor is handed out, or under
-// exprMutex().
+// operand pointers stay after evaluation - they are facts about an immutable value, and the idiom
+// recognisers compare them by identity - and only `pending`, `users` and `dead` change.  Fields
+// other than those are written before the tensor is handed out, or under exprMutex().
+//
+// Lifetime.  `users` counts who needs the device buffer: the object header (one, from creation
+// until the tensor's scope ends) and every record that is still pending and has this one as an
+// operand.  When it drops to zero the buffer, the packed form of a weight tensor and the host
+// mirror are freed and the record is marked dead.  The record itself stays allocated until the
+// module is unloaded (about a hundred bytes), so operand pointers never dangle and a use after the
+// end of a scope is caught instead of reading freed memory.
 struct Expr {
     ExprKind kind = ExprKind::Value;
     std::atomic<bool> pending{false};
+    std::atomic<bool> dead{false};
+    std::atomic<int> users{1};
     Expr *a = nullptr, *b = nullptr;
     std::atomic<void *> out{nullptr}; // the tensor's device buffer, allocated at first use (bufferOf)
+    std::atomic<std::byte *> host{nullptr}; // malloc'd host mirror, nullptr while there is none
     uint64_t bytes = 0;
     ct_dtype dtype = CT_F32;
     uint32_t rank  = 0;
@@ -102,6 +120,24 @@ void defer(TensorObject *out, ExprKind kind, const TensorObject *a, const Tensor
 // Deferral is on unless CAMEL_TENSOR_EAGER=1 is set when the module is loaded.
 bool lazyEvaluation();
 void setLazyEvaluation(bool on);
+// Replaces operand `which` (0: a, 1: b) of a pending record, moving its claim on the buffer.
+void rebindOperand(Expr *e, int which, Expr *to);
+
+// ---- scopes ------------------------------------------------------------------------------
+// beginScope() returns a token; endScope(token, keep) ends the life of every tensor created since
+// that token (on any thread) except those in `keep`, which pass to the enclosing scope.  What a kept
+// tensor still needs (operands of a computation it has deferred) survives with it.  Scopes nest;
+// tokens must be ended innermost first.  A scheduler calls these around a region whose only
+// surviving values it knows - a `sync` block or a function frame: its result slot is the keep list.
+uint64_t beginScope();
+void endScope(uint64_t token, std::span<TensorObject *const> keep);
+// Ends the life of one tensor, whichever scope it belongs to: for a host that knows a value's last
+// use (a loop variable that has just been replaced).  No effect on a tensor already released.
+void releaseTensor(TensorObject *t);
+// Bytes of device memory the module's tensors own right now (packed weight layouts included).
+uint64_t liveDeviceBytes();
+// Device-to-host copies made for host reads (print, equals, indexing) since the module was loaded.
+uint64_t hostReadCopies();
 
 class TensorObject : public rtdata::Object {
   public:
@@ -133,7 +169,7 @@ class TensorObject : public rtdata::Object {
         if (expr_->pending.load(std::memory_order_acquire))
             evaluate(expr_);
         void *p = expr_->out.load(std::memory_order_acquire);
-        return p ? p : bufferOf(expr_);
+        return p ? p : bufferOf(expr_); // bufferOf raises for a tensor whose scope has ended
     }
     // How this tensor came about (see Expr); never null, stable while the object moves.
     Expr *expr() const { return expr_; }
@@ -161,7 +197,6 @@ class TensorObject : public rtdata::Object {
     uint64_t numel_;
     uint64_t byteSize_;
     Expr *expr_;
-    mutable std::atomic<std::byte *> host_; // malloc'd mirror, nullptr while stale
     int64_t *shape_;
     int64_t dims_[]; // rank_ entries, in the same allocation as the header
 };
@@ -185,7 +220,7 @@ void ctCheck(ct_status status);
 // take one.  Tensors are immutable values, so the layout never goes stale.
 const void *packedWeightsFor(const TensorObject *w, int64_t k, int64_t n);
 
-// Releases every device buffer created so far (module unload / explicit scope end).
+// Releases every device buffer and record created so far (module unload).
 void releaseAllDeviceBuffers();
 size_t liveDeviceBuffers();
 

@@ -1,5 +1,7 @@
-// Plain-C test harness around the plugin's operator table: builds ArgsViews from raw buffers,
-// calls an operator body exactly as Camel's executors do - op(withView, normView, ctx)
+// NOT part of tensor.cmo: a plain-C harness around the plugin's operator table, linked only into
+// libcamel_tensor_host_test.so (tests and the bench's plugin leg).  It stands in for the `camel`
+// executable, which cannot be built without Clang/Conan/ANTLR: it builds ArgsViews from raw
+// buffers, calls an operator body exactly as Camel's executors do - op(withView, normView, ctx)
 // (src/passes/sched/nodevm/nodevm.cpp:588) - and hands the result back as raw buffers.  The
 // argument and result structs have the layout of the oracle's reference driver, so one Python
 // front end drives both the reference module and this plugin.
@@ -62,6 +64,7 @@ class ScratchAllocator final : public mm::IAllocator {
 };
 
 ScratchAllocator g_scratch;
+ScratchAllocator g_persist; // values that outlive the steps of a loop (weights); released when the loop starts
 void *g_lastOut = nullptr;
 
 TypeCode dtypeCode(int d) { return d == 0 ? TypeCode::Float32 : (d == 1 ? TypeCode::Int64 : TypeCode::Bool); }
@@ -75,12 +78,62 @@ Type *tensorTypeFor(int dtype) {
     return cache[k];
 }
 
+// A nested Camel array (the value of a literal such as [[1.0, 2.0], [3.0, 4.0]]) and its type;
+// leaf codes: 0 float32, 1 int64, 2 bool, 3 float64, 4 int32.
+Type *leafType(int dtype) {
+    switch (dtype) {
+    case 0:
+        return Type::Float32();
+    case 1:
+        return Type::Int64();
+    case 2:
+        return Type::Bool();
+    case 3:
+        return Type::Float64();
+    default:
+        return Type::Int32();
+    }
+}
+
+Type *nestedArrayType(int dtype, int rank) {
+    Type *t = leafType(dtype);
+    for (int level = 0; level < rank; ++level)
+        t = ArrayType::create(t);
+    return t;
+}
+
+::Array *nestedArray(int dtype, int rank, const int64_t *shape, const double *&leaves) {
+    using camel::core::rtdata::Object;
+    ::Array *arr = ::Array::create(g_scratch, static_cast<size_t>(shape[0]));
+    for (int64_t i = 0; i < shape[0]; ++i) {
+        const size_t at = static_cast<size_t>(i);
+        if (rank > 1) {
+            arr->set<Object *>(at, static_cast<Object *>(nestedArray(dtype, rank - 1, shape + 1, leaves)));
+            continue;
+        }
+        const double v = *leaves++;
+        if (dtype == 0)
+            arr->set<float>(at, static_cast<float>(v));
+        else if (dtype == 1)
+            arr->set<int64_t>(at, static_cast<int64_t>(v));
+        else if (dtype == 2)
+            arr->set<bool>(at, v != 0.0);
+        else if (dtype == 3)
+            arr->set<double>(at, v);
+        else
+            arr->set<int32_t>(at, static_cast<int32_t>(v));
+    }
+    return arr;
+}
+
 } // namespace
 
 extern "C" {
 
-// kind (low byte): 0 tensor, 1 int64, 2 float64, 3 float32, 4 int32, 5 bool, 6 int64 array;
-// kind | 0x100 places the argument in the `with` list instead of the `norm` list.
+// kind (low byte): 0 tensor, 1 int64, 2 float64, 3 float32, 4 int32, 5 bool, 6 int64 array,
+// 7 session handle, 8 nested array literal (`rank` levels of extents `shape`, leaves from `data`
+// as doubles, leaf type `dtype`); kind | 0x100 places the argument in the `with` list instead of
+// the `norm` list.
 struct camel_host_arg {
     int32_t kind, dtype, rank, pad_;
     const int64_t *shape;
@@ -157,6 +210,13 @@ static std::string buildArgs(int nargs, const camel_host_arg *args, VecArgsView 
                 return "bad session handle";
             dst.slots.push_back(g_session[static_cast<size_t>(a.i64)].slot);
             dst.types.push_back(g_session[static_cast<size_t>(a.i64)].type);
+            break;
+        }
+        case 8: {
+            const double *leaves = static_cast<const double *>(a.data);
+            ::Array *arr         = nestedArray(a.dtype, a.rank, a.shape, leaves);
+            dst.slots.push_back(camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(arr)));
+            dst.types.push_back(nestedArrayType(a.dtype, a.rank));
             break;
         }
         default:
@@ -446,6 +506,223 @@ int camel_host_threads_idioms(const float *host, int64_t rows, int64_t cols, int
         return failed;
     } catch (const std::exception &e) {
         return failWith(err, errlen, -1, e.what());
+    }
+}
+
+// ---- what the module keeps on the device, and the scopes that end it -------------------------
+
+uint64_t camel_host_live_device_bytes(void) { return camel::tensor::liveDeviceBytes(); }
+uint64_t camel_host_live_device_buffers(void) { return camel::tensor::liveDeviceBuffers(); }
+uint64_t camel_host_read_copies(void) { return camel::tensor::hostReadCopies(); }
+
+// A scope over session values: everything created after `begin` except the handles in `keep` is
+// released at `end` (the values stay in the session table but must not be used again).
+uint64_t camel_host_scope_begin(void) { return camel::tensor::beginScope(); }
+
+int camel_host_scope_end(uint64_t token, int nkeep, const int64_t *keep, char *err, int errlen) {
+    try {
+        std::vector<TensorObject *> kept;
+        for (int i = 0; i < nkeep; ++i) {
+            if (keep[i] < 0 || keep[i] >= static_cast<int64_t>(g_session.size()) || g_session[keep[i]].kind != 0)
+                return failWith(err, errlen, 2, "bad session handle in the keep list");
+            kept.push_back(camel::core::rtdata::fromSlot<TensorObject *>(g_session[keep[i]].slot));
+        }
+        camel::tensor::endScope(token, kept);
+        return 0;
+    } catch (const std::exception &e) {
+        return failWith(err, errlen, 1, e.what());
+    }
+}
+
+// The training loop of test/run/nn/mnist.cml:27-41 (`update`, applied `steps` times), operator by
+// operator through the plugin's bodies, each step inside a scope whose only surviving value is the
+// new W - what a scheduler does that ends a frame when `update` returns.  x [n, d] (bias column
+// included), y one-hot [n, classes], w [d, classes] in, w out.  live_bytes_out (may be null)
+// receives the module's device bytes after every step; seconds_out the wall time of the loop
+// including the final read-back.  use_scopes == 0 runs the same loop without scopes.
+int camel_host_sgd_loop(
+    const float *x, const float *y, float *w, int64_t n, int64_t d, int64_t classes, double lr, int steps,
+    int use_scopes, uint64_t *live_bytes_out, double *seconds_out, char *err, int errlen) {
+    try {
+        g_session.clear();
+        g_scratch.releaseAll();
+        camel::tensor::releaseAllDeviceBuffers();
+        static const auto ops = getTensorOpsMap();
+        camel::core::context::Context *nullCtx = nullptr;
+        using camel::core::rtdata::fromSlot;
+        using camel::core::rtdata::toSlot;
+        using Arg = std::pair<slot_t, Type *>;
+        auto call = [&](const char *op, std::initializer_list<Arg> args) {
+            VecArgsView with, norm;
+            for (const auto &a : args) {
+                norm.slots.push_back(a.first);
+                norm.types.push_back(a.second);
+            }
+            return ops.at(op)(with, norm, *nullCtx);
+        };
+        auto objSlot = [](TensorObject *t) { return toSlot(static_cast<camel::core::rtdata::Object *>(t)); };
+        auto shapeArg = [&](int64_t a, int64_t b) -> Arg {
+            ::Array *arr = ::Array::create(g_scratch, 2);
+            arr->set<int64_t>(0, a);
+            arr->set<int64_t>(1, b);
+            return {toSlot(static_cast<camel::core::rtdata::Object *>(arr)), intArrayType()};
+        };
+        Type *f32T = tensorTypeFor(0);
+        int64_t xs[2] = {n, d}, ys[2] = {n, classes}, ws[2] = {d, classes};
+        Arg X{objSlot(TensorObject::fromHost(TypeCode::Float32, xs, x, g_scratch)), f32T};
+        Arg Y{objSlot(TensorObject::fromHost(TypeCode::Float32, ys, y, g_scratch)), f32T};
+        Arg W{objSlot(TensorObject::fromHost(TypeCode::Float32, ws, w, g_scratch)), f32T};
+        Arg one{toSlot<int64_t>(1), Type::Int64()};
+        ct_sync();
+        auto t0 = std::chrono::steady_clock::now();
+        for (int step = 0; step < steps; ++step) {
+            uint64_t scope = use_scopes ? camel::tensor::beginScope() : 0;
+            // let logits = X @ W;  let probs = softmax(logits)            (mnist.cml:13-25, 29-30)
+            Arg logits{call("matmul", {X, W}), f32T};
+            Arg rowMax{call("max_axis", {logits, one}), f32T};
+            Arg rowMax2{call("reshape", {rowMax, shapeArg(n, 1)}), f32T};
+            Arg ones1{call("ones", {shapeArg(1, classes)}), f32T};
+            Arg spreadMax{call("matmul", {rowMax2, ones1}), f32T};
+            Arg stable{call("subtract", {logits, spreadMax}), f32T};
+            Arg expLogits{call("exp", {stable}), f32T};
+            Arg rowSum{call("sum_axis", {expLogits, one}), f32T};
+            Arg rowSum2{call("reshape", {rowSum, shapeArg(n, 1)}), f32T};
+            Arg ones2{call("ones", {shapeArg(1, classes)}), f32T};
+            Arg spreadSum{call("matmul", {rowSum2, ones2}), f32T};
+            Arg probs{call("divide", {expLogits, spreadSum}), f32T};
+            // let grad = transpose(X) @ (probs - y_onehot);  W - lr * (1.0 / m) * grad   (mnist.cml:32-33)
+            Arg diff{call("subtract", {probs, Y}), f32T};
+            Arg xt{call("transpose", {X}), f32T};
+            Arg grad{call("matmul", {xt, diff}), f32T};
+            Arg scale{toSlot<double>(lr * (1.0 / static_cast<double>(n))), Type::Float64()};
+            Arg scaled{call("multiply", {scale, grad}), f32T};
+            Arg next{call("subtract", {W, scaled}), f32T};
+            if (use_scopes) {
+                TensorObject *keep[1] = {fromSlot<TensorObject *>(next.first)};
+                keep[0]->deviceData(); // the frame's result is computed before the frame ends
+                camel::tensor::endScope(scope, keep);
+            }
+            if (use_scopes) // the loop variable has been replaced: the old weights have had their last use
+                camel::tensor::releaseTensor(fromSlot<TensorObject *>(W.first));
+            W = next;
+            if (live_bytes_out)
+                live_bytes_out[step] = camel::tensor::liveDeviceBytes();
+        }
+        TensorObject *wt = fromSlot<TensorObject *>(W.first);
+        std::memcpy(w, wt->rawData(), wt->byteSize());
+        auto t1 = std::chrono::steady_clock::now();
+        if (seconds_out)
+            *seconds_out = std::chrono::duration<double>(t1 - t0).count();
+        if (ct_check() != CT_OK)
+            return failWith(err, errlen, 1, ct_last_error());
+        return 0;
+    } catch (const camel::core::error::RuntimeFault &f) {
+        return failWith(err, errlen, 1, faultText(f));
+    } catch (const std::exception &e) {
+        return failWith(err, errlen, 1, e.what());
+    }
+}
+
+// The MLP forward of a Camel program, per step, the way a scheduler runs it: the batch arrives in
+// host memory (a tensor is made from it: one host-to-device copy), three operator calls through
+// operator_t, then the host reads the probabilities and the arg-max back (two device-to-host
+// copies through the tensor's host view); the step's values die with its frame (a scope).
+// Weights are tensors that live across steps.  mode 0: the fused operators dense_relu<w,b>,
+// dense_relu<w,b>, dense_softmax<w,b>, argmax.  mode 1: the module's small operators only, as the
+// reference's programs spell them - `x @ w`, `h * (h > 0)`, the softmax function of
+// mnist.cml:13-25 (no bias terms) - which run through the deferred-expression recognisers.
+// x: [steps_distinct][batch][d0] host batches used round-robin.  probs/argmax receive the last
+// step's results; step_seconds[steps] the wall time of every step.
+int camel_host_mlp_forward(
+    int mode, const float *x, int steps_distinct, int64_t batch, int64_t d0, int64_t d1, int64_t d2, int64_t d3,
+    const float *w1, const float *b1, const float *w2, const float *b2, const float *w3, const float *b3, int steps,
+    float *probs, int64_t *argmax, double *step_seconds, uint64_t *launches_out, char *err, int errlen) {
+    try {
+        g_session.clear();
+        g_scratch.releaseAll();
+        g_persist.releaseAll();
+        camel::tensor::releaseAllDeviceBuffers();
+        camel::tensor::setLazyEvaluation(true);
+        static const auto ops = getTensorOpsMap();
+        camel::core::context::Context *nullCtx = nullptr;
+        using camel::core::rtdata::fromSlot;
+        using camel::core::rtdata::toSlot;
+        using Arg = std::pair<slot_t, Type *>;
+        auto call = [&](const char *op, std::initializer_list<Arg> with_args, std::initializer_list<Arg> args) {
+            VecArgsView with, norm;
+            for (const auto &a : with_args) {
+                with.slots.push_back(a.first);
+                with.types.push_back(a.second);
+            }
+            for (const auto &a : args) {
+                norm.slots.push_back(a.first);
+                norm.types.push_back(a.second);
+            }
+            return ops.at(op)(with, norm, *nullCtx);
+        };
+        auto objSlot = [](TensorObject *t) { return toSlot(static_cast<camel::core::rtdata::Object *>(t)); };
+        auto shapeArg = [&](int64_t a, int64_t b) -> Arg {
+            ::Array *arr = ::Array::create(g_scratch, 2);
+            arr->set<int64_t>(0, a);
+            arr->set<int64_t>(1, b);
+            return {toSlot(static_cast<camel::core::rtdata::Object *>(arr)), intArrayType()};
+        };
+        Type *f32T = tensorTypeFor(0), *i64T = tensorTypeFor(1);
+        auto weight = [&](const float *host, int64_t r, int64_t c) -> Arg {
+            int64_t shape[2] = {r, c};
+            return {objSlot(TensorObject::fromHost(TypeCode::Float32, std::span<const int64_t>(shape, c ? 2 : 1), host, g_persist)), f32T};
+        };
+        Arg W1 = weight(w1, d0, d1), W2 = weight(w2, d1, d2), W3 = weight(w3, d2, d3);
+        Arg B1 = weight(b1, d1, 0), B2 = weight(b2, d2, 0), B3 = weight(b3, d3, 0);
+        Arg one{toSlot<int64_t>(1), Type::Int64()};
+        auto softmaxIdiom = [&](Arg logits, int64_t n, int64_t k) -> Arg {
+            Arg rowMax2{call("reshape", {}, {Arg{call("max_axis", {}, {logits, one}), f32T}, shapeArg(n, 1)}), f32T};
+            Arg spreadMax{call("matmul", {}, {rowMax2, Arg{call("ones", {}, {shapeArg(1, k)}), f32T}}), f32T};
+            Arg expLogits{call("exp", {}, {Arg{call("subtract", {}, {logits, spreadMax}), f32T}}), f32T};
+            Arg rowSum2{call("reshape", {}, {Arg{call("sum_axis", {}, {expLogits, one}), f32T}, shapeArg(n, 1)}), f32T};
+            Arg spreadSum{call("matmul", {}, {rowSum2, Arg{call("ones", {}, {shapeArg(1, k)}), f32T}}), f32T};
+            return {call("divide", {}, {expLogits, spreadSum}), f32T};
+        };
+        auto reluIdiom = [&](Arg h) -> Arg {
+            Arg zero{toSlot<double>(0.0), Type::Float64()};
+            Arg mask{call("gt", {}, {h, zero}), tensorTypeFor(2)};
+            return {call("multiply", {}, {h, mask}), f32T};
+        };
+        const uint64_t launches0 = ct_launch_count();
+        for (int step = 0; step < steps; ++step) {
+            const float *batch_host = x + static_cast<size_t>(step % steps_distinct) * batch * d0;
+            auto t0           = std::chrono::steady_clock::now();
+            uint64_t scope    = camel::tensor::beginScope();
+            int64_t xshape[2] = {batch, d0};
+            Arg X{objSlot(TensorObject::fromHost(TypeCode::Float32, xshape, batch_host, g_scratch)), f32T};
+            Arg P{0, f32T};
+            if (mode == 0) {
+                Arg h1{call("dense_relu", {W1, B1}, {X}), f32T};
+                Arg h2{call("dense_relu", {W2, B2}, {h1}), f32T};
+                P = Arg{call("dense_softmax", {W3, B3}, {h2}), f32T};
+            } else {
+                Arg h1 = reluIdiom(Arg{call("matmul", {}, {X, W1}), f32T});
+                Arg h2 = reluIdiom(Arg{call("matmul", {}, {h1, W2}), f32T});
+                P      = softmaxIdiom(Arg{call("matmul", {}, {h2, W3}), f32T}, batch, d3);
+            }
+            Arg A{call("argmax_axis", {}, {P, one}), i64T};
+            TensorObject *pt = fromSlot<TensorObject *>(P.first), *at = fromSlot<TensorObject *>(A.first);
+            std::memcpy(probs, pt->rawData(), pt->byteSize());
+            std::memcpy(argmax, at->rawData(), at->byteSize());
+            camel::tensor::endScope(scope, {});
+            if ((step & 15) == 15)
+                g_scratch.releaseAll(); // headers of finished steps (the weights' come from g_persist)
+            step_seconds[step] = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        }
+        if (launches_out)
+            *launches_out = ct_launch_count() - launches0;
+        if (ct_check() != CT_OK)
+            return failWith(err, errlen, 1, ct_last_error());
+        return 0;
+    } catch (const camel::core::error::RuntimeFault &f) {
+        return failWith(err, errlen, 1, faultText(f));
+    } catch (const std::exception &e) {
+        return failWith(err, errlen, 1, e.what());
     }
 }
 

@@ -233,7 +233,7 @@ TensorObject *tryRelu(TensorObject *a, TensorObject *b) {
         // The product of the matmul was never written.  If the mask is read later it is taken from
         // the result: (h > 0) == (h * (h > 0) > 0) for every h (-0.0, NaN and infinities included).
         if (stillPending(mask))
-            mask->a = out->expr();
+            ctn::rebindOperand(mask, 0, out->expr());
     } else {
         ctn::evaluate(h);
         ctn::ctCheck(ct_relu(f32(h), h->numel, static_cast<float *>(out->deviceData())));
@@ -272,6 +272,8 @@ TensorObject *trySoftmax(TensorObject *a, TensorObject *b) {
         return nullptr;
     if (!isF32(logits) || logits->rank != 2 || logits->numel == 0)
         return nullptr;
+    if (logits->dead.load(std::memory_order_acquire))
+        return nullptr; // matched through records that have already run: the logits themselves are gone
     TensorObject *out = newTensor(TypeCode::Float32, shapeOf(a));
     auto *dst         = static_cast<float *>(out->deviceData());
     bool transposedLhs =

@@ -22,6 +22,13 @@
  *    error, synchronise that stream before returning; the others do not.
  *  - There is no CPU fallback: without a usable CUDA device every compute entry point
  *    returns CT_ERR_NO_DEVICE.
+ *  - The selected device belongs to the process, not to the calling thread: every entry point
+ *    makes it the calling thread's current CUDA device before it does anything else, so worker
+ *    threads of a scheduler need no set-up of their own.
+ *  - Environment, read once at first use: CAMEL_TENSOR_PRECISION = 3xtf32 | bf16 and
+ *    CAMEL_TENSOR_DEVICES = "2" or "0,1,2,3" (the process takes the entry at index LOCAL_RANK,
+ *    else CAMEL_TENSOR_RANK, else 0, modulo the list's length); ct_set_precision / ct_set_device
+ *    override them, a malformed value makes the first call fail with CT_ERR_INVALID.
  */
 #ifndef CAMEL_TENSOR_B200_H
 #define CAMEL_TENSOR_B200_H
@@ -76,8 +83,16 @@ ct_status ct_set_stream(void *stream);
 ct_status ct_sync(void);
 /* Synchronises and reports errors that kernels of earlier asynchronous calls raised on the
  * device (CT_ERR_TIMEOUT: a bounded wait in a contraction kernel ran out; its output is then
- * undefined). */
+ * undefined).  The record is sticky: no entry point clears it on the way in, contraction kernels
+ * launched after it return at once without writing, and it stays until ct_check (or a *_host
+ * entry point) has reported it once - so a failure between two checks is never lost, however many
+ * calls were enqueued after it.  ct_matmul_f32_static keeps its own status word (status_dev) and
+ * is not covered by ct_check. */
 ct_status ct_check(void);
+/* Host-side fault injection for tests of that path: writes device error word `word` (0 division
+ * by zero, 1 log domain, 2 kernel timeout) with `value` (1..255) in stream order, as if a kernel
+ * had raised it.  Nothing on the GPU waits, traps or faults.  No reference counterpart. */
+ct_status ct_inject_status(int word, uint32_t value);
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t ct_launch_count(void);
 /* Device timing per kernel family: while enabled, each launch is bracketed by CUDA events on
@@ -86,6 +101,14 @@ uint64_t ct_launch_count(void);
  * "softmax"); NULL reads all. */
 ct_status ct_profile_enable(int on);
 ct_status ct_profile_read(const char *kernel, double *total_ms_host, uint64_t *launches_host);
+/* The tensor pipe's own ceiling, measured: every SM issues `mma_groups` x 4 tcgen05.mma of
+ * 128 x 256 x (32 bytes of k) back to back on operands already in shared memory (kind::tf32 for
+ * CT_PREC_3XTF32, kind::f16 on bf16 for CT_PREC_BF16), `launches` launches in a row, timed with
+ * CUDA events.  A short burst (one launch of ~50 us) and a seconds-long run give the two figures
+ * a roofline needs: the 3xTF32 contractions spend three such MMAs per product, so their ceiling
+ * is the tf32 figure / 3.  No reference counterpart (a measurement, not an operator). */
+ct_status ct_measure_mma_peak(
+    ct_precision kind, int mma_groups, int launches, double *tflops_host, double *ms_host);
 ct_status ct_set_precision(ct_precision precision);
 ct_precision ct_get_precision(void);
 

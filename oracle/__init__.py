@@ -33,11 +33,23 @@ class OracleError(RuntimeError):
     pass
 
 
+def reference_checkout() -> str | None:
+    """Where the reference's sources are: $CAMEL_REF, else the sibling folder `reference` next to
+    the repository; None if neither holds the tensor module."""
+    import os
+
+    for cand in (os.environ.get("CAMEL_REF"), str(HERE.parent.parent / "reference")):
+        if cand and (Path(cand) / "modules" / "tensor" / "runtime.cpp").exists():
+            return cand
+    return None
+
+
 def build(ref: bool = True) -> None:
     """Compiles the checkers (make); the reference one only where its sources are present."""
     subprocess.run(["make", "-s", "-C", str(HERE), "oracle"], check=True)
-    if ref:
-        subprocess.run(["make", "-s", "-j8", "-C", str(HERE), "all"], check=True)
+    src = reference_checkout() if ref else None
+    if src:
+        subprocess.run(["make", "-s", "-j8", "-C", str(HERE), "all", f"REF={src}"], check=True)
 
 
 def norm(a) -> tuple[np.ndarray, int]:
@@ -256,6 +268,19 @@ class IntArray:
         self.items = [int(i) for i in items]
 
 
+class NestedArray:
+    """Marks a (nested) list as a Camel array literal, e.g. [[1.0, 2.0], [3.0, 4.0]]; `leaf` names
+    the element type of the innermost arrays: "f32", "i64", "bool", "f64" or "i32"."""
+
+    LEAF = {"f32": 0, "i64": 1, "bool": 2, "f64": 3, "i32": 4}
+
+    def __init__(self, items, leaf="f64"):
+        self.values = np.ascontiguousarray(np.asarray(items, dtype=np.float64))
+        if self.values.ndim < 1:
+            raise OracleError("an array literal has at least one level")
+        self.leaf = self.LEAF[leaf]
+
+
 class Float32(float):
     """Marks a scalar as Camel float32 (plain Python floats are float64)."""
 
@@ -331,6 +356,10 @@ def _marshal(args):
             shp = (C.c_int64 * max(1, arr.ndim))(*arr.shape)
             keep += [arr, shp]
             x.kind, x.dtype, x.rank, x.shape, x.data = 0, dt, arr.ndim, shp, arr.ctypes.data
+        elif isinstance(a, NestedArray):
+            shp = (C.c_int64 * a.values.ndim)(*a.values.shape)
+            keep += [a.values, shp]
+            x.kind, x.dtype, x.rank, x.shape, x.data = 8, a.leaf, a.values.ndim, shp, a.values.ctypes.data
         elif isinstance(a, IntArray):
             shp = (C.c_int64 * max(1, len(a.items)))(*a.items)
             keep.append(shp)

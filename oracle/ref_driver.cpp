@@ -72,6 +72,60 @@ class InputAllocator final : public mm::IAllocator {
 
 InputAllocator g_inputs;
 size_t g_nurseryBytes = 0;
+
+// A nested Camel array (the value of a literal such as [[1.0, 2.0], [3.0, 4.0]]) and its type.
+Type *leafType(int dtype) {
+    switch (dtype) {
+    case 0:
+        return Type::Float32();
+    case 1:
+        return Type::Int64();
+    case 2:
+        return Type::Bool();
+    case 3:
+        return Type::Float64();
+    default:
+        return Type::Int32();
+    }
+}
+
+Type *nestedArrayType(int dtype, int rank) {
+    Type *t = leafType(dtype);
+    for (int level = 0; level < rank; ++level)
+        t = ArrayType::create(t);
+    return t;
+}
+
+::Array *nestedArray(int dtype, int rank, const int64_t *shape, const double *&leaves, mm::IAllocator &alloc) {
+    ::Array *arr = ::Array::create(alloc, static_cast<size_t>(shape[0]));
+    for (int64_t i = 0; i < shape[0]; ++i) {
+        if (rank > 1) {
+            arr->set<camel::core::rtdata::Object *>(
+                static_cast<size_t>(i),
+                static_cast<camel::core::rtdata::Object *>(nestedArray(dtype, rank - 1, shape + 1, leaves, alloc)));
+            continue;
+        }
+        double v = *leaves++;
+        switch (dtype) {
+        case 0:
+            arr->set<float>(static_cast<size_t>(i), static_cast<float>(v));
+            break;
+        case 1:
+            arr->set<int64_t>(static_cast<size_t>(i), static_cast<int64_t>(v));
+            break;
+        case 2:
+            arr->set<bool>(static_cast<size_t>(i), v != 0.0);
+            break;
+        case 3:
+            arr->set<double>(static_cast<size_t>(i), v);
+            break;
+        default:
+            arr->set<int32_t>(static_cast<size_t>(i), static_cast<int32_t>(v));
+            break;
+        }
+    }
+    return arr;
+}
 void *g_lastOut       = nullptr;
 
 TypeCode dtypeCode(int dtype) {
@@ -118,8 +172,9 @@ Type *tensorTypeFor(int dtype) {
 extern "C" {
 
 // kind: 0 tensor, 1 int64 scalar, 2 float64 scalar, 3 float32 scalar, 4 int32 scalar,
-//       5 bool scalar, 6 int64 array (e.g. a shape)
-// dtype (tensors): 0 float32, 1 int64, 2 bool(u8)
+//       5 bool scalar, 6 int64 array (e.g. a shape), 8 nested array literal: `rank` levels of
+//       extents `shape`, leaves read from `data` (doubles, row-major) as the type `dtype` names
+// dtype (tensors): 0 float32, 1 int64, 2 bool(u8); (array leaves): also 3 float64, 4 int32
 struct camel_ref_arg {
     int32_t kind;
     int32_t dtype;
@@ -215,6 +270,14 @@ int camel_ref_call(
                     camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(arr)));
                 static Type *intArray = ArrayType::create(Type::Int64());
                 norm.types.push_back(intArray);
+                break;
+            }
+            case 8: {
+                const double *leaves = static_cast<const double *>(a.data);
+                ::Array *arr         = nestedArray(a.dtype, a.rank, a.shape, leaves, g_inputs);
+                norm.slots.push_back(
+                    camel::core::rtdata::toSlot(static_cast<camel::core::rtdata::Object *>(arr)));
+                norm.types.push_back(nestedArrayType(a.dtype, a.rank));
                 break;
             }
             default:

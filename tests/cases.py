@@ -457,3 +457,75 @@ CASES = build_cases()
 
 # Cases whose outputs involve tensor-core contractions on the GPU (compared by tolerance there).
 TOLERANCE_CASES = {name for name, _ in CASES if name.startswith(("matmul_f32", "dense_layers", "conv2d_"))}
+
+
+# ---- the graph boundary: array literals in, host reads out ---------------------------------
+#
+# Calls that go through `backend.call(op, *args)` of oracle.Reference (the compiled reference, or
+# the plugin's harness - same front end).  Each entry: (name, op, argument builder).  The golden
+# file tests/golden/boundary.json holds what the compiled reference returned / printed.
+
+def capture_stdout(fn):
+    """Runs fn() and returns (its result, what the process wrote to file descriptor 1 meanwhile):
+    `show` prints from C++."""
+    import os
+    import sys
+    import tempfile
+
+    sys.stdout.flush()
+    saved = os.dup(1)
+    with tempfile.TemporaryFile() as tmp:
+        os.dup2(tmp.fileno(), 1)
+        try:
+            result = fn()
+        finally:
+            os.dup2(saved, 1)
+            os.close(saved)
+        tmp.seek(0)
+        return result, tmp.read().decode()
+
+
+def boundary_cases():
+    from oracle import NestedArray
+
+    lit = [[1.5, -2.0, 3.25], [4.0, 5.5, -0.0]]
+    f = np.array([[1.5, -2.0, 3.0], [4.0, 5.5, 0.0]], np.float32)
+    wide = (np.arange(40, dtype=np.float32).reshape(2, 20) - 7.5) * np.float32(1.0e3 / 3)
+    cube = np.arange(24, dtype=np.float32).reshape(2, 3, 4) / 8
+    return [
+        # tensorFromArray (runtime.cpp:153-219, 1067-1077): dtype from the leaf type
+        ("from_array_f64", "reshape", lambda: (NestedArray(lit, "f64"), IntArray([3, 2]))),
+        ("from_array_f32", "reshape", lambda: (NestedArray(lit, "f32"), IntArray([6]))),
+        ("from_array_i64", "reshape", lambda: (NestedArray([[1, 2], [3, 4], [5, 6]], "i64"), IntArray([2, 3]))),
+        ("from_array_i32_rank3", "reshape", lambda: (NestedArray(np.arange(24).reshape(2, 3, 4), "i32"), IntArray([4, 6]))),
+        ("from_array_bool", "reshape", lambda: (NestedArray([[1, 0, 1]], "bool"), IntArray([3]))),
+        ("concat_arrays", "concat", lambda: (NestedArray(lit, "f64"), NestedArray([[7.0, 8.0, 9.0]], "f64"), 0)),
+        # == with an array operand (operators.cpp:923-956)
+        ("eq_tensor_array", "eq", lambda: (f, NestedArray(lit, "f64"))),
+        ("eq_array_tensor", "eq", lambda: (NestedArray(lit, "f64"), f)),
+        ("eq_array_scalar", "eq", lambda: (NestedArray([1, 2, 2, 3], "i64"), 2)),
+        # host reads (runtime.cpp:1047-1065, 606-612)
+        ("idx_1d", "idx", lambda: (np.array([0.5, 1.5, -2.5, 1e-3], np.float32), 2)),
+        ("idx_1d_int", "idx", lambda: (np.arange(5) * 3, 4)),
+        ("idx_2d", "idx2d", lambda: (f, 1, 2)),
+        ("shape_rank3", "shape", lambda: (cube,)),
+        # print (runtime.cpp:417-528): element formats, row wrapping at column 100, nesting
+        ("show_f32", "show", lambda: (f,)),
+        ("show_wrapped_rows", "show", lambda: (wide,)),
+        ("show_rank3", "show", lambda: (cube,)),
+        ("show_rank1_mixed", "show", lambda: (np.array([0.0, -0.0, 1e10, 12345.678, 1e-5, np.inf, np.nan, -1.0], np.float32),)),
+        ("show_bool", "show", lambda: (np.array([[1, 0], [0, 1]], np.uint8),)),
+        ("show_array_literal", "show", lambda: (NestedArray(lit, "f64"),)),
+        ("show_empty", "show", lambda: (np.zeros((0, 3), np.float32),)),
+    ]
+
+
+def run_boundary_case(backend, op, build_args):
+    """-> a JSON-able record of what the call returned and printed."""
+    result, printed = capture_stdout(lambda: backend.call(op, *build_args()))
+    if isinstance(result, np.ndarray):
+        rec = {"dtype": str(result.dtype), "shape": list(result.shape), "hex": result.tobytes().hex()}
+    else:
+        rec = {"value": result}
+    rec["printed"] = printed
+    return rec

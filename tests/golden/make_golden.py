@@ -19,7 +19,7 @@ sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
 
 import oracle  # noqa: E402
-from cases import CASES, RefBackend  # noqa: E402
+from cases import CASES, RefBackend, boundary_cases, run_boundary_case  # noqa: E402
 
 
 def main():
@@ -32,6 +32,13 @@ def main():
     path = Path(__file__).resolve().parent / "tensor_ops.npz"
     np.savez_compressed(path, **out)
     print(f"wrote {path}: {len(out)} arrays, {path.stat().st_size / 1e6:.2f} MB")
+    # array literals in, host reads and printed text out (tests/cases.py: boundary_cases)
+    import json
+
+    boundary = {name: run_boundary_case(oracle.ref(), op, build) for name, op, build in boundary_cases()}
+    bpath = Path(__file__).resolve().parent / "boundary.json"
+    bpath.write_text(json.dumps(boundary, indent=1) + "\n")
+    print(f"wrote {bpath}: {len(boundary)} calls")
     # group \t uri \t signature of getTensorOperatorGroups() (modules/tensor/operators.cpp:196-583)
     table = Path(__file__).resolve().parent / "operator_table.tsv"
     table.write_text("".join("\t".join(row) + "\n" for row in oracle.ref().groups()))

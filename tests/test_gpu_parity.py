@@ -893,3 +893,88 @@ def test_full_size_conv_linearity(T):
     ref = oracle.port().conv2d(x1[:2].cpu().numpy(), wt.cpu().numpy(), np.zeros(128, np.float32), 1, 1, 0)
     got = y1[:2].cpu().numpy()
     assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) <= 1e-5
+
+
+def test_gemm_bf16_mode_long_k(T):
+    """bf16-in / float32-accumulate at a long reduction (k = 16384, the k of BASELINE configs[4]),
+    against float64: the stated tolerance of that mode, 1e-2 of the largest entry, and the
+    component-wise error against sum |a||b| (bf16 rounding of both operands: 2^-8 each)."""
+    import camel_b200
+    from camel_b200 import _lib
+
+    rng = np.random.default_rng(61)
+    m, k, n = 1024, 16384, 1024
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    _lib.check(camel_b200.lib.ct_set_precision(_lib.PREC_BF16))
+    try:
+        got = T.matmul(T.from_numpy(a), T.from_numpy(b)).numpy()
+        T.check_async()
+    finally:
+        _lib.check(camel_b200.lib.ct_set_precision(_lib.PREC_3XTF32))
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    err = float(np.max(np.abs(got - ref)) / np.max(np.abs(ref)))
+    comp = float(np.max(np.abs(got - ref) / (np.abs(a).astype(np.float64) @ np.abs(b))))
+    print(f"bf16 {m}x{k}x{n}: max|d|/max|ref|={err:.3e} componentwise={comp:.3e}")
+    assert err <= 1e-2
+    assert comp <= 2.0 ** -7
+
+
+def test_kernel_timeout_is_reported_once_and_sticks_until_checked(T):
+    """The error path of a bounded in-kernel wait, exercised from the host: the timeout word is
+    written as a kernel would write it (ct_inject_status; nothing on the GPU waits).  While it is
+    set, contraction kernels return at once without writing; calls enqueued after it do not erase
+    it; ct_check reports it exactly once with the block that gave up; afterwards products are
+    correct again."""
+    import time
+
+    import camel_b200
+    from camel_b200._lib import ERR_TIMEOUT, check, lib
+
+    rng = np.random.default_rng(62)
+    a_np = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
+    b_np = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
+    a, b = T.from_numpy(a_np), T.from_numpy(b_np)
+    good = T.matmul(a, b).numpy()
+    T.check_async()
+
+    out = T.Tensor(0, (512, 512))
+    check(lib.ct_fill(0, 7.0, 512 * 512, out.ptr))
+    check(lib.ct_inject_status(2, 42))  # as if block 41 of an earlier launch had given up
+    t0 = time.perf_counter()
+    check(lib.ct_matmul(0, a.ptr, 0, b.ptr, 512, 512, 512, out.ptr))   # enqueued after the failure
+    check(lib.ct_matmul(0, a.ptr, 0, b.ptr, 512, 512, 512, out.ptr))   # a second one does not clear it
+    elementwise = T.add(a, b).numpy()                                  # other operators are unaffected
+    assert time.perf_counter() - t0 < 1.0, "the launches must return at once, not wait out a budget"
+    assert np.array_equal(out.numpy(), np.full((512, 512), 7.0, np.float32))
+    assert np.array_equal(elementwise, a_np + b_np)
+    assert lib.ct_check() == ERR_TIMEOUT
+    assert "block 41" in lib.ct_last_error().decode()
+    assert lib.ct_check() == 0  # reported once, then clear
+    with pytest.raises(camel_b200.CamelTensorError):
+        check(lib.ct_inject_status(99, 1))
+    check(lib.ct_matmul(0, a.ptr, 0, b.ptr, 512, 512, 512, out.ptr))
+    assert out.numpy().tobytes() == good.tobytes()
+    T.check_async()
+    # the host-buffer form reports it by itself
+    check(lib.ct_inject_status(2, 3))
+    host_out = np.zeros((512, 512), np.float32)
+    rc = lib.ct_matmul_host(a_np.ctypes.data, b_np.ctypes.data, 512, 512, 512, host_out.ctypes.data)
+    assert rc == ERR_TIMEOUT and "block 2" in lib.ct_last_error().decode()
+    assert lib.ct_check() == 0
+
+
+def test_tensor_pipe_peak_measurement(T):
+    """ct_measure_mma_peak: back-to-back kind::tf32 MMAs on resident operands.  The rate has to lie
+    between what the GEMM kernel already reaches (3 x 250 TFLOP/s) and the nominal 1.2 PFLOP/s."""
+    import ctypes as C
+
+    from camel_b200._lib import PREC_3XTF32, PREC_BF16, check, lib
+
+    tf, ms = C.c_double(), C.c_double()
+    check(lib.ct_measure_mma_peak(PREC_3XTF32, 200, 1, C.byref(tf), C.byref(ms)))
+    print(f"tf32 MMA burst: {tf.value:.1f} TFLOP/s in {ms.value * 1e3:.1f} us")
+    assert 600.0 <= tf.value <= 1300.0
+    check(lib.ct_measure_mma_peak(PREC_BF16, 200, 1, C.byref(tf), C.byref(ms)))
+    print(f"bf16 MMA burst: {tf.value:.1f} TFLOP/s in {ms.value * 1e3:.1f} us")
+    assert 1200.0 <= tf.value <= 2600.0

@@ -176,3 +176,180 @@ def test_plugin_dlpack_device_export_and_import():
     rc = lib.camel_host_dlpack_roundtrip(a.ctypes.data, 37, 19, out.ctypes.data, err, 512)
     assert rc == 0, (rc, err.value.decode())
     assert out.tobytes() == a.tobytes()
+
+
+def _boundary_golden():
+    import json
+
+    return json.loads((ROOT / "tests" / "golden" / "boundary.json").read_text())
+
+
+@needs_build
+@pytest.mark.gpu
+def test_plugin_graph_boundary_matches_reference(plugin):
+    """Array literals in (tensorFromArray, `==` with an array operand, concat of arrays), host
+    reads out (idx, idx2d, shape) and the printed form of `show`: the plugin returns and prints
+    what the compiled reference did (tests/golden/boundary.json), byte for byte."""
+    from cases import boundary_cases, run_boundary_case
+
+    golden = _boundary_golden()
+    for name, op, build in boundary_cases():
+        got = run_boundary_case(plugin, op, build)
+        assert got == golden[name], f"{name}: {got} != {golden[name]}"
+
+
+@needs_build
+@pytest.mark.gpu
+def test_plugin_host_reads_copy_once(plugin):
+    """idx / idx2d / show / == read a device tensor on the host: the first read of a tensor copies it
+    device-to-host once, later reads of the same tensor reuse the mirror; operators between
+    device tensors copy nothing."""
+    import ctypes as C
+
+    from cases import capture_stdout
+
+    lib = plugin.lib
+    lib.camel_host_read_copies.restype = C.c_uint64
+    s = plugin.session()
+    a = np.arange(12, dtype=np.float32).reshape(3, 4)
+    v = np.array([0.5, 1.5, -2.5], np.float32)
+    ha, hv = s.put(a), s.put(v)
+    before = lib.camel_host_read_copies()
+    hb = s.call("add", ha, ha)
+    hc = s.call("multiply", hb, 0.5)
+    s.finish(hc)
+    assert lib.camel_host_read_copies() == before            # device to device: no host copy
+    assert s.fetch(s.call("idx", hv, 2)) == -2.5
+    assert lib.camel_host_read_copies() == before + 1        # the first host read of v
+    assert s.fetch(s.call("idx", hv, 0)) == 0.5
+    assert lib.camel_host_read_copies() == before + 1        # the mirror is reused
+    assert s.fetch(s.call("idx2d", hc, 2, 3)) == 11.0
+    assert lib.camel_host_read_copies() == before + 2        # hc evaluated and read once
+    _, text = capture_stdout(lambda: s.call("show", hc))
+    assert text.startswith("tensor([[") and lib.camel_host_read_copies() == before + 2
+    with pytest.raises(oracle.OracleError, match="out of bounds"):
+        s.call("idx", hv, 3)
+    with pytest.raises(oracle.OracleError, match="rank-1"):
+        s.call("idx", ha, 0)
+
+
+def _sgd_loop(lib, x, y, w, lr, steps, scopes):
+    import ctypes as C
+
+    n, d = x.shape
+    classes = y.shape[1]
+    w = w.copy()
+    live = (C.c_uint64 * steps)()
+    secs = C.c_double()
+    err = C.create_string_buffer(512)
+    lib.camel_host_sgd_loop.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_double,
+                                        C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_double), C.c_char_p, C.c_int]
+    rc = lib.camel_host_sgd_loop(x.ctypes.data, y.ctypes.data, w.ctypes.data, n, d, classes, lr, steps, int(scopes),
+                                 C.cast(live, C.c_void_p), C.byref(secs), err, 512)
+    assert rc == 0, err.value.decode()
+    return w, np.array(list(live), dtype=np.uint64), secs.value
+
+
+@needs_build
+@pytest.mark.gpu
+def test_plugin_training_loop_holds_device_memory_flat(plugin):
+    """The loop of test/run/nn/mnist.cml:27-41 at MNIST size (60000 x 785 x 10), 2000 steps through
+    the operator bodies, each step inside a scope whose only surviving value is the new W (the replaced
+    W is released at its last use): the
+    module's device bytes are the same after every step (X, y, W and nothing else), and the weights
+    equal the same steps computed in float64.  Without scopes the same loop grows every step, which
+    is what the reference's collector (no finalisers, no root set: include/camel/core/mm/gen.h:224-227)
+    leaves a module with."""
+    rng = np.random.default_rng(71)
+    n, d, classes = 60000, 785, 10
+    x = rng.uniform(0, 1, (n, d)).astype(np.float32)
+    x[:, -1] = 1.0
+    labels = rng.integers(0, classes, n)
+    y = np.eye(classes, dtype=np.float32)[labels]
+    w0 = np.zeros((d, classes), np.float32)
+    w, live, secs = _sgd_loop(plugin.lib, x, y, w0, 0.1, 2000, True)
+    resident = x.nbytes + y.nbytes + w0.nbytes
+    print(f"2000 steps in {secs:.2f} s ({secs / 2000 * 1e6:.0f} us per step); device bytes {int(live[0])} .. {int(live[-1])}")
+    assert len(set(live.tolist())) == 1, "device memory must not change from step to step"
+    assert resident <= int(live[0]) <= resident + 4096
+    # the first 20 steps against float64 (the operators round to float32 at every step)
+    w20, _, _ = _sgd_loop(plugin.lib, x, y, w0, 0.1, 20, True)
+    ref = w0.astype(np.float64)
+    xd, yd = x.astype(np.float64), y.astype(np.float64)
+    for _ in range(20):
+        logits = xd @ ref
+        e = np.exp(logits - logits.max(axis=1, keepdims=True))
+        ref = ref - 0.1 / n * (xd.T @ (e / e.sum(axis=1, keepdims=True) - yd))
+    assert np.max(np.abs(w20 - ref)) <= 1e-5 * max(1.0, float(np.max(np.abs(ref))))
+    # no scopes: every step leaves its values behind
+    _, grow, _ = _sgd_loop(plugin.lib, x[:6000], y[:6000], w0, 0.1, 30, False)
+    assert np.all(np.diff(grow.astype(np.int64)) > 0)
+    # eager evaluation inside scopes is flat as well, and gives the same weights as the deferred run
+    plugin.session(lazy=False)
+    w_eager, live_eager, _ = _sgd_loop(plugin.lib, x[:6000], y[:6000], w0, 0.1, 30, True)
+    plugin.session(lazy=True)
+    w_lazy, _, _ = _sgd_loop(plugin.lib, x[:6000], y[:6000], w0, 0.1, 30, True)
+    assert len(set(live_eager.tolist())) == 1
+    assert np.max(np.abs(w_eager - w_lazy)) <= 1e-6  # fused softmax: within 4 ulp of the operator chain
+
+
+@needs_build
+@pytest.mark.gpu
+def test_plugin_scope_semantics(plugin):
+    """A kept value survives its scope together with what it still needs; everything else is
+    released; a released tensor raises when used."""
+    import ctypes as C
+
+    lib = plugin.lib
+    lib.camel_host_live_device_bytes.restype = C.c_uint64
+    lib.camel_host_scope_begin.restype = C.c_uint64
+    lib.camel_host_scope_end.argtypes = [C.c_uint64, C.c_int, C.POINTER(C.c_int64), C.c_char_p, C.c_int]
+    err = C.create_string_buffer(512)
+    s = plugin.session(lazy=True)
+    a = np.random.default_rng(5).uniform(-1, 1, (256, 128)).astype(np.float32)
+    ha = s.put(a)
+    s.finish(ha)
+    base = lib.camel_host_live_device_bytes()
+    assert base == a.nbytes
+    tok = lib.camel_host_scope_begin()
+    hb = s.call("add", ha, ha)              # computed at once
+    hm = s.call("gt", hb, 0.0)              # deferred: needs hb
+    hc = s.call("multiply", hb, 3.0)        # deferred, dropped with the scope
+    assert s.pending(hm) and s.pending(hc)
+    keep = (C.c_int64 * 1)(hm.index)
+    assert lib.camel_host_scope_end(tok, 1, keep, err, 512) == 0, err.value.decode()
+    # hb is still held (the kept mask has not run); hc never ran and owns nothing
+    assert lib.camel_host_live_device_bytes() == base + a.nbytes
+    mask = s.fetch(hm)
+    assert np.array_equal(mask, (a + a > 0).astype(np.uint8))
+    # the mask has run: hb is free of it and gone; the mask's own buffer remains
+    assert lib.camel_host_live_device_bytes() == base + a.size
+    for dead in (hb, hc):
+        with pytest.raises(oracle.OracleError, match="after the scope"):
+            s.fetch(dead)
+    with pytest.raises(oracle.OracleError, match="after the scope"):
+        s.fetch(s.call("add", hb, ha))
+    assert np.array_equal(s.fetch(s.call("add", ha, ha)), a + a)  # values outside the scope are untouched
+
+
+@needs_build
+@pytest.mark.gpu
+def test_plugin_reports_kernel_timeout_at_the_host_read(plugin):
+    """A contraction whose bounded wait ran out (the device word written from the host, nothing
+    waits on the GPU) surfaces as the operator's RuntimeFault when its result is read on the host,
+    not as silent garbage; afterwards the plugin works again."""
+    from camel_b200._lib import check, lib
+
+    rng = np.random.default_rng(9)
+    a = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
+    s = plugin.session(lazy=True)
+    ha = s.put(a)
+    check(lib.ct_inject_status(2, 8))
+    hp = s.call("matmul", ha, ha)
+    with pytest.raises(oracle.OracleError, match="bounded wait"):
+        s.fetch(hp)
+    s = plugin.session(lazy=True)
+    ha = s.put(a)
+    got = s.fetch(s.call("matmul", ha, ha))
+    ref = (a.astype(np.float64) @ a.astype(np.float64)).astype(np.float32)
+    assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) <= 1e-5

@@ -27,8 +27,10 @@ def test_static_matmul_matches_regular_entry_point_twice():
 
     rng = np.random.default_rng(42)
     status = T.Tensor(_lib.I64, (1,))  # 8 bytes of device memory; the first 4 are the status word
-    # two calls in a row with different shapes: the second must not see anything of the first
-    for (m, k, n) in ((384, 300, 512), (200, 1000, 136)):
+    # calls in a row with different shapes: none may see anything of the one before.  The third
+    # fills the 16 MiB exactly and takes the 128 x 256 tiles; then a width that is no multiple of
+    # four (scalar stores), fewer rows than a tile, and k = 0 (the product is all zeros).
+    for (m, k, n) in ((384, 300, 512), (200, 1000, 136), (4096, 256, 4096), (300, 64, 130), (100, 40, 260), (33, 0, 70)):
         a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
         b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
         ta, tb = T.from_numpy(a), T.from_numpy(b)
@@ -40,6 +42,9 @@ def test_static_matmul_matches_regular_entry_point_twice():
         got = out.numpy()
         assert int(status.numpy()[0]) & 0xFFFFFFFF == 0, "the kernel reported a timed-out wait"
         ref = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+        if k == 0:
+            assert not got.any() and not want.any()
+            continue
         assert _rel(got, want) <= GEMM_TOL
         assert _rel(got, ref) <= GEMM_TOL
 
