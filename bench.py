@@ -1,16 +1,23 @@
 #!/usr/bin/env python
 """Benchmark of the tensor hot path: `python bench.py --gpus N --steps K --warmup W`.
 
+With no --workload the headline is the MLP forward (BASELINE configs[1]); the same run then
+measures, a few steps each, every other configuration and kernel family and attaches them to the
+one JSON line under "extras" (so that every quoted number has a line in a driver-run record).
+
 Workloads (seeded synthetic inputs with the shapes and distributions of the reference
 configurations; no dataset is used):
   mlp    3-layer MLP forward, batch 4096, 784->1024->1024->10, relu/relu/softmax+argmax
-         (metric: samples/s) - the default
+         (metric: samples/s) - the headline
   gemm   one fp32 GEMM M=N=K (default 16384, --size), 3xTF32 (or --precision bf16)
   gemm_sharded  the same product with the rows of A split over the ranks and C all-gathered in
          row panels on a side stream while the next panel computes (strong scaling)
   conv   conv2d 256x64x56x56 * 128x64x3x3, pad 1, + bias + relu
   cnn    conv32-conv64-pool-dense128-dense10 forward on 1x28x28 images, batch 8192
   add, mul, scale, relu, gt, exp, log, sum, softmax   2^28 float32 (HBM-bound)
+  sum_axis0, sum_axis1, argmax_rows, transpose, maxpool, fill, split_rows   the remaining
+         HBM-bound kernel families (axis reductions, movement, pooling, constructors, GEMM pre-pass)
+  mma_peak   the tensor pipe's ceiling: back-to-back tcgen05.mma on resident operands
 
 Under torchrun every rank runs the same per-GPU workload on its own shard (weak scaling, no
 data-path collective: samples / row blocks are independent; gemm_sharded is the exception);
@@ -46,10 +53,12 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi (every 100 ms) for the whole run;
+    `window(t0, t1)` summarises the samples that fell inside a timed region."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,power.draw")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
@@ -65,26 +74,37 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
-    def stop(self):
+    def window(self, t0, t1):
+        """Clocks seen between host times t0 and t1 (a sample describes the 100 ms before it, so
+        the window is widened by that much; a region shorter than the sampling period takes the
+        nearest sample)."""
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        sm, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        deadline = time.time() + 0.25
+        while time.time() < deadline and not any(t >= t1 for t, _ in self.rows):
+            time.sleep(0.02)
+        rows = [r for t, r in self.rows if t0 <= t <= t1 + 0.12]
+        if not rows and self.rows:
+            rows = [min(self.rows, key=lambda tr: abs(tr[0] - t1))[1]]
+        sm, mx, power, reasons = [], None, [], set()
+        for r in rows:
             try:
                 sm.append(float(r[0]))
                 mx = float(r[1])
-                for n, v in zip(names, r[2:6]):
+                for n, v in zip(self.NAMES, r[2:6]):
                     if v.lower().startswith("active"):
                         reasons.add(n)
+                power.append(float(r[6]))
             except (ValueError, IndexError):
                 continue
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "power_w": float(np.median(power)) if power else None}
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
 
 
 # ---------------------------------------------------------------------------------------
@@ -183,6 +203,8 @@ def run_reference(args, rank):
     the batch (samples / row blocks) in parallel, one process per core."""
     if rank != 0:
         return
+    if args.workload == "default":
+        args.workload = "mlp"  # the headline
     metric, unit = {"mlp": ("mlp_forward_samples_per_s", "samples/s"),
                     "gemm": ("gemm_fp32_tflops", "TFLOP/s")}.get(args.workload, (None, None))
     if metric is None:
@@ -356,8 +378,8 @@ class MlpWorkload(Workload):
     def ncu_traffic(self):
         if self.batch != 4096:
             return None, "captured at batch 4096 only"
-        return 38.1e6, ("profiles/mlp_forward_launch_list_and_gemm.md: 43.4 MB (k=1024) and 32.9 MB (k=784) per "
-                        "launch = the operand planes read once; the result stays in L2")
+        return 38.1e6, ("ncu capture of this workload: 43.4 MB (k=1024) and 32.9 MB (k=784) per launch = the "
+                        "operand planes read once; the result stays in L2")
 
     def resident_bytes(self):
         return self.x.nbytes + sum(t.nbytes for t in self.w) + 2 * self.batch * 1024 * 4
@@ -372,7 +394,7 @@ class MlpWorkload(Workload):
 class GemmWorkload(Workload):
     name, metric, unit = "gemm", "gemm_fp32_tflops", "TFLOP/s"
 
-    def __init__(self, torch, T, n, precision):
+    def __init__(self, torch, T, n, precision, e2e=True):
         self.T, self.n, self.precision = T, n, precision
         dev = torch.device("cuda")
         g = torch.Generator(device=dev)
@@ -385,10 +407,11 @@ class GemmWorkload(Workload):
         self.a = T.wrap_device(self.a_t.data_ptr(), 0, (n, n), keep=self.a_t)
         self.b = T.wrap_device(self.b_t.data_ptr(), 0, (n, n), keep=self.b_t)
         self.e2e_rows = min(n, 2048)
-        self.a_host = _pin(torch, self.a_t[: self.e2e_rows].cpu().numpy())
-        self.c_host = _pin_empty((self.e2e_rows, n), np.float32)
         self.h2d = self.e2e_rows * n * 4
         self.d2h = self.e2e_rows * n * 4
+        if e2e:
+            self.a_host = _pin(torch, self.a_t[: self.e2e_rows].cpu().numpy())
+            self.c_host = _pin_empty((self.e2e_rows, n), np.float32)
 
     def step(self):
         from camel_b200._lib import check, lib
@@ -415,7 +438,7 @@ class GemmWorkload(Workload):
 
     def ncu_traffic(self):
         if self.n == 4096:
-            return 690.7e6, "profiles/gemm_tc_kernel_gemm4096.md (335 MB algorithmic: operand tiles re-read 2.1x)"
+            return 690.7e6, "ncu capture at 4096^3 (335 MB algorithmic: operand tiles re-read 2.1x)"
         return None, ("captured at 4096^3 only: the re-read factor depends on how the raster groups fit in L2 "
                       "and does not scale with the flops")
 
@@ -516,12 +539,13 @@ class ShardedGemmWorkload(Workload):
 class ConvWorkload(Workload):
     name, metric, unit = "conv", "conv2d_fp32_tflops", "TFLOP/s"
 
-    def __init__(self, torch, T, batch):
+    def __init__(self, torch, T, batch, e2e=True):
         self.T, self.batch = T, batch
         x, w, b = conv_inputs(batch)
         self.x, self.w, self.b = T.from_numpy(x), T.from_numpy(w), T.from_numpy(b)
-        self.x_host = _pin(torch, x)
-        self.out_host = _pin_empty((batch, 128, 56, 56), np.float32)
+        if e2e:
+            self.x_host = _pin(torch, x)
+            self.out_host = _pin_empty((batch, 128, 56, 56), np.float32)
         self.h2d, self.d2h = x.nbytes, batch * 128 * 56 * 56 * 4
         self.flops = 2.0 * batch * 128 * 56 * 56 * 64 * 9
 
@@ -545,8 +569,8 @@ class ConvWorkload(Workload):
         # and at full size the whole result goes to DRAM (at batch 32 most of it was still in L2)
         reads = 52.1e6 * self.batch / 32.0
         writes = self.batch * 128 * 56 * 56 * 4.0
-        return reads + writes, ("profiles/conv2d_and_elementwise_kernels.md: reads scaled from the batch-32 capture "
-                                "by the batch, writes = the size of the result")
+        return reads + writes, ("ncu capture at batch 32: reads scaled by the batch (planes are read once), "
+                                "writes = the size of the result")
 
     def resident_bytes(self):
         return self.h2d + self.d2h
@@ -590,8 +614,8 @@ class AddWorkload(Workload):
         return 12.0 * self.n
 
     def ncu_traffic(self):
-        return 12.0 * self.n, ("profiles/conv2d_and_elementwise_kernels.md: the 2^26 capture moved its algorithmic "
-                               "12 B/element (reads exact, the tail of the writes still in L2); scaled by n")
+        return 12.0 * self.n, ("ncu capture at 2^26 elements moved its algorithmic 12 B/element (reads exact, the "
+                               "tail of the writes still in L2); scaled by n")
 
     def resident_bytes(self):
         return 12 * self.n
@@ -606,23 +630,38 @@ class HbmWorkload(Workload):
     bound = "hbm"
     unit = "GB/s"
     #        op: (bytes per element, profile family)
-    OPS = {"relu": (8, "elementwise"), "exp": (8, "elementwise"), "log": (8, "elementwise"),
+    OPS = {"add": (12, "elementwise"), "relu": (8, "elementwise"), "exp": (8, "elementwise"), "log": (8, "elementwise"),
            "mul": (12, "elementwise"), "scale": (8, "elementwise"), "gt": (5, "elementwise"),
            "sum": (4, "reduce"), "softmax": (8, "softmax")}
 
-    def __init__(self, torch, T, op, n):
+    def __init__(self, torch, T, op, n, on_device=False):
         if op == "softmax":
             n = min(n, 1 << 26)  # 8192 rows of 8192: a row stays in the registers of one block
         self.T, self.op, self.n = T, op, n
         self.bpe, self.dominant = self.OPS[op]
         self.name, self.metric = op, f"elementwise_{op}_gbs"
-        rng = np.random.default_rng(6)
-        x = rng.uniform(-1, 1, n).astype(np.float32)
-        if op == "log":
-            x = x + np.float32(1.0001)  # shifted to (0, 2): log throws on values <= 0
-        self.x = T.from_numpy(x.reshape(8192, -1) if op == "softmax" else x)
-        self.y = T.from_numpy(rng.uniform(-1, 1, n).astype(np.float32)) if op == "mul" else None
         self.e2e_n = min(n, 1 << 24)
+        if on_device:
+            # the same distribution drawn on the device (seeded): a gigabyte of host RNG per operator
+            # would dominate a run that measures many of them
+            g = torch.Generator(device="cuda")
+            g.manual_seed(6)
+            xt = torch.rand(n, generator=g, device="cuda", dtype=torch.float32) * 2 - 1
+            if op == "log":
+                xt += 1.0001
+            self.x = T.wrap_device(xt.data_ptr(), 0, (8192, n // 8192) if op == "softmax" else (n,), keep=xt)
+            self.y = None
+            if op in ("mul", "add"):
+                yt = torch.rand(n, generator=g, device="cuda", dtype=torch.float32) * 2 - 1
+                self.y = T.wrap_device(yt.data_ptr(), 0, (n,), keep=yt)
+            x = xt[: self.e2e_n].cpu().numpy()
+        else:
+            rng = np.random.default_rng(6)
+            x = rng.uniform(-1, 1, n).astype(np.float32)
+            if op == "log":
+                x = x + np.float32(1.0001)  # shifted to (0, 2): log throws on values <= 0
+            self.x = T.from_numpy(x.reshape(8192, -1) if op == "softmax" else x)
+            self.y = T.from_numpy(rng.uniform(-1, 1, n).astype(np.float32)) if op in ("mul", "add") else None
         self.x_host = _pin(torch, x[: self.e2e_n])
         self.o_host = _pin_empty((self.e2e_n,), np.float32)
         self.h2d, self.d2h = 4 * self.e2e_n, 4 * self.e2e_n
@@ -638,6 +677,8 @@ class HbmWorkload(Workload):
             return T.log(x)
         if self.op == "mul":
             return T.multiply(x, self.y)
+        if self.op == "add":
+            return T.add(x, self.y)
         if self.op == "scale":
             return T.multiply(x, 0.5)
         if self.op == "gt":
@@ -652,8 +693,8 @@ class HbmWorkload(Workload):
     def e2e_step(self):
         from camel_b200._lib import check, lib
         check(lib.ct_h2d(self.x_small.ptr, self.x_host.data_ptr(), self.h2d))
-        if self.op == "mul":
-            out = self.T.multiply(self.x_small, self.x_small)
+        if self.op in ("mul", "add"):
+            out = (self.T.multiply if self.op == "mul" else self.T.add)(self.x_small, self.x_small)
         else:
             out = self._run(self.x_small)
         if isinstance(out, float):
@@ -673,8 +714,8 @@ class HbmWorkload(Workload):
 
     def ncu_traffic(self):
         if self.op in ("exp", "softmax"):
-            return float(self.bpe) * self.n, ("profiles/conv2d_and_elementwise_kernels.md: the 2^26 capture read and "
-                                               "wrote every element once (8 B/element); scaled by n")
+            return float(self.bpe) * self.n, ("ncu capture at 2^26 elements read and wrote every element once "
+                                               "(8 B/element); scaled by n")
         return None, "no ncu capture of this operator"
 
     def resident_bytes(self):
@@ -684,13 +725,138 @@ class HbmWorkload(Workload):
         return {"workload": f"{self.op} over {self.n} float32 ({self.bpe} B/element)"}
 
 
+class KernelFamilyWorkload(Workload):
+    """The HBM-bound kernel families that are not elementwise maps: axis reductions, transpose,
+    max-pool, constructors and the GEMM operand pre-pass.  Inputs are drawn on the device (seeded).
+    `bytes` is the algorithmic traffic of one call: what must be read plus what must be written."""
+
+    bound, unit = "hbm", "GB/s"
+
+    def __init__(self, torch, T, kind):
+        from camel_b200._lib import check, lib
+        self.T, self.kind, self.lib, self.check = T, kind, lib, check
+        self.name, self.metric = kind, f"{kind}_gbs"
+        g = torch.Generator(device="cuda")
+        g.manual_seed(7)
+        rand = lambda *shape: torch.rand(shape, generator=g, device="cuda", dtype=torch.float32) * 2 - 1  # noqa: E731
+        wrap = lambda t: T.wrap_device(t.data_ptr(), 0, tuple(t.shape), keep=t)  # noqa: E731
+        self.h2d = self.d2h = 0
+        if kind in ("sum_axis0", "sum_axis1", "max_axis1", "argmax_axis1"):
+            r = c = 8192
+            self.x = wrap(rand(r, c))
+            out = c if kind == "sum_axis0" else r
+            self.bytes = 4.0 * r * c + (8.0 if kind.startswith("argmax") else 4.0) * out
+            self.dominant = "reduce"
+            self.desc = f"{kind} of {r} x {c} float32"
+        elif kind == "argmax_rows":
+            r, c = 1 << 22, 10  # the classifier's shape (4096 x 10) is 160 KB: far below anything measurable
+            self.x = wrap(rand(r, c))
+            self.bytes = 4.0 * r * c + 8.0 * r
+            self.dominant = "reduce"
+            self.desc = f"argmax over the 10 columns of {r} rows (the classifier's row shape, many rows)"
+        elif kind == "transpose":
+            r = c = 8192
+            self.x = wrap(rand(r, c))
+            self.bytes = 8.0 * r * c
+            self.dominant = "transpose"
+            self.desc = f"transpose of {r} x {c} float32"
+        elif kind == "maxpool":
+            self.x = wrap(rand(2048, 64, 28, 28))
+            self.bytes = 5.0 * self.x.numel
+            self.dominant = "maxpool"
+            self.desc = "maxpool2d 2x2 of 2048 x 64 x 28 x 28 (BASELINE configs[3] layer shape, a quarter of its batch)"
+        elif kind == "fill":
+            self.n = 1 << 28
+            self.out = T.Tensor(0, (self.n,))
+            self.bytes = 4.0 * self.n
+            self.dominant = "elementwise"
+            self.desc = f"full([{self.n}], 1.5): 4 B/element written"
+        elif kind == "split_rows":
+            import ctypes as C
+            self.rows, self.k = 16384, 8192
+            self.x = wrap(rand(self.rows, self.k))
+            self.packed = C.c_void_p()
+            self.bytes = 12.0 * self.rows * self.k
+            self.dominant = "gemm_prepass"
+            self.desc = f"operand pre-pass of the 3xTF32 GEMM over {self.rows} x {self.k} float32 (4 B read, 8 B written per element)"
+        else:
+            raise ValueError(kind)
+
+    def step(self):
+        T, k = self.T, self.kind
+        if k == "sum_axis0":
+            self.out = T.sum(self.x, 0)
+        elif k == "sum_axis1":
+            self.out = T.sum(self.x, 1)
+        elif k == "max_axis1":
+            self.out = T.max(self.x, 1)
+        elif k in ("argmax_axis1", "argmax_rows"):
+            self.out = T.argmax(self.x, 1)
+        elif k == "transpose":
+            self.out = T.transpose(self.x)
+        elif k == "maxpool":
+            self.out = T.maxpool2d(self.x, 2)
+        elif k == "fill":
+            self.check(self.lib.ct_fill(0, 1.5, self.n, self.out.ptr))
+        else:
+            import ctypes as C
+            self.check(self.lib.ct_rows_pack(self.x.ptr, self.rows, self.k, C.byref(self.packed)))
+
+    def units_per_step(self):
+        return self.bytes / 1e9
+
+    def algorithmic_per_step(self):
+        return self.bytes
+
+    def resident_bytes(self):
+        return self.bytes
+
+    def config(self):
+        return {"workload": self.desc}
+
+    def close(self):
+        if getattr(self, "packed", None):
+            self.lib.ct_rows_free(self.packed)
+            self.packed = None
+
+
+class Gemm512Workload(Workload):
+    """BASELINE configs[0]: fp32 GEMM M=N=K=512, U(-1,1), seed 0, through the matmul operator.
+    0.27 GFLOP: launch- and latency-bound, reported without a roofline expectation."""
+
+    name, metric, unit = "gemm512", "gemm_fp32_tflops", "TFLOP/s"
+
+    def __init__(self, torch, T):
+        rng = np.random.default_rng(0)
+        self.T = T
+        self.a = T.from_numpy(rng.uniform(-1, 1, (512, 512)).astype(np.float32))
+        self.b = T.from_numpy(rng.uniform(-1, 1, (512, 512)).astype(np.float32))
+        self.h2d = self.d2h = 0
+
+    def step(self):
+        self.out = self.T.matmul(self.a, self.b)
+
+    def units_per_step(self):
+        return 2.0 * 512 ** 3 / 1e12
+
+    def algorithmic_per_step(self):
+        return 2.0 * 512 ** 3
+
+    def resident_bytes(self):
+        return 3 * 512 * 512 * 4
+
+    def config(self):
+        return {"workload": "gemm fp32 M=N=K=512 U(-1,1) seed 0 (BASELINE configs[0]): latency-bound",
+                "precision": "3xtf32"}
+
+
 class CnnWorkload(Workload):
     """BASELINE configs[3]: conv 1->32 +relu, conv 32->64 +relu, 2x2 maxpool, flatten,
     dense 12544->128 +relu, dense 128->10 +softmax, on 1x28x28 Uniform(0,1) images."""
 
     name, metric, unit = "cnn", "cnn_forward_samples_per_s", "samples/s"
 
-    def __init__(self, torch, T, batch):
+    def __init__(self, torch, T, batch, fuse_pool=True):
         self.T, self.batch = T, batch
         rng = np.random.default_rng(4)
 
@@ -708,7 +874,7 @@ class CnnWorkload(Workload):
         self.arg_host = _pin_empty((batch,), np.int64)
         self.h2d, self.d2h = x.nbytes, batch * 48
         self.flops = 2.0 * batch * (28 * 28 * (32 * 9 + 64 * 288) + 12544 * 128 + 1280)
-        self.fuse_pool = not os.environ.get("CAMEL_BENCH_UNFUSED_POOL")
+        self.fuse_pool = fuse_pool
 
     def forward(self, x):
         T = self.T
@@ -749,6 +915,283 @@ class CnnWorkload(Workload):
                 if self.T._weight_cache else "transposed and split at every call"}
 
 
+class Bench:
+    """Timing harness shared by the headline and the extras: CUDA events on the launching stream
+    around every step, L2 flushed between steps when the working set is smaller than L2, a barrier
+    and a device synchronisation on both sides, the slowest rank's time."""
+
+    def __init__(self, torch, dist, lib, check, T, rank, world, sampler):
+        self.torch, self.dist, self.lib, self.check, self.T = torch, dist, lib, check, T
+        self.rank, self.world, self.sampler = rank, world, sampler
+        self.flush_buf = None
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def flush_for(self, wl):
+        if wl.resident_bytes() >= 2 * L2_BYTES:
+            return None
+        if self.flush_buf is None:
+            self.flush_buf = self.torch.empty(L2_BYTES * 2, dtype=self.torch.uint8, device="cuda")
+        return self.flush_buf
+
+    def reduce_max(self, v):
+        from camel_b200 import sharding
+        return sharding.reduce_max(self.dist, self.torch, v, "cuda")
+
+    def timed(self, fn, steps, flush):
+        torch = self.torch
+        evs = []
+        self.barrier()
+        for _ in range(steps):
+            if flush is not None:
+                flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            evs.append((e0, e1))
+        self.barrier()
+        return sum(a.elapsed_time(b) for a, b in evs)
+
+    def measure(self, wl, steps, warmup, min_gpu_s=0.0, max_blocks=2000):
+        """Resident throughput of `wl`: `warmup` untimed steps, then blocks of exactly `steps`
+        timed steps, repeated until `min_gpu_s` seconds of device time have been timed (one block
+        if 0); the reported time per step is the median block's.  Then the dominant kernel's own
+        launch durations from the library's event brackets on the same inputs."""
+        lib, check, T = self.lib, self.check, self.T
+        flush = self.flush_for(wl)
+        for _ in range(max(warmup, 3)):
+            wl.step()
+        T.check_async()
+        replayed = getattr(wl, "graph", None) is not None
+        launches0 = lib.ct_launch_count()
+        t0 = time.time()
+        blocks = [self.reduce_max(self.timed(wl.step, steps, flush))]
+        launches = lib.ct_launch_count() - launches0
+        # every rank must run the same number of blocks: the count comes from the first block's
+        # (already max-reduced) time
+        extra_blocks = 0
+        if min_gpu_s > 0 and blocks[0] > 0:
+            extra_blocks = min(max_blocks, int(np.ceil(min_gpu_s * 1e3 / blocks[0])))
+        for _ in range(extra_blocks):
+            blocks.append(self.reduce_max(self.timed(wl.step, steps, flush)))
+        t1 = time.time()
+        clocks = self.sampler.window(t0, t1) if self.sampler is not None else None
+        # The dominant kernel's own launch durations: a second pass over the same inputs with the
+        # library's event brackets on (they switch programmatic dependent launch off, so that a
+        # bracket times one kernel alone; the timed region above ran without them).  A replayed
+        # graph bypasses the brackets, so that pass runs call by call.
+        prof_steps = min(steps, 10)
+        check(lib.ct_profile_enable(1))
+        self.timed(wl.eager_step if replayed else wl.step, prof_steps, flush)
+        tot, cnt = ctypes_double(), ctypes_u64()
+        check(lib.ct_profile_read(wl.dominant.encode(), tot, cnt))
+        check(lib.ct_profile_read(None, None, None))
+        check(lib.ct_profile_enable(0))
+        T.check_async()
+        ms_block = float(np.median(blocks))
+        return {"ms_per_step": ms_block / steps, "blocks": len(blocks), "gpu_s": float(sum(blocks)) / 1e3,
+                "launches": int(launches), "dom_ms": tot.value / max(1, cnt.value),
+                "launches_per_step": cnt.value / prof_steps, "clocks": clocks,
+                "flush": flush is not None}
+
+
+def measured_mma_peaks(lib, check, sampler):
+    """The tensor pipe's ceiling on this GPU, now: tcgen05.mma back to back on resident operands
+    (ct_measure_mma_peak).  Burst = the rate between two short launches of 70 and 240 us (what a
+    short kernel can be held against); sustained = a run of about two seconds (what a kernel
+    inside a long, power-capped step can be held against)."""
+    import ctypes as C
+    from camel_b200._lib import PREC_3XTF32, PREC_BF16
+
+    out = {}
+    tf, ms = C.c_double(), C.c_double()
+    for name, kind in (("tf32", PREC_3XTF32), ("bf16", PREC_BF16)):
+        # a launch pays ~15 us of set-up besides its MMAs: the pipe's own rate is the difference
+        # quotient of two launch sizes (best of five each), 200 and 800 groups of four MMAs per SM
+        best = {}
+        for groups in (200, 800):
+            t_best, f_best = None, None
+            for _ in range(5):
+                check(lib.ct_measure_mma_peak(kind, groups, 1, C.byref(tf), C.byref(ms)))
+                if t_best is None or ms.value < t_best:
+                    t_best, f_best = ms.value, tf.value * ms.value  # tflops * ms = Gflop
+            best[groups] = (t_best, f_best)
+        burst = (best[800][1] - best[200][1]) / (best[800][0] - best[200][0])
+        check(lib.ct_measure_mma_peak(kind, 800, 20, C.byref(tf), C.byref(ms)))
+        n = max(20, min(20000, int(2000.0 / max(ms.value / 20, 1e-3))))
+        t0 = time.time()
+        check(lib.ct_measure_mma_peak(kind, 800, n, C.byref(tf), C.byref(ms)))
+        clocks = sampler.window(t0, time.time()) if sampler is not None else None
+        out[name] = {"burst_tflops": burst, "burst_launch_us": [best[200][0] * 1e3, best[800][0] * 1e3],
+                     "sustained_tflops": tf.value, "sustained_s": ms.value / 1e3, "sustained_clocks": clocks}
+    return out
+
+
+def roofline_of(wl, m, pk, mma, precision):
+    """roofline object of one measured workload.  Tensor-bound kernels are held against the measured
+    MMA rate of this run (tf32 / 3 for the 3xTF32 scheme): the burst figure for launches shorter
+    than 5 ms, the sustained one for longer launches; the figure derived from the driver-written
+    bf16 GEMM peak is kept beside it.  `frac_at_clock` scales the burst ceiling (taken at the
+    maximum SM clock) to the median SM clock sampled during this workload."""
+    dom_ms = m["dom_ms"]
+    alg = wl.algorithmic_per_step() / max(1.0, m["launches_per_step"])
+    out = {"bound": wl.bound, "kernel": wl.dominant, "launches_per_step": m["launches_per_step"],
+           "avg_launch_ms": dom_ms}
+    if wl.bound == "tensor":
+        achieved = alg / (dom_ms / 1e3) / 1e12 if dom_ms > 0 else 0.0
+        kind = "bf16" if precision == "bf16" else "tf32"
+        div = 1.0 if precision == "bf16" else 3.0
+        derived = pk["bf16_tflops"] / (1.0 if precision == "bf16" else 6.0)
+        if mma is not None:
+            which = "burst" if dom_ms < 5.0 else "sustained"
+            peak = mma[kind][f"{which}_tflops"] / div
+            note = (f"measured in this run: tcgen05.mma kind::{'f16 (bf16)' if kind == 'bf16' else 'tf32'} back to back on "
+                    f"resident operands, {which} figure" + ("" if precision == "bf16" else " / 3 (three MMAs per product)"))
+            out["peak_burst"] = mma[kind]["burst_tflops"] / div
+            out["peak_sustained"] = mma[kind]["sustained_tflops"] / div
+        else:
+            peak, note = derived, "derived (no MMA measurement on this rank)"
+        out.update({"achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
+                    "peak_note": note, "peak_derived_from_bf16_gemm": derived,
+                    "frac_of_derived": achieved / derived if derived else None})
+        c = m.get("clocks") or {}
+        if mma is not None and c.get("sm_mhz") and c.get("sm_max_mhz"):
+            at_clock = mma[kind]["burst_tflops"] / div * c["sm_mhz"] / c["sm_max_mhz"]
+            out["frac_at_clock"] = achieved / at_clock
+            out["time_x_mhz"] = dom_ms * c["sm_mhz"]
+    else:
+        achieved = alg / (dom_ms / 1e3) / 1e9 if dom_ms > 0 else 0.0
+        out.update({"achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"], "peak_note": f"{pk['source']} STREAM-style copy"})
+    traffic, traffic_note = wl.ncu_traffic() if precision != "bf16" else (None, "no ncu capture in bf16 mode")
+    out.update({"traffic": traffic, "traffic_unit": "bytes per launch", "traffic_note": traffic_note})
+    return out
+
+
+EXTRA_STEPS = {"gemm": 5, "gemm_bf16": 5, "gemm512": 50, "conv": 10, "cnn": 5, "gemm_sharded": 3}
+
+
+def run_extras(bench, args, pk, mma):
+    """Every other configuration and kernel family, a few steps each, for the `extras` list."""
+    import gc
+
+    torch, T, lib, check = bench.torch, bench.T, bench.lib, bench.check
+    from camel_b200 import _lib
+
+    names = ["gemm512", "gemm", "gemm_bf16", "conv", "cnn"]
+    if bench.world > 1:
+        names.append("gemm_sharded")
+    else:
+        names += ["add", "mul", "scale", "relu", "gt", "sum", "exp", "log", "softmax", "sum_axis0", "sum_axis1",
+                  "max_axis1", "argmax_axis1", "argmax_rows", "transpose", "maxpool", "fill", "split_rows"]
+    out = []
+    for name in names:
+        precision = "bf16" if name == "gemm_bf16" else "3xtf32"
+        if precision == "bf16":
+            check(lib.ct_set_precision(_lib.PREC_BF16))
+        try:
+            if name == "gemm512":
+                wl = Gemm512Workload(torch, T)
+            elif name in ("gemm", "gemm_bf16"):
+                wl = GemmWorkload(torch, T, 16384, precision, e2e=False)
+            elif name == "gemm_sharded":
+                wl = ShardedGemmWorkload(torch, bench.dist, T, 16384, bench.world, bench.rank)
+            elif name == "conv":
+                wl = ConvWorkload(torch, T, 256, e2e=False)
+            elif name == "cnn":
+                wl = CnnWorkload(torch, T, 8192)
+            elif name in HbmWorkload.OPS:
+                wl = HbmWorkload(torch, T, name, 1 << 28, on_device=True)
+            else:
+                wl = KernelFamilyWorkload(torch, T, name)
+            steps = EXTRA_STEPS.get(name, 10)
+            m = bench.measure(wl, steps, 3)
+            # whole-job aggregate: a rank's units per step (its share, for a strong-scaling job) x ranks
+            value = wl.units_per_step() * bench.world / (m["ms_per_step"] / 1e3)
+            rec = {"workload": name, "metric": wl.metric, "value": value, "unit": wl.unit,
+                   "ms_per_step": m["ms_per_step"], "steps": steps, "scaling": wl.scaling,
+                   "config": wl.config(), "gpu_launches": m["launches"], "clocks": m["clocks"],
+                   "l2": "flushed between steps" if m["flush"] else "inputs larger than L2"}
+            if name != "gemm512":
+                rec["roofline"] = roofline_of(wl, m, pk, mma, precision)
+            out.append(rec)
+        finally:
+            if precision == "bf16":
+                check(lib.ct_set_precision(_lib.PREC_3XTF32))
+        if hasattr(wl, "close"):
+            wl.close()
+        del wl
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
+
+
+def plugin_leg(args, batch, world_reduce):
+    """The headline's end-to-end number through the plugin's operator bodies, driven the way a
+    scheduler drives them (src/passes/sched/nodevm/nodevm.cpp:557-591): per step a host batch
+    becomes a tensor (host-to-device copy), the operators are called through operator_t, and the
+    host reads probabilities and arg-max back; wall clock in C++ around each step.  mode 0: the
+    fused operators; mode 1: the module's small operators (deferred-expression path)."""
+    import ctypes as C
+
+    harness = ROOT / "camel_b200" / "host" / "_build" / "libcamel_tensor_host_test.so"
+    if not harness.exists():
+        return None
+    h = C.CDLL(str(harness))
+    x, w, b = mlp_inputs(batch)
+    xs = np.ascontiguousarray(np.stack([x, x[::-1]]))
+    probs, arg = np.zeros((batch, 10), np.float32), np.zeros(batch, np.int64)
+    steps = max(20, args.steps)
+    out = {}
+    for mode, key in ((0, "fused_operators"), (1, "small_operators")):
+        secs = (C.c_double * steps)()
+        launches, err = C.c_uint64(), C.create_string_buffer(512)
+        P = lambda a: C.c_void_p(a.ctypes.data)  # noqa: E731
+        rc = h.camel_host_mlp_forward(
+            C.c_int(mode), P(xs), C.c_int(2), C.c_int64(batch), C.c_int64(784), C.c_int64(1024), C.c_int64(1024),
+            C.c_int64(10), P(w[0]), P(b[0]), P(w[1]), P(b[1]), P(w[2]), P(b[2]), C.c_int(steps), P(probs), P(arg),
+            secs, C.byref(launches), err, C.c_int(512))
+        if rc != 0:
+            raise RuntimeError("plugin leg: " + err.value.decode())
+        t = np.array(list(secs))[3:]  # the first steps build the weights' tensor-core layout
+        med = world_reduce(float(np.median(t)))
+        out[key] = {"seconds_per_step": med, "launches_per_step": launches.value / steps,
+                    "argmax_checksum": int(arg.sum()), "probs_row_sums_ok": bool(np.all(np.abs(probs.sum(1) - 1) < 1e-4))}
+    return out
+
+
+def h2d_ceiling(bench, nbytes, copies=40):
+    """Bare host-to-device bandwidth of this rank while every rank copies at once: `copies`
+    cudaMemcpyAsync of the step's input size from page-locked memory, no kernels."""
+    import ctypes as C
+
+    lib, check = bench.lib, bench.check
+    src = _Pinned((nbytes,), np.uint8)
+    dst = bench.T.Tensor(2, (nbytes,))
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    check(lib.ct_event_create(C.byref(e0)))
+    check(lib.ct_event_create(C.byref(e1)))
+    for _ in range(3):
+        check(lib.ct_h2d_async(dst.ptr, src.data_ptr(), nbytes))
+    bench.barrier()
+    check(lib.ct_event_record(e0))
+    for _ in range(copies):
+        check(lib.ct_h2d_async(dst.ptr, src.data_ptr(), nbytes))
+    check(lib.ct_event_record(e1))
+    bench.barrier()
+    ms = C.c_float()
+    check(lib.ct_event_elapsed_ms(e0, e1, C.byref(ms)))
+    check(lib.ct_event_destroy(e0))
+    check(lib.ct_event_destroy(e1))
+    ms_max = bench.reduce_max(float(ms.value))
+    return nbytes * copies / (ms_max / 1e3) / 1e9
+
+
 def run_gpu(args, rank, world):
     import torch
 
@@ -760,7 +1203,7 @@ def run_gpu(args, rank, world):
 
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    import camel_b200
+    import camel_b200  # noqa: F401
     from camel_b200 import _lib, tensor as T
     from camel_b200._lib import check, lib
 
@@ -770,139 +1213,135 @@ def run_gpu(args, rank, world):
         check(lib.ct_set_precision(_lib.PREC_BF16))
     T.set_weight_cache(not args.no_weight_cache)
 
-    if args.workload == "mlp":
-        wl = MlpWorkload(torch, T, args.batch or 4096, use_graph=not args.eager)
-    elif args.workload == "gemm":
-        wl = GemmWorkload(torch, T, args.size, args.precision)
-    elif args.workload == "gemm_sharded":
-        wl = ShardedGemmWorkload(torch, dist, T, args.size, world, rank)
-    elif args.workload == "conv":
-        wl = ConvWorkload(torch, T, args.batch or 256)
-    elif args.workload == "cnn":
-        wl = CnnWorkload(torch, T, args.batch or 8192)
-    elif args.workload in HbmWorkload.OPS:
-        wl = HbmWorkload(torch, T, args.workload, args.size if args.size != 16384 else 1 << 28)
-    else:
-        wl = AddWorkload(torch, T, args.size if args.size != 16384 else 1 << 28)
-
-    flush = torch.empty(L2_BYTES * 2, dtype=torch.uint8, device="cuda") if wl.resident_bytes() < 2 * L2_BYTES else None
-
-    def barrier():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        """K steps, CUDA events around each step on the launching stream, L2 flushed between
-        steps when the working set is smaller than L2; returns total device ms."""
-        evs = []
-        barrier()
-        for _ in range(steps):
-            if flush is not None:
-                flush.fill_(1)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            fn()
-            e1.record()
-            evs.append((e0, e1))
-        barrier()
-        return sum(a.elapsed_time(b) for a, b in evs)
-
-    for _ in range(max(args.warmup, 3)):
-        wl.step()
-    T.check_async()
-
-    sampler = ClockSampler(local)
-    if rank == 0:
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler is not None:
         sampler.start()
-    replayed = getattr(wl, "graph", None) is not None
-    if not replayed:
-        check(lib.ct_profile_enable(1))
-    launches0 = lib.ct_launch_count()
-    ms = timed(wl.step, args.steps)
-    launches = lib.ct_launch_count() - launches0
-    prof_steps = args.steps
-    if replayed:
-        # a replayed graph bypasses the per-launch event brackets: time the dominant kernel on
-        # the same inputs, call by call, right after the timed region
-        prof_steps = min(args.steps, 10)
-        check(lib.ct_profile_enable(1))
-        timed(wl.eager_step, prof_steps)
-    tot, cnt = ctypes_double(), ctypes_u64()
-    check(lib.ct_profile_read(wl.dominant.encode(), tot, cnt))
-    check(lib.ct_profile_read(None, None, None))
-    check(lib.ct_profile_enable(0))
-    clocks = sampler.stop() if rank == 0 else None
-    T.check_async()
+    bench = Bench(torch, dist, lib, check, T, rank, world, sampler)
+    pk = peaks()
+    headline = args.workload == "default"
+    name = "mlp" if headline else args.workload
+
+    if name == "mma_peak":
+        mma = measured_mma_peaks(lib, check, sampler) if rank == 0 else None
+        if rank == 0:
+            print(json.dumps({"metric": "tensor_pipe_peak_tflops", "unit": "TFLOP/s", "n_gpus": 1,
+                              "value": mma["tf32"]["burst_tflops"], "mma_peak": mma,
+                              "config": {"workload": "tcgen05.mma 128x256 back to back on resident operands, one CTA per SM"}}))
+        if sampler is not None:
+            sampler.stop()
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    if name == "mlp":
+        wl = MlpWorkload(torch, T, args.batch or 4096, use_graph=not args.eager)
+    elif name == "gemm":
+        wl = GemmWorkload(torch, T, args.size, args.precision)
+    elif name == "gemm512":
+        wl = Gemm512Workload(torch, T)
+    elif name == "gemm_sharded":
+        wl = ShardedGemmWorkload(torch, dist, T, args.size, world, rank)
+    elif name == "conv":
+        wl = ConvWorkload(torch, T, args.batch or 256)
+    elif name == "cnn":
+        wl = CnnWorkload(torch, T, args.batch or 8192, fuse_pool=not args.unfused_pool)
+    elif name == "add":
+        wl = AddWorkload(torch, T, args.size if args.size != 16384 else 1 << 28)
+    elif name in HbmWorkload.OPS:
+        wl = HbmWorkload(torch, T, name, args.size if args.size != 16384 else 1 << 28)
+    else:
+        wl = KernelFamilyWorkload(torch, T, name)
+
+    # the tensor pipe's ceiling, measured first on rank 0 (the other ranks wait at the next barrier)
+    mma = None
+    if rank == 0 and (wl.bound == "tensor" or headline):
+        mma = measured_mma_peaks(lib, check, sampler)
+
+    m = bench.measure(wl, args.steps, args.warmup, min_gpu_s=1.0 if headline else 0.0)
+    ms_per_step = m["ms_per_step"]
+    # whole-job aggregate: a rank's units per step (its share, for a strong-scaling job) x ranks
+    value = wl.units_per_step() * world / (ms_per_step / 1e3)
 
     # end to end through host buffers
-    streamed = hasattr(wl, "e2e_run") and not args.eager
-    if streamed:
-        wl.e2e_run(3, flush)
-        e2e_steps = max(1, args.steps)
-        barrier()
-        t0 = time.perf_counter()
-        e2e_ms_dev = wl.e2e_run(e2e_steps, flush)
-        barrier()
-    else:
-        for _ in range(2):
-            wl.e2e_step()
-        e2e_steps = max(1, min(args.steps, 10))
-        barrier()
-        t0 = time.perf_counter()
-        e2e_ms_dev = timed(wl.e2e_step, e2e_steps)
-    e2e_wall = time.perf_counter() - t0
-    T.check_async()
+    flush = bench.flush_for(wl)
+    e2e = None
+    if hasattr(wl, "e2e_step") or hasattr(wl, "e2e_run"):
+        streamed = hasattr(wl, "e2e_run") and not args.eager
+        if streamed:
+            wl.e2e_run(3, flush)
+            e2e_steps = max(1, args.steps)
+            bench.barrier()
+            t0 = time.perf_counter()
+            e2e_ms_dev = wl.e2e_run(e2e_steps, flush)
+            bench.barrier()
+        else:
+            for _ in range(2):
+                wl.e2e_step()
+            e2e_steps = max(1, min(args.steps, 10))
+            bench.barrier()
+            t0 = time.perf_counter()
+            e2e_ms_dev = bench.timed(wl.e2e_step, e2e_steps, flush)
+        e2e_wall = time.perf_counter() - t0
+        T.check_async()
+        e2e_ms = bench.reduce_max(max(e2e_ms_dev, 0.0))
+        e2e_units = getattr(wl, "e2e_units_per_step", wl.units_per_step)()
+        e2e = {"value": e2e_units * e2e_steps * world / (e2e_ms / 1e3), "unit": wl.unit,
+               "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "steps": e2e_steps, "wall_s": e2e_wall,
+               "mode": "copy in / kernels / copy out of consecutive steps overlapped on three streams"
+               if streamed else "copy in, kernels, copy out one after the other, each step"}
+        if wl.h2d:
+            e2e["h2d_ceiling_gbs_per_gpu"] = h2d_ceiling(bench, wl.h2d)
+            e2e["h2d_gbs_per_gpu_achieved"] = wl.h2d * e2e_steps / (e2e_ms / 1e3) / 1e9
 
-    def reduce_max(v):
-        from camel_b200 import sharding
-        return sharding.reduce_max(dist, torch, v, "cuda")
+    plugin = None
+    if name == "mlp" and not args.eager:
+        if hasattr(wl, "pipe") and wl.pipe is not None:
+            wl.pipe.close()
+            wl.pipe = None
+        plugin = plugin_leg(args, wl.batch, bench.reduce_max)
 
-    ms = reduce_max(ms)
-    e2e_ms = reduce_max(max(e2e_ms_dev, 0.0))
-    value = wl.units_per_step() * args.steps * world / (ms / 1e3)
-    e2e_units = getattr(wl, "e2e_units_per_step", wl.units_per_step)()
-    e2e_value = e2e_units * e2e_steps * world / (e2e_ms / 1e3)
+    extras = run_extras(bench, args, pk, mma) if headline and not args.no_extras else None
 
     if rank == 0:
-        pk = peaks()
-        dom_ms = tot.value / max(1, cnt.value)
-        launches_per_step = cnt.value / prof_steps
-        alg = wl.algorithmic_per_step() / max(1.0, launches_per_step)
-        if wl.bound == "tensor":
-            if args.precision == "bf16":
-                peak, peak_note = pk["bf16_tflops"], f"{pk['source']} bf16 dense burst"
-            else:
-                peak = pk["bf16_tflops"] / 6.0
-                peak_note = (f"{pk['source']} bf16 dense burst / 2 (tf32 rate) / 3 (three MMAs per product); "
-                             f"sustained variant {pk['bf16_tflops_sustained'] / 6.0:.1f}")
-            achieved = alg / (dom_ms / 1e3) / 1e12 if dom_ms > 0 else 0.0
-            runit = "TFLOP/s"
-        else:
-            peak, peak_note = pk["hbm_gbs"], f"{pk['source']} STREAM-style copy"
-            achieved = alg / (dom_ms / 1e3) / 1e9 if dom_ms > 0 else 0.0
-            runit = "GB/s"
-        traffic, traffic_note = wl.ncu_traffic() if args.precision != "bf16" else (None, "no ncu capture in bf16 mode")
-        roofline = {"bound": wl.bound, "kernel": wl.dominant, "achieved": achieved, "peak": peak, "unit": runit,
-                    "frac": achieved / peak if peak else None, "traffic": traffic, "traffic_unit": "bytes per launch",
-                    "traffic_note": traffic_note, "peak_note": peak_note,
-                    "launches_per_step": launches_per_step, "avg_launch_ms": dom_ms}
+        roofline = roofline_of(wl, m, pk, mma, args.precision)
         cpu = cpu_baseline(args) if world == 1 and not args.no_cpu_baseline else None
         line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-                "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": wl.scaling, "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, f32 accumulate)"
                 if args.precision != "bf16" else "bf16 in / f32 accumulate", "data": "synthetic",
                 "config": {"parallelism": f"{world} ranks, independent shards, no data-path collective",
-                           **wl.config(), "l2": "flushed between steps" if flush is not None else "inputs larger than L2"},
-                "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
-                        "steps": e2e_steps, "wall_s": e2e_wall,
-                        "mode": "copy in / kernels / copy out of consecutive steps overlapped on three streams"
-                        if streamed else "copy in, kernels, copy out one after the other, each step"},
-                "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks}
+                           **wl.config(), "l2": "flushed between steps" if m["flush"] else "inputs larger than L2"},
+                "timed_region": {"blocks_of_steps": m["blocks"], "gpu_s": m["gpu_s"],
+                                 "rule": "blocks of exactly `steps` timed steps; ms_per_step is the median block's"},
+                "gpu_launches": m["launches"], "roofline": roofline, "clocks": m["clocks"]}
+        if plugin is not None:
+            # the headline end-to-end figure: through the plugin's operator bodies, host buffers in and out
+            fused = plugin["fused_operators"]
+            line["e2e"] = {"value": wl.batch * world / fused["seconds_per_step"], "unit": wl.unit,
+                           "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
+                           "seconds_per_step": fused["seconds_per_step"], "launches_per_step": fused["launches_per_step"],
+                           "mode": "per step: host batch -> tensor (pageable host memory, one synchronous copy), dense_relu, "
+                                   "dense_relu, dense_softmax, argmax through operator_t, host read-back of both results; "
+                                   "wall clock in C++ around the step, median step, slowest rank"}
+            small = plugin["small_operators"]
+            line["e2e_plugin_small_operators"] = {
+                "value": wl.batch * world / small["seconds_per_step"], "unit": wl.unit,
+                "seconds_per_step": small["seconds_per_step"], "launches_per_step": small["launches_per_step"],
+                "mode": "the same step written with the module's small operators (x @ w, h * (h > 0), the softmax "
+                        "function of mnist.cml:13-25): deferred expressions recognised and fused by the plugin"}
+            if e2e is not None:
+                line["e2e_pipelined"] = e2e
+        elif e2e is not None:
+            line["e2e"] = e2e
+        if mma is not None:
+            line["mma_peak"] = mma
+        if extras is not None:
+            line["extras"] = extras
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line))
+    if sampler is not None:
+        sampler.stop()
     if dist is not None:
         dist.destroy_process_group()
 
@@ -938,8 +1377,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="mlp", choices=["mlp", "gemm", "gemm_sharded", "conv", "cnn", "add", "relu", "exp", "log", "mul", "scale", "gt", "sum",
-                             "softmax"])
+    ap.add_argument("--workload", default="default",
+                    choices=["default", "mlp", "gemm", "gemm512", "gemm_sharded", "conv", "cnn", "add", "relu", "exp", "log",
+                             "mul", "scale", "gt", "sum", "softmax", "sum_axis0", "sum_axis1", "max_axis1",
+                             "argmax_axis1", "argmax_rows", "transpose", "maxpool", "fill", "split_rows", "mma_peak"],
+                    help="default: the MLP forward as the headline plus every other workload under `extras`")
+    ap.add_argument("--no-extras", action="store_true", help="the headline only")
+    ap.add_argument("--unfused-pool", action="store_true", help="cnn: conv2d then maxpool2d instead of the fused call")
     ap.add_argument("--size", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "bf16"])

@@ -37,6 +37,7 @@ PROTOTYPES = {
     "ct_check": (_int, []),
     "ct_inject_status": (_int, [_int, C.c_uint32]),
     "ct_measure_mma_peak": (_int, [_int, _int, _int, C.POINTER(_dbl), C.POINTER(_dbl)]),
+    "ct_measure_mma_rate": (_int, [_int, _int, _int, _int, _int, C.POINTER(_dbl), C.POINTER(_dbl)]),
     "ct_launch_count": (_u64, []),
     "ct_profile_enable": (_int, [_int]),
     "ct_profile_read": (_int, [C.c_char_p, C.POINTER(_dbl), C.POINTER(_u64)]),

@@ -660,6 +660,7 @@ ct_status ct_maxpool2d(
         return CT_OK;
     if (!x || !out)
         return fail(CT_ERR_INVALID, "maxpool2d: null pointer");
+    ProfScope prof("maxpool");
     if (window == 2 && (w & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
         (reinterpret_cast<uintptr_t>(out) & 7u) == 0)
         maxpool2x2_wide_kernel<<<capped_blocks(st, total / 2, 32), 256, 0, stream()>>>(x, n * c, h, w, ho, wo, out);

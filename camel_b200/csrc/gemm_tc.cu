@@ -1441,7 +1441,11 @@ namespace {
 // out[i] = act(sum_z partial[z][i] + bias[i % n]), slices added in ascending order.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(
     const float *__restrict__ partial, int splits, int64_t total, int64_t n, const float *__restrict__ bias,
-    int act, float *__restrict__ out) {
+    int act, float *__restrict__ out, const uint32_t *__restrict__ flags) {
+    // the slices were not computed if the launch before this one gave up (or never started because
+    // an earlier failure is still on record): write nothing rather than sums of stale partials
+    if (*reinterpret_cast<const volatile uint32_t *>(flags + FLAG_TIMEOUT) != 0)
+        return;
     int64_t step = (int64_t)gridDim.x * 256;
     for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
         float v = partial[i];
@@ -1513,7 +1517,7 @@ ct_status gemm_planes(
             if (blocks > cap)
                 blocks = cap;
             ProfScope prof("gemm_splitk_reduce");
-            splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(partial, splits, total, n, bias, act, out);
+            splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream()>>>(partial, splits, total, n, bias, act, out, st->flags_dev);
             CT_LAUNCH_CHECK("splitk_reduce");
             return CT_OK;
         }

@@ -22,7 +22,7 @@ constexpr int kPeakThreads = 128;
 
 // kind: 0 = kind::tf32, 1 = kind::f16 with bf16 operands
 template <int KIND>
-__global__ void __launch_bounds__(kPeakThreads, 1) mma_peak_kernel(int mma_groups, uint32_t *status) {
+__global__ void __launch_bounds__(kPeakThreads, 1) mma_peak_kernel(int mma_groups, uint32_t *status, int mma_m, int mma_n) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_done;
     __shared__ uint32_t tmem_base_slot;
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kPeakThreads, 1) mma_peak_kernel(int mma_group
     const uint32_t tmem_base = tmem_base_slot;
 
     if (warp == 1 && (threadIdx.x & 31) == 0) {
-        const uint32_t idesc = make_idesc(KIND == 0 ? 2u : 1u, 128, kPeakBN);
+        const uint32_t idesc = make_idesc(KIND == 0 ? 2u : 1u, (uint32_t)mma_m, (uint32_t)mma_n);
         for (int g = 0; g < mma_groups; ++g) {
             const uint32_t set = smem_base + (uint32_t)(g & 1) * (kPeakABytes + kPeakBBytes);
             const uint64_t da = smem_desc_k<kPeakRowB>(set), db = smem_desc_k<kPeakRowB>(set + kPeakABytes);
@@ -95,8 +95,19 @@ using namespace ct;
 // Runs `launches` back-to-back launches of the MMA loop (mma_groups x 4 MMAs of 128 x 256 x 8
 // (tf32) or 128 x 256 x 16 (bf16) per CTA, one CTA per SM), timed with CUDA events on the current
 // stream.  *tflops_host = dense MMA rate over the whole timed region; *ms_host its duration.
+// A launch also pays its set-up (operand fill, TMEM allocation, launch latency: some 15 us), so
+// the pipe's own rate is the difference quotient of two launch sizes, (flop(g2) - flop(g1)) /
+// (t(g2) - t(g1)); the caller forms it from two calls.
 extern "C" ct_status ct_measure_mma_peak(
     ct_precision kind, int mma_groups, int launches, double *tflops_host, double *ms_host) {
+    return ct_measure_mma_rate(kind, 128, kPeakBN, mma_groups, launches, tflops_host, ms_host);
+}
+
+// The same loop with another MMA shape (m = 64 or 128 rows, n = 16..256 columns in steps of 16):
+// how the pipe's rate depends on the shape a kernel can give it.  A layer with 64 output channels
+// cannot fill 256 columns; what its kernel reaches has to be read against the rate of its shape.
+extern "C" ct_status ct_measure_mma_rate(
+    ct_precision kind, int mma_m, int mma_n, int mma_groups, int launches, double *tflops_host, double *ms_host) {
     OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
@@ -104,6 +115,8 @@ extern "C" ct_status ct_measure_mma_peak(
         return fail(CT_ERR_INVALID, "ct_measure_mma_peak: mma_groups in [2, 2^20], launches in [1, 2^20]");
     if (kind != CT_PREC_3XTF32 && kind != CT_PREC_BF16)
         return fail(CT_ERR_INVALID, "ct_measure_mma_peak: unknown kind");
+    if ((mma_m != 64 && mma_m != 128) || mma_n < 16 || mma_n > kPeakBN || (mma_n & 15) != 0)
+        return fail(CT_ERR_INVALID, "ct_measure_mma_rate: m must be 64 or 128, n a multiple of 16 up to %d", kPeakBN);
     // the in-kernel wait for the last MMA is bounded by one second: keep a launch far below that
     if ((double)mma_groups * 4 * 70e-9 > 0.25)
         return fail(CT_ERR_TOO_LARGE, "ct_measure_mma_peak: a launch of %d MMA groups would run too long", mma_groups);
@@ -113,11 +126,11 @@ extern "C" ct_status ct_measure_mma_peak(
     cudaEvent_t e0, e1;
     CT_CUDA(cudaEventCreate(&e0));
     CT_CUDA(cudaEventCreate(&e1));
-    kernel<<<st->sm_count, kPeakThreads, kPeakSmem, stream()>>>(mma_groups, st->flags_dev + 3); // warm-up
+    kernel<<<st->sm_count, kPeakThreads, kPeakSmem, stream()>>>(mma_groups, st->flags_dev + 3, mma_m, mma_n); // warm-up
     CT_LAUNCH_CHECK("mma_peak");
     CT_CUDA(cudaEventRecord(e0, stream()));
     for (int i = 0; i < launches; ++i) {
-        kernel<<<st->sm_count, kPeakThreads, kPeakSmem, stream()>>>(mma_groups, st->flags_dev + 3);
+        kernel<<<st->sm_count, kPeakThreads, kPeakSmem, stream()>>>(mma_groups, st->flags_dev + 3, mma_m, mma_n);
         CT_LAUNCH_CHECK("mma_peak");
     }
     CT_CUDA(cudaEventRecord(e1, stream()));
@@ -131,7 +144,7 @@ extern "C" ct_status ct_measure_mma_peak(
     if (bad)
         return fail(CT_ERR_TIMEOUT, "ct_measure_mma_peak: the wait for the last MMA ran out (block %u)", bad - 1);
     const double k_per_mma = kind == CT_PREC_3XTF32 ? 8.0 : 16.0;
-    const double flop = 2.0 * 128 * kPeakBN * k_per_mma * 4.0 * mma_groups * (double)st->sm_count * launches;
+    const double flop = 2.0 * mma_m * mma_n * k_per_mma * 4.0 * mma_groups * (double)st->sm_count * launches;
     if (tflops_host)
         *tflops_host = ms > 0 ? flop / (ms * 1e-3) / 1e12 : 0.0;
     if (ms_host)

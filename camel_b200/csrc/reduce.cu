@@ -284,6 +284,7 @@ __global__ void __launch_bounds__(256) reduce_cols_kernel(const T *in, int64_t r
 
 template <int KIND, typename T, typename OT>
 ct_status reduce_axis_typed(const T *in, int64_t rows, int64_t cols, int axis, OT *out) {
+    ProfScope prof("reduce");
     if (axis == 1) {
         if (rows == 0)
             return CT_OK;
@@ -624,6 +625,7 @@ ct_status concat_typed(
     uint64_t cap    = (uint64_t)st->sm_count * 16;
     if (blocks > cap)
         blocks = cap;
+    ProfScope prof("concat");
     concat_kernel<U><<<(unsigned)blocks, 256, 0, stream()>>>(
         static_cast<const U *>(l), static_cast<const U *>(r), outer, ll, rl, static_cast<U *>(o));
     CT_LAUNCH_CHECK("concat");
@@ -719,6 +721,7 @@ ct_status ct_transpose(ct_dtype dt, const void *in, int64_t rows, int64_t cols, 
     dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
     if ((rows + 31) / 32 > 65535)
         return fail(CT_ERR_TOO_LARGE, "transpose: too many rows");
+    ProfScope prof("transpose");
     switch (dt) {
     case CT_F32:
         transpose_kernel<float><<<grid, 256, 0, stream()>>>(

@@ -97,8 +97,9 @@ ct_status ct_inject_status(int word, uint32_t value);
 uint64_t ct_launch_count(void);
 /* Device timing per kernel family: while enabled, each launch is bracketed by CUDA events on
  * the launching stream.  ct_profile_read synchronises, sums and clears the records filed under
- * `kernel` ("gemm_tc", "gemm_prepass", "gemm_skinny", "im2col", "elementwise", "reduce",
- * "softmax"); NULL reads all. */
+ * `kernel` ("gemm_tc", "gemm_prepass", "gemm_skinny", "gemm_splitk_reduce", "weights_pack",
+ * "conv_prepass", "conv_small_c", "im2col", "elementwise", "reduce", "softmax", "transpose",
+ * "concat", "maxpool"); NULL reads all. */
 ct_status ct_profile_enable(int on);
 ct_status ct_profile_read(const char *kernel, double *total_ms_host, uint64_t *launches_host);
 /* The tensor pipe's own ceiling, measured: every SM issues `mma_groups` x 4 tcgen05.mma of
@@ -109,6 +110,12 @@ ct_status ct_profile_read(const char *kernel, double *total_ms_host, uint64_t *l
  * is the tf32 figure / 3.  No reference counterpart (a measurement, not an operator). */
 ct_status ct_measure_mma_peak(
     ct_precision kind, int mma_groups, int launches, double *tflops_host, double *ms_host);
+/* The same measurement for another MMA shape: mma_m = 64 or 128 rows, mma_n = 16..256 columns (a
+ * multiple of 16).  The rate the pipe gives a narrow shape is what a layer with few output
+ * channels can be held against.  No reference counterpart. */
+ct_status ct_measure_mma_rate(
+    ct_precision kind, int mma_m, int mma_n, int mma_groups, int launches, double *tflops_host,
+    double *ms_host);
 ct_status ct_set_precision(ct_precision precision);
 ct_precision ct_get_precision(void);
 

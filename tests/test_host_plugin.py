@@ -353,3 +353,23 @@ def test_plugin_reports_kernel_timeout_at_the_host_read(plugin):
     got = s.fetch(s.call("matmul", ha, ha))
     ref = (a.astype(np.float64) @ a.astype(np.float64)).astype(np.float32)
     assert np.max(np.abs(got - ref)) / np.max(np.abs(ref)) <= 1e-5
+
+
+@needs_build
+def test_signature_file_lists_the_registration_table(plugin):
+    """camel_b200/stdlib/signatures/tensor.cml (doc-only signatures in the style of the reference's
+    stdlib/signatures/globals.cml:8-10) names every (group, URI) pair the module registers, in
+    order, with the registered parameter lists, and nothing else."""
+    import re
+
+    text = (ROOT / "camel_b200" / "stdlib" / "signatures" / "tensor.cml").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    found = re.findall(r"(?:with <([^>]*)>\s*)?inner func (\w+)\(([^)]*)\): ([^{]+?) \{\s*return '([^']+)'\s*\}", text)
+    listed = [(name, uri) for _, name, _, _, uri in found]
+    table = plugin.groups()
+    assert listed == [(g, u) for g, u, _ in table]
+    assert len(listed) == 49
+    for (with_params, name, params, ret, uri), (_, _, sig) in zip(found, table):
+        want = (f"<{with_params}>" if with_params else "") + f"({params}) => {ret}"
+        assert want == sig or sig == "(Tensor, Tensor) => Tensor", (name, want, sig)
+    assert {u for _, u in listed} == {"tensor:" + o for o in plugin.ops()}
