@@ -489,6 +489,11 @@ class ShardedGemmWorkload(Workload):
         check(lib.ct_weights_pack(self.b_t.data_ptr(), n, n, C.byref(self.b_packed)))
         self.a_packed = C.c_void_p()  # planes of this rank's rows of A: refilled every step, allocated once
         self.side = torch.cuda.Stream()
+        # all bands in one launch: per-band counters of finished tiles, which the side stream waits on
+        self.band_done = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.band_rows = (C.c_int64 * len(self.bands))(*[cnt for _, cnt, _, _ in self.bands])
+        self.band_out = (C.c_void_p * len(self.bands))(*[self.c_t.data_ptr() + g0 * n * 4 for _, _, g0, _ in self.bands])
+        self.band_tiles = (C.c_uint32 * len(self.bands))()
         torch.cuda.synchronize()
         self.h2d = self.d2h = 0
 
@@ -497,15 +502,21 @@ class ShardedGemmWorkload(Workload):
         from camel_b200._lib import check, lib
         torch, n = self.torch, self.n
         check(lib.ct_rows_pack(self.a_t.data_ptr(), self.rows, n, C.byref(self.a_packed)))
-        for off, cnt, g0, band0 in self.bands:
-            check(lib.ct_matmul_packed_rows(self.a_packed, off, cnt, self.b_packed, self.c_t.data_ptr() + g0 * n * 4))
-            if self.world > 1:
-                done = torch.cuda.Event()
-                done.record()
-                with torch.cuda.stream(self.side):
-                    self.side.wait_event(done)
-                    self.sharding.gather_band(self.dist, self.c_t, band0, cnt, self.rank, self.world)
+        # One launch computes the bands in order and counts finished tiles per band; the side stream
+        # waits for a band's count and all-gathers it while the same launch works on the next band.
+        self.band_done.zero_()
+        cleared = torch.cuda.Event()
+        cleared.record()
+        check(lib.ct_matmul_packed_bands(self.a_packed, self.b_packed, len(self.bands), self.band_rows, self.band_out,
+                                         self.band_done.data_ptr(), self.band_tiles))
         if self.world > 1:
+            with torch.cuda.stream(self.side):
+                self.side.wait_event(cleared)  # not before the counters of the previous step were cleared
+                for j, (off, cnt, g0, band0) in enumerate(self.bands):
+                    check(lib.ct_set_stream(self.side.cuda_stream))
+                    check(lib.ct_stream_wait_value(self.band_done.data_ptr() + 4 * j, self.band_tiles[j]))
+                    check(lib.ct_set_stream(None))
+                    self.sharding.gather_band(self.dist, self.c_t, band0, cnt, self.rank, self.world)
             torch.cuda.current_stream().wait_stream(self.side)
         if not self.checked:  # untimed: the first warm-up step
             self.checked = True
@@ -530,7 +541,7 @@ class ShardedGemmWorkload(Workload):
 
     def config(self):
         return {"workload": f"gemm fp32 M=N=K={self.n}, A row-sharded over {self.world} ranks, C all-gathered "
-                            f"in place in {self.panels} bands of halving size overlapped with compute, B and its tensor-core layout "
+                            f"in place in {self.panels} bands of halving size (one launch, a band travels as soon as its tiles are done), B and its tensor-core layout "
                             f"placed once (BASELINE configs[4])",
                 "precision": "3xtf32", "e2e": "same as value: operands are resident by construction",
                 "parallelism": f"{self.world} ranks, rows of A and C sharded, NCCL all-gather of C on a side stream"}
@@ -1254,7 +1265,7 @@ def run_gpu(args, rank, world):
 
     # the tensor pipe's ceiling, measured first on rank 0 (the other ranks wait at the next barrier)
     mma = None
-    if rank == 0 and (wl.bound == "tensor" or headline):
+    if rank == 0 and (wl.bound == "tensor" or headline) and not args.no_peak:
         mma = measured_mma_peaks(lib, check, sampler)
 
     m = bench.measure(wl, args.steps, args.warmup, min_gpu_s=1.0 if headline else 0.0)
@@ -1383,6 +1394,9 @@ def main():
                              "argmax_axis1", "argmax_rows", "transpose", "maxpool", "fill", "split_rows", "mma_peak"],
                     help="default: the MLP forward as the headline plus every other workload under `extras`")
     ap.add_argument("--no-extras", action="store_true", help="the headline only")
+    ap.add_argument("--no-peak", action="store_true",
+                    help="skip the tensor-pipe measurement (thousands of launches: unwanted under a profiler); the "
+                         "roofline then falls back to the figure derived from the driver-written bf16 GEMM peak")
     ap.add_argument("--unfused-pool", action="store_true", help="cnn: conv2d then maxpool2d instead of the fused call")
     ap.add_argument("--size", type=int, default=16384)
     ap.add_argument("--batch", type=int, default=0)

@@ -91,6 +91,8 @@ PROTOTYPES = {
     "ct_rows_pack": (_int, [_vp, _i64, _i64, C.POINTER(_vp)]),
     "ct_rows_free": (_int, [_vp]),
     "ct_matmul_packed_rows": (_int, [_vp, _i64, _i64, _vp, _vp]),
+    "ct_matmul_packed_bands": (_int, [_vp, _vp, _int, C.POINTER(_i64), C.POINTER(_vp), _vp, C.POINTER(C.c_uint32)]),
+    "ct_stream_wait_value": (_int, [_vp, C.c_uint32]),
     "ct_dense_packed": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp]),
     "ct_conv2d": (_int, [_vp, _vp, _vp] + [_i64] * 9 + [_int, _vp]),
     "ct_conv2d_maxpool2": (_int, [_vp, _vp, _vp] + [_i64] * 9 + [_int, _vp]),

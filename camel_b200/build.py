@@ -19,7 +19,7 @@ OBJ_DIR = ROOT / "build"
 LIB = ROOT / "libcamel_tensor_b200.so"
 
 SOURCES = ["runtime.cu", "elementwise.cu", "reduce.cu", "gemm_simt.cu", "gemm_tc.cu", "contract.cu",
-           "graph.cu", "peak.cu"]
+           "graph.cu", "peak.cu", "conv_tmem.cu", "conv_halo.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

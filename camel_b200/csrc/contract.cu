@@ -1,6 +1,7 @@
 // Entry points of the contractions (matmul, dense, conv2d) and maxpool2d: argument checks,
 // dispatch between the tensor-core kernel and the CUDA-core kernels, and the conv2d lowering.
 #include "common.cuh"
+#include "tmap.cuh"
 #include "split.cuh"
 
 #include <cuda_bf16.h>
@@ -283,15 +284,20 @@ __global__ void __launch_bounds__(256) maxpool2x2_kernel(
 }
 
 // The same on widths that are a multiple of 4: two 128-bit loads and one 64-bit store per thread.
+// IDX: the type the flat index is divided in (32-bit divisions where the element count allows:
+// two 64-bit divisions per thread cost more than the loads they address).
+template <typename IDX>
 __global__ void __launch_bounds__(256) maxpool2x2_wide_kernel(
     const float *__restrict__ x, int64_t planes, int64_t h, int64_t w, int64_t ho, int64_t wo,
     float *__restrict__ out) {
-    const int64_t pairs = wo >> 1;
-    int64_t total       = planes * ho * pairs;
-    int64_t step        = (int64_t)gridDim.x * 256;
-    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
-        int64_t px = i % pairs, oy = (i / pairs) % ho, p = i / (pairs * ho);
-        const float *src = x + (p * h + oy * 2) * w + px * 4;
+    const IDX pairs = (IDX)(wo >> 1), rows = (IDX)ho;
+    const IDX total = (IDX)(planes * ho) * pairs;
+    const IDX step  = (IDX)gridDim.x * 256;
+    for (IDX i = (IDX)blockIdx.x * 256 + threadIdx.x; i < total; i += step) {
+        const IDX row = i / pairs, px = i - row * pairs; // row = plane * ho + oy
+        const IDX p64 = row / rows, oy = row - p64 * rows;
+        const int64_t p  = (int64_t)p64;
+        const float *src = x + (p * h + (int64_t)oy * 2) * w + (int64_t)px * 4;
         float4 a         = __ldcs(reinterpret_cast<const float4 *>(src));
         float4 b         = __ldcs(reinterpret_cast<const float4 *>(src + w));
         float m0 = a.x, m1 = a.z; // the window's first element seeds, later ones win on strict '>'
@@ -307,7 +313,7 @@ __global__ void __launch_bounds__(256) maxpool2x2_wide_kernel(
             m1 = b.z;
         if (b.w > m1)
             m1 = b.w;
-        __stcs(reinterpret_cast<float2 *>(out + (p * ho + oy) * wo + px * 2), make_float2(m0, m1));
+        __stcs(reinterpret_cast<float2 *>(out + (p * ho + (int64_t)oy) * wo + (int64_t)px * 2), make_float2(m0, m1));
     }
 }
 
@@ -512,9 +518,13 @@ ct_status ct_conv2d_maxpool2(
     // the short-patch, tiny or few-filter shapes that it serves with float64 CUDA-core kernels
     const int64_t kdim = c * kh * kw, pix = ho * wo;
     const bool tensor_core = kdim > kSmallPatch && !(kdim * ko * pix * n < kTinyMacs * 8 || ko < 16 || pix < 64);
-    const bool fused = tensor_core && stride == 1 && c >= 16 && ko <= 64 && ko > 0 && wo <= 128 && (wo & 1) == 0 && (ho & 1) == 0 &&
-                       kp_i <= 1024 * (kblock / 32) && pooled_tile_rows(ho, wo) >= 2 && conv_tile_rows(ho, wo) > 0 &&
-                       n > 0;
+    const bool swap_kernel = ko <= 64 && ko > 0 && wo <= 128 && kp_i <= 1024 * (kblock / 32) && pooled_tile_rows(ho, wo) >= 2;
+    // the layer's kernel is chosen without regard to the pool (conv2d_run), so that the fused and the
+    // two-step form run the same arithmetic; the pool is fused where that kernel can do it
+    bool tmem_pool         = false;
+    const bool tmem_kernel = kblock == 32 && conv_tmem_applicable(c, h, wd, ko, kh, kw, stride, pad, &tmem_pool);
+    const bool fused = tensor_core && stride == 1 && c >= 16 && (wo & 1) == 0 && (ho & 1) == 0 && conv_tile_rows(ho, wo) > 0 &&
+                       n > 0 && (tmem_kernel ? tmem_pool : swap_kernel);
     if (fused)
         return conv2d_run(x, w, bias, n, c, h, wd, ko, kh, kw, stride, pad, act, out, 2);
     // not a shape of the fused kernel: the convolution into a temporary, then maxpool2d
@@ -591,6 +601,18 @@ static ct_status conv2d_run(
     // patch matrix is never materialised - each k-block is one shifted 4-D TMA box.
     const int th = (stride == 1 && c >= 16 && wo <= 256 && wd <= 0x7fffffff && h <= 0x7fffffff)
                        ? conv_tile_rows(ho, wo) : 0;
+    if (th > 0 && mode == 0 && conv_tmem_applicable(c, h, wd, ko, kh, kw, stride, pad)) {
+        // few channels on both sides: the filters stay in tensor memory, a tile's input is fetched
+        // once (conv_tmem.cu); only the input needs the NHWC hi/lo planes
+        size_t x_plane = align_up((size_t)n * h * wd * 32 * 4);
+        CT_TRY(ensure_ws(&st->gemm_ws, &st->gemm_ws_bytes, 2 * x_plane));
+        uint8_t *ws = static_cast<uint8_t *>(st->gemm_ws);
+        {
+            ProfScope prof("conv_prepass");
+            CT_TRY(nhwc_planes(st, mode, x, n, c, h * wd, 32, ws, ws + x_plane));
+        }
+        return conv_tmem_filters(st, ws, ws + x_plane, w, bias, n, c, h, wd, ko, kh, kw, pad, act, pool, out);
+    }
     if (th > 0) {
         int64_t c_pad  = (c + kblock - 1) / kblock * kblock;
         int64_t taps   = kh * kw;
@@ -613,6 +635,9 @@ static ct_status conv2d_run(
             CT_LAUNCH_CHECK("conv_weight_planes");
             CT_TRY(nhwc_planes(st, mode, x, n, c, h * wd, c_pad, x_hi, x_lo));
         }
+        if (mode == 0 && pool == 0 && conv_halo_applicable(c_pad, h, wd, ko, kh, kw, stride, pad))
+            // many filters: one input halo per tile and channel block serves every tap (conv_halo.cu)
+            return conv_halo_stream(st, w_hi, w_lo, x_hi, x_lo, n, c_pad, h, wd, ko, kh, kw, pad, bias, act, out);
         ConvGeom g;
         g.c_pad = (int)c_pad;
         g.h = (int)h, g.w = (int)wd, g.ho = (int)ho, g.wo = (int)wo;
@@ -663,7 +688,10 @@ ct_status ct_maxpool2d(
     ProfScope prof("maxpool");
     if (window == 2 && (w & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
         (reinterpret_cast<uintptr_t>(out) & 7u) == 0)
-        maxpool2x2_wide_kernel<<<capped_blocks(st, total / 2, 32), 256, 0, stream()>>>(x, n * c, h, w, ho, wo, out);
+        if (total / 2 + (int64_t)st->sm_count * 32 * 256 < 0x7fffffffll)
+            maxpool2x2_wide_kernel<uint32_t><<<capped_blocks(st, total / 2, 32), 256, 0, stream()>>>(x, n * c, h, w, ho, wo, out);
+        else
+            maxpool2x2_wide_kernel<uint64_t><<<capped_blocks(st, total / 2, 32), 256, 0, stream()>>>(x, n * c, h, w, ho, wo, out);
     else if (window == 2 && (w & 1) == 0 && (reinterpret_cast<uintptr_t>(x) & 7u) == 0)
         maxpool2x2_kernel<<<capped_blocks(st, total, 32), 256, 0, stream()>>>(x, n * c, h, w, ho, wo, out);
     else

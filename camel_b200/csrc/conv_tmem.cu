@@ -1,0 +1,453 @@
+// conv2d for layers with few channels on both sides (at most 32 in, at most 64 out, a small
+// filter; the 32 -> 64 channel 3x3 layer of a small CNN): the filters live in tensor memory.
+//
+// Why another kernel.  With 64 output channels the tensor core cannot be given a wide tile:
+// measured on B200 (ct_measure_mma_rate), tcgen05.mma kind::tf32 of 128 x N x 8 takes ~138 clocks
+// at N = 256, ~73 at N = 128, ~54 at N = 64 and never less than ~49, and M = 64 takes as long as
+// M = 128.  The pixels-on-rows kernel (conv_swap_stream_kernel) issues 128 x 64 x 8 MMAs and
+// re-fetches, per filter tap, a shifted copy of the same pixels and the tap's filter rows; its
+// operands cross shared memory twice (TMA in, MMA out), about 10 KB per MMA, and that traffic,
+// not the tensor pipe, sets its pace (~80 clocks per MMA).  Here
+//   * the filters are the A operand and stay in TENSOR MEMORY for the whole launch: rows 0..63
+//     hold the tf32 "hi" part of the 64 filters, rows 64..127 the "lo" part, 8 columns per k-step
+//     (tap, group of 8 input channels) - written once per CTA with tcgen05.st, never re-read from
+//     shared memory;
+//   * the pixels are the B operand, N = 128 per tile: th output rows of PW = w + 2 pad positions
+//     (the two halo columns of every row are computed and dropped).  A tile's input - th + kh - 1
+//     rows of PW positions, halo included, zeros outside the image - is fetched ONCE by one 4-D
+//     TMA box per plane; because a position's row index in the box is y * PW + x, the pixels a
+//     tap (r, s) needs are the same rows shifted by r * PW + s, i.e. the same shared memory
+//     through a descriptor whose start address is moved by that many 128-byte rows;
+//   * per k-step two MMAs, [W_hi; W_lo] x X_hi and [W_hi; W_lo] x X_lo, accumulate into one
+//     128 x 128 accumulator: lane c holds W_hi . (X_hi + X_lo), lane 64 + c holds W_lo . (X_hi +
+//     X_lo); the epilogue adds the two lanes (all four terms of the split product).
+// Shared-memory traffic per k-step drops to ~9 KB for 146 clocks of tensor work, so the tensor
+// pipe is the bound again: ~0.7 of the 3xTF32 ceiling for this shape instead of ~0.3.
+//
+// Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer (and TMEM owner), warps 2-9
+// epilogue: each drains a 32-lane x 64-column block of the accumulator into a shared-memory block
+// [lane][position] (128-bit stores), which frees the accumulator for the next tile's MMAs; then
+// warp e writes out channels e, e + 8, ...: hi lane + lo lane, bias, relu, optional 2x2 max-pool,
+// its lanes over consecutive positions, so a store instruction covers consecutive pixels of one
+// NCHW channel plane.  The epilogue of tile i runs while the MMAs of tile i + 1 are issued; it has
+// to stay shorter than those (~2.7 us), which is why a position's pixel offset is computed once per
+// kernel, not per value.  One CTA per SM walks the tiles.  Every wait is bounded.
+#include "common.cuh"
+#include "tc_ptx.cuh"
+#include "split.cuh"
+#include "tmap.cuh"
+
+namespace ct {
+namespace {
+
+using namespace ptx;
+
+constexpr int kTA_EpiWarps  = 8;
+constexpr int kTA_Threads   = 64 + 32 * kTA_EpiWarps;
+constexpr int kTA_MaxKSteps = 48;                 // 8 TMEM columns each: 384 of the 512 columns
+constexpr int kTA_DCol      = kTA_MaxKSteps * 8;  // the accumulator's first column
+constexpr int kTA_N         = 128;                // positions per tile (MMA N)
+constexpr int kTA_StageRowF = kTA_N + 4;          // epilogue staging: [128 lanes][132] floats: rows 16-byte aligned,
+                                                  // 128-bit stores of 8 consecutive lanes fall into distinct banks
+constexpr int kTA_StagingBytes = 128 * kTA_StageRowF * 4;
+
+struct ConvTmemParams {
+    const float *w;   // filters [ko][c][kh][kw], float32
+    const float *bias;
+    float *out;       // [batch][ko][ho][wo], or [batch][ko][ho/2][wo/2] with pool
+    uint32_t *flags;
+    int ko, c, kh, kw, pad;
+    int ho, wo, pw;   // pw = input width + 2 pad: positions per tile row
+    int th;           // output rows per tile
+    int tiles_y;      // ceil(ho / th)
+    int ksteps;       // kh * kw * 4
+    int box_bytes;    // bytes of one plane's TMA box
+    int plane_bytes;  // shared-memory bytes reserved per plane (box plus the rows shifted reads run into)
+    int stages;
+    int act, pool;
+};
+
+__device__ __forceinline__ void tmem_st_32x32_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_tf32_a_tmem(
+    uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
+        "}\n"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
+    const __grid_constant__ CUtensorMap map_x_hi, const __grid_constant__ CUtensorMap map_x_lo,
+    const ConvTmemParams p, const int total_tiles) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bar_full[4];
+    __shared__ uint64_t bar_empty[4];
+    __shared__ uint64_t bar_tmem_full;
+    __shared__ uint64_t bar_tmem_empty;
+    __shared__ uint64_t bar_done;
+    __shared__ uint64_t bar_epi; // the four epilogue warps meet here (bounded, unlike bar.sync)
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag_s;
+    volatile int *abort_flag = &abort_flag_s;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0)
+        abort_flag_s = *reinterpret_cast<volatile uint32_t *>(p.flags + FLAG_TIMEOUT) != 0 ? 1 : 0;
+    __syncthreads();
+    if (abort_flag_s)
+        return;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t stage_bytes = 2u * (uint32_t)p.plane_bytes;
+    float *staging = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)) + (uint32_t)p.stages * stage_bytes);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_tmem_full), 1);
+        mbar_init(smem_u32(&bar_tmem_empty), kTA_EpiWarps);
+        mbar_init(smem_u32(&bar_done), 1);
+        mbar_init(smem_u32(&bar_epi), kTA_EpiWarps);
+        mbar_fence_init();
+        prefetch_tensormap(&map_x_hi);
+        prefetch_tensormap(&map_x_lo);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    // ---- the filters go to tensor memory, once: warps 2..5 own the four lane quarters ----------
+    if (warp >= 2 && warp < 6) {
+        const int quarter = warp & 3;
+        const int m       = quarter * 32 + lane;      // TMEM lane = row of the A operand
+        const int ch      = m & 63;                   // filter
+        const bool lo_row = m >= 64;                  // rows 64..127: the low parts
+        const int taps    = p.kh * p.kw;
+        for (int ks = 0; ks < p.ksteps; ++ks) {
+            const int tap = ks >> 2, c0 = (ks & 3) * 8;
+            uint32_t v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float x = 0.0f;
+                if (ch < p.ko && c0 + j < p.c)
+                    x = p.w[((int64_t)ch * p.c + (c0 + j)) * taps + tap];
+                float hi, lo;
+                split_tf32(x, hi, lo);
+                v[j] = __float_as_uint(lo_row ? lo : hi);
+            }
+            tmem_st_32x32_x8(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ks * 8), v);
+        }
+        tmem_st_wait();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+
+    if (warp == 0) {
+        // ===== TMA producer: one halo box per plane and tile =====
+        if (lane == 0) {
+            int i = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++i) {
+                const int img = tile / p.tiles_y, ty = tile - img * p.tiles_y;
+                const int s       = i % p.stages;
+                const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
+                if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t full = smem_u32(&bar_full[s]);
+                const uint32_t dst  = smem_base + (uint32_t)s * stage_bytes;
+                mbar_expect_tx(full, 2u * (uint32_t)p.box_bytes);
+                const int32_t w0 = -p.pad, h0 = ty * p.th - p.pad;
+                tma_load_4d(dst, &map_x_hi, full, 0, w0, h0, img);
+                tma_load_4d(dst + (uint32_t)p.plane_bytes, &map_x_lo, full, 0, w0, h0, img);
+            }
+            if (*abort_flag) {
+                // unwind: let the copies still in flight land before the CTA goes away
+                const int first = i - p.stages < 0 ? 0 : i - p.stages;
+                for (int k2 = first; k2 < i; ++k2) {
+                    const uint32_t bar = smem_u32(&bar_full[k2 % p.stages]);
+                    const uint32_t ph  = (uint32_t)(k2 / p.stages) & 1u;
+                    const uint64_t t0  = globaltimer_ns();
+                    while (!mbar_try_wait(bar, ph) && globaltimer_ns() - t0 < kWaitBudgetNs) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        if (lane == 0) {
+            const uint32_t idesc  = make_idesc(2u, 128, (uint32_t)kTA_N);
+            const uint32_t d_tmem = tmem_base + (uint32_t)kTA_DCol;
+            int i = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++i) {
+                const int s       = i % p.stages;
+                const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
+                // the accumulator of the previous tile has been drained
+                if (!mbar_wait(smem_u32(&bar_tmem_empty), ((uint32_t)i & 1u) ^ 1u, abort_flag) ||
+                    !mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t x_hi = smem_base + (uint32_t)s * stage_bytes;
+                const uint32_t x_lo = x_hi + (uint32_t)p.plane_bytes;
+                int ks = 0;
+                for (int r = 0; r < p.kh; ++r) {
+                    for (int sx = 0; sx < p.kw; ++sx) {
+                        // the tap's pixels: the same box, (r * pw + sx) rows of 128 bytes further on
+                        const uint32_t shift = (uint32_t)(r * p.pw + sx) * 128u;
+                        const uint64_t db_hi = smem_desc_k<128>(x_hi + shift), db_lo = smem_desc_k<128>(x_lo + shift);
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk, ++ks) {
+                            const uint64_t adv    = (uint64_t)(kk * 32 >> 4);
+                            const uint32_t a_tmem = tmem_base + (uint32_t)(ks * 8);
+                            mma_tf32_a_tmem(d_tmem, a_tmem, db_lo + adv, idesc, ks == 0 ? 0u : 1u);
+                            mma_tf32_a_tmem(d_tmem, a_tmem, db_hi + adv, idesc, 1u);
+                        }
+                    }
+                }
+                tc_commit(smem_u32(&bar_empty[s]));   // the stage is free once these MMAs have retired
+                tc_commit(smem_u32(&bar_tmem_full));  // and the accumulator is complete
+            }
+            if (!ok || *abort_flag) {
+                tc_commit(smem_u32(&bar_done));
+                const uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(smem_u32(&bar_done), 0) && globaltimer_ns() - t0 < kWaitBudgetNs) {
+                }
+            }
+        }
+    } else {
+        // ===== epilogue =====
+        const int quarter = warp & 3;        // TMEM lanes this warp may read: 32 * quarter ..
+        const int ew      = warp - 2;        // 0..7: which channels this warp writes out
+        const int half    = ew >> 2;         // which 64 columns of the accumulator it drains
+        uint32_t epi_phase = 0;
+        auto epi_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(smem_u32(&bar_epi));
+            bool ok = mbar_wait(smem_u32(&bar_epi), epi_phase, abort_flag);
+            epi_phase ^= 1u;
+            return __all_sync(0xffffffffu, ok);
+        };
+        // Where this lane's positions land, once for the whole kernel: position pos = lane + 32 g
+        // of a tile is pixel (y, x) = (pos / pw, pos % pw) of the tile's rows; -1 for the halo columns
+        // and past the tile.  With the pool: lane q = pooled pixel (py, px) of the tile.
+        int off[4], yy[4];
+        const int npos = p.th * p.pw;
+        const int pw2 = p.wo >> 1, ph2 = p.ho >> 1;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const int pos = lane + 32 * g;
+            off[g] = -1, yy[g] = 0;
+            if (p.pool == 0) {
+                const int y = pos / p.pw, x = pos - y * p.pw;
+                if (pos < npos && x < p.wo)
+                    off[g] = y * p.wo + x, yy[g] = y;
+            } else {
+                const int py = pos / pw2, px = pos - py * pw2;
+                if (py < (p.th >> 1))
+                    off[g] = (2 * py) * p.pw + 2 * px, yy[g] = py; // here: the window's first position
+            }
+        }
+        int i = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++i) {
+            const int img = tile / p.tiles_y, ty = tile - img * p.tiles_y;
+            bool got = mbar_wait(smem_u32(&bar_tmem_full), (uint32_t)i & 1u, abort_flag);
+            if (!__all_sync(0xffffffffu, got))
+                break;
+            tc_fence_after_sync();
+            // lane m of the accumulator -> row m of the staging block
+            float4 *mine = reinterpret_cast<float4 *>(staging + (quarter * 32 + lane) * kTA_StageRowF + half * 64);
+            const uint32_t taddr =
+                tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(kTA_DCol + half * 64);
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + g * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    mine[g * 8 + j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(smem_u32(&bar_tmem_empty)); // the next tile's MMAs may start
+            if (!epi_sync())
+                break;
+            const int y0 = ty * p.th;
+            if (p.pool == 0) {
+                for (int ch = ew; ch < p.ko; ch += kTA_EpiWarps) {
+                    const float *hi = staging + ch * kTA_StageRowF, *lo = staging + (64 + ch) * kTA_StageRowF;
+                    const float b   = p.bias ? p.bias[ch] : 0.0f;
+                    float *plane    = p.out + (((int64_t)img * p.ko + ch) * p.ho + y0) * p.wo;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        if (off[g] >= 0 && y0 + yy[g] < p.ho) {
+                            float v = __fadd_rn(hi[lane + 32 * g], lo[lane + 32 * g]);
+                            if (p.bias)
+                                v = __fadd_rn(v, b);
+                            if (p.act == CT_ACT_RELU)
+                                v = __fmul_rn(v, v > 0.0f ? 1.0f : 0.0f);
+                            plane[off[g]] = v;
+                        }
+                    }
+                }
+            } else {
+                // 2x2 max-pool of the activated values; window order and strict '>' as in
+                // maxpool2d (the first element seeds, a NaN never wins)
+                for (int ch = ew; ch < p.ko; ch += kTA_EpiWarps) {
+                    const float *hi = staging + ch * kTA_StageRowF, *lo = staging + (64 + ch) * kTA_StageRowF;
+                    const float b   = p.bias ? p.bias[ch] : 0.0f;
+                    float *plane    = p.out + (((int64_t)img * p.ko + ch) * ph2 + (y0 >> 1)) * pw2;
+                    auto value = [&](int pos) {
+                        float v = __fadd_rn(hi[pos], lo[pos]);
+                        if (p.bias)
+                            v = __fadd_rn(v, b);
+                        if (p.act == CT_ACT_RELU)
+                            v = __fmul_rn(v, v > 0.0f ? 1.0f : 0.0f);
+                        return v;
+                    };
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        if (off[g] >= 0 && (y0 >> 1) + yy[g] < ph2) {
+                            const int pos = off[g];
+                            float best = value(pos);
+                            const float v1 = value(pos + 1), v2 = value(pos + p.pw), v3 = value(pos + p.pw + 1);
+                            if (v1 > best)
+                                best = v1;
+                            if (v2 > best)
+                                best = v2;
+                            if (v3 > best)
+                                best = v3;
+                            plane[lane + 32 * g] = best; // pooled pixels of a tile are consecutive: py * pw2 + px
+                        }
+                    }
+                }
+            }
+            if (!epi_sync()) // the staging block is rewritten by the next tile
+                break;
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && *abort_flag)
+        atomicExch(p.flags + FLAG_TIMEOUT, 1u + (uint32_t)blockIdx.x);
+}
+
+} // namespace
+
+// Whether the filters-in-tensor-memory kernel takes this layer.  The answer does not depend on
+// whether a max-pool is fused, so that conv2d and conv2d + pool of one layer run the same arithmetic;
+// *pool_ok says whether the fused 2x2 pool is possible (even output extents, two rows per tile).
+bool conv_tmem_applicable(int64_t c, int64_t h, int64_t w, int64_t ko, int64_t kh, int64_t kw, int64_t stride,
+                          int64_t pad, bool *pool_ok) {
+    if (pool_ok)
+        *pool_ok = false;
+    if (stride != 1 || c < 1 || c > 32 || ko < 1 || ko > 64 || kh * kw * 4 > kTA_MaxKSteps)
+        return false;
+    const int64_t pw = w + 2 * pad, wo = pw - kw + 1, ho = h + 2 * pad - kh + 1;
+    if (wo < 1 || ho < 1 || pw > kTA_N || pw > 256)
+        return false;
+    int64_t th = kTA_N / pw;
+    if (th > ho)
+        th = ho;
+    if (th < 1 || th + kh - 1 > 256)
+        return false;
+    // worth it only where the tile is reasonably full (else the pixels-on-rows kernel)
+    if (!(th * pw >= 96 || th == ho))
+        return false;
+    if (pool_ok)
+        *pool_ok = (wo & 1) == 0 && (ho & 1) == 0 && th >= 2;
+    return true;
+}
+
+// x_hi / x_lo: NHWC planes [batch][h][w][32] of the input (float32 hi / lo parts).
+ct_status conv_tmem_filters(
+    DeviceState *st, const void *x_hi, const void *x_lo, const float *w, const float *bias, int64_t batch, int64_t c,
+    int64_t h, int64_t wd, int64_t ko, int64_t kh, int64_t kw, int64_t pad, int act, int pool, float *out) {
+    ConvTmemParams p;
+    p.w = w, p.bias = bias, p.out = out, p.flags = st->flags_dev;
+    p.ko = (int)ko, p.c = (int)c, p.kh = (int)kh, p.kw = (int)kw, p.pad = (int)pad;
+    p.pw = (int)(wd + 2 * pad);
+    p.wo = p.pw - (int)kw + 1;
+    p.ho = (int)(h + 2 * pad - kh + 1);
+    p.th = kTA_N / p.pw < p.ho ? kTA_N / p.pw : p.ho;
+    if (pool)
+        p.th &= ~1;
+    p.tiles_y = (p.ho + p.th - 1) / p.th;
+    p.ksteps  = (int)(kh * kw * 4);
+    const int box_rows = p.th + (int)kh - 1;
+    p.box_bytes        = box_rows * p.pw * 128;
+    // a tap's shifted window of kTA_N rows may run past the box: reserve those rows too
+    int rows_needed = ((int)kh - 1) * p.pw + ((int)kw - 1) + kTA_N;
+    if (rows_needed < box_rows * p.pw)
+        rows_needed = box_rows * p.pw;
+    p.plane_bytes = (rows_needed * 128 + 1023) & ~1023;
+    p.act = act, p.pool = pool;
+    const int budget = 226 * 1024 - 1024 - kTA_StagingBytes;
+    p.stages         = budget / (2 * p.plane_bytes);
+    if (p.stages > 4)
+        p.stages = 4;
+    if (p.stages < 2 || p.th < 1)
+        return fail(CT_ERR_INVALID, "conv2d: internal tile shape %d x %d not usable", p.th, p.pw);
+    const int64_t tiles = (int64_t)p.tiles_y * batch;
+    if (tiles > 0x7fffffffll)
+        return fail(CT_ERR_TOO_LARGE, "conv2d: too many tiles");
+    CUtensorMap mx_hi, mx_lo;
+    // planes [batch][h][w][32 channels]; box = 32 channels x pw positions x (th + kh - 1) rows of one
+    // image, 128-byte swizzle; positions outside the image read as zero: the padding
+    const uint64_t dims[4]    = {32, (uint64_t)wd, (uint64_t)h, (uint64_t)batch};
+    const uint64_t strides[3] = {128, 128ull * (uint64_t)wd, 128ull * (uint64_t)wd * (uint64_t)h};
+    const uint32_t box[4]     = {32, (uint32_t)p.pw, (uint32_t)box_rows, 1};
+    CT_TRY(encode_tiled_map_f32(&mx_hi, x_hi, 4, dims, strides, box, /*swizzle_bytes=*/128));
+    CT_TRY(encode_tiled_map_f32(&mx_lo, x_lo, 4, dims, strides, box, 128));
+    const size_t smem = (size_t)p.stages * 2 * p.plane_bytes + kTA_StagingBytes + 1024;
+    static bool attr_set_dev[16] = {}; // the attribute belongs to a device's context
+    bool &attr_set = attr_set_dev[st->device & 15];
+    if (!attr_set) {
+        CT_CUDA(cudaFuncSetAttribute(conv_tmem_filters_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        attr_set = true;
+    }
+    const unsigned grid = (unsigned)(tiles < st->sm_count ? tiles : st->sm_count);
+    ProfScope prof("gemm_tc");
+    conv_tmem_filters_kernel<<<grid, kTA_Threads, smem, stream()>>>(mx_hi, mx_lo, p, (int)tiles);
+    CT_LAUNCH_CHECK("conv_tmem_filters");
+    return CT_OK;
+}
+
+} // namespace ct

@@ -34,6 +34,7 @@
 #include "common.cuh"
 #include "tc_ptx.cuh"
 #include "split.cuh"
+#include "tmap.cuh"
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -98,7 +99,25 @@ struct GemmParams {
     int conv_kw;      // filter width (taps are numbered r * kw + s)
     int conv_pad;
     int conv_th;      // output rows per tile
+    // Row bands (bands > 0): the row tiles are dealt out band by band - band b holds the row tiles
+    // [band_first[b], band_first[b + 1]) - and every CTA adds one to band_done[b] after its tile's
+    // stores: a stream that waits for band_done[b] to reach the band's tile count (ct_stream_wait_value)
+    // may then read the band, while later bands are still being computed by the same launch.
+    int bands;
+    int band_first[9];
+    int64_t band_out_off[8]; // elements added to `out` for the tiles of band b (bands need not be adjacent in C)
+    uint32_t *band_done;
 };
+
+// The band plan of the product being enqueued (set under the entry point's lock by
+// ct_matmul_packed_bands, read by launch_gemm); bands == 0: none.
+struct BandPlan {
+    int bands = 0;
+    int first[9];
+    int64_t out_off[8];
+    uint32_t *done = nullptr;
+};
+BandPlan g_band_plan;
 
 // ---- operand pre-pass ---------------------------------------------------------------------
 
@@ -257,13 +276,22 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
         abort_flag_s = *reinterpret_cast<volatile uint32_t *>(p.flags + FLAG_TIMEOUT) != 0 ? 1 : 0;
     }
     __syncthreads();
-    if (abort_flag_s)
-        return;
 
     // tile coordinates: groups of 16 row-tiles sweep the column tiles, so that the CTAs
     // running at the same time share operand tiles in L2
-    int tm, tn, tz;
-    {
+    int tm, tn, tz, band = 0;
+    if (p.bands > 0) {
+        // band by band; inside a band its row tiles sweep the column tiles together
+        tz      = 0;
+        int bid = blockIdx.x;
+        while (band + 1 < p.bands && bid >= (p.band_first[band + 1] - p.band_first[band]) * p.tiles_n) {
+            bid -= (p.band_first[band + 1] - p.band_first[band]) * p.tiles_n;
+            ++band;
+        }
+        const int gm = p.band_first[band + 1] - p.band_first[band];
+        tm           = p.band_first[band] + bid % gm;
+        tn           = bid / gm;
+    } else {
         int per_batch  = p.tiles_m * p.tiles_n;
         tz             = blockIdx.x / per_batch;
         int bid        = blockIdx.x - tz * per_batch;
@@ -274,6 +302,12 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
         int in_group   = bid - g * group_size;
         tm             = first_m + in_group % gm;
         tn             = in_group / gm;
+    }
+    if (abort_flag_s) {
+        // a waiting stream is released also when the launch has failed; the failure is on record
+        if (threadIdx.x == 0 && p.bands > 0)
+            atomicAdd(p.band_done + band, 1u);
+        return;
     }
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -470,7 +504,7 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
             int64_t row  = (int64_t)tm * BM + quarter * 32 + lane;
             int64_t col0 = (int64_t)tn * p.tile_n + half * 128;
             int64_t lim  = (int64_t)(tn + 1) * p.tile_n < p.n ? (int64_t)(tn + 1) * p.tile_n : p.n;
-            float *out_z = p.out + (int64_t)tz * p.out_batch_stride;
+            float *out_z = p.out + (int64_t)tz * p.out_batch_stride + (p.bands > 0 ? p.band_out_off[band] : 0);
             if ((p.ldc & 3) == 0 && (col0 & 3) == 0 && (reinterpret_cast<uintptr_t>(out_z) & 15u) == 0) {
                 // A thread holds 128 consecutive columns of one row, so storing straight from the
                 // registers writes 32 scattered 16-byte pieces per instruction, and the tile's store
@@ -521,7 +555,7 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
                     }
                 }
             } else if (row < p.m) {
-                float *dst      = p.out + (int64_t)tz * p.out_batch_stride + row * p.ldc;
+                float *dst      = out_z + row * p.ldc;
                 const float rb  = (p.bias && p.bias_per_row) ? p.bias[row] : 0.0f;
                 const bool vec4 = (p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
 #pragma unroll
@@ -567,6 +601,13 @@ __global__ void __launch_bounds__(Cfg<BN, MODE, RB>::kThreads, 1) gemm_tc_kernel
     }
     if (threadIdx.x == 0 && *abort_flag)
         atomicExch(p.flags + FLAG_TIMEOUT, 1u + (uint32_t)blockIdx.x);
+    if (threadIdx.x == 0 && p.bands > 0) {
+        // every store of this tile was issued before the __syncthreads above: make them visible to
+        // the device before the band's count moves (also on the failure path, so that a waiting
+        // stream is always released; the failure itself is on record in the error word)
+        __threadfence();
+        atomicAdd(p.band_done + band, 1u);
+    }
 }
 
 // ---- the same pipeline, many short tiles per CTA ------------------------------------------
@@ -1239,6 +1280,33 @@ ct_status encode_fn(EncodeTiledFn *out) {
     return CT_OK;
 }
 
+} // namespace
+
+ct_status encode_tiled_map_f32(
+    CUtensorMap *map, const void *base, int rank, const uint64_t *dims, const uint64_t *strides, const uint32_t *box,
+    int swizzle_bytes) {
+    EncodeTiledFn fn;
+    CT_TRY(encode_fn(&fn));
+    cuuint64_t d[5], s[4];
+    cuuint32_t b[5], e[5];
+    for (int i = 0; i < rank; ++i) {
+        d[i] = dims[i];
+        b[i] = box[i];
+        e[i] = 1;
+        if (i + 1 < rank)
+            s[i] = strides[i];
+    }
+    CUresult r = fn(
+        map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), d, s, b, e,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return CT_OK;
+}
+
+namespace {
+
 // Tensor map over a plane [rows][kp] (kp contiguous); box = one k-block x box_rows rows,
 // 128-byte swizzle, out-of-range rows read as zero.
 ct_status make_plane_map(
@@ -1332,6 +1400,16 @@ ct_status launch_gemm(
     p.kb_per_split = splits > 1 ? (p.num_k_blocks + splits - 1) / splits : 0;
     p.conv         = 0;
     p.conv_cblocks = p.conv_kw = p.conv_pad = p.conv_th = 0;
+    p.bands        = 0;
+    p.band_done    = nullptr;
+    if (g_band_plan.bands > 0 && !cg && splits == 1 && batch == 1) {
+        p.bands     = g_band_plan.bands;
+        p.band_done = g_band_plan.done;
+        for (int b = 0; b <= p.bands; ++b)
+            p.band_first[b] = g_band_plan.first[b];
+        for (int b = 0; b < p.bands; ++b)
+            p.band_out_off[b] = g_band_plan.out_off[b];
+    }
     if (cg) {
         p.tile_n       = cg->th * cg->wo;
         p.tiles_n      = (cg->ho + cg->th - 1) / cg->th;
@@ -1349,7 +1427,7 @@ ct_status launch_gemm(
     if constexpr (RB == 64) {
         // more tiles than SMs, each with a k range short enough for one accumulation (k <= 1024,
         // the error stays at the level of the chunked form): one CTA per SM walks the tiles
-        if (splits == 1 && p.num_k_blocks <= 64 && tiles > st->sm_count) {
+        if (splits == 1 && p.num_k_blocks <= 64 && tiles > st->sm_count && p.bands == 0) {
             using S = StreamCfg<BN, MODE>;
             static bool stream_attr_set_dev[16] = {}; // the attribute belongs to a device's context
             bool &stream_attr_set       = stream_attr_set_dev[st->device & 15];
@@ -1797,6 +1875,89 @@ extern "C" ct_status ct_matmul_packed_rows(
     return res;
 }
 
+// A product in row bands with ONE launch.  Computing the bands of a sharded product as separate
+// launches costs every band its own partly filled last wave of tiles (16384 columns are 64 tiles of
+// 256: a band of 1024 rows is 512 tiles = 3.46 waves on 148 SMs); one launch over all bands has one
+// last wave.  The tiles are dealt out band by band, every CTA counts itself into band_done[b] when its
+// tile is stored, and a stream that has to move band b elsewhere waits for the count
+// (ct_stream_wait_value) instead of for the whole launch.
+extern "C" ct_status ct_matmul_packed_bands(
+    const void *a_packed, const void *w_packed, int nbands, const int64_t *band_rows_host,
+    float *const *band_out_host, uint32_t *band_done_dev, uint32_t *band_tiles_host) {
+    OpLock op_lock;
+    DeviceState *st;
+    CT_TRY(current(&st));
+    const PackedRows *pr    = static_cast<const PackedRows *>(a_packed);
+    const PackedWeights *pw = static_cast<const PackedWeights *>(w_packed);
+    if (!pr || pr->magic != kPackedRowsMagic || !pw || pw->magic != kPackedMagic)
+        return fail(CT_ERR_INVALID, "ct_matmul_packed_bands: not a packed operand");
+    int dev = -1;
+    CT_CUDA(cudaGetDevice(&dev));
+    if (pr->mode != pw->mode || pr->k != pw->k || pr->kp != pw->kp || pr->device != dev || pw->device != dev)
+        return fail(CT_ERR_INVALID, "ct_matmul_packed_bands: operands of different inner size, precision or device");
+    if (nbands < 1 || nbands > 8 || !band_rows_host || !band_out_host || !band_done_dev)
+        return fail(CT_ERR_INVALID, "ct_matmul_packed_bands: 1 to 8 bands, with rows, outputs and counters");
+    BandPlan plan;
+    plan.bands   = nbands;
+    plan.done    = band_done_dev;
+    int64_t row  = 0;
+    plan.first[0] = 0;
+    const bool wide = pw->n > 128; // the tile width launch_gemm will pick is decided in gemm_planes; counts below use it
+    for (int b = 0; b < nbands; ++b) {
+        const int64_t rows = band_rows_host[b];
+        if (rows <= 0 || !band_out_host[b] || (b + 1 < nbands && rows % BM != 0))
+            return fail(CT_ERR_INVALID, "ct_matmul_packed_bands: bands are non-empty and all but the last a multiple of %d rows", BM);
+        // tiles of band b write to band_out_host[b] + (row - first row of the band) * n
+        plan.out_off[b] = (band_out_host[b] - band_out_host[0]) - row * pw->n;
+        row += rows;
+        plan.first[b + 1] = (int)((row + BM - 1) / BM);
+    }
+    if (row != pr->m)
+        return fail(CT_ERR_INVALID, "ct_matmul_packed_bands: the bands hold %lld rows, the packed matrix %lld",
+                    (long long)row, (long long)pr->m);
+    // the tile width gemm_planes will choose (same rule)
+    const int64_t tiles256 = ((pr->m + BM - 1) / BM) * ((pw->n + 255) / 256);
+    const bool bn256       = wide && tiles256 >= st->sm_count / 2;
+    const int64_t tiles_n  = (pw->n + (bn256 ? 255 : 127)) / (bn256 ? 256 : 128);
+    for (int b = 0; b < nbands; ++b)
+        if (band_tiles_host)
+            band_tiles_host[b] = (uint32_t)((plan.first[b + 1] - plan.first[b]) * tiles_n);
+    g_no_splitk   = true; // the split-K partial sums live in a shared workspace
+    g_band_plan   = plan;
+    ct_status res = gemm_planes(st, pr->mode, pr->hi, pr->lo, pw->hi, pw->lo, pr->m, pw->n, pr->kp, nullptr, CT_ACT_NONE,
+                                band_out_host[0], 1, 0, 0);
+    g_band_plan.bands = 0;
+    g_no_splitk       = false;
+    return res;
+}
+
+// The current stream waits (the host does not) until the 32-bit word at addr_dev is >= value.
+extern "C" ct_status ct_stream_wait_value(const uint32_t *addr_dev, uint32_t value) {
+    DeviceState *st;
+    CT_TRY(current(&st));
+    typedef CUresult (*WaitFn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+    static WaitFn fn = nullptr;
+    static std::mutex mu;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!fn) {
+            void *sym = nullptr;
+            cudaDriverEntryPointQueryResult qres;
+            CT_CUDA(cudaGetDriverEntryPoint("cuStreamWaitValue32", &sym, cudaEnableDefault, &qres));
+            if (qres != cudaDriverEntryPointSuccess || !sym)
+                return fail(CT_ERR_CUDA, "cuStreamWaitValue32 is not available from this driver");
+            fn = reinterpret_cast<WaitFn>(sym);
+        }
+    }
+    if (!addr_dev)
+        return fail(CT_ERR_INVALID, "ct_stream_wait_value: null address");
+    CUresult r = fn(reinterpret_cast<CUstream>(stream()), reinterpret_cast<CUdeviceptr>(addr_dev), value,
+                    CU_STREAM_WAIT_VALUE_GEQ);
+    if (r != CUDA_SUCCESS)
+        return fail(CT_ERR_CUDA, "cuStreamWaitValue32 failed with code %d", (int)r);
+    return CT_OK;
+}
+
 // ---- matmul without any allocation --------------------------------------------------------
 //
 // Some hosts of this library may not allocate device memory when they call it: a plugin that is
@@ -1879,6 +2040,8 @@ ct_status launch_static(
     p.kb_per_split     = 0;
     p.conv             = 0;
     p.conv_cblocks = p.conv_kw = p.conv_pad = p.conv_th = 0;
+    p.bands        = 0;
+    p.band_done    = nullptr;
     CT_CUDA(cudaFuncSetAttribute(
         gemm_tc_kernel<BN, MODE_3X>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     gemm_tc_kernel<BN, MODE_3X><<<(unsigned)(p.tiles_m * p.tiles_n), C::kThreads, C::kSmemBytes, stream()>>>(

@@ -305,6 +305,309 @@ ct_status reduce_axis_typed(const T *in, int64_t rows, int64_t cols, int axis, O
     return CT_OK;
 }
 
+
+// ---- float32 fast paths of the axis reductions ------------------------------------------------
+//
+// The generic kernels above fold one element at a time through float64 and a (value, index) pair
+// with a seed test: right for every dtype, but far from HBM speed.  For float32 the reference's
+// scan (runtime.cpp:940-946, 983-991: element 0 seeds, a later element replaces on strict '>')
+// has a closed form that needs no seed state inside the loop:
+//     if x[0] is NaN          -> (NaN, 0): nothing is ever greater than a NaN seed
+//     else                    -> (largest non-NaN value, the first index that holds it); a NaN
+//                                elsewhere never wins because 'NaN > best' is false
+// so a thread keeps (best = -inf, idx = none), takes x when x > best (comparisons of floats are
+// the comparisons of their float64 values), partial results merge by "greater value, then smaller
+// index", and an empty result (every element -inf or NaN) falls back to element 0.  Sums still
+// accumulate in float64.
+
+struct BestF {
+    float v;
+    int64_t idx; // INT64_MAX: nothing taken yet
+};
+constexpr int64_t kNoIndex = 0x7fffffffffffffffll;
+
+__device__ __forceinline__ void best_take(BestF &b, float x, int64_t i) {
+    if (x > b.v) {
+        b.v   = x;
+        b.idx = i;
+    }
+}
+__device__ __forceinline__ void best_merge(BestF &a, float v, int64_t idx) {
+    if (v > a.v || (v == a.v && idx < a.idx)) {
+        a.v   = v;
+        a.idx = idx;
+    }
+}
+__device__ __forceinline__ BestF warp_best(BestF a) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float v     = __shfl_xor_sync(0xffffffffu, a.v, o);
+        int64_t idx = __shfl_xor_sync(0xffffffffu, a.idx, o);
+        best_merge(a, v, idx);
+    }
+    return a;
+}
+// The reference's result from the merged state and the line's first element.
+template <int KIND, typename OT> __device__ __forceinline__ void best_store(OT *out, int64_t at, BestF b, float first) {
+    if (first != first || b.idx == kNoIndex) { // NaN seed, or nothing ever exceeded -inf
+        b.v   = first;
+        b.idx = 0;
+    }
+    if (KIND == RED_MAX)
+        out[at] = (OT)b.v;
+    else
+        out[at] = (OT)b.idx;
+}
+
+// axis = 1, rows of at most 32 columns (a classifier's logits: 10): a block stages 256 * RPT whole
+// rows in shared memory with coalesced 128-bit loads (all of them in flight before the first is
+// used), then every thread scans RPT rows in order.
+template <int KIND, typename OT, int RPT>
+__global__ void __launch_bounds__(256) reduce_rows_narrow_f32_kernel(
+    const float *__restrict__ in, int64_t rows, int cols, OT *__restrict__ out) {
+    extern __shared__ float stage[];
+    constexpr int kRows = 256 * RPT;
+    const int64_t row0  = (int64_t)blockIdx.x * kRows;
+    const int64_t left  = rows - row0;
+    const int nrows     = left < kRows ? (int)left : kRows;
+    const int count     = nrows * cols;
+    const float *src    = in + row0 * cols;
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+        const int nvec = count >> 2;
+        for (int i = threadIdx.x; i < nvec; i += 256)
+            reinterpret_cast<float4 *>(stage)[i] = __ldcs(reinterpret_cast<const float4 *>(src) + i);
+        for (int i = (nvec << 2) + threadIdx.x; i < count; i += 256)
+            stage[i] = src[i];
+    } else {
+        for (int i = threadIdx.x; i < count; i += 256)
+            stage[i] = src[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < RPT; ++k) {
+        const int row = threadIdx.x + 256 * k; // consecutive threads, consecutive rows: coalesced results
+        if (row >= nrows)
+            break;
+        const float *r = stage + row * cols;
+        if (KIND == RED_SUM) {
+            double acc = 0.0;
+            for (int j = 0; j < cols; ++j)
+                acc += (double)r[j];
+            out[row0 + row] = (OT)(float)acc;
+        } else {
+            BestF b{-INFINITY, kNoIndex};
+            for (int j = 0; j < cols; ++j)
+                best_take(b, r[j], j);
+            best_store<KIND, OT>(out, row0 + row, b, r[0]);
+        }
+    }
+}
+
+// axis = 1, wider rows: GROUP threads per row (a warp, or the whole block), 128-bit loads.
+template <int KIND, typename OT, int GROUP>
+__global__ void __launch_bounds__(256) reduce_rows_f32_kernel(
+    const float *__restrict__ in, int64_t rows, int64_t cols, OT *__restrict__ out) {
+    constexpr int kGroupsPerBlock = 256 / GROUP;
+    __shared__ double s_sum[8];
+    __shared__ float s_v[8];
+    __shared__ long long s_i[8];
+    const int64_t row = (int64_t)blockIdx.x * kGroupsPerBlock + (GROUP == 256 ? 0 : (int)(threadIdx.x / GROUP));
+    if (row >= rows)
+        return; // GROUP == 256: never taken (one row per block); a warp leaves as a whole
+    const int t    = threadIdx.x % GROUP;
+    const float *r = in + row * cols;
+    double acc     = 0.0;
+    BestF b{-INFINITY, kNoIndex};
+    const bool vec = (cols & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0;
+    if (vec) {
+        const float4 *r4   = reinterpret_cast<const float4 *>(r);
+        const int64_t nvec = cols >> 2;
+#pragma unroll 4
+        for (int64_t j = t; j < nvec; j += GROUP) {
+            const float4 q = __ldcs(r4 + j);
+            if (KIND == RED_SUM) {
+                acc += ((double)q.x + (double)q.y) + ((double)q.z + (double)q.w);
+            } else {
+                best_take(b, q.x, 4 * j);
+                best_take(b, q.y, 4 * j + 1);
+                best_take(b, q.z, 4 * j + 2);
+                best_take(b, q.w, 4 * j + 3);
+            }
+        }
+    } else {
+        for (int64_t j = t; j < cols; j += GROUP) {
+            const float x = r[j];
+            if (KIND == RED_SUM)
+                acc += (double)x;
+            else
+                best_take(b, x, j);
+        }
+    }
+    if (KIND == RED_SUM) {
+        acc = warp_sum(acc);
+        if (GROUP == 256) {
+            if ((threadIdx.x & 31) == 0)
+                s_sum[threadIdx.x >> 5] = acc;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                double total = 0.0;
+                for (int w = 0; w < 8; ++w)
+                    total += s_sum[w];
+                out[row] = (OT)(float)total;
+            }
+        } else if (t == 0) {
+            out[row] = (OT)(float)acc;
+        }
+    } else {
+        b = warp_best(b);
+        if (GROUP == 256) {
+            if ((threadIdx.x & 31) == 0) {
+                s_v[threadIdx.x >> 5] = b.v;
+                s_i[threadIdx.x >> 5] = b.idx;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                for (int w = 1; w < 8; ++w)
+                    best_merge(b, s_v[w], s_i[w]);
+                best_store<KIND, OT>(out, row, b, r[0]);
+            }
+        } else if (t == 0) {
+            best_store<KIND, OT>(out, row, b, r[0]);
+        }
+    }
+}
+
+// axis = 0: a block owns 128 columns (a thread 4 of them: one 128-bit load per row) and a slice
+// of the rows; its 8 row-lanes stride over the slice with four loads in flight.  Slices leave
+// partial results in a workspace [slices][cols]; a second kernel folds them in slice order, so the
+// result does not depend on how the rows were cut.
+struct ColPartial {
+    double sum;
+    float v;
+    int64_t idx;
+};
+
+template <int KIND>
+__global__ void __launch_bounds__(256) reduce_cols_f32_kernel(
+    const float *__restrict__ in, int64_t rows, int64_t cols, int64_t rows_per_slice, double *__restrict__ psum,
+    float *__restrict__ pv, int64_t *__restrict__ pidx) {
+    __shared__ double s_sum[8][129];
+    __shared__ float s_v[8][129];
+    __shared__ long long s_i[8][129];
+    const int tx       = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t col  = ((int64_t)blockIdx.x * 32 + tx) * 4;
+    const int64_t r0   = (int64_t)blockIdx.y * rows_per_slice;
+    const int64_t r1   = r0 + rows_per_slice < rows ? r0 + rows_per_slice : rows;
+    double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+    BestF b0{-INFINITY, kNoIndex}, b1 = b0, b2 = b0, b3 = b0;
+    if (col < cols) { // cols is a multiple of 4 on this path
+#pragma unroll 4
+        for (int64_t i = r0 + ty; i < r1; i += 8) {
+            const float4 q = __ldcs(reinterpret_cast<const float4 *>(in + i * cols + col));
+            if (KIND == RED_SUM) {
+                a0 += (double)q.x, a1 += (double)q.y, a2 += (double)q.z, a3 += (double)q.w;
+            } else {
+                best_take(b0, q.x, i), best_take(b1, q.y, i), best_take(b2, q.z, i), best_take(b3, q.w, i);
+            }
+        }
+    }
+    if (KIND == RED_SUM) {
+        s_sum[ty][tx * 4] = a0, s_sum[ty][tx * 4 + 1] = a1, s_sum[ty][tx * 4 + 2] = a2, s_sum[ty][tx * 4 + 3] = a3;
+    } else {
+        s_v[ty][tx * 4] = b0.v, s_v[ty][tx * 4 + 1] = b1.v, s_v[ty][tx * 4 + 2] = b2.v, s_v[ty][tx * 4 + 3] = b3.v;
+        s_i[ty][tx * 4] = b0.idx, s_i[ty][tx * 4 + 1] = b1.idx, s_i[ty][tx * 4 + 2] = b2.idx, s_i[ty][tx * 4 + 3] = b3.idx;
+    }
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        const int64_t c = (int64_t)blockIdx.x * 128 + threadIdx.x;
+        if (c < cols) {
+            const int64_t at = (int64_t)blockIdx.y * cols + c;
+            if (KIND == RED_SUM) {
+                double total = 0.0;
+                for (int w = 0; w < 8; ++w)
+                    total += s_sum[w][threadIdx.x];
+                psum[at] = total;
+            } else {
+                BestF b{s_v[0][threadIdx.x], s_i[0][threadIdx.x]};
+                for (int w = 1; w < 8; ++w)
+                    best_merge(b, s_v[w][threadIdx.x], s_i[w][threadIdx.x]);
+                pv[at]   = b.v;
+                pidx[at] = b.idx;
+            }
+        }
+    }
+}
+
+template <int KIND, typename OT>
+__global__ void __launch_bounds__(256) reduce_cols_finish_f32_kernel(
+    const float *__restrict__ in, int64_t cols, int slices, const double *__restrict__ psum,
+    const float *__restrict__ pv, const int64_t *__restrict__ pidx, OT *__restrict__ out) {
+    const int64_t c = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (c >= cols)
+        return;
+    if (KIND == RED_SUM) {
+        double total = 0.0;
+        for (int s = 0; s < slices; ++s)
+            total += psum[(int64_t)s * cols + c];
+        out[c] = (OT)(float)total;
+    } else {
+        BestF b{-INFINITY, kNoIndex};
+        for (int s = 0; s < slices; ++s)
+            best_merge(b, pv[(int64_t)s * cols + c], pidx[(int64_t)s * cols + c]);
+        best_store<KIND, OT>(out, c, b, in[c]);
+    }
+}
+
+template <int KIND, typename OT>
+ct_status reduce_axis_f32(DeviceState *st, const float *in, int64_t rows, int64_t cols, int axis, OT *out) {
+    ProfScope prof("reduce");
+    if (axis == 1) {
+        if (rows == 0)
+            return CT_OK;
+        if (cols <= 32 && rows >= 1024 * (int64_t)st->sm_count && cols <= 11) {
+            // many short rows: four rows per thread (up to 44 KB of a block's rows in flight)
+            const unsigned blocks = (unsigned)((rows + 1023) / 1024);
+            reduce_rows_narrow_f32_kernel<KIND, OT, 4>
+                <<<blocks, 256, (size_t)1024 * cols * sizeof(float), stream()>>>(in, rows, (int)cols, out);
+        } else if (cols <= 32) {
+            const unsigned blocks = (unsigned)((rows + 255) / 256);
+            reduce_rows_narrow_f32_kernel<KIND, OT, 1>
+                <<<blocks, 256, (size_t)256 * cols * sizeof(float), stream()>>>(in, rows, (int)cols, out);
+        } else if (cols <= 1024) {
+            reduce_rows_f32_kernel<KIND, OT, 32><<<(unsigned)((rows + 7) / 8), 256, 0, stream()>>>(in, rows, cols, out);
+        } else {
+            reduce_rows_f32_kernel<KIND, OT, 256><<<(unsigned)rows, 256, 0, stream()>>>(in, rows, cols, out);
+        }
+        CT_LAUNCH_CHECK("reduce(axis=1)");
+        return CT_OK;
+    }
+    if (cols == 0)
+        return CT_OK;
+    // axis = 0: enough row slices that the grid covers the machine a few times over
+    const int64_t col_blocks = (cols + 127) / 128;
+    int64_t slices           = ((int64_t)st->sm_count * 4 + col_blocks - 1) / col_blocks;
+    if (slices > rows / 64)
+        slices = rows / 64;
+    if (slices < 1)
+        slices = 1;
+    if (slices > 1024)
+        slices = 1024;
+    const int64_t rows_per_slice = (rows + slices - 1) / slices;
+    slices                       = rows_per_slice > 0 ? (rows + rows_per_slice - 1) / rows_per_slice : 1;
+    const size_t per = (size_t)slices * cols;
+    CT_TRY(ensure_ws(&st->reduce_ws, &st->reduce_ws_bytes, per * (sizeof(double) + sizeof(float) + sizeof(int64_t)) + 64));
+    double *psum  = static_cast<double *>(st->reduce_ws);
+    int64_t *pidx = reinterpret_cast<int64_t *>(psum + per);
+    float *pv     = reinterpret_cast<float *>(pidx + per);
+    dim3 grid((unsigned)col_blocks, (unsigned)slices);
+    reduce_cols_f32_kernel<KIND><<<grid, 256, 0, stream()>>>(in, rows, cols, rows_per_slice, psum, pv, pidx);
+    CT_LAUNCH_CHECK("reduce(axis=0)");
+    reduce_cols_finish_f32_kernel<KIND, OT>
+        <<<(unsigned)((cols + 255) / 256), 256, 0, stream()>>>(in, cols, (int)slices, psum, pv, pidx, out);
+    CT_LAUNCH_CHECK("reduce(axis=0, finish)");
+    return CT_OK;
+}
+
 template <int KIND, typename OT>
 ct_status reduce_axis(int dt, const void *in, int64_t rows, int64_t cols, int64_t axis, OT *out, const char *name) {
     OpLock op_lock;
@@ -324,6 +627,9 @@ ct_status reduce_axis(int dt, const void *in, int64_t rows, int64_t cols, int64_
         return fail(CT_ERR_INVALID, "%s(axis): empty reduction", name);
     if (rows > 0x7fffffffll * 8 || cols > 0x7fffffffll * 32)
         return fail(CT_ERR_TOO_LARGE, "%s: dimension too large", name);
+    if (dt == CT_F32 && rows > 0 && cols > 0 && cols <= 0x7fffffffll &&
+        (axis == 1 || ((cols & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0 && rows >= 64)))
+        return reduce_axis_f32<KIND, OT>(st, static_cast<const float *>(in), rows, cols, (int)axis, out);
     switch (dt) {
     case CT_F32:
         return reduce_axis_typed<KIND, float, OT>(static_cast<const float *>(in), rows, cols, (int)axis, out);
@@ -604,6 +910,36 @@ __global__ void __launch_bounds__(256) transpose_kernel(const T *in, int64_t row
     }
 }
 
+// float32 with both extents multiples of four: 64 x 64 tiles, 128-bit loads along the input rows
+// and 128-bit stores along the output rows (four times the bytes in flight per thread of the
+// element-wise kernel above).
+__global__ void __launch_bounds__(256) transpose_f32x4_kernel(
+    const float *__restrict__ in, int64_t rows, int64_t cols, float *__restrict__ out) {
+    __shared__ float tile[64][65];
+    const int q      = threadIdx.x & 15;  // which group of four along the contiguous direction
+    const int lane_r = threadIdx.x >> 4;  // 0..15
+    const int64_t c0 = (int64_t)blockIdx.x * 64, r0 = (int64_t)blockIdx.y * 64;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int r      = lane_r + 16 * k;
+        const int64_t gr = r0 + r, gc = c0 + q * 4;
+        if (gr < rows && gc < cols) {
+            const float4 v = __ldcs(reinterpret_cast<const float4 *>(in + gr * cols + gc));
+            tile[r][q * 4] = v.x, tile[r][q * 4 + 1] = v.y, tile[r][q * 4 + 2] = v.z, tile[r][q * 4 + 3] = v.w;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int c      = lane_r + 16 * k; // input column = output row
+        const int64_t gc = c0 + c, gr = r0 + q * 4;
+        if (gc < cols && gr < rows) {
+            const float4 v = make_float4(tile[q * 4][c], tile[q * 4 + 1][c], tile[q * 4 + 2][c], tile[q * 4 + 3][c]);
+            __stcs(reinterpret_cast<float4 *>(out + gc * rows + gr), v);
+        }
+    }
+}
+
 // out viewed as [outer][lhs_len + rhs_len] bytes-items of `unit` bytes each.
 template <typename U>
 __global__ void __launch_bounds__(256) concat_kernel(
@@ -722,6 +1058,14 @@ ct_status ct_transpose(ct_dtype dt, const void *in, int64_t rows, int64_t cols, 
     if ((rows + 31) / 32 > 65535)
         return fail(CT_ERR_TOO_LARGE, "transpose: too many rows");
     ProfScope prof("transpose");
+    if (dt == CT_F32 && (rows & 3) == 0 && (cols & 3) == 0 && (rows + 63) / 64 <= 65535 &&
+        ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0) {
+        dim3 grid64((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
+        transpose_f32x4_kernel<<<grid64, 256, 0, stream()>>>(
+            static_cast<const float *>(in), rows, cols, static_cast<float *>(out));
+        CT_LAUNCH_CHECK("transpose");
+        return CT_OK;
+    }
     switch (dt) {
     case CT_F32:
         transpose_kernel<float><<<grid, 256, 0, stream()>>>(

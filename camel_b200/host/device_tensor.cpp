@@ -70,8 +70,12 @@ void dropUser(Expr *e) {
     if (!e || e->users.fetch_sub(1, std::memory_order_acq_rel) != 1)
         return;
     e->dead.store(true, std::memory_order_release);
-    if (void *buf = e->out.exchange(nullptr, std::memory_order_acq_rel))
+    if (e->aliasOf) {
+        e->out.store(nullptr, std::memory_order_release); // the buffer belongs to the record it is a view of
+        dropUser(e->aliasOf);
+    } else if (void *buf = e->out.exchange(nullptr, std::memory_order_acq_rel)) {
         freeDevice(buf);
+    }
     std::free(e->host.exchange(nullptr, std::memory_order_acq_rel));
     if (e->pending.exchange(false, std::memory_order_acq_rel)) { // it will never run: its operands are free of it
         dropUser(e->a);
@@ -303,7 +307,23 @@ bool lazyEvaluation() {
 
 void setLazyEvaluation(bool on) { g_lazy.store(on ? 1 : 0, std::memory_order_relaxed); }
 
+void makeAlias(TensorObject *out, const TensorObject *src) {
+    Expr *root = src->expr();
+    while (root->aliasOf)
+        root = root->aliasOf;
+    root->users.fetch_add(1, std::memory_order_acq_rel);
+    out->expr()->aliasOf = root;
+}
+
 void *bufferOf(Expr *e) {
+    if (e->aliasOf) {
+        if (e->dead.load(std::memory_order_acquire))
+            throw std::runtime_error("Tensor used after the scope that created it has ended");
+        evaluate(e->aliasOf);
+        void *p = bufferOf(e->aliasOf);
+        e->out.store(p, std::memory_order_release); // later reads take the fast path
+        return p;
+    }
     static std::mutex once;
     std::lock_guard<std::mutex> lock(once);
     void *p = e->out.load(std::memory_order_relaxed);

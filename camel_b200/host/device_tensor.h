@@ -91,6 +91,7 @@ struct Expr {
     std::atomic<bool> pending{false};
     std::atomic<bool> dead{false};
     std::atomic<int> users{1};
+    Expr *aliasOf = nullptr; // this tensor is another shape over that record's buffer (reshape, flatten)
     Expr *a = nullptr, *b = nullptr;
     std::atomic<void *> out{nullptr}; // the tensor's device buffer, allocated at first use (bufferOf)
     std::atomic<std::byte *> host{nullptr}; // malloc'd host mirror, nullptr while there is none
@@ -122,6 +123,10 @@ bool lazyEvaluation();
 void setLazyEvaluation(bool on);
 // Replaces operand `which` (0: a, 1: b) of a pending record, moving its claim on the buffer.
 void rebindOperand(Expr *e, int which, Expr *to);
+// Makes `out` (freshly created, same dtype and element count) a second shape over `src`'s device
+// buffer instead of a copy: tensors are immutable values, so no reader can tell the difference.
+// `out` keeps `src`'s buffer alive for as long as it lives itself.
+void makeAlias(TensorObject *out, const TensorObject *src);
 
 // ---- scopes ------------------------------------------------------------------------------
 // beginScope() returns a token; endScope(token, keep) ends the life of every tensor created since

@@ -67,4 +67,29 @@ class B200TensorModule : public BuiltinModule {
 extern "C" {
 int camel_module_abi_version(void) { return CAMEL_MODULE_ABI_VERSION; }
 Module *camel_module_create(Context *ctx) { return new B200TensorModule(ctx->shared_from_this()); }
+
+// Optional hooks for a host that knows where values die (it finds them with dlsym on the loaded
+// module; a host that does not look for them loses nothing but device memory).  The collector has
+// no finalisers (include/camel/core/mm/gen.h:224-227), so without these the module keeps every
+// device buffer until it is unloaded.  A scheduler calls begin when it enters a function frame or a
+// `sync` block and end when it leaves, passing the Tensor objects among the values that leave the
+// region (its result slot; for a tail call, the arguments of the next iteration): everything else
+// the region created on the device is released, and what a kept value still needs survives with it.
+uint64_t camel_tensor_scope_begin(void) { return camel::tensor::beginScope(); }
+
+void camel_tensor_scope_end(uint64_t token, void *const *kept_tensor_objects, size_t count) {
+    std::vector<camel::tensor::TensorObject *> keep;
+    for (size_t i = 0; i < count; ++i)
+        keep.push_back(static_cast<camel::tensor::TensorObject *>(
+            static_cast<camel::core::rtdata::Object *>(kept_tensor_objects[i])));
+    camel::tensor::endScope(token, keep);
+}
+
+// One value's last use (a loop variable that has just been replaced).
+void camel_tensor_release(void *tensor_object) {
+    camel::tensor::releaseTensor(static_cast<camel::tensor::TensorObject *>(
+        static_cast<camel::core::rtdata::Object *>(tensor_object)));
+}
+
+uint64_t camel_tensor_live_device_bytes(void) { return camel::tensor::liveDeviceBytes(); }
 }

@@ -693,7 +693,10 @@ CT_OP(__tensor_reshape__) {
             ctn::defer(out, ExprKind::Column, t); // `reshape(row_max, [n, 1])` of the softmax idiom
             return wrap(out);
         }
-        ctn::ctCheck(ct_d2d(out->deviceData(), t->deviceData(), t->byteSize())); // a copy, as in the reference
+        // the reference copies (runtime.cpp:692-702); tensors are immutable values, so a second shape
+        // over the same device buffer is the same value without the pass over HBM.  An array
+        // argument was just uploaded into a tensor of its own: that tensor is the source.
+        ctn::makeAlias(out, t);
         return wrap(out);
     });
 }
@@ -756,7 +759,7 @@ CT_OP(__tensor_flatten__) {
         int64_t rows      = x->dim(0);
         int64_t shape[2]  = {rows, rows ? static_cast<int64_t>(x->numel()) / rows : 0};
         TensorObject *out = newTensor(x->dtype(), shape);
-        ctn::ctCheck(ct_d2d(out->deviceData(), x->deviceData(), x->byteSize()));
+        ctn::makeAlias(out, x); // reshape(x, [n, rest]): the same buffer under another shape
         return wrap(out);
     });
 }

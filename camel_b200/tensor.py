@@ -427,9 +427,10 @@ def reshape(t: Tensor, new_shape) -> Tensor:
         n *= d
     if n != t.numel:
         raise _invalid("reshape changes tensor element count")
-    out = Tensor(t.dtype, shp)
-    check(lib.ct_d2d(out.ptr, t.ptr, t.nbytes))  # the reference copies too (runtime.cpp:692-702)
-    return out
+    # The reference copies (runtime.cpp:692-702).  Tensors are immutable values, so a second shape
+    # over the same device buffer is the same value without the pass over HBM; `keep` holds the
+    # owner alive.
+    return Tensor(t.dtype, shp, ptr=t.ptr, keep=t)
 
 
 def idx(t: Tensor, i: int) -> float:

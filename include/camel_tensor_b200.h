@@ -286,6 +286,21 @@ ct_status ct_rows_pack(const float *a_dev, int64_t m, int64_t k, void **packed_i
 ct_status ct_rows_free(void *packed);
 ct_status ct_matmul_packed_rows(
     const void *a_packed, int64_t row0, int64_t rows, const void *w_packed, float *out_dev);
+/* The same product with all row bands in ONE launch, for a caller that sends each band on its way
+ * as soon as it is complete (the all-gather of a row-sharded product): band b is band_rows_host[b]
+ * consecutive rows of the packed left operand (all but the last a multiple of 128) and is written to
+ * band_out_host[b] (row-major, n columns; the bands need not be adjacent in the result).  The tiles
+ * are computed band by band; band_done_dev[b] (device words that the CALLER clears before the call,
+ * and before the waiting stream may look at them: an event between the clear and the waits) counts
+ * the finished tiles of band b and reaches band_tiles_host[b] when the band is complete - a second
+ * stream waits for that with ct_stream_wait_value while the launch goes on with the later bands.  Separate launches per band would each end in a partly filled wave of tiles; this has one.
+ * Same arithmetic and bytes as ct_matmul_packed_rows.  No reference counterpart. */
+ct_status ct_matmul_packed_bands(
+    const void *a_packed, const void *w_packed, int nbands, const int64_t *band_rows_host,
+    float *const *band_out_host, uint32_t *band_done_dev, uint32_t *band_tiles_host);
+/* The current stream (ct_set_stream) waits until the 32-bit device word at addr_dev is >= value;
+ * the host does not wait.  No reference counterpart. */
+ct_status ct_stream_wait_value(const uint32_t *addr_dev, uint32_t value);
 ct_status ct_dense_packed(
     const float *x_dev, const float *w_dev, const void *packed, const float *bias_dev, int64_t m,
     int64_t k, int64_t n, ct_activation act, float *out_dev, int64_t *argmax_dev);

@@ -356,6 +356,36 @@ def build_cases():
             outs += [be.max_axis(a, ax), be.argmax_axis(a, ax)]
         return outs
 
+    for shape in ((200, 132), (4100, 12), (70, 2052), (1000, 10), (513, 64), (66, 1028)):
+        @case(f"axis_reduce_wide_{shape[0]}x{shape[1]}")
+        def _(be, shape=shape):
+            # shapes of the vectorised float32 kernels: narrow rows staged in shared memory, a warp or
+            # a block per row with 128-bit loads, columns cut into row slices; with the values that
+            # decide the scan's semantics placed where slices, lanes and vectors meet
+            rng = np.random.default_rng(40 + shape[0] + shape[1])
+            a = np.round(_f(rng, shape, -3, 3) * 4) / 4      # many ties: the first maximum must win
+            r, c = shape
+            a[0, 1] = np.nan                                  # NaN seeds column 1 (axis 0) ...
+            a[2, 0] = np.nan                                  # ... and row 2 (axis 1)
+            a[r // 2, c // 2] = np.nan                        # a NaN that is no seed never wins
+            a[:, 3] = -np.inf                                 # nothing exceeds the seed: index 0
+            a[5, :] = -np.inf
+            a[r - 1, 2] = np.inf
+            a[7, c - 1] = np.inf
+            a[1, 4], a[r - 2, 4] = 3.0, 3.0                   # equal maxima far apart
+            a[6, 5], a[6, c - 2] = 3.0, 3.0
+            a[0, 6], a[r - 1, 6] = -0.0, 0.0                  # +0 does not replace -0
+            outs = []
+            for ax in (0, 1):
+                outs += [be.sum_axis(np.nan_to_num(a, nan=0.5, posinf=2.0, neginf=-2.0), ax), be.max_axis(a, ax),
+                         be.argmax_axis(a, ax)]
+            return outs
+
+    @case("transpose_tiles")
+    def _(be):
+        rng = np.random.default_rng(41)
+        return [be.transpose(_f(rng, shape)) for shape in ((64, 64), (128, 68), (4, 260), (132, 4), (200, 196), (60, 7))]
+
     @case("movement")
     def _(be):
         rng = np.random.default_rng(14)

@@ -38,6 +38,10 @@ def test_cmo_exports_loader_entry_points():
     syms = subprocess.run(["nm", "-D", "--defined-only", str(CMO)], capture_output=True, text=True).stdout
     assert " T camel_module_abi_version" in syms
     assert " T camel_module_create" in syms
+    # the optional lifetime hooks a scheduler finds with dlsym
+    for hook in ("camel_tensor_scope_begin", "camel_tensor_scope_end", "camel_tensor_release",
+                 "camel_tensor_live_device_bytes"):
+        assert f" T {hook}" in syms
 
 
 @needs_build
