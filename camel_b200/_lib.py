@@ -9,7 +9,10 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libcamel_tensor_b200.so"
+import os
+
+# CAMEL_TENSOR_LIB: another build of the same library (e.g. one compiled with tracing)
+LIB_PATH = Path(os.environ.get("CAMEL_TENSOR_LIB") or Path(__file__).resolve().parent / "libcamel_tensor_b200.so")
 
 # ct_status
 OK, ERR_INVALID, ERR_CUDA, ERR_DIV_ZERO, ERR_LOG_DOMAIN, ERR_TIMEOUT, ERR_NO_DEVICE, ERR_TOO_LARGE = range(8)
@@ -37,6 +40,7 @@ PROTOTYPES = {
     "ct_check": (_int, []),
     "ct_inject_status": (_int, [_int, C.c_uint32]),
     "ct_measure_mma_peak": (_int, [_int, _int, _int, C.POINTER(_dbl), C.POINTER(_dbl)]),
+    "ct_measure_mma_rate_shifted": (_int, [_int, _int, _int, _int, _int, _int, C.POINTER(_dbl), C.POINTER(_dbl)]),
     "ct_measure_mma_rate": (_int, [_int, _int, _int, _int, _int, C.POINTER(_dbl), C.POINTER(_dbl)]),
     "ct_launch_count": (_u64, []),
     "ct_profile_enable": (_int, [_int]),

@@ -20,6 +20,28 @@
 #include "tc_ptx.cuh"
 #include "tmap.cuh"
 
+// Optional per-CTA clock accounting for tuning; compiled in only with -DCT_CONV_TRACE.
+#ifdef CT_CONV_TRACE
+__device__ unsigned long long g_halo_trace[256 * 16];
+#define CH_CLOCK() clock64()
+#define CH_ACCUM(slot, cycles)                                                          \
+    do {                                                                                \
+        if (blockIdx.x < 256)                                                           \
+            g_halo_trace[blockIdx.x * 16 + (slot)] += (unsigned long long)(cycles);     \
+    } while (0)
+extern "C" int ct_debug_halo_trace(unsigned long long *host, int count, int clear) {
+    int rc = (int)cudaMemcpyFromSymbol(host, g_halo_trace, sizeof(unsigned long long) * (size_t)count);
+    if (clear) {
+        static unsigned long long zeros[256 * 16];
+        cudaMemcpyToSymbol(g_halo_trace, zeros, sizeof(zeros));
+    }
+    return rc;
+}
+#else
+#define CH_CLOCK() 0ll
+#define CH_ACCUM(slot, cycles) do { } while (0)
+#endif
+
 namespace ct {
 namespace {
 
@@ -36,6 +58,7 @@ constexpr int kH_Threads    = 64 + 32 * kH_EpiWarps;
 constexpr int kH_EpiRowBytes  = 64 * 4 + 16;          // 64 columns staged at a time, rows padded
 constexpr int kH_EpiWarpBytes = 32 * kH_EpiRowBytes;
 constexpr int kH_EpiBytes     = kH_EpiWarps * kH_EpiWarpBytes;
+constexpr int kH_BiasSlots    = 256;                  // output channels whose bias is kept in shared memory
 
 struct ConvHaloParams {
     const float *bias;
@@ -64,6 +87,8 @@ __global__ void __launch_bounds__(kH_Threads, 1) conv_halo_stream_kernel(
     __shared__ uint64_t bar_done;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag_s;
+    // the layer's bias, read once: a load per stored row would put a trip to L2 in front of the add
+    __shared__ float bias_s[kH_BiasSlots];
     volatile int *abort_flag = &abort_flag_s;
 
     const int warp = threadIdx.x >> 5;
@@ -71,6 +96,8 @@ __global__ void __launch_bounds__(kH_Threads, 1) conv_halo_stream_kernel(
 
     if (threadIdx.x == 0)
         abort_flag_s = *reinterpret_cast<volatile uint32_t *>(p.flags + FLAG_TIMEOUT) != 0 ? 1 : 0;
+    for (int c = threadIdx.x; c < kH_BiasSlots; c += kH_Threads)
+        bias_s[c] = (p.bias && c < p.ko) ? p.bias[c] : 0.0f;
     __syncthreads();
     if (abort_flag_s)
         return;
@@ -176,31 +203,38 @@ __global__ void __launch_bounds__(kH_Threads, 1) conv_halo_stream_kernel(
             const uint32_t idesc = make_idesc(2u, 128, (uint32_t)p.n_mma);
             int ka = 0, kh2 = 0, i = 0;
             bool ok = true;
+            const long long t_start = CH_CLOCK();
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++i) {
                 const int buf = i & 1;
+                const long long t0 = CH_CLOCK();
                 if (!mbar_wait(smem_u32(&bar_tmem_empty[buf]), (((uint32_t)i >> 1) & 1u) ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
+                CH_ACCUM(0, CH_CLOCK() - t0); // waiting for an accumulator
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * 256u;
                 bool first = true;
                 for (int cb = 0; cb < p.cblocks && ok; ++cb, ++kh2) {
                     const int hs = kh2 % kH_HaloStages;
+                    const long long t1 = CH_CLOCK();
                     if (!mbar_wait(smem_u32(&bar_h_full[hs]), (uint32_t)(kh2 / kH_HaloStages) & 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
+                    CH_ACCUM(1, CH_CLOCK() - t1); // waiting for a halo
                     const uint32_t x_hi = halo_base + (uint32_t)hs * halo_stage;
                     const uint32_t x_lo = x_hi + (uint32_t)p.halo_plane_bytes;
                     int tap = 0;
                     for (int r = 0; r < p.kh && ok; ++r) {
                         for (int sx = 0; sx < p.kw; ++sx, ++tap, ++ka) {
                             const int s = ka % kH_AStages;
+                            const long long t2 = CH_CLOCK();
                             if (!mbar_wait(smem_u32(&bar_a_full[s]), (uint32_t)(ka / kH_AStages) & 1u, abort_flag)) {
                                 ok = false;
                                 break;
                             }
+                            CH_ACCUM(2, CH_CLOCK() - t2); // waiting for filter planes
                             tc_fence_after_sync();
                             const uint32_t a_hi = smem_base + (uint32_t)s * kH_AStageBytes, a_lo = a_hi + kH_ABytes;
                             // the tap's pixels: the halo, (r * pw + sx) rows of 64 bytes further on
@@ -224,6 +258,8 @@ __global__ void __launch_bounds__(kH_Threads, 1) conv_halo_stream_kernel(
                 if (ok)
                     tc_commit(smem_u32(&bar_tmem_full[buf]));
             }
+            CH_ACCUM(3, CH_CLOCK() - t_start); // the MMA thread's whole loop
+            CH_ACCUM(4, i);
             if (!ok || *abort_flag) {
                 tc_commit(smem_u32(&bar_done));
                 const uint64_t t0 = globaltimer_ns();
@@ -240,7 +276,7 @@ __global__ void __launch_bounds__(kH_Threads, 1) conv_halo_stream_kernel(
         const int sub = lane & 15, rr = lane >> 4;
         // where this lane's columns land: column col = half * 128 + h2 * 64 + sub * 4 + q is position
         // (y, x) = (col / pw, col % pw); -1 for the halo columns and past the tile
-        int off[2][4], yy[2][4];
+        int off[2][4];
         const int npos = p.th * p.pw;
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2)
@@ -249,16 +285,18 @@ __global__ void __launch_bounds__(kH_Threads, 1) conv_halo_stream_kernel(
                 const int col = half * 128 + h2 * 64 + sub * 4 + q;
                 const int y = col / p.pw, x = col - y * p.pw;
                 off[h2][q] = (col < npos && x < p.wo) ? y * p.wo + x : -1;
-                yy[h2][q]  = y;
             }
+        const int col_base = half * 128 + sub * 4;
         int i = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++i) {
             int tm, ty, img;
             coords(tile, tm, ty, img);
             const int buf = i & 1;
+            const long long e0 = CH_CLOCK();
             bool got = mbar_wait(smem_u32(&bar_tmem_full[buf]), ((uint32_t)i >> 1) & 1u, abort_flag);
             if (!__all_sync(0xffffffffu, got))
                 break;
+            const long long e1 = CH_CLOCK();
             tc_fence_after_sync();
             float acc[128];
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * 256 + half * 128);
@@ -278,6 +316,9 @@ __global__ void __launch_bounds__(kH_Threads, 1) conv_halo_stream_kernel(
 
             const int row0 = tm * 128 + quarter * 32; // first output channel of this warp's block
             const int y0   = ty * p.th;
+            // positions of rows past the image's last row (a partial last tile) are dropped:
+            // position col lies in row col / pw, so the valid ones are col < rows_left * pw
+            const int col_limit = (p.ho - y0 < p.th ? p.ho - y0 : p.th) * p.pw;
             float *out_img = p.out + ((int64_t)img * p.ko) * p.ho * p.wo + (int64_t)y0 * p.wo;
 #pragma unroll
             for (int h2 = 0; h2 < 2; ++h2) {
@@ -296,11 +337,11 @@ __global__ void __launch_bounds__(kH_Threads, 1) conv_halo_stream_kernel(
                     if (ch < p.ko) {
                         const float4 q4 = *reinterpret_cast<const float4 *>(stg + r_in * kH_EpiRowBytes + sub * 16);
                         const float v[4] = {q4.x, q4.y, q4.z, q4.w};
-                        const float b    = p.bias ? p.bias[ch] : 0.0f;
+                        const float b    = ch < kH_BiasSlots ? bias_s[ch] : (p.bias ? p.bias[ch] : 0.0f);
                         float *plane     = out_img + (int64_t)ch * p.ho * p.wo;
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
-                            if (off[h2][q] >= 0 && y0 + yy[h2][q] < p.ho) {
+                            if (off[h2][q] >= 0 && col_base + h2 * 64 + q < col_limit) {
                                 float x = v[q];
                                 if (p.bias)
                                     x = __fadd_rn(x, b);
@@ -312,6 +353,10 @@ __global__ void __launch_bounds__(kH_Threads, 1) conv_halo_stream_kernel(
                     }
                 }
                 __syncwarp(); // the block is rewritten by the next half / tile
+            }
+            if (warp == 2 && lane == 0) {
+                CH_ACCUM(5, e1 - e0);          // epilogue: waiting for a complete accumulator
+                CH_ACCUM(6, CH_CLOCK() - e1);  // drain and store
             }
         }
     }
@@ -350,7 +395,7 @@ bool halo_geometry(int64_t h, int64_t w, int64_t kh, int64_t kw, int64_t pad, Ha
         rows = (int64_t)g->box_rows * pw;
     g->plane_bytes = (int)((rows * kH_RowB + 1023) & ~1023ll);
     g->smem = (size_t)kH_AStages * kH_AStageBytes + (size_t)kH_HaloStages * 2 * g->plane_bytes + kH_EpiBytes + 1024;
-    return g->smem <= 226 * 1024;
+    return g->smem <= 225 * 1024; // 227 KB per CTA less the kernel's static shared memory
 }
 
 } // namespace
@@ -403,11 +448,13 @@ ct_status conv_halo_stream(
     const uint32_t xbox[4]  = {kH_BlockK, (uint32_t)g.pw, (uint32_t)g.box_rows, 1};
     CT_TRY(encode_tiled_map_f32(&mx_hi, x_hi, 4, xdims, xstr, xbox, kH_RowB));
     CT_TRY(encode_tiled_map_f32(&mx_lo, x_lo, 4, xdims, xstr, xbox, kH_RowB));
-    static bool attr_set_dev[16] = {}; // the attribute belongs to a device's context
-    bool &attr_set = attr_set_dev[st->device & 15];
-    if (!attr_set) {
-        CT_CUDA(cudaFuncSetAttribute(conv_halo_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        attr_set = true;
+    // the kernel also has a little static shared memory (barriers, the bias): ask for exactly what
+    // this geometry needs, remembering the largest request per device
+    static size_t attr_bytes_dev[16] = {};
+    size_t &attr_bytes = attr_bytes_dev[st->device & 15];
+    if (g.smem > attr_bytes) {
+        CT_CUDA(cudaFuncSetAttribute(conv_halo_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));
+        attr_bytes = g.smem;
     }
     const unsigned grid = (unsigned)(tiles < st->sm_count ? tiles : st->sm_count);
     ProfScope prof("gemm_tc");

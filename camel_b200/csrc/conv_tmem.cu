@@ -37,6 +37,28 @@
 #include "split.cuh"
 #include "tmap.cuh"
 
+// Optional per-CTA clock accounting for tuning; compiled in only with -DCT_CONV_TRACE.
+#ifdef CT_CONV_TRACE
+__device__ unsigned long long g_conv_trace[256 * 16];
+#define CV_CLOCK() clock64()
+#define CV_ACCUM(slot, cycles)                                                          \
+    do {                                                                                \
+        if (blockIdx.x < 256)                                                           \
+            g_conv_trace[blockIdx.x * 16 + (slot)] += (unsigned long long)(cycles);     \
+    } while (0)
+extern "C" int ct_debug_conv_trace(unsigned long long *host, int count, int clear) {
+    int rc = (int)cudaMemcpyFromSymbol(host, g_conv_trace, sizeof(unsigned long long) * (size_t)count);
+    if (clear) {
+        static unsigned long long zeros[256 * 16];
+        cudaMemcpyToSymbol(g_conv_trace, zeros, sizeof(zeros));
+    }
+    return rc;
+}
+#else
+#define CV_CLOCK() 0ll
+#define CV_ACCUM(slot, cycles) do { } while (0)
+#endif
+
 namespace ct {
 namespace {
 
@@ -205,15 +227,23 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
             const uint32_t d_tmem = tmem_base + (uint32_t)kTA_DCol;
             int i = 0;
             bool ok = true;
+            const long long t_start = CV_CLOCK();
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++i) {
                 const int s       = i % p.stages;
                 const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
                 // the accumulator of the previous tile has been drained
-                if (!mbar_wait(smem_u32(&bar_tmem_empty), ((uint32_t)i & 1u) ^ 1u, abort_flag) ||
-                    !mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag)) {
+                const long long t0 = CV_CLOCK();
+                if (!mbar_wait(smem_u32(&bar_tmem_empty), ((uint32_t)i & 1u) ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
+                const long long t1 = CV_CLOCK();
+                if (!mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                CV_ACCUM(0, t1 - t0);          // waiting for the accumulator
+                CV_ACCUM(1, CV_CLOCK() - t1);  // waiting for the halo
                 tc_fence_after_sync();
                 const uint32_t x_hi = smem_base + (uint32_t)s * stage_bytes;
                 const uint32_t x_lo = x_hi + (uint32_t)p.plane_bytes;
@@ -235,6 +265,8 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
                 tc_commit(smem_u32(&bar_empty[s]));   // the stage is free once these MMAs have retired
                 tc_commit(smem_u32(&bar_tmem_full));  // and the accumulator is complete
             }
+            CV_ACCUM(2, CV_CLOCK() - t_start); // the MMA thread's whole loop
+            CV_ACCUM(3, i);
             if (!ok || *abort_flag) {
                 tc_commit(smem_u32(&bar_done));
                 const uint64_t t0 = globaltimer_ns();
@@ -276,12 +308,23 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
                     off[g] = (2 * py) * p.pw + 2 * px, yy[g] = py; // here: the window's first position
             }
         }
+        // this warp's channels are the same for every tile: their bias values are read once (a load
+        // per channel inside the tile loop costs a trip to L2 that the add then waits for)
+        float bias_r[64 / kTA_EpiWarps];
+#pragma unroll
+        for (int j = 0; j < 64 / kTA_EpiWarps; ++j) {
+            const int ch = ew + kTA_EpiWarps * j;
+            bias_r[j]    = (p.bias && ch < p.ko) ? p.bias[ch] : 0.0f;
+        }
         int i = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++i) {
             const int img = tile / p.tiles_y, ty = tile - img * p.tiles_y;
+            const long long e0 = CV_CLOCK();
             bool got = mbar_wait(smem_u32(&bar_tmem_full), (uint32_t)i & 1u, abort_flag);
             if (!__all_sync(0xffffffffu, got))
                 break;
+            const long long e1 = CV_CLOCK();
+            const int y0 = ty * p.th;
             tc_fence_after_sync();
             // lane m of the accumulator -> row m of the staging block
             float4 *mine = reinterpret_cast<float4 *>(staging + (quarter * 32 + lane) * kTA_StageRowF + half * 64);
@@ -301,32 +344,50 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(smem_u32(&bar_tmem_empty)); // the next tile's MMAs may start
+            const long long e2 = CV_CLOCK();
             if (!epi_sync())
                 break;
-            const int y0 = ty * p.th;
-            if (p.pool == 0) {
-                for (int ch = ew; ch < p.ko; ch += kTA_EpiWarps) {
-                    const float *hi = staging + ch * kTA_StageRowF, *lo = staging + (64 + ch) * kTA_StageRowF;
-                    const float b   = p.bias ? p.bias[ch] : 0.0f;
-                    float *plane    = p.out + (((int64_t)img * p.ko + ch) * p.ho + y0) * p.wo;
+            const long long e3 = CV_CLOCK();
+            // which of this lane's four positions are stored for this tile (rows past the image's
+            // last row of a partial tile are not)
+            unsigned okmask = 0;
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        if (off[g] >= 0 && y0 + yy[g] < p.ho) {
-                            float v = __fadd_rn(hi[lane + 32 * g], lo[lane + 32 * g]);
+            for (int g = 0; g < 4; ++g)
+                if (off[g] >= 0 && (p.pool ? (y0 >> 1) + yy[g] < ph2 : y0 + yy[g] < p.ho))
+                    okmask |= 1u << g;
+            if (p.pool == 0) {
+#pragma unroll
+                for (int j = 0; j < 64 / kTA_EpiWarps; ++j) {
+                    const int ch = ew + kTA_EpiWarps * j;
+                    if (ch < p.ko) {
+                        const float *hi = staging + ch * kTA_StageRowF + lane, *lo = hi + 64 * kTA_StageRowF;
+                        const float b   = bias_r[j];
+                        float *plane    = p.out + (((int64_t)img * p.ko + ch) * p.ho + y0) * p.wo;
+                        float v[4];
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) { // the loads and the arithmetic of all four, then the stores
+                            v[g] = __fadd_rn(hi[32 * g], lo[32 * g]);
                             if (p.bias)
-                                v = __fadd_rn(v, b);
+                                v[g] = __fadd_rn(v[g], b);
                             if (p.act == CT_ACT_RELU)
-                                v = __fmul_rn(v, v > 0.0f ? 1.0f : 0.0f);
-                            plane[off[g]] = v;
+                                v[g] = __fmul_rn(v[g], v[g] > 0.0f ? 1.0f : 0.0f);
                         }
+#pragma unroll
+                        for (int g = 0; g < 4; ++g)
+                            if (okmask & (1u << g))
+                                plane[off[g]] = v[g];
                     }
                 }
             } else {
                 // 2x2 max-pool of the activated values; window order and strict '>' as in
                 // maxpool2d (the first element seeds, a NaN never wins)
-                for (int ch = ew; ch < p.ko; ch += kTA_EpiWarps) {
+#pragma unroll
+                for (int j = 0; j < 64 / kTA_EpiWarps; ++j) {
+                    const int ch = ew + kTA_EpiWarps * j;
+                    if (ch >= p.ko)
+                        break;
                     const float *hi = staging + ch * kTA_StageRowF, *lo = staging + (64 + ch) * kTA_StageRowF;
-                    const float b   = p.bias ? p.bias[ch] : 0.0f;
+                    const float b   = bias_r[j];
                     float *plane    = p.out + (((int64_t)img * p.ko + ch) * ph2 + (y0 >> 1)) * pw2;
                     auto value = [&](int pos) {
                         float v = __fadd_rn(hi[pos], lo[pos]);
@@ -338,7 +399,7 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
                     };
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        if (off[g] >= 0 && (y0 >> 1) + yy[g] < ph2) {
+                        if (okmask & (1u << g)) {
                             const int pos = off[g];
                             float best = value(pos);
                             const float v1 = value(pos + 1), v2 = value(pos + p.pw), v3 = value(pos + p.pw + 1);
@@ -353,8 +414,16 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
                     }
                 }
             }
+            const long long e4 = CV_CLOCK();
             if (!epi_sync()) // the staging block is rewritten by the next tile
                 break;
+            if (warp == 2 && lane == 0) {
+                CV_ACCUM(4, e1 - e0);           // epilogue: waiting for the accumulator to be complete
+                CV_ACCUM(5, e2 - e1);           // drain
+                CV_ACCUM(6, e3 - e2);           // first meeting of the epilogue warps
+                CV_ACCUM(7, e4 - e3);           // add, activate, store
+                CV_ACCUM(8, CV_CLOCK() - e4);   // second meeting
+            }
         }
     }
 

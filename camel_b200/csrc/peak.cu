@@ -17,12 +17,14 @@ constexpr int kPeakBN      = 256;
 constexpr int kPeakRowB    = 128;
 constexpr int kPeakABytes  = 128 * kPeakRowB;
 constexpr int kPeakBBytes  = kPeakBN * kPeakRowB;
-constexpr int kPeakSmem    = 2 * (kPeakABytes + kPeakBBytes) + 1024; // two operand sets, alternated
+constexpr int kPeakShiftMax = 16;                                   // B tiles may be read from up to 16 rows further on
+constexpr int kPeakSmem    = 2 * (kPeakABytes + kPeakBBytes) + kPeakShiftMax * kPeakRowB + 1024; // two operand sets, alternated
 constexpr int kPeakThreads = 128;
 
 // kind: 0 = kind::tf32, 1 = kind::f16 with bf16 operands
 template <int KIND>
-__global__ void __launch_bounds__(kPeakThreads, 1) mma_peak_kernel(int mma_groups, uint32_t *status, int mma_m, int mma_n) {
+__global__ void __launch_bounds__(kPeakThreads, 1) mma_peak_kernel(
+    int mma_groups, uint32_t *status, int mma_m, int mma_n, int b_row_shift, int a_in_tmem) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_done;
     __shared__ uint32_t tmem_base_slot;
@@ -34,7 +36,7 @@ __global__ void __launch_bounds__(kPeakThreads, 1) mma_peak_kernel(int mma_group
     // Operand values: a fixed pattern of finite numbers in (-1, 1).  Their arrangement in the
     // swizzled tile is irrelevant here (no result is read), their being non-zero is not: an
     // all-zero operand draws less power and would flatter the sustained figure.
-    for (int i = threadIdx.x; i < 2 * (kPeakABytes + kPeakBBytes) / 4; i += kPeakThreads) {
+    for (int i = threadIdx.x; i < (2 * (kPeakABytes + kPeakBBytes) + kPeakShiftMax * kPeakRowB) / 4; i += kPeakThreads) {
         uint32_t h = (uint32_t)i * 2654435761u + blockIdx.x * 40503u;
         float v    = ((h >> 9) & 0xffff) * (1.0f / 32768.0f) - 1.0f;
         if (KIND == 0) {
@@ -64,15 +66,29 @@ __global__ void __launch_bounds__(kPeakThreads, 1) mma_peak_kernel(int mma_group
         const uint32_t idesc = make_idesc(KIND == 0 ? 2u : 1u, (uint32_t)mma_m, (uint32_t)mma_n);
         for (int g = 0; g < mma_groups; ++g) {
             const uint32_t set = smem_base + (uint32_t)(g & 1) * (kPeakABytes + kPeakBBytes);
-            const uint64_t da = smem_desc_k<kPeakRowB>(set), db = smem_desc_k<kPeakRowB>(set + kPeakABytes);
-            const uint32_t d  = tmem_base + (uint32_t)((g >> 1) & 1) * kPeakBN;
+            const uint64_t da = smem_desc_k<kPeakRowB>(set);
+            const uint64_t db = smem_desc_k<kPeakRowB>(set + kPeakABytes + (uint32_t)b_row_shift * kPeakRowB);
+            // A from tensor memory: one accumulator (columns 0..255), the A tiles in columns 256..
+            const uint32_t d  = tmem_base + (a_in_tmem ? 0u : (uint32_t)((g >> 1) & 1) * kPeakBN);
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) { // four k-steps of 32 bytes per 128-byte operand row
                 const uint64_t adv = (uint64_t)(kk * 32 >> 4);
-                if (KIND == 0)
-                    mma_tf32(d, da + adv, db + adv, idesc, g < 2 && kk == 0 ? 0u : 1u);
-                else
-                    mma_f16(d, da + adv, db + adv, idesc, g < 2 && kk == 0 ? 0u : 1u);
+                const uint32_t acc = g < 2 && kk == 0 ? 0u : 1u;
+                if (KIND == 0 && a_in_tmem) {
+                    asm volatile(
+                        "{\n\t"
+                        ".reg .pred p;\n\t"
+                        "setp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
+                        "}\n"
+                        :
+                        : "r"(d), "r"(tmem_base + 256u + (uint32_t)(((g & 7) * 4 + kk) * 8)), "l"(db + adv), "r"(idesc), "r"(acc)
+                        : "memory");
+                } else if (KIND == 0) {
+                    mma_tf32(d, da + adv, db + adv, idesc, acc);
+                } else {
+                    mma_f16(d, da + adv, db + adv, idesc, acc);
+                }
             }
         }
         tc_commit(smem_u32(&bar_done));
@@ -108,6 +124,20 @@ extern "C" ct_status ct_measure_mma_peak(
 // cannot fill 256 columns; what its kernel reaches has to be read against the rate of its shape.
 extern "C" ct_status ct_measure_mma_rate(
     ct_precision kind, int mma_m, int mma_n, int mma_groups, int launches, double *tflops_host, double *ms_host) {
+    return ct_measure_mma_rate_shifted(kind, mma_m, mma_n, 0, mma_groups, launches, tflops_host, ms_host);
+}
+
+// ... and with the B tile read from b_row_shift rows (of 128 bytes) past a swizzle-aligned start:
+// what an implicit-GEMM convolution does when it addresses a filter tap's pixels inside one halo
+// box through a moved descriptor.
+extern "C" ct_status ct_measure_mma_rate_shifted(
+    ct_precision kind, int mma_m, int mma_n, int b_row_shift, int mma_groups, int launches, double *tflops_host,
+    double *ms_host) {
+    // b_row_shift + 256: the A operand comes from tensor memory instead of shared memory (tf32 only)
+    const int a_in_tmem = b_row_shift >= 256 ? 1 : 0;
+    b_row_shift -= 256 * a_in_tmem;
+    if (a_in_tmem && kind != CT_PREC_3XTF32)
+        return fail(CT_ERR_INVALID, "ct_measure_mma_rate_shifted: A from tensor memory is measured for tf32 only");
     OpLock op_lock;
     DeviceState *st;
     CT_TRY(current(&st));
@@ -115,6 +145,8 @@ extern "C" ct_status ct_measure_mma_rate(
         return fail(CT_ERR_INVALID, "ct_measure_mma_peak: mma_groups in [2, 2^20], launches in [1, 2^20]");
     if (kind != CT_PREC_3XTF32 && kind != CT_PREC_BF16)
         return fail(CT_ERR_INVALID, "ct_measure_mma_peak: unknown kind");
+    if (b_row_shift < 0 || b_row_shift > kPeakShiftMax)
+        return fail(CT_ERR_INVALID, "ct_measure_mma_rate_shifted: shift of 0 to %d rows", kPeakShiftMax);
     if ((mma_m != 64 && mma_m != 128) || mma_n < 16 || mma_n > kPeakBN || (mma_n & 15) != 0)
         return fail(CT_ERR_INVALID, "ct_measure_mma_rate: m must be 64 or 128, n a multiple of 16 up to %d", kPeakBN);
     // the in-kernel wait for the last MMA is bounded by one second: keep a launch far below that
@@ -126,11 +158,11 @@ extern "C" ct_status ct_measure_mma_rate(
     cudaEvent_t e0, e1;
     CT_CUDA(cudaEventCreate(&e0));
     CT_CUDA(cudaEventCreate(&e1));
-    kernel<<<st->sm_count, kPeakThreads, kPeakSmem, stream()>>>(mma_groups, st->flags_dev + 3, mma_m, mma_n); // warm-up
+    kernel<<<st->sm_count, kPeakThreads, kPeakSmem, stream()>>>(mma_groups, st->flags_dev + 3, mma_m, mma_n, b_row_shift, a_in_tmem); // warm-up
     CT_LAUNCH_CHECK("mma_peak");
     CT_CUDA(cudaEventRecord(e0, stream()));
     for (int i = 0; i < launches; ++i) {
-        kernel<<<st->sm_count, kPeakThreads, kPeakSmem, stream()>>>(mma_groups, st->flags_dev + 3, mma_m, mma_n);
+        kernel<<<st->sm_count, kPeakThreads, kPeakSmem, stream()>>>(mma_groups, st->flags_dev + 3, mma_m, mma_n, b_row_shift, a_in_tmem);
         CT_LAUNCH_CHECK("mma_peak");
     }
     CT_CUDA(cudaEventRecord(e1, stream()));

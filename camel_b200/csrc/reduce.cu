@@ -403,6 +403,40 @@ __global__ void __launch_bounds__(256) reduce_rows_narrow_f32_kernel(
     }
 }
 
+// axis = 1, very many rows of a few columns (a classifier's logits over a large batch): a thread
+// reads its own row with 64-bit loads straight from global memory - a warp's 32 rows are one
+// contiguous piece, so every fetched line is used completely (by several of the warp's loads, out
+// of L1) - and scans it in order; no staging, no barrier, results coalesced.
+template <int KIND, typename OT>
+__global__ void __launch_bounds__(256) reduce_rows_direct_f32_kernel(
+    const float *__restrict__ in, int64_t rows, int cols, OT *__restrict__ out) {
+    const int64_t row = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (row >= rows)
+        return;
+    const float2 *r = reinterpret_cast<const float2 *>(in + row * cols); // cols even, base 8-byte aligned
+    const int pairs = cols >> 1;
+    float first     = 0.0f;
+    double acc      = 0.0;
+    BestF b{-INFINITY, kNoIndex};
+#pragma unroll 8
+    for (int j = 0; j < pairs; ++j) {
+        const float2 q = __ldg(r + j);
+        if (j == 0)
+            first = q.x;
+        if (KIND == RED_SUM) {
+            acc += (double)q.x;
+            acc += (double)q.y;
+        } else {
+            best_take(b, q.x, 2 * j);
+            best_take(b, q.y, 2 * j + 1);
+        }
+    }
+    if (KIND == RED_SUM)
+        out[row] = (OT)(float)acc;
+    else
+        best_store<KIND, OT>(out, row, b, first);
+}
+
 // axis = 1, wider rows: GROUP threads per row (a warp, or the whole block), 128-bit loads.
 template <int KIND, typename OT, int GROUP>
 __global__ void __launch_bounds__(256) reduce_rows_f32_kernel(
@@ -564,7 +598,10 @@ ct_status reduce_axis_f32(DeviceState *st, const float *in, int64_t rows, int64_
     if (axis == 1) {
         if (rows == 0)
             return CT_OK;
-        if (cols <= 32 && rows >= 1024 * (int64_t)st->sm_count && cols <= 11) {
+        if (cols <= 32 && (cols & 1) == 0 && rows >= 256 * (int64_t)st->sm_count &&
+            (reinterpret_cast<uintptr_t>(in) & 7u) == 0) {
+            reduce_rows_direct_f32_kernel<KIND, OT><<<(unsigned)((rows + 255) / 256), 256, 0, stream()>>>(in, rows, (int)cols, out);
+        } else if (cols <= 32 && rows >= 1024 * (int64_t)st->sm_count && cols <= 11) {
             // many short rows: four rows per thread (up to 44 KB of a block's rows in flight)
             const unsigned blocks = (unsigned)((rows + 1023) / 1024);
             reduce_rows_narrow_f32_kernel<KIND, OT, 4>

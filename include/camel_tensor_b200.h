@@ -116,6 +116,12 @@ ct_status ct_measure_mma_peak(
 ct_status ct_measure_mma_rate(
     ct_precision kind, int mma_m, int mma_n, int mma_groups, int launches, double *tflops_host,
     double *ms_host);
+/* ... and with the B tile read b_row_shift rows (of 128 bytes, 0..16) past a swizzle-aligned
+ * start, as the convolution kernels do when they address a filter tap's pixels inside one halo box;
+ * b_row_shift + 256 also takes the A operand from tensor memory instead of shared memory (tf32). */
+ct_status ct_measure_mma_rate_shifted(
+    ct_precision kind, int mma_m, int mma_n, int b_row_shift, int mma_groups, int launches,
+    double *tflops_host, double *ms_host);
 ct_status ct_set_precision(ct_precision precision);
 ct_precision ct_get_precision(void);
 
@@ -299,7 +305,8 @@ ct_status ct_matmul_packed_bands(
     const void *a_packed, const void *w_packed, int nbands, const int64_t *band_rows_host,
     float *const *band_out_host, uint32_t *band_done_dev, uint32_t *band_tiles_host);
 /* The current stream (ct_set_stream) waits until the 32-bit device word at addr_dev is >= value;
- * the host does not wait.  No reference counterpart. */
+ * the host does not wait.  The word must lie in memory from cudaMalloc (a stream wait does not
+ * accept the stream-ordered pool that ct_alloc draws from).  No reference counterpart. */
 ct_status ct_stream_wait_value(const uint32_t *addr_dev, uint32_t value);
 ct_status ct_dense_packed(
     const float *x_dev, const float *w_dev, const void *packed, const float *bias_dev, int64_t m,

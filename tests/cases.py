@@ -356,7 +356,7 @@ def build_cases():
             outs += [be.max_axis(a, ax), be.argmax_axis(a, ax)]
         return outs
 
-    for shape in ((200, 132), (4100, 12), (70, 2052), (1000, 10), (513, 64), (66, 1028)):
+    for shape in ((200, 132), (4100, 12), (70, 2052), (1000, 10), (513, 64), (66, 1028), (40000, 10)):
         @case(f"axis_reduce_wide_{shape[0]}x{shape[1]}")
         def _(be, shape=shape):
             # shapes of the vectorised float32 kernels: narrow rows staged in shared memory, a warp or
