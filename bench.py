@@ -968,10 +968,11 @@ class Bench:
         self.barrier()
         return sum(a.elapsed_time(b) for a, b in evs)
 
-    def measure(self, wl, steps, warmup, min_gpu_s=0.0, max_blocks=2000):
+    def measure(self, wl, steps, warmup, min_gpu_s=0.0, max_blocks=2000, min_blocks=1):
         """Resident throughput of `wl`: `warmup` untimed steps, then blocks of exactly `steps`
-        timed steps, repeated until `min_gpu_s` seconds of device time have been timed (one block
-        if 0); the reported time per step is the median block's.  Then the dominant kernel's own
+        timed steps, repeated until `min_gpu_s` seconds of device time have been timed and at
+        least `min_blocks` blocks; the reported time per step is the median block's (a host that is
+        descheduled between two launches of a short block would otherwise show up as GPU time).  Then the dominant kernel's own
         launch durations from the library's event brackets on the same inputs."""
         lib, check, T = self.lib, self.check, self.T
         flush = self.flush_for(wl)
@@ -985,9 +986,9 @@ class Bench:
         launches = lib.ct_launch_count() - launches0
         # every rank must run the same number of blocks: the count comes from the first block's
         # (already max-reduced) time
-        extra_blocks = 0
+        extra_blocks = min_blocks - 1
         if min_gpu_s > 0 and blocks[0] > 0:
-            extra_blocks = min(max_blocks, int(np.ceil(min_gpu_s * 1e3 / blocks[0])))
+            extra_blocks = max(extra_blocks, min(max_blocks, int(np.ceil(min_gpu_s * 1e3 / blocks[0]))))
         for _ in range(extra_blocks):
             blocks.append(self.reduce_max(self.timed(wl.step, steps, flush)))
         t1 = time.time()
@@ -1040,6 +1041,13 @@ def measured_mma_peaks(lib, check, sampler):
         clocks = sampler.window(t0, time.time()) if sampler is not None else None
         out[name] = {"burst_tflops": burst, "burst_launch_us": [best[200][0] * 1e3, best[800][0] * 1e3],
                      "sustained_tflops": tf.value, "sustained_s": ms.value / 1e3, "sustained_clocks": clocks}
+        # the same pipe in its own clock domain (stamps inside the kernel): SM cycles per 128 x 256 MMA
+        # and the SM clock the measuring loop really ran at
+        cpm, mhz = C.c_double(), C.c_double()
+        check(lib.ct_measure_mma_clocks(kind, 128, 256, C.byref(cpm), C.byref(mhz)))
+        k = 8 if name == "tf32" else 16
+        out[name].update({"clocks_per_mma_128x256": cpm.value, "sm_mhz_in_kernel": mhz.value,
+                          "flop_per_clk_per_sm": 2.0 * 128 * 256 * k / cpm.value if cpm.value > 0 else None})
     return out
 
 
@@ -1047,8 +1055,8 @@ def roofline_of(wl, m, pk, mma, precision):
     """roofline object of one measured workload.  Tensor-bound kernels are held against the measured
     MMA rate of this run (tf32 / 3 for the 3xTF32 scheme): the burst figure for launches shorter
     than 5 ms, the sustained one for longer launches; the figure derived from the driver-written
-    bf16 GEMM peak is kept beside it.  `frac_at_clock` scales the burst ceiling (taken at the
-    maximum SM clock) to the median SM clock sampled during this workload."""
+    bf16 GEMM peak is kept beside it.  `frac_at_clock` holds the kernel against the pipe's rate per SM cycle
+    (cycle stamps inside the measuring kernel) times the median SM clock sampled during this workload."""
     dom_ms = m["dom_ms"]
     alg = wl.algorithmic_per_step() / max(1.0, m["launches_per_step"])
     out = {"bound": wl.bound, "kernel": wl.dominant, "launches_per_step": m["launches_per_step"],
@@ -1071,8 +1079,12 @@ def roofline_of(wl, m, pk, mma, precision):
                     "peak_note": note, "peak_derived_from_bf16_gemm": derived,
                     "frac_of_derived": achieved / derived if derived else None})
         c = m.get("clocks") or {}
-        if mma is not None and c.get("sm_mhz") and c.get("sm_max_mhz"):
-            at_clock = mma[kind]["burst_tflops"] / div * c["sm_mhz"] / c["sm_max_mhz"]
+        if mma is not None and c.get("sm_mhz") and mma[kind].get("flop_per_clk_per_sm"):
+            # the pipe's rate per SM clock (cycle stamps inside the measuring kernel) x SMs x the clock
+            # sampled during this workload: what the MMAs alone would reach at the clock the power
+            # cap left this kernel
+            at_clock = mma[kind]["flop_per_clk_per_sm"] * SM_COUNT * c["sm_mhz"] * 1e6 / 1e12 / div
+            out["peak_at_clock"] = at_clock
             out["frac_at_clock"] = achieved / at_clock
             out["time_x_mhz"] = dom_ms * c["sm_mhz"]
     else:
@@ -1083,6 +1095,8 @@ def roofline_of(wl, m, pk, mma, precision):
     out.update({"traffic": traffic, "traffic_unit": "bytes per launch", "traffic_note": traffic_note})
     return out
 
+
+SM_COUNT = 148  # B200
 
 EXTRA_STEPS = {"gemm": 5, "gemm_bf16": 5, "gemm512": 50, "conv": 10, "cnn": 5, "gemm_sharded": 3}
 
@@ -1121,7 +1135,7 @@ def run_extras(bench, args, pk, mma):
             else:
                 wl = KernelFamilyWorkload(torch, T, name)
             steps = EXTRA_STEPS.get(name, 10)
-            m = bench.measure(wl, steps, 3)
+            m = bench.measure(wl, steps, 3, min_blocks=3)
             # whole-job aggregate: a rank's units per step (its share, for a strong-scaling job) x ranks
             value = wl.units_per_step() * bench.world / (m["ms_per_step"] / 1e3)
             rec = {"workload": name, "metric": wl.metric, "value": value, "unit": wl.unit,
@@ -1156,15 +1170,20 @@ def plugin_leg(args, batch, world_reduce):
     h = C.CDLL(str(harness))
     x, w, b = mlp_inputs(batch)
     xs = np.ascontiguousarray(np.stack([x, x[::-1]]))
+    # the same two batches in page-locked memory (a host that page-locks its input buffers) and in
+    # ordinary memory (where the reference's allocator puts large tensors: gen.h:259-271)
+    locked = _Pinned(xs.shape, np.float32)
+    locked.numpy()[...] = xs
     probs, arg = np.zeros((batch, 10), np.float32), np.zeros(batch, np.int64)
     steps = max(20, args.steps)
     out = {}
-    for mode, key in ((0, "fused_operators"), (1, "small_operators")):
+    for mode, key, src in ((0, "fused_operators", locked.data_ptr()), (0, "fused_operators_pageable", xs.ctypes.data),
+                           (1, "small_operators", locked.data_ptr())):
         secs = (C.c_double * steps)()
         launches, err = C.c_uint64(), C.create_string_buffer(512)
         P = lambda a: C.c_void_p(a.ctypes.data)  # noqa: E731
         rc = h.camel_host_mlp_forward(
-            C.c_int(mode), P(xs), C.c_int(2), C.c_int64(batch), C.c_int64(784), C.c_int64(1024), C.c_int64(1024),
+            C.c_int(mode), C.c_void_p(src), C.c_int(2), C.c_int64(batch), C.c_int64(784), C.c_int64(1024), C.c_int64(1024),
             C.c_int64(10), P(w[0]), P(b[0]), P(w[1]), P(b[1]), P(w[2]), P(b[2]), C.c_int(steps), P(probs), P(arg),
             secs, C.byref(launches), err, C.c_int(512))
         if rc != 0:
@@ -1206,8 +1225,10 @@ def h2d_ceiling(bench, nbytes, copies=40):
 def run_gpu(args, rank, world):
     import torch
 
+    global SM_COUNT
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    SM_COUNT = torch.cuda.get_device_properties(local).multi_processor_count
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -1268,7 +1289,7 @@ def run_gpu(args, rank, world):
     if rank == 0 and (wl.bound == "tensor" or headline) and not args.no_peak:
         mma = measured_mma_peaks(lib, check, sampler)
 
-    m = bench.measure(wl, args.steps, args.warmup, min_gpu_s=1.0 if headline else 0.0)
+    m = bench.measure(wl, args.steps, args.warmup, min_gpu_s=1.0 if headline else 0.0, min_blocks=3)
     ms_per_step = m["ms_per_step"]
     # whole-job aggregate: a rank's units per step (its share, for a strong-scaling job) x ranks
     value = wl.units_per_step() * world / (ms_per_step / 1e3)
@@ -1331,9 +1352,15 @@ def run_gpu(args, rank, world):
             line["e2e"] = {"value": wl.batch * world / fused["seconds_per_step"], "unit": wl.unit,
                            "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                            "seconds_per_step": fused["seconds_per_step"], "launches_per_step": fused["launches_per_step"],
-                           "mode": "per step: host batch -> tensor (pageable host memory, one synchronous copy), dense_relu, "
+                           "mode": "per step: host batch in page-locked memory -> tensor (one synchronous copy), dense_relu, "
                                    "dense_relu, dense_softmax, argmax through operator_t, host read-back of both results; "
                                    "wall clock in C++ around the step, median step, slowest rank"}
+            pageable = plugin["fused_operators_pageable"]
+            line["e2e_plugin_pageable_host"] = {
+                "value": wl.batch * world / pageable["seconds_per_step"], "unit": wl.unit,
+                "seconds_per_step": pageable["seconds_per_step"],
+                "mode": "the same step with the host batch in ordinary (pageable) memory, where the reference's "
+                        "allocator keeps large tensors: the copy is staged by the driver"}
             small = plugin["small_operators"]
             line["e2e_plugin_small_operators"] = {
                 "value": wl.batch * world / small["seconds_per_step"], "unit": wl.unit,

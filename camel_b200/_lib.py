@@ -42,6 +42,7 @@ PROTOTYPES = {
     "ct_measure_mma_peak": (_int, [_int, _int, _int, C.POINTER(_dbl), C.POINTER(_dbl)]),
     "ct_measure_mma_rate_shifted": (_int, [_int, _int, _int, _int, _int, _int, C.POINTER(_dbl), C.POINTER(_dbl)]),
     "ct_measure_mma_rate": (_int, [_int, _int, _int, _int, _int, C.POINTER(_dbl), C.POINTER(_dbl)]),
+    "ct_measure_mma_clocks": (_int, [_int, _int, _int, C.POINTER(_dbl), C.POINTER(_dbl)]),
     "ct_launch_count": (_u64, []),
     "ct_profile_enable": (_int, [_int]),
     "ct_profile_read": (_int, [C.c_char_p, C.POINTER(_dbl), C.POINTER(_u64)]),

@@ -330,20 +330,24 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
             float4 *mine = reinterpret_cast<float4 *>(staging + (quarter * 32 + lane) * kTA_StageRowF + half * 64);
             const uint32_t taddr =
                 tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(kTA_DCol + half * 64);
-#pragma unroll
-            for (int g = 0; g < 2; ++g) {
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + g * 32, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    mine[g * 8 + j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-            }
+            // both halves of this warp's 64 columns are requested before the one wait, and the
+            // accumulator is handed back as soon as the values are in registers: the next tile's
+            // MMAs then start while these threads are still writing the staging block
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(taddr, r0);
+            tmem_ld_32x32(taddr + 32, r1);
+            tmem_ld_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(smem_u32(&bar_tmem_empty)); // the next tile's MMAs may start
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                mine[j]     = make_float4(__uint_as_float(r0[4 * j]), __uint_as_float(r0[4 * j + 1]),
+                                          __uint_as_float(r0[4 * j + 2]), __uint_as_float(r0[4 * j + 3]));
+                mine[8 + j] = make_float4(__uint_as_float(r1[4 * j]), __uint_as_float(r1[4 * j + 1]),
+                                          __uint_as_float(r1[4 * j + 2]), __uint_as_float(r1[4 * j + 3]));
+            }
             const long long e2 = CV_CLOCK();
             if (!epi_sync())
                 break;

@@ -1604,6 +1604,13 @@ ct_status gemm_planes(
     if (mode == MODE_3X) {
         // 128 x 256 tiles of two float32 planes: 64-byte k-blocks give four 48 KB stages instead
         // of two 96 KB ones
+#ifdef CT_STREAM128
+        if (wide && !conv) {
+            const int64_t tiles128 = ((m + BM - 1) / BM) * ((n + 127) / 128) * batch;
+            if (tiles256 < st->sm_count && tiles128 > st->sm_count && kp <= 1024 && g_band_plan.bands == 0)
+                return launch_gemm<128, MODE_3X, 64>(CT_GEMM_ARGS);
+        }
+#endif
         if (wide)
             return launch_gemm<256, MODE_3X, 64>(CT_GEMM_ARGS);
         return launch_gemm<128, MODE_3X>(CT_GEMM_ARGS);

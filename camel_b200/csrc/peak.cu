@@ -18,8 +18,15 @@ constexpr int kPeakRowB    = 128;
 constexpr int kPeakABytes  = 128 * kPeakRowB;
 constexpr int kPeakBBytes  = kPeakBN * kPeakRowB;
 constexpr int kPeakShiftMax = 16;                                   // B tiles may be read from up to 16 rows further on
-constexpr int kPeakSmem    = 2 * (kPeakABytes + kPeakBBytes) + kPeakShiftMax * kPeakRowB + 1024; // two operand sets, alternated
+constexpr int kPeakOperands = 2 * (kPeakABytes + kPeakBBytes) + kPeakShiftMax * kPeakRowB + 1024; // two operand sets, alternated
+constexpr int kPeakSmem     = kPeakOperands > 120 * 1024 ? kPeakOperands : 120 * 1024; // more than half of an SM's shared
+                                                                                        // memory: never two CTAs on one SM
 constexpr int kPeakThreads = 128;
+
+// SM cycles and nanoseconds that the MMA loop of the launch's first CTA took (the last launch wins):
+// cycles / MMA is the pipe's rate in the clock domain it runs in, cycles / ns the SM clock the loop
+// really ran at, whatever a sampled clock reading says.
+__device__ unsigned long long g_peak_stamp[2];
 
 // kind: 0 = kind::tf32, 1 = kind::f16 with bf16 operands
 template <int KIND>
@@ -64,6 +71,8 @@ __global__ void __launch_bounds__(kPeakThreads, 1) mma_peak_kernel(
 
     if (warp == 1 && (threadIdx.x & 31) == 0) {
         const uint32_t idesc = make_idesc(KIND == 0 ? 2u : 1u, (uint32_t)mma_m, (uint32_t)mma_n);
+        const long long c0   = clock64();
+        const uint64_t n0    = globaltimer_ns();
         for (int g = 0; g < mma_groups; ++g) {
             const uint32_t set = smem_base + (uint32_t)(g & 1) * (kPeakABytes + kPeakBBytes);
             const uint64_t da = smem_desc_k<kPeakRowB>(set);
@@ -94,6 +103,10 @@ __global__ void __launch_bounds__(kPeakThreads, 1) mma_peak_kernel(
         tc_commit(smem_u32(&bar_done));
         if (!mbar_wait(smem_u32(&bar_done), 0, &abort_flag_s))
             atomicExch(status, 1u + blockIdx.x);
+        if (blockIdx.x == 0) {
+            g_peak_stamp[0] = (unsigned long long)(clock64() - c0);
+            g_peak_stamp[1] = (unsigned long long)(globaltimer_ns() - n0);
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -181,5 +194,35 @@ extern "C" ct_status ct_measure_mma_rate_shifted(
         *tflops_host = ms > 0 ? flop / (ms * 1e-3) / 1e12 : 0.0;
     if (ms_host)
         *ms_host = ms;
+    return CT_OK;
+}
+
+// The pipe's rate in its own clock domain: SM cycles per MMA of the given shape (difference
+// quotient of two launch sizes, so that the loop's set-up and the final wait cancel) and the SM
+// clock the loops really ran at (cycles / nanoseconds of the longer launch, both stamped inside
+// the kernel).  flop per clock and SM = 2 * mma_m * mma_n * k / clocks_per_mma with k = 8 (tf32) or
+// 16 (bf16); times the SM count and a clock it gives the ceiling at that clock, which is what a
+// kernel timed under a power cap has to be read against.
+extern "C" ct_status ct_measure_mma_clocks(
+    ct_precision kind, int mma_m, int mma_n, double *clocks_per_mma_host, double *sm_mhz_host) {
+    const int groups[2] = {200, 800};
+    double cycles[2] = {0, 0}, ns[2] = {0, 0};
+    for (int i = 0; i < 2; ++i) {
+        double best = 0;
+        for (int rep = 0; rep < 3; ++rep) {
+            CT_TRY(ct_measure_mma_rate(kind, mma_m, mma_n, groups[i], 1, nullptr, nullptr));
+            unsigned long long stamp[2];
+            CT_CUDA(cudaMemcpyFromSymbol(stamp, g_peak_stamp, sizeof(stamp)));
+            if (rep == 0 || (double)stamp[0] < best) {
+                best      = (double)stamp[0];
+                cycles[i] = (double)stamp[0];
+                ns[i]     = (double)stamp[1];
+            }
+        }
+    }
+    if (clocks_per_mma_host)
+        *clocks_per_mma_host = (cycles[1] - cycles[0]) / (4.0 * (groups[1] - groups[0]));
+    if (sm_mhz_host)
+        *sm_mhz_host = ns[1] > 0 ? cycles[1] / ns[1] * 1e3 : 0.0;
     return CT_OK;
 }

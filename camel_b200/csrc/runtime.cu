@@ -1,6 +1,7 @@
 // Library state: error text, device/stream selection, storage entry points.
 #include "common.cuh"
 
+#include <atomic>
 #include <cctype>
 #include <cstdio>
 #include <cstring>
@@ -256,66 +257,120 @@ bool local_cpus_of_device(int dev, cpu_set_t *set) {
 //
 // The reference keeps tensors in ordinary (pageable) host memory, so that is what a program hands
 // the module at a graph boundary.  cudaMemcpy from pageable memory is staged by the driver through
-// its own buffers by one thread: about 18 GB/s on the hosts measured, a third of what the link
-// gives page-locked memory (54 GB/s).  For large sources ct_h2d stages the copy itself: a few host
-// threads copy 2 MiB chunks into a small ring of page-locked buffers while earlier chunks are
-// already on their way to the device, so that the copy runs at the speed of the slower of the two
-// stages instead of at the speed of one thread.
+// its own buffers by one thread: measured 18 GB/s for 16 MB falling to 11 GB/s for 256 MB, against
+// the 54 GB/s the link gives page-locked memory.  For sources of 32 MiB and more ct_h2d stages the
+// copy itself: a few host threads copy chunks into a ring of page-locked buffers while earlier
+// chunks are already on their way to the device (measured 28-32 GB/s at 64 MB, 28-40 GB/s at
+// 256 MB).  Chunks are finished in order (workers claim consecutive chunks from one counter); the
+// calling thread copies the first chunk (it is awake; the workers sleep between calls), then only
+// issues transfers.  The hand-offs are atomics, not locks.  Below 32 MiB the plain path stays:
+// waking the workers costs as much as they save.
 namespace ct {
 namespace {
 
-constexpr size_t kStageChunk   = 2u << 20;
-constexpr int kStageSlots      = 8;
-constexpr int kStageWorkers    = 4;
-constexpr size_t kStageMinimum = 4u << 20; // smaller copies go the plain way
+#ifndef CT_STAGE_CHUNK_KB
+#define CT_STAGE_CHUNK_KB 1024
+#endif
+#ifndef CT_STAGE_WORKERS
+#define CT_STAGE_WORKERS 4
+#endif
+constexpr size_t kStageChunk   = (size_t)CT_STAGE_CHUNK_KB << 10;
+constexpr size_t kStageRing    = 16u << 20;                   // page-locked bytes held by the ring
+constexpr int kStageSlots      = (int)(kStageRing / kStageChunk);
+constexpr int kStageWorkers    = CT_STAGE_WORKERS;
+constexpr size_t kStageMinimum = 32u << 20; // smaller copies go the plain way: waking the workers costs more
+                                            // than they save (12 MB: 650-1000 us staged, 690 us plain)
+
+inline void cpu_relax() {
+#if defined(__x86_64__) || defined(__i386__)
+    __builtin_ia32_pause();
+#else
+    std::this_thread::yield();
+#endif
+}
 
 class HostStager {
   public:
-    // Copies `bytes` from pageable `src` to device `dst` on `s`; returns when the host buffer may be reused.
+    // Copies `bytes` from pageable `src` to device `dst` on `s`.  On return every chunk has been
+    // copied out of `src` and handed to the stream.
     cudaError_t copy(void *dst, const void *src, size_t bytes, cudaStream_t s) {
         std::lock_guard<std::mutex> whole(call_mutex_); // one staged copy at a time: the ring is shared
         cudaError_t e = ensure();
         if (e != cudaSuccess)
             return e;
-        const size_t chunks = (bytes + kStageChunk - 1) / kStageChunk;
-        size_t submitted = 0, issued = 0;
-        while (issued < chunks) {
-            // keep the workers busy: a chunk may be submitted once its slot's previous transfer is done
-            while (submitted < chunks && submitted < issued + kStageSlots) {
-                const int slot = (int)(submitted % kStageSlots);
-                if (slot_busy_[slot]) {
-                    e = cudaEventSynchronize(slot_done_[slot]);
-                    if (e != cudaSuccess)
-                        return e;
-                    slot_busy_[slot] = false;
-                }
-                const size_t off = submitted * kStageChunk;
-                const size_t len = bytes - off < kStageChunk ? bytes - off : kStageChunk;
-                {
-                    std::lock_guard<std::mutex> lock(mutex_);
-                    jobs_.push_back(Job{static_cast<const char *>(src) + off, slot_mem_[slot], len, submitted});
-                }
-                wake_.notify_one();
-                ++submitted;
+        // transfers of an earlier call that the caller did not wait for still own their slots
+        for (int i = 0; i < kStageSlots; ++i)
+            if (slot_pending_[i]) {
+                e = cudaEventSynchronize(slot_done_[i]);
+                if (e != cudaSuccess)
+                    return e;
+                slot_pending_[i] = false;
             }
-            // the next chunk in order: wait for its host copy, then send it
-            {
-                std::unique_lock<std::mutex> lock(mutex_);
-                finished_.wait(lock, [&] { return done_through_[issued % kStageSlots] == issued + 1 + epoch_; });
-            }
-            const int slot   = (int)(issued % kStageSlots);
-            const size_t off = issued * kStageChunk;
-            const size_t len = bytes - off < kStageChunk ? bytes - off : kStageChunk;
-            e = cudaMemcpyAsync(static_cast<char *>(dst) + off, slot_mem_[slot], len, cudaMemcpyHostToDevice, s);
-            if (e == cudaSuccess)
-                e = cudaEventRecord(slot_done_[slot], s);
-            if (e != cudaSuccess)
-                return e;
-            slot_busy_[slot] = true;
-            ++issued;
+        src_    = static_cast<const char *>(src);
+        bytes_  = bytes;
+        chunks_ = (bytes + kStageChunk - 1) / kStageChunk;
+        next_.store(1, std::memory_order_relaxed); // chunk 0 is this thread's
+        retired_.store(0, std::memory_order_relaxed);
+        abort_.store(false, std::memory_order_relaxed);
+        {
+            std::lock_guard<std::mutex> lock(mutex_);
+            open_ = true;
+            ++epoch_;
         }
-        epoch_ += chunks; // chunk numbers never repeat, so a stale completion mark cannot be mistaken
-        return cudaSuccess;
+        if (chunks_ > 1)
+            wake_.notify_all();
+        fill(0);
+
+        size_t issued = 0, retired = 0;
+        cudaError_t result = cudaSuccess;
+        while (issued < chunks_) {
+            const int slot = (int)(issued % kStageSlots);
+            if (ready_[slot].load(std::memory_order_acquire) == base_ + issued + 1) {
+                const size_t off = issued * kStageChunk;
+                const size_t len = bytes - off < kStageChunk ? bytes - off : kStageChunk;
+                e = cudaMemcpyAsync(static_cast<char *>(dst) + off, slot_mem_[slot], len, cudaMemcpyHostToDevice, s);
+                if (e == cudaSuccess)
+                    e = cudaEventRecord(slot_done_[slot], s);
+                if (e != cudaSuccess) {
+                    result = e;
+                    break;
+                }
+                slot_pending_[slot] = true;
+                ++issued;
+            } else {
+                cpu_relax();
+            }
+            // slots whose transfer has finished go back to the workers (only a copy longer than the
+            // ring ever waits for one)
+            if (chunks_ > (size_t)kStageSlots)
+                while (retired < issued) {
+                    cudaError_t q = cudaEventQuery(slot_done_[retired % kStageSlots]);
+                    if (q == cudaErrorNotReady) {
+                        cudaGetLastError();
+                        break;
+                    }
+                    if (q != cudaSuccess) {
+                        result = q;
+                        break;
+                    }
+                    slot_pending_[retired % kStageSlots] = false;
+                    ++retired;
+                    retired_.store(retired, std::memory_order_release);
+                }
+            if (result != cudaSuccess)
+                break;
+        }
+        // close the call: no worker may touch its state after this returns
+        abort_.store(result != cudaSuccess, std::memory_order_release);
+        next_.store(chunks_, std::memory_order_release);
+        {
+            std::lock_guard<std::mutex> lock(mutex_);
+            open_ = false;
+        }
+        while (active_.load(std::memory_order_acquire) != 0)
+            cpu_relax();
+        base_ += chunks_; // chunk sequence numbers never repeat, so a stale mark cannot be mistaken
+        return result;
     }
 
     ~HostStager() {
@@ -330,15 +385,8 @@ class HostStager {
     }
 
   private:
-    struct Job {
-        const char *src;
-        void *dst;
-        size_t len;
-        size_t index;
-    };
-
     cudaError_t ensure() {
-        if (ready_)
+        if (ready_state_)
             return cudaSuccess;
         for (int i = 0; i < kStageSlots; ++i) {
             cudaError_t e = cudaHostAlloc(&slot_mem_[i], kStageChunk, cudaHostAllocDefault);
@@ -346,45 +394,63 @@ class HostStager {
                 e = cudaEventCreateWithFlags(&slot_done_[i], cudaEventDisableTiming);
             if (e != cudaSuccess)
                 return e;
-            slot_busy_[i]    = false;
-            done_through_[i] = 0;
+            slot_pending_[i] = false;
+            ready_[i].store(0, std::memory_order_relaxed);
         }
         for (int i = 0; i < kStageWorkers; ++i)
             workers_.emplace_back([this] { work(); });
-        ready_ = true;
+        ready_state_ = true;
         return cudaSuccess;
     }
 
+    // host copy of chunk c into its slot, once the slot's previous transfer is over
+    void fill(size_t c) {
+        while (c >= retired_.load(std::memory_order_acquire) + (size_t)kStageSlots) {
+            if (abort_.load(std::memory_order_acquire))
+                return;
+            cpu_relax();
+        }
+        const int slot   = (int)(c % kStageSlots);
+        const size_t off = c * kStageChunk;
+        const size_t len = bytes_ - off < kStageChunk ? bytes_ - off : kStageChunk;
+        memcpy(slot_mem_[slot], src_ + off, len);
+        ready_[slot].store(base_ + c + 1, std::memory_order_release);
+    }
+
     void work() {
+        size_t seen = 0;
         for (;;) {
-            Job job;
             {
                 std::unique_lock<std::mutex> lock(mutex_);
-                wake_.wait(lock, [&] { return stop_ || !jobs_.empty(); });
+                wake_.wait(lock, [&] { return stop_ || (open_ && epoch_ != seen); });
                 if (stop_)
                     return;
-                job = jobs_.front();
-                jobs_.pop_front();
+                seen = epoch_;
+                active_.fetch_add(1, std::memory_order_acq_rel); // under the lock: copy() closes the call under it
             }
-            memcpy(job.dst, job.src, job.len);
-            {
-                std::lock_guard<std::mutex> lock(mutex_);
-                done_through_[job.index % kStageSlots] = job.index + 1 + epoch_;
+            for (;;) {
+                const size_t c = next_.fetch_add(1, std::memory_order_acq_rel);
+                if (c >= chunks_ || abort_.load(std::memory_order_acquire))
+                    break;
+                fill(c);
             }
-            finished_.notify_all();
+            active_.fetch_sub(1, std::memory_order_acq_rel);
         }
     }
 
     std::mutex call_mutex_, mutex_;
-    std::condition_variable wake_, finished_;
-    std::deque<Job> jobs_;
+    std::condition_variable wake_;
     std::vector<std::thread> workers_;
     void *slot_mem_[kStageSlots]        = {};
     cudaEvent_t slot_done_[kStageSlots] = {};
-    bool slot_busy_[kStageSlots]        = {};
-    size_t done_through_[kStageSlots]   = {};
-    size_t epoch_                       = 0;
-    bool ready_ = false, stop_ = false;
+    bool slot_pending_[kStageSlots]     = {};
+    std::atomic<size_t> ready_[kStageSlots];
+    std::atomic<size_t> next_{0}, retired_{0};
+    std::atomic<int> active_{0};
+    std::atomic<bool> abort_{false};
+    const char *src_ = nullptr;
+    size_t bytes_ = 0, chunks_ = 0, base_ = 0, epoch_ = 0;
+    bool ready_state_ = false, stop_ = false, open_ = false;
 };
 
 HostStager g_stager;

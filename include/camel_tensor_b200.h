@@ -122,6 +122,12 @@ ct_status ct_measure_mma_rate(
 ct_status ct_measure_mma_rate_shifted(
     ct_precision kind, int mma_m, int mma_n, int b_row_shift, int mma_groups, int launches,
     double *tflops_host, double *ms_host);
+/* The pipe's rate in its own clock domain, from stamps taken inside the kernel: SM cycles per MMA
+ * of the shape (k = 8 for tf32, 16 for bf16) and the SM clock in MHz that the measuring loop
+ * really ran at.  flop per clock and SM = 2 * mma_m * mma_n * k / *clocks_per_mma_host.  No
+ * reference counterpart. */
+ct_status ct_measure_mma_clocks(
+    ct_precision kind, int mma_m, int mma_n, double *clocks_per_mma_host, double *sm_mhz_host);
 ct_status ct_set_precision(ct_precision precision);
 ct_precision ct_get_precision(void);
 

@@ -978,6 +978,13 @@ def test_tensor_pipe_peak_measurement(T):
     check(lib.ct_measure_mma_peak(PREC_BF16, 800, 1, C.byref(tf), C.byref(ms)))
     print(f"bf16 MMA burst: {tf.value:.1f} TFLOP/s in {ms.value * 1e3:.1f} us")
     assert 1200.0 <= tf.value <= 2500.0  # nominal 2.25 PFLOP/s dense
+    # the same pipe in SM cycles (stamps inside the kernel): a 128 x 256 x 8 tf32 MMA needs 128 cycles at
+    # the nominal 8192 flop per cycle and SM; and the clock those cycles were counted at
+    cpm, mhz = C.c_double(), C.c_double()
+    check(lib.ct_measure_mma_clocks(PREC_3XTF32, 128, 256, C.byref(cpm), C.byref(mhz)))
+    print(f"tf32 128x256x8: {cpm.value:.1f} SM cycles per MMA at {mhz.value:.0f} MHz")
+    assert 120.0 <= cpm.value <= 200.0
+    assert 700.0 <= mhz.value <= 2100.0
 
 
 def test_packed_bands_one_launch_with_completion_counters(T):
@@ -1061,3 +1068,20 @@ def test_packed_bands_one_launch_with_completion_counters(T):
         check(lib.ct_weights_free(wp))
         check(lib.ct_event_destroy(ev))
         check(lib.ct_stream_destroy(side))
+
+
+@pytest.mark.parametrize("nbytes", [(32 << 20) - 4, 32 << 20, (33 << 20) + 12, (100 << 20) + 4])
+def test_large_copies_from_ordinary_host_memory(T, nbytes):
+    """ct_h2d from pageable memory: sources of 32 MiB and more are staged through the library's ring of
+    page-locked buffers by several host threads (one below the limit takes the plain path; one longer
+    than the 16 MiB ring makes slots come round again).  Every byte has to arrive, twice in a row."""
+    from camel_b200._lib import check, lib
+
+    n = nbytes // 4
+    rng = np.random.default_rng(nbytes)
+    t = T.Tensor(0, (n,))
+    for _ in range(2):
+        src = rng.random(n, dtype=np.float32)
+        check(lib.ct_h2d(t.ptr, src.ctypes.data, n * 4))
+        back = t.numpy()
+        assert back.tobytes() == src.tobytes()
