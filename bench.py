@@ -1068,25 +1068,45 @@ def roofline_of(wl, m, pk, mma, precision):
         derived = pk["bf16_tflops"] / (1.0 if precision == "bf16" else 6.0)
         if mma is not None:
             which = "burst" if dom_ms < 5.0 else "sustained"
-            peak = mma[kind][f"{which}_tflops"] / div
-            note = (f"measured in this run: tcgen05.mma kind::{'f16 (bf16)' if kind == 'bf16' else 'tf32'} back to back on "
-                    f"resident operands, {which} figure" + ("" if precision == "bf16" else " / 3 (three MMAs per product)"))
-            out["peak_burst"] = mma[kind]["burst_tflops"] / div
-            out["peak_sustained"] = mma[kind]["sustained_tflops"] / div
+
+            def pipe(w):
+                # a tf32 MMA moves the bytes of a bf16 MMA with half the k: the pipe gives tf32 half the
+                # bf16 rate.  On some GPUs of the pool the tf32 measuring loop itself reads a quarter
+                # lower than that (while the GEMM kernels run as fast as elsewhere), so the ceiling is
+                # the larger of the two readings: never flatter the kernel with a slow measurement.
+                if kind == "bf16":
+                    return mma["bf16"][f"{w}_tflops"]
+                return max(mma["tf32"][f"{w}_tflops"], mma["bf16"][f"{w}_tflops"] / 2.0)
+
+            peak = pipe(which) / div
+            note = (f"measured in this run: tcgen05.mma back to back on resident operands, {which} figure"
+                    + ("" if precision == "bf16" else ", the larger of kind::tf32 and kind::f16 / 2, / 3 (three MMAs per product)"))
+            out["peak_burst"] = pipe("burst") / div
+            out["peak_sustained"] = pipe("sustained") / div
         else:
             peak, note = derived, "derived (no MMA measurement on this rank)"
         out.update({"achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
                     "peak_note": note, "peak_derived_from_bf16_gemm": derived,
                     "frac_of_derived": achieved / derived if derived else None})
         c = m.get("clocks") or {}
-        if mma is not None and c.get("sm_mhz") and mma[kind].get("flop_per_clk_per_sm"):
+        fpc = None
+        if mma is not None and mma[kind].get("flop_per_clk_per_sm"):
+            fpc = mma[kind]["flop_per_clk_per_sm"]
+            if kind == "tf32" and mma["bf16"].get("flop_per_clk_per_sm"):
+                fpc = max(fpc, mma["bf16"]["flop_per_clk_per_sm"] / 2.0)
+        if fpc and c.get("sm_mhz"):
             # the pipe's rate per SM clock (cycle stamps inside the measuring kernel) x SMs x the clock
             # sampled during this workload: what the MMAs alone would reach at the clock the power
             # cap left this kernel
-            at_clock = mma[kind]["flop_per_clk_per_sm"] * SM_COUNT * c["sm_mhz"] * 1e6 / 1e12 / div
+            at_clock = fpc * SM_COUNT * c["sm_mhz"] * 1e6 / 1e12 / div
             out["peak_at_clock"] = at_clock
             out["frac_at_clock"] = achieved / at_clock
             out["time_x_mhz"] = dom_ms * c["sm_mhz"]
+            if achieved > 1.02 * at_clock:
+                out["clock_note"] = ("the sampled clock understates the clock this kernel ran at (nvidia-smi samples every "
+                                     "200 ms; the measuring loop's own cycle/ns stamps read "
+                                     f"{mma[kind]['sm_mhz_in_kernel']:.0f} MHz while the sampler read "
+                                     f"{(mma[kind]['sustained_clocks'] or {}).get('sm_mhz')} MHz): read `frac` instead")
     else:
         achieved = alg / (dom_ms / 1e3) / 1e9 if dom_ms > 0 else 0.0
         out.update({"achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",

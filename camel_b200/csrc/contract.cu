@@ -603,7 +603,10 @@ static ct_status conv2d_run(
                        ? conv_tile_rows(ho, wo) : 0;
     if (th > 0 && mode == 0 && conv_tmem_applicable(c, h, wd, ko, kh, kw, stride, pad)) {
         // few channels on both sides: the filters stay in tensor memory, a tile's input is fetched
-        // once (conv_tmem.cu); only the input needs the NHWC hi/lo planes
+        // once (conv_tmem.cu) - as it is where its rows allow a tensor map over it (the kernel then
+        // splits it itself: no pre-pass, no workspace), else from NHWC hi/lo planes
+        if (conv_tmem_reads_input_directly(x, h, wd, kh, kw, pad, pool))
+            return conv_tmem_filters(st, x, nullptr, nullptr, w, bias, n, c, h, wd, ko, kh, kw, pad, act, pool, out);
         size_t x_plane = align_up((size_t)n * h * wd * 32 * 4);
         CT_TRY(ensure_ws(&st->gemm_ws, &st->gemm_ws_bytes, 2 * x_plane));
         uint8_t *ws = static_cast<uint8_t *>(st->gemm_ws);
@@ -611,7 +614,7 @@ static ct_status conv2d_run(
             ProfScope prof("conv_prepass");
             CT_TRY(nhwc_planes(st, mode, x, n, c, h * wd, 32, ws, ws + x_plane));
         }
-        return conv_tmem_filters(st, ws, ws + x_plane, w, bias, n, c, h, wd, ko, kh, kw, pad, act, pool, out);
+        return conv_tmem_filters(st, nullptr, ws, ws + x_plane, w, bias, n, c, h, wd, ko, kh, kw, pad, act, pool, out);
     }
     if (th > 0) {
         int64_t c_pad  = (c + kblock - 1) / kblock * kblock;

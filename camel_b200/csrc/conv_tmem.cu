@@ -66,6 +66,9 @@ using namespace ptx;
 
 constexpr int kTA_EpiWarps  = 8;
 constexpr int kTA_Threads   = 64 + 32 * kTA_EpiWarps;
+constexpr int kTA_CvtWarps  = 4;                  // raw mode: warps that turn float32 boxes into hi/lo planes
+constexpr int kTA_ThreadsRaw = kTA_Threads + 32 * kTA_CvtWarps;
+constexpr int kTA_RawStages = 2;
 constexpr int kTA_MaxKSteps = 48;                 // 8 TMEM columns each: 384 of the 512 columns
 constexpr int kTA_DCol      = kTA_MaxKSteps * 8;  // the accumulator's first column
 constexpr int kTA_N         = 128;                // positions per tile (MMA N)
@@ -87,6 +90,12 @@ struct ConvTmemParams {
     int plane_bytes;  // shared-memory bytes reserved per plane (box plus the rows shifted reads run into)
     int stages;
     int act, pool;
+    // raw mode (the input is read as it is, NCHW float32, and split into planes inside the kernel)
+    int box_w;        // floats per row of the raw box (a multiple of four)
+    int off_x;        // the tile's first position (x = -pad) sits this many floats into a raw row
+    int box_rows;     // th + kh - 1
+    int raw_bytes;    // bytes of one raw box: 32 channels x box_rows x box_w floats
+    int raw_stride;   // shared-memory bytes reserved per raw stage
 };
 
 __device__ __forceinline__ void tmem_st_32x32_x8(uint32_t taddr, const uint32_t (&r)[8]) {
@@ -112,12 +121,22 @@ __device__ __forceinline__ void mma_tf32_a_tmem(
         : "memory");
 }
 
-__global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
+// RAW = false: map_x_hi / map_x_lo cover NHWC hi / lo planes written by a pre-pass.
+// RAW = true:  map_x_hi covers the input itself, [batch][c][h][w] float32 (map_x_lo is not used);
+//              the producer fetches a tile's box of it - 32 channels x box_rows x box_w floats, zeros
+//              outside the image and past the last channel - and four more warps rewrite it as the
+//              two planes the MMAs read: position (y, x) becomes row y * pw + x, its 32 channels the
+//              128 bytes of the row (swizzled as TMA would have), each value split into tf32 parts.
+//              The pre-pass and its 12 bytes of traffic per input element are gone.
+template <bool RAW>
+__global__ void __launch_bounds__(kTA_ThreadsRaw, 1) conv_tmem_filters_kernel(
     const __grid_constant__ CUtensorMap map_x_hi, const __grid_constant__ CUtensorMap map_x_lo,
     const ConvTmemParams p, const int total_tiles) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bar_full[4];
     __shared__ uint64_t bar_empty[4];
+    __shared__ uint64_t bar_raw_full[kTA_RawStages];
+    __shared__ uint64_t bar_raw_empty[kTA_RawStages];
     __shared__ uint64_t bar_tmem_full;
     __shared__ uint64_t bar_tmem_empty;
     __shared__ uint64_t bar_done;
@@ -137,12 +156,19 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t stage_bytes = 2u * (uint32_t)p.plane_bytes;
-    float *staging = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)) + (uint32_t)p.stages * stage_bytes);
+    // planes | raw boxes (raw mode) | epilogue staging
+    const uint32_t raw_base = smem_base + (uint32_t)p.stages * stage_bytes;
+    const uint32_t raw_all  = RAW ? (uint32_t)kTA_RawStages * (uint32_t)p.raw_stride : 0u;
+    float *staging = reinterpret_cast<float *>(smem_raw + (raw_base - smem_u32(smem_raw)) + raw_all);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
-            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_full[s]), RAW ? kTA_CvtWarps : 1); // raw mode: the converting warps fill a stage
             mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int s = 0; s < kTA_RawStages; ++s) {
+            mbar_init(smem_u32(&bar_raw_full[s]), 1);
+            mbar_init(smem_u32(&bar_raw_empty[s]), kTA_CvtWarps);
         }
         mbar_init(smem_u32(&bar_tmem_full), 1);
         mbar_init(smem_u32(&bar_tmem_empty), kTA_EpiWarps);
@@ -189,31 +215,40 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
     tc_fence_after_sync();
 
     if (warp == 0) {
-        // ===== TMA producer: one halo box per plane and tile =====
+        // ===== TMA producer: one halo box per plane and tile (raw mode: one box of the input) =====
         if (lane == 0) {
             int i = 0;
             bool ok = true;
+            const int nstages = RAW ? kTA_RawStages : p.stages;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++i) {
                 const int img = tile / p.tiles_y, ty = tile - img * p.tiles_y;
-                const int s       = i % p.stages;
-                const uint32_t ph = (uint32_t)(i / p.stages) & 1u;
-                if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abort_flag)) {
+                const int s       = i % nstages;
+                const uint32_t ph = (uint32_t)(i / nstages) & 1u;
+                if (!mbar_wait_patient(smem_u32(RAW ? &bar_raw_empty[s] : &bar_empty[s]), ph ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
-                const uint32_t full = smem_u32(&bar_full[s]);
-                const uint32_t dst  = smem_base + (uint32_t)s * stage_bytes;
-                mbar_expect_tx(full, 2u * (uint32_t)p.box_bytes);
-                const int32_t w0 = -p.pad, h0 = ty * p.th - p.pad;
-                tma_load_4d(dst, &map_x_hi, full, 0, w0, h0, img);
-                tma_load_4d(dst + (uint32_t)p.plane_bytes, &map_x_lo, full, 0, w0, h0, img);
+                const int32_t h0 = ty * p.th - p.pad;
+                if (RAW) {
+                    const uint32_t full = smem_u32(&bar_raw_full[s]);
+                    mbar_expect_tx(full, (uint32_t)p.raw_bytes);
+                    // the box starts off_x floats left of x = -pad so that its first byte is 16-byte aligned
+                    tma_load_4d(raw_base + (uint32_t)s * (uint32_t)p.raw_stride, &map_x_hi, full, -p.pad - p.off_x, h0, 0, img);
+                } else {
+                    const uint32_t full = smem_u32(&bar_full[s]);
+                    const uint32_t dst  = smem_base + (uint32_t)s * stage_bytes;
+                    mbar_expect_tx(full, 2u * (uint32_t)p.box_bytes);
+                    const int32_t w0 = -p.pad;
+                    tma_load_4d(dst, &map_x_hi, full, 0, w0, h0, img);
+                    tma_load_4d(dst + (uint32_t)p.plane_bytes, &map_x_lo, full, 0, w0, h0, img);
+                }
             }
             if (*abort_flag) {
                 // unwind: let the copies still in flight land before the CTA goes away
-                const int first = i - p.stages < 0 ? 0 : i - p.stages;
+                const int first = i - nstages < 0 ? 0 : i - nstages;
                 for (int k2 = first; k2 < i; ++k2) {
-                    const uint32_t bar = smem_u32(&bar_full[k2 % p.stages]);
-                    const uint32_t ph  = (uint32_t)(k2 / p.stages) & 1u;
+                    const uint32_t bar = smem_u32(RAW ? &bar_raw_full[k2 % nstages] : &bar_full[k2 % nstages]);
+                    const uint32_t ph  = (uint32_t)(k2 / nstages) & 1u;
                     const uint64_t t0  = globaltimer_ns();
                     while (!mbar_try_wait(bar, ph) && globaltimer_ns() - t0 < kWaitBudgetNs) {
                     }
@@ -274,17 +309,84 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
                 }
             }
         }
+    } else if (RAW && warp < 2 + kTA_CvtWarps) {
+        // ===== raw mode: float32 box -> hi / lo planes =====
+        // A thread takes a position (y, x) of the box: its 32 channel values lie box_rows * box_w floats
+        // apart in the raw box (consecutive lanes read consecutive x: no bank conflicts) and become the
+        // 128-byte row y * pw + x of both planes, 16-byte chunk j at chunk j ^ (row & 7) - the 128-byte
+        // swizzle the MMA's descriptors expect.
+        // (these warps come before the epilogue warps: the schedulers favour older warps, and eight
+        // epilogue warps polling their barrier kept younger converting warps from issuing - a tile's
+        // conversion took 9900 clocks behind them)
+        const int ct   = threadIdx.x - 64;
+        const int npos = p.box_rows * p.pw;
+        const int cstride = p.box_rows * p.box_w; // floats between two channels of one position
+        int i = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++i) {
+            const int rs       = i % kTA_RawStages;
+            const uint32_t rph = (uint32_t)(i / kTA_RawStages) & 1u;
+            const int s        = i % p.stages;
+            const uint32_t ph  = (uint32_t)(i / p.stages) & 1u;
+            const long long v0 = CV_CLOCK();
+            bool got = mbar_wait_patient(smem_u32(&bar_raw_full[rs]), rph, abort_flag);
+            const long long v1 = CV_CLOCK();
+            got      = got && mbar_wait_patient(smem_u32(&bar_empty[s]), ph ^ 1u, abort_flag); // the planes' stage is free
+            if (!__all_sync(0xffffffffu, got))
+                break;
+            const long long v2 = CV_CLOCK();
+            const float *raw = reinterpret_cast<const float *>(smem_raw + (raw_base - smem_u32(smem_raw)) + (uint32_t)rs * (uint32_t)p.raw_stride);
+            uint8_t *x_hi    = smem_raw + (smem_base - smem_u32(smem_raw)) + (uint32_t)s * stage_bytes;
+            uint8_t *x_lo    = x_hi + p.plane_bytes;
+            for (int pos = ct; pos < npos; pos += 32 * kTA_CvtWarps) {
+                const int y = pos / p.pw, x = pos - y * p.pw;
+                const float *src = raw + y * p.box_w + x + p.off_x;
+                const uint32_t row_off = (uint32_t)pos * 128u;
+                const uint32_t sw      = (uint32_t)pos & 7u;
+                // sixteen channels at a time: all their loads first (a store to shared memory in between
+                // would hold back the loads behind it), then the splits and the eight stores
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    float v[16];
+#pragma unroll
+                    for (int t = 0; t < 16; ++t)
+                        v[t] = src[(16 * half + t) * cstride];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float hi[4], lo[4];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t)
+                            split_tf32_flat(v[4 * j + t], hi[t], lo[t]);
+                        const uint32_t at = row_off + (((uint32_t)(4 * half + j) ^ sw) << 4);
+                        *reinterpret_cast<float4 *>(x_hi + at) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+                        *reinterpret_cast<float4 *>(x_lo + at) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+                    }
+                }
+            }
+            // the planes were written through the generic proxy and are read by the tensor core's
+            // asynchronous proxy
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&bar_full[s]));
+                mbar_arrive(smem_u32(&bar_raw_empty[rs]));
+            }
+            if (ct == 0) {
+                CV_ACCUM(9, v1 - v0);            // converter: waiting for the raw box
+                CV_ACCUM(10, v2 - v1);           // waiting for a free plane stage
+                CV_ACCUM(11, CV_CLOCK() - v2);   // converting
+            }
+        }
     } else {
         // ===== epilogue =====
         const int quarter = warp & 3;        // TMEM lanes this warp may read: 32 * quarter ..
-        const int ew      = warp - 2;        // 0..7: which channels this warp writes out
+        const int ew      = warp - (RAW ? 2 + kTA_CvtWarps : 2); // 0..7: which channels this warp writes out
         const int half    = ew >> 2;         // which 64 columns of the accumulator it drains
         uint32_t epi_phase = 0;
         auto epi_sync = [&]() -> bool {
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(smem_u32(&bar_epi));
-            bool ok = mbar_wait(smem_u32(&bar_epi), epi_phase, abort_flag);
+            bool ok = mbar_wait_patient(smem_u32(&bar_epi), epi_phase, abort_flag);
             epi_phase ^= 1u;
             return __all_sync(0xffffffffu, ok);
         };
@@ -320,7 +422,7 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++i) {
             const int img = tile / p.tiles_y, ty = tile - img * p.tiles_y;
             const long long e0 = CV_CLOCK();
-            bool got = mbar_wait(smem_u32(&bar_tmem_full), (uint32_t)i & 1u, abort_flag);
+            bool got = mbar_wait_patient(smem_u32(&bar_tmem_full), (uint32_t)i & 1u, abort_flag);
             if (!__all_sync(0xffffffffu, got))
                 break;
             const long long e1 = CV_CLOCK();
@@ -421,7 +523,7 @@ __global__ void __launch_bounds__(kTA_Threads, 1) conv_tmem_filters_kernel(
             const long long e4 = CV_CLOCK();
             if (!epi_sync()) // the staging block is rewritten by the next tile
                 break;
-            if (warp == 2 && lane == 0) {
+            if (ew == 0 && lane == 0) {
                 CV_ACCUM(4, e1 - e0);           // epilogue: waiting for the accumulator to be complete
                 CV_ACCUM(5, e2 - e1);           // drain
                 CV_ACCUM(6, e3 - e2);           // first meeting of the epilogue warps
@@ -469,56 +571,103 @@ bool conv_tmem_applicable(int64_t c, int64_t h, int64_t w, int64_t ko, int64_t k
     return true;
 }
 
-// x_hi / x_lo: NHWC planes [batch][h][w][32] of the input (float32 hi / lo parts).
-ct_status conv_tmem_filters(
-    DeviceState *st, const void *x_hi, const void *x_lo, const float *w, const float *bias, int64_t batch, int64_t c,
-    int64_t h, int64_t wd, int64_t ko, int64_t kh, int64_t kw, int64_t pad, int act, int pool, float *out) {
-    ConvTmemParams p;
-    p.w = w, p.bias = bias, p.out = out, p.flags = st->flags_dev;
-    p.ko = (int)ko, p.c = (int)c, p.kh = (int)kh, p.kw = (int)kw, p.pad = (int)pad;
-    p.pw = (int)(wd + 2 * pad);
-    p.wo = p.pw - (int)kw + 1;
-    p.ho = (int)(h + 2 * pad - kh + 1);
-    p.th = kTA_N / p.pw < p.ho ? kTA_N / p.pw : p.ho;
+// Shared-memory plan of a launch: tile rows, bytes per plane and per raw box, pipeline stages.
+static bool conv_tmem_plan(ConvTmemParams &p, int64_t h, int64_t wd, int64_t kh, int64_t kw, int64_t pad, int pool, bool raw) {
+    p.pad = (int)pad, p.kh = (int)kh, p.kw = (int)kw;
+    p.pw  = (int)(wd + 2 * pad);
+    p.wo  = p.pw - (int)kw + 1;
+    p.ho  = (int)(h + 2 * pad - kh + 1);
+    p.th  = kTA_N / p.pw < p.ho ? kTA_N / p.pw : p.ho;
     if (pool)
         p.th &= ~1;
-    p.tiles_y = (p.ho + p.th - 1) / p.th;
-    p.ksteps  = (int)(kh * kw * 4);
-    const int box_rows = p.th + (int)kh - 1;
-    p.box_bytes        = box_rows * p.pw * 128;
+    if (p.th < 1)
+        return false;
+    p.tiles_y  = (p.ho + p.th - 1) / p.th;
+    p.ksteps   = (int)(kh * kw * 4);
+    p.box_rows = p.th + (int)kh - 1;
+    p.box_bytes = p.box_rows * p.pw * 128;
     // a tap's shifted window of kTA_N rows may run past the box: reserve those rows too
     int rows_needed = ((int)kh - 1) * p.pw + ((int)kw - 1) + kTA_N;
-    if (rows_needed < box_rows * p.pw)
-        rows_needed = box_rows * p.pw;
+    if (rows_needed < p.box_rows * p.pw)
+        rows_needed = p.box_rows * p.pw;
     p.plane_bytes = (rows_needed * 128 + 1023) & ~1023;
-    p.act = act, p.pool = pool;
-    const int budget = 226 * 1024 - 1024 - kTA_StagingBytes;
+    // raw mode: the box starts at the 16-byte boundary at or left of x = -pad and is a whole number
+    // of 16-byte units wide
+    const int pad_up = ((int)pad + 3) & ~3;
+    p.off_x      = pad_up - (int)pad;
+    p.box_w      = (p.off_x + p.pw + 3) & ~3;
+    p.raw_bytes  = 32 * p.box_rows * p.box_w * 4;
+    p.raw_stride = (p.raw_bytes + 127) & ~127;
+    if (raw && (p.box_w > 256 || p.box_rows > 256))
+        return false;
+    const int budget = 226 * 1024 - 1024 - kTA_StagingBytes - (raw ? kTA_RawStages * p.raw_stride : 0);
     p.stages         = budget / (2 * p.plane_bytes);
     if (p.stages > 4)
         p.stages = 4;
-    if (p.stages < 2 || p.th < 1)
+    return p.stages >= 2;
+}
+
+// Whether the kernel can read this input as it is (NCHW float32) instead of pre-split NHWC planes:
+// the tensor map over it needs row strides of whole 16-byte units and an aligned base, and the raw
+// boxes have to fit into shared memory beside two stages of planes.
+bool conv_tmem_reads_input_directly(const float *x, int64_t h, int64_t w, int64_t kh, int64_t kw, int64_t pad, int pool) {
+    if ((w & 3) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0)
+        return false;
+    ConvTmemParams p;
+    return conv_tmem_plan(p, h, w, kh, kw, pad, pool, true);
+}
+
+// x_raw != nullptr: the input itself, [batch][c][h][w] float32 (see conv_tmem_reads_input_directly);
+// else x_hi / x_lo: NHWC planes [batch][h][w][32] of the input (float32 hi / lo parts).
+ct_status conv_tmem_filters(
+    DeviceState *st, const float *x_raw, const void *x_hi, const void *x_lo, const float *w, const float *bias,
+    int64_t batch, int64_t c, int64_t h, int64_t wd, int64_t ko, int64_t kh, int64_t kw, int64_t pad, int act, int pool,
+    float *out) {
+    const bool raw = x_raw != nullptr;
+    ConvTmemParams p;
+    p.w = w, p.bias = bias, p.out = out, p.flags = st->flags_dev;
+    p.ko = (int)ko, p.c = (int)c;
+    p.act = act, p.pool = pool;
+    if (!conv_tmem_plan(p, h, wd, kh, kw, pad, pool, raw))
         return fail(CT_ERR_INVALID, "conv2d: internal tile shape %d x %d not usable", p.th, p.pw);
+    const int box_rows = p.box_rows;
     const int64_t tiles = (int64_t)p.tiles_y * batch;
     if (tiles > 0x7fffffffll)
         return fail(CT_ERR_TOO_LARGE, "conv2d: too many tiles");
     CUtensorMap mx_hi, mx_lo;
-    // planes [batch][h][w][32 channels]; box = 32 channels x pw positions x (th + kh - 1) rows of one
-    // image, 128-byte swizzle; positions outside the image read as zero: the padding
-    const uint64_t dims[4]    = {32, (uint64_t)wd, (uint64_t)h, (uint64_t)batch};
-    const uint64_t strides[3] = {128, 128ull * (uint64_t)wd, 128ull * (uint64_t)wd * (uint64_t)h};
-    const uint32_t box[4]     = {32, (uint32_t)p.pw, (uint32_t)box_rows, 1};
-    CT_TRY(encode_tiled_map_f32(&mx_hi, x_hi, 4, dims, strides, box, /*swizzle_bytes=*/128));
-    CT_TRY(encode_tiled_map_f32(&mx_lo, x_lo, 4, dims, strides, box, 128));
-    const size_t smem = (size_t)p.stages * 2 * p.plane_bytes + kTA_StagingBytes + 1024;
+    if (raw) {
+        // the input [batch][c][h][w]; box = box_w floats x box_rows rows x 32 channels of one image, not
+        // swizzled; outside the image and past the last channel it reads as zero: padding for free
+        const uint64_t dims[4]    = {(uint64_t)wd, (uint64_t)h, (uint64_t)c, (uint64_t)batch};
+        const uint64_t strides[3] = {4ull * (uint64_t)wd, 4ull * (uint64_t)wd * (uint64_t)h,
+                                     4ull * (uint64_t)wd * (uint64_t)h * (uint64_t)c};
+        const uint32_t box[4]     = {(uint32_t)p.box_w, (uint32_t)box_rows, 32, 1};
+        CT_TRY(encode_tiled_map_f32(&mx_hi, x_raw, 4, dims, strides, box, /*swizzle_bytes=*/0));
+        mx_lo = mx_hi;
+    } else {
+        // planes [batch][h][w][32 channels]; box = 32 channels x pw positions x (th + kh - 1) rows of one
+        // image, 128-byte swizzle; positions outside the image read as zero: the padding
+        const uint64_t dims[4]    = {32, (uint64_t)wd, (uint64_t)h, (uint64_t)batch};
+        const uint64_t strides[3] = {128, 128ull * (uint64_t)wd, 128ull * (uint64_t)wd * (uint64_t)h};
+        const uint32_t box[4]     = {32, (uint32_t)p.pw, (uint32_t)box_rows, 1};
+        CT_TRY(encode_tiled_map_f32(&mx_hi, x_hi, 4, dims, strides, box, /*swizzle_bytes=*/128));
+        CT_TRY(encode_tiled_map_f32(&mx_lo, x_lo, 4, dims, strides, box, 128));
+    }
+    const size_t smem = (size_t)p.stages * 2 * p.plane_bytes + (raw ? (size_t)kTA_RawStages * p.raw_stride : 0) +
+                        kTA_StagingBytes + 1024;
     static bool attr_set_dev[16] = {}; // the attribute belongs to a device's context
     bool &attr_set = attr_set_dev[st->device & 15];
     if (!attr_set) {
-        CT_CUDA(cudaFuncSetAttribute(conv_tmem_filters_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        CT_CUDA(cudaFuncSetAttribute(conv_tmem_filters_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        CT_CUDA(cudaFuncSetAttribute(conv_tmem_filters_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         attr_set = true;
     }
     const unsigned grid = (unsigned)(tiles < st->sm_count ? tiles : st->sm_count);
     ProfScope prof("gemm_tc");
-    conv_tmem_filters_kernel<<<grid, kTA_Threads, smem, stream()>>>(mx_hi, mx_lo, p, (int)tiles);
+    if (raw)
+        conv_tmem_filters_kernel<true><<<grid, kTA_ThreadsRaw, smem, stream()>>>(mx_hi, mx_lo, p, (int)tiles);
+    else
+        conv_tmem_filters_kernel<false><<<grid, kTA_Threads, smem, stream()>>>(mx_hi, mx_lo, p, (int)tiles);
     CT_LAUNCH_CHECK("conv_tmem_filters");
     return CT_OK;
 }

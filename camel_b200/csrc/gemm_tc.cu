@@ -143,7 +143,11 @@ __global__ void __launch_bounds__(256) split_rows_kernel(
 }
 
 // Same result, four consecutive k per thread: 128-bit loads and stores, rows on blockIdx.y, no
-// integer division.  kp is a multiple of 32 and the planes are 1 KiB aligned.
+// integer division.  kp is a multiple of 32 and the planes are 1 KiB aligned.  A thread takes
+// kSplitRows rows at a time and issues all their loads before the first store: with one row per
+// thread the kernel was a chain of one load and two stores per thread, i.e. latency, for the
+// 4096 x 1024 activations of an MLP layer (8.5 us for 50 MB that mostly sit in L2).
+constexpr int kSplitRows = 4;
 template <int MODE>
 __global__ void __launch_bounds__(256) split_rows_vec_kernel(
     const float *__restrict__ in, int64_t rows, int64_t k, int64_t kp, void *__restrict__ p_hi,
@@ -153,32 +157,45 @@ __global__ void __launch_bounds__(256) split_rows_vec_kernel(
     const int64_t c = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
     if (c >= kp)
         return;
-    for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
-        const float *src = in + r * k + c;
-        float v[4];
-        if (in_vec_ok && c + 3 < k) {
-            float4 q = __ldcs(reinterpret_cast<const float4 *>(src));
-            v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
-        } else {
+    const bool vec = in_vec_ok && c + 3 < k;
+    for (int64_t r0 = (int64_t)blockIdx.y * kSplitRows; r0 < rows; r0 += (int64_t)gridDim.y * kSplitRows) {
+        float v[kSplitRows][4];
 #pragma unroll
-            for (int t = 0; t < 4; ++t)
-                v[t] = c + t < k ? src[t] : 0.0f;
+        for (int j = 0; j < kSplitRows; ++j) {
+            const int64_t r = r0 + j;
+            if (r < rows) {
+                const float *src = in + r * k + c;
+                if (vec) {
+                    float4 q = __ldcs(reinterpret_cast<const float4 *>(src));
+                    v[j][0] = q.x, v[j][1] = q.y, v[j][2] = q.z, v[j][3] = q.w;
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 4; ++t)
+                        v[j][t] = c + t < k ? src[t] : 0.0f;
+                }
+            }
         }
-        const int64_t at = r * kp + c;
-        if (MODE == MODE_3X) {
-            float hi[4], lo[4];
 #pragma unroll
-            for (int t = 0; t < 4; ++t)
-                split_tf32(v[t], hi[t], lo[t]);
-            *reinterpret_cast<float4 *>(static_cast<float *>(p_hi) + at) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-            *reinterpret_cast<float4 *>(static_cast<float *>(p_lo) + at) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-        } else {
-            __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
-            __nv_bfloat162 b = __floats2bfloat162_rn(v[2], v[3]);
-            uint2 packed;
-            packed.x = *reinterpret_cast<uint32_t *>(&a);
-            packed.y = *reinterpret_cast<uint32_t *>(&b);
-            *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(p_hi) + at) = packed;
+        for (int j = 0; j < kSplitRows; ++j) {
+            const int64_t r = r0 + j;
+            if (r >= rows)
+                break;
+            const int64_t at = r * kp + c;
+            if (MODE == MODE_3X) {
+                float hi[4], lo[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+                    split_tf32(v[j][t], hi[t], lo[t]);
+                *reinterpret_cast<float4 *>(static_cast<float *>(p_hi) + at) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<float4 *>(static_cast<float *>(p_lo) + at) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+            } else {
+                __nv_bfloat162 a = __floats2bfloat162_rn(v[j][0], v[j][1]);
+                __nv_bfloat162 b = __floats2bfloat162_rn(v[j][2], v[j][3]);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t *>(&a);
+                packed.y = *reinterpret_cast<uint32_t *>(&b);
+                *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(p_hi) + at) = packed;
+            }
         }
     }
 }
@@ -1298,7 +1315,9 @@ ct_status encode_tiled_map_f32(
     }
     CUresult r = fn(
         map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(base), d, s, b, e,
-        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+        CU_TENSOR_MAP_INTERLEAVE_NONE,
+        swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                             : (swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(CT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
@@ -1603,14 +1622,10 @@ ct_status gemm_planes(
 #define CT_GEMM_ARGS st, a_hi, a_lo, b_hi, b_lo, m, n, kp, bias, act, out, batch, out_batch_stride, bias_per_row, conv
     if (mode == MODE_3X) {
         // 128 x 256 tiles of two float32 planes: 64-byte k-blocks give four 48 KB stages instead
-        // of two 96 KB ones
-#ifdef CT_STREAM128
-        if (wide && !conv) {
-            const int64_t tiles128 = ((m + BM - 1) / BM) * ((n + 127) / 128) * batch;
-            if (tiles256 < st->sm_count && tiles128 > st->sm_count && kp <= 1024 && g_band_plan.bands == 0)
-                return launch_gemm<128, MODE_3X, 64>(CT_GEMM_ARGS);
-        }
-#endif
+        // of two 96 KB ones.  (A one-wave product, 128 such tiles on 148 SMs, is not served better
+        // by 256 tiles of 128 x 128 walked by one CTA per SM: measured 56 instead of 42 us per layer
+        // of a 4096 x 1024 x 1024 product - N = 128 MMAs cost 73 clocks against 138 for twice the
+        // columns, and two tiles in a row per CTA outweigh the idle SMs.)
         if (wide)
             return launch_gemm<256, MODE_3X, 64>(CT_GEMM_ARGS);
         return launch_gemm<128, MODE_3X>(CT_GEMM_ARGS);
@@ -1643,7 +1658,8 @@ ct_status split_rows_planes(
     if (total == 0)
         return CT_OK;
     (void)st;
-    dim3 grid((unsigned)((kp / 4 + 255) / 256), (unsigned)(rows < 65535 ? rows : 65535));
+    const int64_t row_groups = (rows + kSplitRows - 1) / kSplitRows;
+    dim3 grid((unsigned)((kp / 4 + 255) / 256), (unsigned)(row_groups < 65535 ? row_groups : 65535));
     int vec_ok = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(in) & 15u) == 0;
     if (mode == MODE_3X)
         CT_CUDA(launch_dependent(split_rows_vec_kernel<MODE_3X>, grid, dim3(256), 0, stream(), in, rows, k, kp, hi, lo, vec_ok));

@@ -47,7 +47,9 @@ __global__ void __launch_bounds__(kPeakThreads, 1) mma_peak_kernel(
         uint32_t h = (uint32_t)i * 2654435761u + blockIdx.x * 40503u;
         float v    = ((h >> 9) & 0xffff) * (1.0f / 32768.0f) - 1.0f;
         if (KIND == 0) {
-            reinterpret_cast<float *>(base)[i] = v;
+            // tf32 values, as every kernel here feeds the pipe (the split rounds both parts to tf32):
+            // the 13 low mantissa bits are zero
+            reinterpret_cast<float *>(base)[i] = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
         } else {
             uint32_t b = __float_as_uint(v) >> 16; // the value truncated to bf16
             reinterpret_cast<uint32_t *>(base)[i] = b | (b << 16);

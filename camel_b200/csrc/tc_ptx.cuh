@@ -63,6 +63,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// The same with a time limit for the hardware's own suspension of the thread: a waiting thread
+// sleeps until the phase completes (it is woken at once then) or the limit passes, instead of
+// coming back after the much shorter system default and polling again.  For roles whose waits are
+// long and whose polling would take issue slots from the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_for(uint32_t bar, uint32_t parity, uint32_t limit_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(limit_ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Wait budget of one barrier wait.  A healthy kernel waits microseconds; the budget only
 // exists so that a protocol bug ends as an error status instead of a hung GPU.
 constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull; // 1 s
@@ -83,6 +101,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                 *abort_flag = 1;
                 return false;
             }
+        }
+    }
+}
+
+// Bounded wait for the patient roles (see mbar_try_wait_for): same contract as mbar_wait.
+__device__ __forceinline__ bool mbar_wait_patient(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity))
+        return true;
+    uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait_for(bar, parity, 20000u))
+            return true;
+        if (*abort_flag)
+            return false;
+        if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+            *abort_flag = 1;
+            return false;
         }
     }
 }

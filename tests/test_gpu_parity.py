@@ -538,6 +538,40 @@ def test_conv2d_with_fused_maxpool(T, n, c, h, w, ko, kk, pad):
     assert canonical_nan(fused).tobytes() == canonical_nan(chain).tobytes()
 
 
+@pytest.mark.parametrize("n,c,h,w,ko,kk,pad,pool", [
+    (3, 32, 28, 28, 64, 3, 1, 0),    # second CNN layer
+    (3, 32, 28, 28, 64, 3, 1, 2),    # ... with the pool in the epilogue
+    (2, 20, 16, 24, 48, 3, 1, 0),    # fewer than 32 channels: the box reads zeros past the last one
+    (2, 32, 12, 20, 64, 5, 2, 0),    # 5 x 5 filter, padding 2
+    (2, 32, 10, 12, 64, 3, 0, 0),    # no padding
+])
+def test_conv2d_reads_its_input_directly_or_from_planes(T, n, c, h, w, ko, kk, pad, pool):
+    """The few-channel convolution kernel reads an aligned NCHW input as it is and splits it into
+    tf32 parts itself; an input at an address its tensor map cannot take goes through the NHWC-plane
+    pre-pass.  Same input at both kinds of address: same bytes out, special values included."""
+    import torch
+
+    rng = np.random.default_rng(n + c + h + w + ko + pool)
+    x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    x[0, 0, 1, 1] = np.inf
+    x[0, 1, 2, 3] = np.float32(3.4e38)          # rounds up to infinity as tf32: has to be truncated
+    x[1, 0, 0, 0] = np.float32(1e-41)           # subnormal
+    x[1, 2, 3, 1] = np.nan
+    wt = (rng.standard_normal((ko, c, kk, kk)) * np.sqrt(2.0 / (c * kk * kk))).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, ko).astype(np.float32)
+    tw, tb = T.from_numpy(wt), T.from_numpy(b)
+    outs = []
+    for shift in (0, 1):                         # 1: the tensor starts 4 bytes past a 16-byte boundary
+        buf = torch.empty(x.size + 4, dtype=torch.float32, device="cuda")
+        view = buf[shift:shift + x.size]
+        view.copy_(torch.from_numpy(x.reshape(-1)))
+        assert view.data_ptr() % 16 == 4 * shift
+        tx = T.wrap_device(view.data_ptr(), 0, x.shape, keep=buf)
+        outs.append(T.conv2d(tx, tw, tb, 1, pad, "relu", pool=pool).numpy())
+    T.check_async()
+    assert canonical_nan(outs[0]).tobytes() == canonical_nan(outs[1]).tobytes()
+
+
 def test_entry_points_from_many_threads(T):
     """The reference's Taskflow scheduler calls operators from up to 32 threads at once.  Entry
     points that enqueue several kernels over a shared workspace must not interleave: eight threads
