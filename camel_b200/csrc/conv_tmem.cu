@@ -461,61 +461,84 @@ __global__ void __launch_bounds__(kTA_ThreadsRaw, 1) conv_tmem_filters_kernel(
             for (int g = 0; g < 4; ++g)
                 if (off[g] >= 0 && (p.pool ? (y0 >> 1) + yy[g] < ph2 : y0 + yy[g] < p.ho))
                     okmask |= 1u << g;
+            // Two channels at a time, every load of the pair before the first dependent instruction, no
+            // branch inside: a channel past the last filter or a position that is not stored is masked
+            // at the store (its loads read rows of the staging block that hold nothing of interest).
             if (p.pool == 0) {
 #pragma unroll
-                for (int j = 0; j < 64 / kTA_EpiWarps; ++j) {
-                    const int ch = ew + kTA_EpiWarps * j;
-                    if (ch < p.ko) {
-                        const float *hi = staging + ch * kTA_StageRowF + lane, *lo = hi + 64 * kTA_StageRowF;
-                        const float b   = bias_r[j];
-                        float *plane    = p.out + (((int64_t)img * p.ko + ch) * p.ho + y0) * p.wo;
-                        float v[4];
+                for (int jj = 0; jj < 64 / kTA_EpiWarps; jj += 2) {
+                    float h[2][4], l[2][4];
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) { // the loads and the arithmetic of all four, then the stores
-                            v[g] = __fadd_rn(hi[32 * g], lo[32 * g]);
-                            if (p.bias)
-                                v[g] = __fadd_rn(v[g], b);
-                            if (p.act == CT_ACT_RELU)
-                                v[g] = __fmul_rn(v[g], v[g] > 0.0f ? 1.0f : 0.0f);
-                        }
+                    for (int u = 0; u < 2; ++u) {
+                        const int ch    = ew + kTA_EpiWarps * (jj + u);
+                        const float *hi = staging + ch * kTA_StageRowF + lane, *lo = hi + 64 * kTA_StageRowF;
 #pragma unroll
                         for (int g = 0; g < 4; ++g)
-                            if (okmask & (1u << g))
-                                plane[off[g]] = v[g];
+                            h[u][g] = hi[32 * g], l[u][g] = lo[32 * g];
+                    }
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int ch = ew + kTA_EpiWarps * (jj + u);
+                        const float b = bias_r[jj + u];
+                        float *plane  = p.out + (((int64_t)img * p.ko + ch) * p.ho + y0) * p.wo;
+                        const unsigned mask = ch < p.ko ? okmask : 0u;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            float v = __fadd_rn(h[u][g], l[u][g]);
+                            if (p.bias)
+                                v = __fadd_rn(v, b);
+                            if (p.act == CT_ACT_RELU)
+                                v = __fmul_rn(v, v > 0.0f ? 1.0f : 0.0f);
+                            if (mask & (1u << g))
+                                plane[off[g]] = v;
+                        }
                     }
                 }
             } else {
                 // 2x2 max-pool of the activated values; window order and strict '>' as in
                 // maxpool2d (the first element seeds, a NaN never wins)
+                const int pooled = (p.th >> 1) * pw2;           // pooled pixels of a tile
+                const int groups = (pooled + 31) >> 5;          // the same for every lane: no divergence
 #pragma unroll
-                for (int j = 0; j < 64 / kTA_EpiWarps; ++j) {
-                    const int ch = ew + kTA_EpiWarps * j;
-                    if (ch >= p.ko)
+                for (int g = 0; g < 4; ++g) {
+                    if (g >= groups)
                         break;
-                    const float *hi = staging + ch * kTA_StageRowF, *lo = staging + (64 + ch) * kTA_StageRowF;
-                    const float b   = bias_r[j];
-                    float *plane    = p.out + (((int64_t)img * p.ko + ch) * ph2 + (y0 >> 1)) * pw2;
-                    auto value = [&](int pos) {
-                        float v = __fadd_rn(hi[pos], lo[pos]);
-                        if (p.bias)
-                            v = __fadd_rn(v, b);
-                        if (p.act == CT_ACT_RELU)
-                            v = __fmul_rn(v, v > 0.0f ? 1.0f : 0.0f);
-                        return v;
-                    };
+                    const bool live = (okmask >> g) & 1u;
+                    const int pos   = live ? off[g] : 0;
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        if (okmask & (1u << g)) {
-                            const int pos = off[g];
-                            float best = value(pos);
-                            const float v1 = value(pos + 1), v2 = value(pos + p.pw), v3 = value(pos + p.pw + 1);
-                            if (v1 > best)
-                                best = v1;
-                            if (v2 > best)
-                                best = v2;
-                            if (v3 > best)
-                                best = v3;
-                            plane[lane + 32 * g] = best; // pooled pixels of a tile are consecutive: py * pw2 + px
+                    for (int jj = 0; jj < 64 / kTA_EpiWarps; jj += 2) {
+                        float h[2][4], l[2][4];
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            const int ch    = ew + kTA_EpiWarps * (jj + u);
+                            const float *hi = staging + ch * kTA_StageRowF + pos, *lo = hi + 64 * kTA_StageRowF;
+                            h[u][0] = hi[0], h[u][1] = hi[1], h[u][2] = hi[p.pw], h[u][3] = hi[p.pw + 1];
+                            l[u][0] = lo[0], l[u][1] = lo[1], l[u][2] = lo[p.pw], l[u][3] = lo[p.pw + 1];
+                        }
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            const int ch  = ew + kTA_EpiWarps * (jj + u);
+                            const float b = bias_r[jj + u];
+                            float v[4];
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                v[t] = __fadd_rn(h[u][t], l[u][t]);
+                                if (p.bias)
+                                    v[t] = __fadd_rn(v[t], b);
+                                if (p.act == CT_ACT_RELU)
+                                    v[t] = __fmul_rn(v[t], v[t] > 0.0f ? 1.0f : 0.0f);
+                            }
+                            float best = v[0];
+                            if (v[1] > best)
+                                best = v[1];
+                            if (v[2] > best)
+                                best = v[2];
+                            if (v[3] > best)
+                                best = v[3];
+                            if (live && ch < p.ko) {
+                                float *plane = p.out + (((int64_t)img * p.ko + ch) * ph2 + (y0 >> 1)) * pw2;
+                                plane[lane + 32 * g] = best; // pooled pixels of a tile are consecutive: py * pw2 + px
+                            }
                         }
                     }
                 }
