@@ -867,7 +867,7 @@ class CnnWorkload(Workload):
 
     name, metric, unit = "cnn", "cnn_forward_samples_per_s", "samples/s"
 
-    def __init__(self, torch, T, batch, fuse_pool=True):
+    def __init__(self, torch, T, batch, fuse_pool=True, use_graph=True):
         self.T, self.batch = T, batch
         rng = np.random.default_rng(4)
 
@@ -886,6 +886,17 @@ class CnnWorkload(Workload):
         self.h2d, self.d2h = x.nbytes, batch * 48
         self.flops = 2.0 * batch * (28 * 28 * (32 * 9 + 64 * 288) + 12544 * 128 + 1280)
         self.fuse_pool = fuse_pool
+        # the forward pass is eight launches and as many allocations: record it once, replay per step
+        # (launched call by call, the host falls behind the GPU once the memory pool has served other
+        # workloads: 2.43 instead of 2.05 ms per step with the same kernel times)
+        self.graph = None
+        if use_graph:
+            warm = [self.forward(self.x) for _ in range(2)]
+            T.check_async()
+            with T.Graph() as g:
+                g.keep = self.forward(self.x)
+            self.graph = g
+            del warm
 
     def forward(self, x):
         T = self.T
@@ -899,12 +910,22 @@ class CnnWorkload(Workload):
         return T.dense(h, self.w[3], self.b[3], "softmax", with_argmax=True)
 
     def step(self):
+        if self.graph is not None:
+            self.graph.launch()
+        else:
+            self.out = self.forward(self.x)
+
+    def eager_step(self):
         self.out = self.forward(self.x)
 
     def e2e_step(self):
         from camel_b200._lib import check, lib
         check(lib.ct_h2d(self.x.ptr, self.x_host.data_ptr(), self.h2d))
-        probs, arg = self.forward(self.x)
+        if self.graph is not None:
+            self.graph.launch()
+            probs, arg = self.graph.keep
+        else:
+            probs, arg = self.forward(self.x)
         check(lib.ct_d2h(self.probs_host.data_ptr(), probs.ptr, self.batch * 40))
         check(lib.ct_d2h(self.arg_host.data_ptr(), arg.ptr, self.batch * 8))
 
@@ -1002,6 +1023,13 @@ class Bench:
         self.timed(wl.eager_step if replayed else wl.step, prof_steps, flush)
         tot, cnt = ctypes_double(), ctypes_u64()
         check(lib.ct_profile_read(wl.dominant.encode(), tot, cnt))
+        # every kernel family's share of a step (the library's own brackets, this pass)
+        scopes = {}
+        for name in PROFILE_SCOPES:
+            t_s, n_s = ctypes_double(), ctypes_u64()
+            check(lib.ct_profile_read(name.encode(), t_s, n_s))
+            if n_s.value:
+                scopes[name] = {"ms_per_step": t_s.value / prof_steps, "launches_per_step": n_s.value / prof_steps}
         check(lib.ct_profile_read(None, None, None))
         check(lib.ct_profile_enable(0))
         T.check_async()
@@ -1009,7 +1037,7 @@ class Bench:
         return {"ms_per_step": ms_block / steps, "blocks": len(blocks), "gpu_s": float(sum(blocks)) / 1e3,
                 "launches": int(launches), "dom_ms": tot.value / max(1, cnt.value),
                 "launches_per_step": cnt.value / prof_steps, "clocks": clocks,
-                "flush": flush is not None}
+                "flush": flush is not None, "scopes": scopes}
 
 
 def measured_mma_peaks(lib, check, sampler):
@@ -1117,6 +1145,9 @@ def roofline_of(wl, m, pk, mma, precision):
 
 
 SM_COUNT = 148  # B200
+# the kernel families the library brackets with events when profiling is on (ct_profile_enable)
+PROFILE_SCOPES = ["gemm_tc", "gemm_prepass", "gemm_skinny", "gemm_splitk_reduce", "conv_prepass", "conv_small_c",
+                  "im2col", "maxpool", "elementwise", "reduce", "softmax", "transpose", "concat", "weights_pack"]
 
 EXTRA_STEPS = {"gemm": 5, "gemm_bf16": 5, "gemm512": 50, "conv": 10, "cnn": 5, "gemm_sharded": 3}
 
@@ -1161,7 +1192,8 @@ def run_extras(bench, args, pk, mma):
             rec = {"workload": name, "metric": wl.metric, "value": value, "unit": wl.unit,
                    "ms_per_step": m["ms_per_step"], "steps": steps, "scaling": wl.scaling,
                    "config": wl.config(), "gpu_launches": m["launches"], "clocks": m["clocks"],
-                   "l2": "flushed between steps" if m["flush"] else "inputs larger than L2"}
+                   "l2": "flushed between steps" if m["flush"] else "inputs larger than L2",
+                   "kernel_families_per_step": m["scopes"]}
             if name != "gemm512":
                 rec["roofline"] = roofline_of(wl, m, pk, mma, precision)
             out.append(rec)
@@ -1296,7 +1328,7 @@ def run_gpu(args, rank, world):
     elif name == "conv":
         wl = ConvWorkload(torch, T, args.batch or 256)
     elif name == "cnn":
-        wl = CnnWorkload(torch, T, args.batch or 8192, fuse_pool=not args.unfused_pool)
+        wl = CnnWorkload(torch, T, args.batch or 8192, fuse_pool=not args.unfused_pool, use_graph=not args.eager)
     elif name == "add":
         wl = AddWorkload(torch, T, args.size if args.size != 16384 else 1 << 28)
     elif name in HbmWorkload.OPS:
@@ -1365,7 +1397,8 @@ def run_gpu(args, rank, world):
                            **wl.config(), "l2": "flushed between steps" if m["flush"] else "inputs larger than L2"},
                 "timed_region": {"blocks_of_steps": m["blocks"], "gpu_s": m["gpu_s"],
                                  "rule": "blocks of exactly `steps` timed steps; ms_per_step is the median block's"},
-                "gpu_launches": m["launches"], "roofline": roofline, "clocks": m["clocks"]}
+                "gpu_launches": m["launches"], "roofline": roofline, "clocks": m["clocks"],
+                "kernel_families_per_step": m["scopes"]}
         if plugin is not None:
             # the headline end-to-end figure: through the plugin's operator bodies, host buffers in and out
             fused = plugin["fused_operators"]
