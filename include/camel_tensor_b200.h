@@ -148,6 +148,10 @@ ct_status ct_graph_destroy(void *graph);
 
 ct_status ct_alloc(void **ptr_dev, size_t bytes);
 ct_status ct_free(void *ptr_dev);
+/* Synchronous copy from host memory of any kind.  A source of 32 MiB or more that is not
+ * page-locked is staged by the library itself: a few host threads copy it in chunks into a ring
+ * of page-locked buffers while earlier chunks are on their way to the device (about twice the
+ * rate of the driver's own staging of pageable memory).  On return src_host may be reused. */
 ct_status ct_h2d(void *dst_dev, const void *src_host, size_t bytes);
 ct_status ct_d2h(void *dst_host, const void *src_dev, size_t bytes);
 ct_status ct_d2d(void *dst_dev, const void *src_dev, size_t bytes);
