@@ -598,7 +598,7 @@ ct_status reduce_axis_f32(DeviceState *st, const float *in, int64_t rows, int64_
     if (axis == 1) {
         if (rows == 0)
             return CT_OK;
-        if (cols <= 32 && (cols & 1) == 0 && rows >= 256 * (int64_t)st->sm_count &&
+        if (cols >= 2 && cols <= 32 && (cols & 1) == 0 && rows >= 256 * (int64_t)st->sm_count &&
             (reinterpret_cast<uintptr_t>(in) & 7u) == 0) {
             reduce_rows_direct_f32_kernel<KIND, OT><<<(unsigned)((rows + 255) / 256), 256, 0, stream()>>>(in, rows, (int)cols, out);
         } else if (cols <= 32 && rows >= 1024 * (int64_t)st->sm_count && cols <= 11) {
