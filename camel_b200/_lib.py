@@ -56,6 +56,7 @@ PROTOTYPES = {
     "ct_free": (_int, [_vp]),
     "ct_h2d": (_int, [_vp, _vp, _sz]),
     "ct_d2h": (_int, [_vp, _vp, _sz]),
+    "ct_d2h_checked": (_int, [_vp, _vp, _sz]),
     "ct_d2d": (_int, [_vp, _vp, _sz]),
     "ct_host_alloc": (_int, [C.POINTER(_vp), _sz]),
     "ct_host_free": (_int, [_vp]),

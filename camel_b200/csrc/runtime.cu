@@ -585,6 +585,18 @@ ct_status ct_d2h(void *dst_host, const void *src_dev, size_t bytes) {
     return CT_OK;
 }
 
+// The host read at a graph boundary: the data and the device's error record in one trip (two
+// copies enqueued, one synchronisation), then the error record reported as ct_check does.
+ct_status ct_d2h_checked(void *dst_host, const void *src_dev, size_t bytes) {
+    OpLock op_lock;
+    DeviceState *st;
+    CT_TRY(current(&st));
+    if (bytes > 0)
+        CT_CUDA(cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, stream()));
+    CT_TRY(fetch_flags(st)); // synchronises the stream: both copies have landed
+    return report_timeout(st, "ct_d2h_checked");
+}
+
 ct_status ct_d2d(void *dst_dev, const void *src_dev, size_t bytes) {
     DeviceState *st;
     CT_TRY(current(&st));

@@ -482,9 +482,9 @@ const std::byte *TensorObject::rawData() const {
         if (byteSize_ > 0) {
             // the graph boundary: one device-to-host copy, then the device's error record - a
             // contraction whose bounded wait ran out must not hand its undefined output to the host
-            ct_status status = ct_d2h(mirror, deviceData(), static_cast<size_t>(byteSize_));
-            if (status == CT_OK)
-                status = ct_check();
+            // (one call, one synchronisation: two separate round trips cost a 4096-sample MLP step
+            // 20 of its 440 microseconds)
+            ct_status status = ct_d2h_checked(mirror, deviceData(), static_cast<size_t>(byteSize_));
             if (status != CT_OK) {
                 std::free(mirror);
                 ctCheck(status);

@@ -154,6 +154,11 @@ ct_status ct_free(void *ptr_dev);
  * rate of the driver's own staging of pageable memory).  On return src_host may be reused. */
 ct_status ct_h2d(void *dst_dev, const void *src_host, size_t bytes);
 ct_status ct_d2h(void *dst_host, const void *src_dev, size_t bytes);
+/* ct_d2h followed by ct_check in one trip to the device (the copy of the data and of the error
+ * record are enqueued together and waited for once): what a host read at a graph boundary needs -
+ * a contraction whose bounded wait ran out must not hand its undefined output to the host.  No
+ * reference counterpart (the reference's tensors are host memory). */
+ct_status ct_d2h_checked(void *dst_host, const void *src_dev, size_t bytes);
 ct_status ct_d2d(void *dst_dev, const void *src_dev, size_t bytes);
 
 /* ---- streaming across the graph boundary --------------------------------------------
