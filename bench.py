@@ -1247,6 +1247,47 @@ def plugin_leg(args, batch, world_reduce):
     return out
 
 
+def training_leg(lib):
+    """One update step of the reference's MNIST program (test/run/nn/mnist.cml:27-41) at its own
+    sizes, 60000 x 785 features (bias column included) x 10 classes, operator by operator through
+    the plugin's operator_t bodies with tensors resident: matmul, the ten-operator softmax,
+    subtract, transpose, matmul, multiply, subtract.  Deferred (the module recognises the idioms
+    and launches fused kernels) and eager (every operator launches), wall clock in C++ around the
+    loop including the final read-back of the weights; launches counted by the library."""
+    import ctypes as C
+
+    harness = ROOT / "camel_b200" / "host" / "_build" / "libcamel_tensor_host_test.so"
+    if not harness.exists():
+        return None
+    h = C.CDLL(str(harness))
+    n, d, classes, steps = 60000, 785, 10, 20
+    rng = np.random.default_rng(11)
+    x = rng.uniform(0, 1, (n, d)).astype(np.float32)
+    x[:, -1] = 1.0
+    y = np.zeros((n, classes), np.float32)
+    y[np.arange(n), rng.integers(0, classes, n)] = 1.0
+    out = {"workload": "one update step of test/run/nn/mnist.cml:27-41, 60000 x 785 x 10, through operator_t"}
+    P = lambda a: C.c_void_p(a.ctypes.data)  # noqa: E731
+    lib.ct_launch_count.restype = C.c_uint64
+    for key, lazy in (("deferred", 1), ("eager", 0)):
+        best, launches = None, 0
+        for rep in range(3):  # the first repetition also builds what is built once
+            w = np.zeros((d, classes), np.float32)
+            secs, err = C.c_double(), C.create_string_buffer(512)
+            h.camel_host_session_begin(C.c_int(lazy))
+            l0 = lib.ct_launch_count()
+            rc = h.camel_host_sgd_loop(P(x), P(y), P(w), C.c_int64(n), C.c_int64(d), C.c_int64(classes), C.c_double(0.5),
+                                       C.c_int(steps), C.c_int(1), None, C.byref(secs), err, C.c_int(512))
+            if rc != 0:
+                raise RuntimeError("training leg: " + err.value.decode())
+            launches = lib.ct_launch_count() - l0
+            best = secs.value if best is None else min(best, secs.value)
+        out[key] = {"us_per_step": best / steps * 1e6, "launches_per_step": launches / steps,
+                    "weights_checksum": float(np.abs(w).sum())}
+    h.camel_host_session_begin(C.c_int(1))
+    return out
+
+
 def h2d_ceiling(bench, nbytes, copies=40):
     """Bare host-to-device bandwidth of this rank while every rank copies at once: `copies`
     cudaMemcpyAsync of the step's input size from page-locked memory, no kernels."""
@@ -1385,6 +1426,7 @@ def run_gpu(args, rank, world):
         plugin = plugin_leg(args, wl.batch, bench.reduce_max)
 
     extras = run_extras(bench, args, pk, mma) if headline and not args.no_extras else None
+    training = training_leg(lib) if headline and not args.no_extras and rank == 0 else None
 
     if rank == 0:
         roofline = roofline_of(wl, m, pk, mma, args.precision)
@@ -1428,6 +1470,8 @@ def run_gpu(args, rank, world):
             line["mma_peak"] = mma
         if extras is not None:
             line["extras"] = extras
+        if training is not None:
+            line["plugin_training_step"] = training
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line))
